@@ -1,0 +1,95 @@
+// Host-side plumbing of the C ABI: version, error string, status word, tensor maps.
+#include <mutex>
+
+#include "host.cuh"
+
+namespace pr {
+
+namespace {
+constexpr int kMaxDevices = 64;
+struct StatusSlot {
+  int* host = nullptr;
+  int* dev = nullptr;
+};
+StatusSlot g_status[kMaxDevices];
+std::mutex g_status_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+}  // namespace
+
+int status_word(int device, int** dev_ptr, volatile int** host_ptr) {
+  PR_REQUIRE(device >= 0 && device < kMaxDevices, PR_ERR_BAD_ARG, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_status_mu);
+  StatusSlot& s = g_status[device];
+  if (!s.host) {
+    // Pinned, mapped host memory: 4 bytes per device, kept until the process exits.
+    PR_CUDA(cudaSetDevice(device));
+    void* h = nullptr;
+    PR_CUDA(cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+    void* d = nullptr;
+    PR_CUDA(cudaHostGetDevicePointer(&d, h, 0));
+    *static_cast<volatile int*>(h) = 0;
+    s.host = static_cast<int*>(h);
+    s.dev = static_cast<int*>(d);
+  }
+  if (dev_ptr) *dev_ptr = s.dev;
+  if (host_ptr) *host_ptr = s.host;
+  return PR_OK;
+}
+
+int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  PR_REQUIRE(g_encode != nullptr, PR_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  PR_REQUIRE(rank >= 2 && rank <= 5, PR_ERR_BAD_ARG, "tensor map rank %d", rank);
+  PR_REQUIRE(aligned16(base), PR_ERR_BAD_ARG, "tensor map base %p is not 16-byte aligned", base);
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t bdim[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) {
+      PR_REQUIRE(strides_bytes[i] % 16 == 0, PR_ERR_BAD_ARG, "tensor map stride %d = %llu bytes, not a multiple of 16",
+                 i, (unsigned long long)strides_bytes[i]);
+      gstr[i - 1] = strides_bytes[i];
+    }
+  }
+  PR_REQUIRE((uint64_t)box[0] * elem_bytes % 16 == 0, PR_ERR_BAD_ARG, "tensor map inner box is not 16-byte sized");
+  if (swizzle128)
+    PR_REQUIRE((uint64_t)box[0] * elem_bytes <= 128, PR_ERR_BAD_ARG, "swizzled inner box wider than 128 bytes");
+  CUtensorMapDataType dt = elem_bytes == 2   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                             : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = g_encode(out, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bdim, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  PR_REQUIRE(r == CUDA_SUCCESS, PR_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return PR_OK;
+}
+
+}  // namespace pr
+
+extern "C" int pr_abi_version(void) { return PR_ABI_VERSION; }
+extern "C" const char* pr_last_error(void) { return pr::err_buf(); }
+
+extern "C" int pr_device_status(int device, int* status) {
+  PR_REQUIRE(status != nullptr, PR_ERR_BAD_ARG, "status is null");
+  volatile int* h = nullptr;
+  int rc = pr::status_word(device, nullptr, &h);
+  if (rc != PR_OK) return rc;
+  *status = *h;
+  *h = 0;
+  return PR_OK;
+}
