@@ -1,0 +1,454 @@
+// Fused output kernel: intra-chunk causal power attention, state read-out, merge and
+// normalisation in one pass (the reference's _attention followed by _query_state,
+// retention/_attention/reference.py:10-69 and retention/_query_state/reference.py:36-96,
+// with the gate glue of retention/power_retention_maker.py:180-190).
+//
+// One CTA owns 128 query rows of one (batch, chunk, query head).  For deg = 2
+//     y_i = sum_{j<=i} (s q_i.k_j)^2 e^{a_i-a_j} v_j + phi(q~_i)^T Z_m
+//     l_i = sum_{j<=i} (s q_i.k_j)^2 e^{a_i-a_j}     + q~_i^T Zg_m q~_i
+//     O_i = y_i / l_i,           q~_i = s q_i e^{a_i/2}
+// where Z_m is the state entering the chunk (pair-aligned triangle layout) and Zg_m the
+// scanned Gram matrix of the discounted keys (equivalent to the reference's sum_of_keys).
+// Because both terms share one fp32 accumulator in tensor memory, the reference's
+// rowmax / sqrt(D) range management is not needed.
+//
+// Warp roles: warps 0-3 own one query row per thread (scores -> weights P, expansion
+// phi(q~), epilogue), warp 4 issues TMA loads, warp 5 issues tcgen05.mma.
+//   S = Q K_J^T        : A, B K-major in shared memory (TMA, 128-byte swizzle)
+//   acc += P V_J       : A = P written to tensor memory by the row threads, B = V_J MN-major
+//   acc += phi(q~) Z   : A = expansion written to tensor memory 64 rows at a time,
+//                        B = 64-row blocks of Z by TMA
+//   u = q~ Zg          : A = q~ in tensor memory, B = Zg (hi + lo halves)
+#include "host.cuh"
+#include "layout.cuh"
+#include "sm100.cuh"
+
+namespace pr {
+
+namespace co {
+constexpr int HD = 64;
+constexpr int NS = 4;                 // stages of the expansion / Z ring
+constexpr int THREADS = 192;
+constexpr int TILE_BYTES = 128 * 128;  // 128 rows x 64 16-bit features
+constexpr int Z_BYTES = 64 * 128;      // 64 expanded rows x 64 features
+constexpr int NBLK = t2_dim(HD) / 64;  // 33 blocks of 64 expanded rows
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t COL_ACC = 0, COL_U = 64, COL_S = 128, COL_P = 128, COL_A = 128;
+}  // namespace co
+
+struct ChunkOutParams {
+  int hq, h;            // query heads, kv heads
+  int n_chunks;         // chunks per batch element
+  int cq, ck;           // queries / keys per chunk (query i sits at key position i + ck - cq)
+  int tiles_per_chunk;  // ceil(cq / 128)
+  int state_from_chunk; // chunks >= this read the state (n_chunks: never)
+  int q_gate_last;      // 1: gate the state read-out with the gate at the last key (inference)
+  int normalize;        // 1: O = y / l; 0: O = y (l is written either way when l_out != null)
+  int has_attn;         // 0: no keys at all (state-only read-out)
+  float scale;          // s
+  const float* a;       // [b, n*ck, h] cumulative log gates inside each chunk, or null
+  void* O;              // [b, n*cq, hq, 64]
+  float* l_out;         // [b, n*cq, hq] or null
+  int* status;
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(co::THREADS)
+chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_q,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_ghi,
+                 const __grid_constant__ CUtensorMap tm_glo) {
+  using namespace co;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, attn_done, g_full, acc_done;
+  __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ float sm_ak[2][128];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  uint8_t* smQ = sm;
+  uint8_t* smK = smQ + TILE_BYTES;
+  uint8_t* smV = smK + TILE_BYTES;
+  uint8_t* smZ = smV + TILE_BYTES;        // NS x Z_BYTES
+  uint8_t* smG = smZ + NS * Z_BYTES;      // hi, lo: 2 x Z_BYTES
+
+  const int tile_i = blockIdx.x % p.tiles_per_chunk;
+  const int chunk = blockIdx.x / p.tiles_per_chunk;
+  const int qhead = blockIdx.y, batch = blockIdx.z;
+  const int kvhead = qhead / (p.hq / p.h);
+  const int q_off = p.ck - p.cq;
+  const int row0 = tile_i * 128;
+  const int last_key = min(p.ck - 1, row0 + 127 + q_off);
+  const int nJ = p.has_attn ? last_key / 128 + 1 : 0;
+  const bool has_state = chunk >= p.state_from_chunk;
+  const int n_items = has_state ? NBLK + 1 : 0;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&q_full, 1);
+    mbar_init(&k_full, 1);
+    mbar_init(&k_empty, 1);
+    mbar_init(&v_full, 1);
+    mbar_init(&v_empty, 1);
+    mbar_init(&s_full, 1);
+    mbar_init(&p_full, 4);
+    mbar_init(&attn_done, 1);
+    mbar_init(&g_full, 1);
+    mbar_init(&acc_done, 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&z_full[s], 1);
+      mbar_init(&z_empty[s], 1);
+      mbar_init(&a_full[s], 4);
+      mbar_init(&a_empty[s], 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(&q_full, TILE_BYTES);
+      tma_load_4d(smQ, &tm_q, &q_full, 0, qhead, chunk * p.cq + row0, batch);
+      for (int J = 0; J < nJ && ok; ++J) {
+        ok = mbar_wait(&k_empty, (J & 1) ^ 1, &abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(&k_full, TILE_BYTES);
+        tma_load_4d(smK, &tm_k, &k_full, 0, kvhead, chunk * p.ck + J * 128, batch);
+        ok = mbar_wait(&v_empty, (J & 1) ^ 1, &abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(&v_full, TILE_BYTES);
+        tma_load_4d(smV, &tm_v, &v_full, 0, kvhead, chunk * p.ck + J * 128, batch);
+      }
+      if (ok && has_state) {
+        const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
+        mbar_expect_tx(&g_full, 2 * Z_BYTES);
+        tma_load_2d(smG, &tm_ghi, &g_full, 0, ch * HD);
+        tma_load_2d(smG + Z_BYTES, &tm_glo, &g_full, 0, ch * HD);
+        for (int blk = 0; blk < NBLK; ++blk) {
+          const int s = blk % NS, ph = (blk / NS) & 1;
+          if (!mbar_wait(&z_empty[s], ph ^ 1, &abort_flag)) break;
+          mbar_expect_tx(&z_full[s], Z_BYTES);
+          tma_load_2d(smZ + s * Z_BYTES, &tm_z, &z_full[s], 0, ch * t2_dim(HD) + blk * 64);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(&q_full, 0, &abort_flag);
+      const uint32_t idesc_s = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
+      const uint32_t idesc_v = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
+      const uint32_t idesc_g = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
+      const uint32_t q_addr = smem_u32(smQ), k_addr = smem_u32(smK), v_addr = smem_u32(smV);
+      for (int J = 0; J < nJ && ok; ++J) {
+        ok = mbar_wait(&k_full, J & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + COL_S, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(k_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(&s_full);
+        umma_commit(&k_empty);
+        ok = mbar_wait(&p_full, J & 1, &abort_flag) && mbar_wait(&v_full, J & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + COL_ACC, tmem + COL_P + ks * 8, umma_desc_sw128(v_addr + ks * 2048, 8192, 1024), idesc_v,
+                  (J > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&v_empty);
+        if (J == nJ - 1) umma_commit(&attn_done);
+      }
+      if (ok && has_state) {
+        // item 0: u = q~ Zg (hi then lo)
+        ok = mbar_wait(&a_full[0], 0, &abort_flag) && mbar_wait(&g_full, 0, &abort_flag);
+        if (ok) {
+          tc_fence_after();
+          const uint32_t g_addr = smem_u32(smG);
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ts(tmem + COL_U, tmem + COL_A + ks * 8,
+                      umma_desc_sw128(g_addr + half * Z_BYTES + ks * 32, 16, 1024), idesc_g,
+                      (half > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&a_empty[0]);
+        }
+        for (int it = 1; it <= NBLK && ok; ++it) {
+          const int s = it % NS, ph = (it / NS) & 1;
+          const int zs = (it - 1) % NS, zph = ((it - 1) / NS) & 1;
+          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&z_full[zs], zph, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t z_addr = smem_u32(smZ + zs * Z_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ts(tmem + COL_ACC, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(z_addr + ks * 2048, 8192, 1024),
+                    idesc_v, (nJ > 0 || it > 1 || ks > 0) ? 1u : 0u);
+          umma_commit(&a_empty[s]);
+          umma_commit(&z_empty[zs]);
+        }
+      }
+      if (ok) umma_commit(&acc_done);
+    }
+  } else {
+    // --------------------------------------------------------- row-owning warps
+    const int row = row0 + tid;                 // query index inside the chunk
+    const bool row_valid = row < p.cq;
+    const int qpos = row + q_off;               // key position of this query
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const bool gated = p.a != nullptr;
+    const float* a_chunk = gated ? p.a + ((size_t)batch * p.n_chunks * p.ck + (size_t)chunk * p.ck) * p.h + kvhead
+                                 : nullptr;
+    const float a_i = (gated && row_valid) ? a_chunk[(size_t)qpos * p.h] : 0.f;
+    const float s2 = p.scale * p.scale;
+    float l_acc = 0.f;
+    bool ok = true;
+
+    for (int J = 0; J < nJ; ++J) {
+      const int kp0 = J * 128;
+      {
+        const int kp = kp0 + tid;
+        sm_ak[J & 1][tid] = (gated && kp < p.ck) ? a_chunk[(size_t)kp * p.h] : 0.f;
+      }
+      named_bar_sync(1, 128);
+      ok = mbar_wait(&s_full, J & 1, &abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const float* ak = sm_ak[J & 1];
+      const bool need_mask = (kp0 + 127 > qpos) || (kp0 + 127 >= p.ck);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t sv[32];
+        tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float pv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = q4 * 32 + j + u;
+            const float s = __uint_as_float(sv[j + u]);
+            float w = s2 * s * s;
+            if (gated) w *= __expf(a_i - ak[col]);
+            if (need_mask) {
+              const int kp = kp0 + col;
+              if (kp > qpos || kp >= p.ck) w = 0.f;
+            }
+            pv[u] = w;
+          }
+          pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
+          const float2 back = Pack2<T>::to_f32(pk[j >> 1]);
+          l_acc += back.x + back.y;
+        }
+        tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+    }
+
+    // gated, scaled query row as 32 packed pairs
+    uint32_t q2[32];
+    if (ok && has_state) {
+      ok = mbar_wait(&q_full, 0, &abort_flag);
+      float f = p.scale;
+      if (gated) {
+        const float a_g = p.q_gate_last ? a_chunk[(size_t)(p.ck - 1) * p.h] : a_i;
+        f *= __expf(0.5f * a_g);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(smQ + swz128(tid, j));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = Pack2<T>::to_f32(w[k]);
+          q2[4 * j + k] = Pack2<T>::from_f32(x.x * f, x.y * f);
+        }
+      }
+      // the P columns alias the expansion ring: wait until the last P V product has read them
+      if (ok && nJ > 0) ok = mbar_wait(&attn_done, 0, &abort_flag);
+      tc_fence_after();
+      if (ok) {
+        // item 0: q~ itself (A operand of u = q~ Zg)
+        tmem_st32(tmem + lane_addr + COL_A, q2);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[0]);
+      }
+      // items 1..NBLK: 64 expanded entries (32 packed products) each
+      uint32_t r[32];
+      int cnt = 0;
+#pragma unroll
+      for (int a = 0; a < HD; ++a) {
+        const uint32_t qa = (a & 1) ? dup_hi(q2[a >> 1]) : dup_lo(q2[a >> 1]);
+#pragma unroll
+        for (int j = a >> 1; j < HD / 2; ++j) {
+          r[cnt & 31] = Pack2<T>::mul(qa, q2[j]);
+          ++cnt;
+          if ((cnt & 31) == 0) {
+            const int it = cnt >> 5;  // 1..NBLK
+            const int s = it % NS, ph = (it / NS) & 1;
+            if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+            if (ok) {
+              tc_fence_after();
+              tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+              tmem_wait_st();
+              tc_fence_before();
+            }
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(&a_full[s]);
+          }
+        }
+      }
+    }
+
+    if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
+    tc_fence_after();
+    if (ok) {
+      uint32_t acc[64];
+      tmem_ld32(tmem + lane_addr + COL_ACC, acc);
+      tmem_ld32(tmem + lane_addr + COL_ACC + 32, acc + 32);
+      float l = l_acc;
+      if (has_state) {
+        uint32_t u[64];
+        tmem_ld32(tmem + lane_addr + COL_U, u);
+        tmem_ld32(tmem + lane_addr + COL_U + 32, u + 32);
+        tmem_wait_ld();
+        float ls = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float2 qv = Pack2<T>::to_f32(q2[j]);
+          ls = fmaf(__uint_as_float(u[2 * j]), qv.x, ls);
+          ls = fmaf(__uint_as_float(u[2 * j + 1]), qv.y, ls);
+        }
+        l += ls;
+      } else {
+        tmem_wait_ld();
+      }
+      if (row_valid) {
+        const size_t tok = (size_t)batch * p.n_chunks * p.cq + (size_t)chunk * p.cq + row;
+        const float inv = p.normalize ? 1.f / fmaxf(l, 1e-37f) : 1.f;
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.O) + (tok * p.hq + qhead) * HD);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 v;
+          v.x = Pack2<T>::from_f32(inv * __uint_as_float(acc[8 * j + 0]), inv * __uint_as_float(acc[8 * j + 1]));
+          v.y = Pack2<T>::from_f32(inv * __uint_as_float(acc[8 * j + 2]), inv * __uint_as_float(acc[8 * j + 3]));
+          v.z = Pack2<T>::from_f32(inv * __uint_as_float(acc[8 * j + 4]), inv * __uint_as_float(acc[8 * j + 5]));
+          v.w = Pack2<T>::from_f32(inv * __uint_as_float(acc[8 * j + 6]), inv * __uint_as_float(acc[8 * j + 7]));
+          dst[j] = v;
+        }
+        if (p.l_out != nullptr) p.l_out[tok * p.hq + qhead] = l;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_flag) *p.status = ST_TIMEOUT;
+  if (warp == 0) tmem_dealloc(tmem, co::TMEM_COLS);
+}
+
+}  // namespace pr
+
+extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int hq, int h, int d, const void* Q,
+                            const void* K, const void* V, const float* a, const void* Z, const void* zg_hi,
+                            const void* zg_lo, int state_from_chunk, int q_gate_last, int normalize, float scale,
+                            void* O, float* l_out, int device, void* stream) {
+  using namespace pr;
+  using namespace pr::co;
+  PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && n_chunks > 0 && cq > 0 && ck >= cq && hq > 0 && h > 0 && hq % h == 0, PR_ERR_BAD_ARG,
+             "bad sizes b=%d n=%d cq=%d ck=%d hq=%d h=%d", b, n_chunks, cq, ck, hq, h);
+  PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  const bool has_attn = (K != nullptr && V != nullptr);
+  PR_REQUIRE(Q && O && aligned16(Q) && aligned16(O) && aligned16(K) && aligned16(V), PR_ERR_BAD_ARG,
+             "null or misaligned pointer");
+  PR_REQUIRE(has_attn || Z != nullptr, PR_ERR_BAD_ARG, "neither keys/values nor a state were given");
+  const bool with_state = (Z != nullptr) && state_from_chunk < n_chunks;
+  PR_REQUIRE(!with_state || (zg_hi && zg_lo && aligned16(Z) && aligned16(zg_hi) && aligned16(zg_lo)), PR_ERR_BAD_ARG,
+             "state given without its Gram matrices");
+  PR_REQUIRE(hq <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "hq and b must be <= 65535");
+  PR_CUDA(cudaSetDevice(device));
+  ChunkOutParams p;
+  p.hq = hq;
+  p.h = h;
+  p.n_chunks = n_chunks;
+  p.cq = cq;
+  p.ck = ck;
+  p.tiles_per_chunk = (cq + 127) / 128;
+  p.state_from_chunk = with_state ? state_from_chunk : n_chunks;
+  p.q_gate_last = q_gate_last;
+  p.normalize = normalize;
+  p.has_attn = has_attn ? 1 : 0;
+  p.scale = scale;
+  p.a = a;
+  p.O = O;
+  p.l_out = l_out;
+  int rc = status_word(device, &p.status, nullptr);
+  if (rc) return rc;
+  CUtensorMap tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo;
+  {
+    const uint64_t tq = (uint64_t)n_chunks * cq, tk = (uint64_t)n_chunks * ck;
+    uint64_t dq[4] = {(uint64_t)d, (uint64_t)hq, tq, (uint64_t)b};
+    uint64_t sq[4] = {0, (uint64_t)d * 2, (uint64_t)hq * d * 2, tq * hq * d * 2};
+    uint64_t dk[4] = {(uint64_t)d, (uint64_t)h, tk, (uint64_t)b};
+    uint64_t sk[4] = {0, (uint64_t)d * 2, (uint64_t)h * d * 2, tk * h * d * 2};
+    uint32_t box[4] = {64, 1, 128, 1};
+    if ((rc = make_tmap(&tm_q, Q, 2, 4, dq, sq, box, true))) return rc;
+    if (has_attn) {
+      if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
+      if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
+    } else {
+      tm_k = tm_q;
+      tm_v = tm_q;
+    }
+  }
+  if (with_state) {
+    uint64_t dz[2] = {64, (uint64_t)b * n_chunks * h * t2_dim(d)};
+    uint64_t dg[2] = {64, (uint64_t)b * n_chunks * h * d};
+    uint64_t st[2] = {0, 128};
+    uint32_t box[2] = {64, 64};
+    if ((rc = make_tmap(&tm_z, Z, 2, 2, dz, st, box, true))) return rc;
+    if ((rc = make_tmap(&tm_ghi, zg_hi, 2, 2, dg, st, box, true))) return rc;
+    if ((rc = make_tmap(&tm_glo, zg_lo, 2, 2, dg, st, box, true))) return rc;
+  } else {
+    tm_z = tm_q;
+    tm_ghi = tm_q;
+    tm_glo = tm_q;
+  }
+  const size_t smem = 1024 + 3 * TILE_BYTES + NS * Z_BYTES + 2 * Z_BYTES;
+  dim3 grid(p.tiles_per_chunk * n_chunks, hq, b);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16) {
+    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    chunk_out_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);
+  } else {
+    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    chunk_out_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);
+  }
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}

@@ -1,0 +1,288 @@
+// Token-contracting expansion kernel:  out[D2, e] = w (.) sum_i phi(x_i) v_i^T  per
+// (batch, chunk, head), and the d x d Gram matrix  gram = sum_i xs_i x_i^T.
+//
+// Forward use (the reference's update_state, retention/_update_state/reference.py:31-53):
+//   x = discounted keys, v = values, key weights on -> chunk state S_m; the Gram matrix
+//   of the discounted keys carries the same information as the reference's sum_of_keys
+//   N_m (N[(a,b)] = w(a,b) * gram[a][b]).
+// Backward use (gradient of the state read-out, retention/_query_state/triton.py:337-448):
+//   x = gated queries, v = dO / l, weights off -> dZ_m; xs = x * dl -> gram = d(gram of Z).
+//
+// One CTA owns a tile of 128 expanded rows.  The expansion is never written to shared
+// or global memory: each of 128 threads owns one expanded row (a, b), multiplies rows a
+// and b of the transposed operand (TMA-loaded, 128-byte swizzled) with packed 16-bit
+// multiplies and stores the products straight into tensor memory as the A operand of
+// tcgen05.mma; the values come in by TMA as the MN-major B operand; fp32 accumulation in
+// tensor memory.  The last grid slot in x computes the Gram matrix with both operands
+// in shared memory.
+#include "host.cuh"
+#include "layout.cuh"
+#include "sm100.cuh"
+
+namespace pr {
+
+namespace cs {
+constexpr int HD = 64;          // head dim handled by this build of the kernel
+constexpr int NS = 4;           // pipeline stages
+constexpr int TOK = 64;         // tokens per stage
+constexpr int THREADS = 192;    // warps 0-3 expand + epilogue, 4 TMA, 5 MMA
+constexpr int XT_BYTES = HD * TOK * 2;   // 8 KB
+constexpr int W_BYTES = TOK * HD * 2;    // 8 KB
+constexpr int GA_BYTES = 128 * TOK * 2;  // Gram A operand padded to 128 rows
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t COL_ACC = 0, COL_A = 64;  // A ring: NS x 32 columns
+}  // namespace cs
+
+struct ChunkStateParams {
+  int n_tiles;      // tiles of 128 expanded rows; grid.x = n_tiles + (gram ? 1 : 0)
+  int nh;           // kv heads of the output
+  int group;        // operand heads summed into one output head (GQA ratio in backward)
+  int c, cp;        // chunk length, padded to 64
+  int n_chunks;     // chunks per batch element
+  int key_weights;  // 1: weights {1,2,0}; 0: weights {1,1,0}
+  void* out;        // [b, n, nh, D2, 64]
+  float* gram;      // [b, n, nh, 64, 64] or null
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(cs::THREADS)
+chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap tm_xt,
+                   const __grid_constant__ CUtensorMap tm_xs, const __grid_constant__ CUtensorMap tm_w) {
+  using namespace cs;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t x_full[NS], x_empty[NS], w_full[NS], w_empty[NS], a_full[NS], a_empty[NS], acc_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  uint8_t* smX = sm;                          // NS x XT_BYTES (rows = features, 64 tokens)
+  uint8_t* smW = sm + NS * XT_BYTES;          // NS x W_BYTES  (rows = tokens, 64 features)
+  uint8_t* smG = smW + NS * W_BYTES;          // NS x GA_BYTES (Gram CTA only)
+
+  const int tile = blockIdx.x;
+  const bool gram_cta = (tile == p.n_tiles);
+  const int ch = blockIdx.y;  // (batch * n + chunk) * nh + head
+  const int head = ch % p.nh;
+  const int chunk = (ch / p.nh) % p.n_chunks;
+  const int batch = ch / (p.nh * p.n_chunks);
+  const int kblocks = p.cp / TOK;
+  const int total = kblocks * p.group;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&x_empty[s], gram_cta ? 1 : 4);
+      mbar_init(&w_full[s], 1);
+      mbar_init(&w_empty[s], 1);
+      mbar_init(&a_full[s], 4);
+      mbar_init(&a_empty[s], 1);
+    }
+    mbar_init(&acc_done, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int it = 0; it < total; ++it) {
+        const int s = it % NS, ph = (it / NS) & 1;
+        const int g = it / kblocks, kb = it % kblocks;
+        const int xhead = head * p.group + g;
+        const int xrow = ((batch * p.n_chunks + chunk) * (p.nh * p.group) + xhead) * HD;
+        if (!mbar_wait(&x_empty[s], ph ^ 1, &abort_flag)) break;
+        if (gram_cta) {
+          mbar_expect_tx(&x_full[s], 2 * XT_BYTES);
+          tma_load_2d(smX + s * XT_BYTES, &tm_xt, &x_full[s], kb * TOK, xrow);
+          tma_load_2d(smG + s * GA_BYTES, &tm_xs, &x_full[s], kb * TOK, xrow);
+        } else {
+          mbar_expect_tx(&x_full[s], XT_BYTES);
+          tma_load_2d(smX + s * XT_BYTES, &tm_xt, &x_full[s], kb * TOK, xrow);
+          if (!mbar_wait(&w_empty[s], ph ^ 1, &abort_flag)) break;
+          mbar_expect_tx(&w_full[s], W_BYTES);
+          tma_load_4d(smW + s * W_BYTES, &tm_w, &w_full[s], 0, xhead, chunk * p.c + kb * TOK, batch);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      bool ok = true;
+      if (gram_cta) {
+        const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
+        for (int it = 0; it < total && ok; ++it) {
+          const int s = it % NS, ph = (it / NS) & 1;
+          ok = mbar_wait(&x_full[s], ph, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smG + s * GA_BYTES), b_addr = smem_u32(smX + s * XT_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < TOK / 16; ++ks)
+            umma_ss(tmem + COL_ACC, umma_desc_sw128(a_addr + ks * 32, 16, 1024),
+                    umma_desc_sw128(b_addr + ks * 32, 16, 1024), idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&x_empty[s]);
+        }
+      } else {
+        const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
+        for (int it = 0; it < total && ok; ++it) {
+          const int s = it % NS, ph = (it / NS) & 1;
+          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&w_full[s], ph, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t b_addr = smem_u32(smW + s * W_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < TOK / 16; ++ks)
+            umma_ts(tmem + COL_ACC, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(b_addr + ks * 2048, 8192, 1024),
+                    idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&a_empty[s]);
+          umma_commit(&w_empty[s]);
+        }
+      }
+      if (ok) umma_commit(&acc_done);
+    }
+  } else {
+    // ------------------------------------------------- expansion + epilogue warps
+    const int row_in_tile = warp * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const int D2 = t2_dim(HD);
+    int drow = tile * 128 + row_in_tile;
+    const bool valid = !gram_cta && drow < D2;
+    int a = 0, b = 0;
+    if (valid) t2_decode(HD, drow, &a, &b);
+    bool ok = true;
+    if (!gram_cta) {
+      for (int it = 0; it < total; ++it) {
+        const int s = it % NS, ph = (it / NS) & 1;
+        ok = mbar_wait(&x_full[s], ph, &abort_flag);
+        if (!ok) break;
+        const uint8_t* xs = smX + s * XT_BYTES;
+        uint32_t r[32];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 va = *reinterpret_cast<const uint4*>(xs + swz128(a, j));
+          const uint4 vb = *reinterpret_cast<const uint4*>(xs + swz128(b, j));
+          r[4 * j + 0] = Pack2<T>::mul(va.x, vb.x);
+          r[4 * j + 1] = Pack2<T>::mul(va.y, vb.y);
+          r[4 * j + 2] = Pack2<T>::mul(va.z, vb.z);
+          r[4 * j + 3] = Pack2<T>::mul(va.w, vb.w);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&x_empty[s]);
+        ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[s]);
+      }
+    }
+    if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
+    tc_fence_after();
+    if (ok) {
+      uint32_t acc[64];
+      tmem_ld32(tmem + lane_addr + COL_ACC, acc);
+      tmem_ld32(tmem + lane_addr + COL_ACC + 32, acc + 32);
+      tmem_wait_ld();
+      if (gram_cta) {
+        if (row_in_tile < HD && p.gram != nullptr) {
+          float4* dst = reinterpret_cast<float4*>(p.gram + ((size_t)ch * HD + row_in_tile) * HD);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            dst[j] = make_float4(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]),
+                                 __uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3]));
+        }
+      } else if (valid) {
+        const float wgt = p.key_weights ? t2_key_weight(a, b) : (b < a ? 0.f : 1.f);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.out) + ((size_t)ch * D2 + drow) * HD);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 v;
+          v.x = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 0]), wgt * __uint_as_float(acc[8 * j + 1]));
+          v.y = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 2]), wgt * __uint_as_float(acc[8 * j + 3]));
+          v.z = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 4]), wgt * __uint_as_float(acc[8 * j + 5]));
+          v.w = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 6]), wgt * __uint_as_float(acc[8 * j + 7]));
+          dst[j] = v;
+        }
+      }
+    }
+  }
+  if (tid == 0 && abort_flag) *p.status = ST_TIMEOUT;
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_flag) *p.status = ST_TIMEOUT;
+  if (warp == 0) tmem_dealloc(tmem, cs::TMEM_COLS);
+}
+
+template <typename T>
+static int launch_chunk_state(const ChunkStateParams& p, int b, const CUtensorMap& tm_xt, const CUtensorMap& tm_xs,
+                              const CUtensorMap& tm_w, cudaStream_t stream) {
+  using namespace cs;
+  const size_t smem = 1024 + NS * (XT_BYTES + W_BYTES) + (p.gram ? NS * GA_BYTES : 0);
+  PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(p.n_tiles + (p.gram ? 1 : 0), b * p.n_chunks * p.nh);
+  chunk_state_kernel<T><<<grid, THREADS, smem, stream>>>(p, tm_xt, tm_xs, tm_w);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+}  // namespace pr
+
+extern "C" int pr_chunk_state(int dtype, int b, int t, int nh, int group, int d, int c, const void* xt, const void* xts,
+                              const void* v, void* out, float* gram, int key_weights, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(d == cs::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && t > 0 && nh > 0 && group > 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
+             "bad sizes b=%d t=%d heads=%d group=%d c=%d", b, t, nh, group, c);
+  PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_REQUIRE(xt && v && out && aligned16(xt) && aligned16(v) && aligned16(out), PR_ERR_BAD_ARG,
+             "null or misaligned pointer");
+  PR_REQUIRE(gram == nullptr || (xts != nullptr && aligned16(xts) && aligned16(gram)), PR_ERR_BAD_ARG,
+             "gram requested without a scaled operand");
+  PR_CUDA(cudaSetDevice(device));
+  ChunkStateParams p;
+  p.n_tiles = (t2_dim(d) + 127) / 128;
+  p.nh = nh;
+  p.group = group;
+  p.c = c;
+  p.cp = (c + 63) / 64 * 64;
+  p.n_chunks = t / c;
+  p.key_weights = key_weights;
+  p.out = out;
+  p.gram = gram;
+  int rc = status_word(device, &p.status, nullptr);
+  if (rc) return rc;
+  const int hx = nh * group;
+  CUtensorMap tm_xt, tm_xs, tm_w;
+  {
+    uint64_t dims[2] = {(uint64_t)p.cp, (uint64_t)b * p.n_chunks * hx * d};
+    uint64_t strides[2] = {0, (uint64_t)p.cp * 2};
+    uint32_t box[2] = {64, (uint32_t)d};
+    rc = make_tmap(&tm_xt, xt, 2, 2, dims, strides, box, true);
+    if (rc) return rc;
+    rc = make_tmap(&tm_xs, gram ? xts : xt, 2, 2, dims, strides, box, true);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)d, (uint64_t)hx, (uint64_t)t, (uint64_t)b};
+    uint64_t strides[4] = {0, (uint64_t)d * 2, (uint64_t)hx * d * 2, (uint64_t)t * hx * d * 2};
+    uint32_t box[4] = {64, 1, 64, 1};
+    rc = make_tmap(&tm_w, v, 2, 4, dims, strides, box, true);
+    if (rc) return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == PR_BF16 ? launch_chunk_state<__nv_bfloat16>(p, b, tm_xt, tm_xs, tm_w, s)
+                          : launch_chunk_state<__half>(p, b, tm_xt, tm_xs, tm_w, s);
+}

@@ -1,0 +1,352 @@
+// Gated prefix scan of chunk states over the chunk axis and its reverse-mode
+// counterpart (the reference's discumsum, retention/_discumsum/reference.py:3-15,
+// and the backward recurrence of retention/_discumsum/triton.py:104-204 with the gate
+// index autograd actually yields).  Bandwidth-bound: each thread owns 8 consecutive
+// 16-bit elements (one 128-bit access per chunk), keeps the running state in fp32
+// registers and walks the chunk axis with the next loads already in flight.
+//
+//   forward :  Y[0] = carry_in (0 if absent);  Y[m+1] = Y[m]*exp(A[m]) + X[m]
+//              writes Y[0..n_out-1]  (n_out = n: states entering each chunk, may alias X;
+//              n_out = n+1: the reference's output with the trailing total)
+//   backward:  G[n] = carry_in;  G[m] = dY[m] + exp(A[m]) * G[m+1]
+//              dX[m] = w (.) G[m+1]  (may alias dY),  dA[m] += exp(A[m]) * <Y[m], G[m+1]>
+#include "host.cuh"
+#include "layout.cuh"
+#include "sm100.cuh"
+
+namespace pr {
+
+constexpr int kScanThreads = 256;
+constexpr int kScanUnroll = 4;
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 p = Pack2<T>::to_f32(w[k]);
+    f[2 * k] = p.x;
+    f[2 * k + 1] = p.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  v.x = Pack2<T>::from_f32(f[0], f[1]);
+  v.y = Pack2<T>::from_f32(f[2], f[3]);
+  v.z = Pack2<T>::from_f32(f[4], f[5]);
+  v.w = Pack2<T>::from_f32(f[6], f[7]);
+  return v;
+}
+
+// X, Y: [b, n(_out), h, E]; A: [b, n, h]; carries: [b, h, E] fp32
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restrict__ A,
+                const float* __restrict__ carry_in, float* __restrict__ carry_out, int n, int n_out, int h,
+                size_t E) {
+  const size_t e0 = ((size_t)blockIdx.x * kScanThreads + threadIdx.x) * 8;
+  if (e0 >= E) return;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  float run[8];
+  if (carry_in != nullptr) {
+    const float4* ci = reinterpret_cast<const float4*>(carry_in + ((size_t)batch * h + head) * E + e0);
+    const float4 c0 = ci[0], c1 = ci[1];
+    run[0] = c0.x; run[1] = c0.y; run[2] = c0.z; run[3] = c0.w;
+    run[4] = c1.x; run[5] = c1.y; run[6] = c1.z; run[7] = c1.w;
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) run[k] = 0.f;
+  }
+  const size_t in_stride = (size_t)h * E;
+  const T* xin = X + ((size_t)batch * n * h + head) * E + e0;
+  T* yout = Y + ((size_t)batch * n_out * h + head) * E + e0;
+  const float* Ap = A + (size_t)batch * n * h + head;
+  for (int m0 = 0; m0 < n; m0 += kScanUnroll) {
+    uint4 xv[kScanUnroll];
+    float g[kScanUnroll];
+#pragma unroll
+    for (int u = 0; u < kScanUnroll; ++u) {
+      if (m0 + u < n) {
+        xv[u] = *reinterpret_cast<const uint4*>(xin + (size_t)(m0 + u) * in_stride);
+        g[u] = __expf(Ap[(size_t)(m0 + u) * h]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kScanUnroll; ++u) {
+      if (m0 + u < n) {
+        *reinterpret_cast<uint4*>(yout + (size_t)(m0 + u) * in_stride) = pack8<T>(run);
+        float x[8];
+        unpack8<T>(xv[u], x);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) run[k] = fmaf(run[k], g[u], x[k]);
+      }
+    }
+  }
+  if (n_out > n) *reinterpret_cast<uint4*>(yout + (size_t)n * in_stride) = pack8<T>(run);
+  if (carry_out != nullptr) {
+    float4* co = reinterpret_cast<float4*>(carry_out + ((size_t)batch * h + head) * E + e0);
+    co[0] = make_float4(run[0], run[1], run[2], run[3]);
+    co[1] = make_float4(run[4], run[5], run[6], run[7]);
+  }
+}
+
+// dY, dX: [b, n, h, E] (may alias); Y: [b, n, h, E] states entering each chunk;
+// dA_part: [b, h, gridDim.x, n] per-block partial sums of exp(A[m]) * <Y[m], G[m+1]>.
+// row_weights: apply the key-side weights {1,2,0} of expanded row (e / row_len) to dX.
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict__ dX, const float* __restrict__ A,
+                const float* __restrict__ carry_in, float* __restrict__ carry_out, float* __restrict__ dA_part, int n,
+                int h, size_t E, int row_len, int row_weights) {
+  __shared__ float red[kScanThreads / 32];
+  const size_t e0 = ((size_t)blockIdx.x * kScanThreads + threadIdx.x) * 8;
+  const bool active = e0 < E;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float run[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) run[k] = 0.f;
+  if (active && carry_in != nullptr) {
+    const float4* ci = reinterpret_cast<const float4*>(carry_in + ((size_t)batch * h + head) * E + e0);
+    const float4 c0 = ci[0], c1 = ci[1];
+    run[0] = c0.x; run[1] = c0.y; run[2] = c0.z; run[3] = c0.w;
+    run[4] = c1.x; run[5] = c1.y; run[6] = c1.z; run[7] = c1.w;
+  }
+  float wgt = 1.f;
+  if (active && row_weights) {
+    int a, b;
+    t2_decode(row_len, (int)(e0 / row_len), &a, &b);
+    wgt = t2_key_weight(a, b);
+  }
+  const size_t stride = (size_t)h * E;
+  const size_t base = ((size_t)batch * n * h + head) * E + e0;
+  const float* Ap = A + (size_t)batch * n * h + head;
+  float* part = dA_part + (((size_t)batch * h + head) * gridDim.x + blockIdx.x) * n;
+  for (int m0 = n - 1; m0 >= 0; m0 -= kScanUnroll) {
+    uint4 gv[kScanUnroll], yv[kScanUnroll];
+    float g[kScanUnroll];
+#pragma unroll
+    for (int u = 0; u < kScanUnroll; ++u) {
+      const int m = m0 - u;
+      if (m >= 0 && active) {
+        gv[u] = *reinterpret_cast<const uint4*>(dY + base + (size_t)m * stride);
+        yv[u] = *reinterpret_cast<const uint4*>(Y + base + (size_t)m * stride);
+      }
+      if (m >= 0) g[u] = __expf(Ap[(size_t)m * h]);
+    }
+#pragma unroll
+    for (int u = 0; u < kScanUnroll; ++u) {
+      const int m = m0 - u;
+      if (m < 0) continue;
+      float dot = 0.f;
+      if (active) {
+        float o[8], y[8], dy[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = wgt * run[k];
+        *reinterpret_cast<uint4*>(dX + base + (size_t)m * stride) = pack8<T>(o);
+        unpack8<T>(yv[u], y);
+        unpack8<T>(gv[u], dy);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          dot = fmaf(y[k], run[k], dot);
+          run[k] = fmaf(run[k], g[u], dy[k]);
+        }
+      }
+      dot *= g[u];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      if (lane == 0) red[warp] = dot;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kScanThreads / 32; ++w) s += red[w];
+        part[m] = s;
+      }
+      __syncthreads();
+    }
+  }
+  if (active && carry_out != nullptr) {
+    float4* co = reinterpret_cast<float4*>(carry_out + ((size_t)batch * h + head) * E + e0);
+    co[0] = make_float4(run[0], run[1], run[2], run[3]);
+    co[1] = make_float4(run[4], run[5], run[6], run[7]);
+  }
+}
+
+// ---- Gram matrices (d x d fp32 per chunk): tiny, one thread per element.
+// forward: Zg[m] (entering chunk m) as hi + lo 16-bit halves for the tensor cores,
+// and optionally in fp32 for the backward dot product.
+template <typename T>
+__global__ void scan_gram_fwd_kernel(const float* __restrict__ G, T* __restrict__ hi, T* __restrict__ lo,
+                                     float* __restrict__ full, const float* __restrict__ A,
+                                     const float* __restrict__ carry_in, float* __restrict__ carry_out, int n, int h,
+                                     int E) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  float run = carry_in ? carry_in[((size_t)batch * h + head) * E + e] : 0.f;
+  for (int m = 0; m < n; ++m) {
+    const size_t idx = (((size_t)batch * n + m) * h + head) * E + e;
+    const float x = G[idx];
+    const float g = __expf(A[((size_t)batch * n + m) * h + head]);
+    const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(run)) : T(__float2half_rn(run));
+    hi[idx] = hv;
+    lo[idx] = T(run - float(hv));
+    if (full) full[idx] = run;
+    run = fmaf(run, g, x);
+  }
+  if (carry_out) carry_out[((size_t)batch * h + head) * E + e] = run;
+}
+
+// backward: dG[m] = Gamma[m+1] (+ its transpose: the consumer needs the symmetrised
+// matrix) as hi + lo halves, and the gate-gradient partial sums.
+template <typename T>
+__global__ void scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg, T* __restrict__ hi,
+                                     T* __restrict__ lo, const float* __restrict__ A,
+                                     const float* __restrict__ carry_in, float* __restrict__ carry_out,
+                                     float* __restrict__ dA_part, int n, int h, int d) {
+  // one block per (head, batch), d*d threads' worth of work strided over the block
+  extern __shared__ float sm_run[];  // [d*d] running gradient, then scratch for the reduction
+  __shared__ float red[32];
+  const int E = d * d;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int e = tid; e < E; e += blockDim.x) sm_run[e] = carry_in ? carry_in[((size_t)batch * h + head) * E + e] : 0.f;
+  __syncthreads();
+  for (int m = n - 1; m >= 0; --m) {
+    const size_t base = (((size_t)batch * n + m) * h + head) * E;
+    const float g = __expf(A[((size_t)batch * n + m) * h + head]);
+    float dot = 0.f;
+    for (int e = tid; e < E; e += blockDim.x) {
+      const int r = e / d, cc = e % d;
+      const float sym = sm_run[e] + sm_run[cc * d + r];
+      const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(sym)) : T(__float2half_rn(sym));
+      hi[base + e] = hv;
+      lo[base + e] = T(sym - float(hv));
+      dot = fmaf(Zg[base + e], sm_run[e], dot);
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) sm_run[e] = fmaf(sm_run[e], g, dZg[base + e]);
+    dot *= g;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    if (lane == 0) red[warp] = dot;
+    __syncthreads();
+    if (tid == 0) {
+      float s = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[w];
+      dA_part[((size_t)batch * h + head) * n + m] = s;
+    }
+    __syncthreads();
+  }
+  if (carry_out)
+    for (int e = tid; e < E; e += blockDim.x) carry_out[((size_t)batch * h + head) * E + e] = sm_run[e];
+}
+
+}  // namespace pr
+
+extern "C" int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long long E, const void* X, void* Y,
+                                const float* A, const float* carry_in, float* carry_out, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(b > 0 && n > 0 && h > 0 && E > 0 && E % 8 == 0, PR_ERR_BAD_ARG, "bad sizes b=%d n=%d h=%d E=%lld", b, n,
+             h, E);
+  PR_REQUIRE(n_out == n || n_out == n + 1, PR_ERR_BAD_ARG, "n_out=%d must be n or n+1", n_out);
+  PR_REQUIRE(n_out == n || X != Y, PR_ERR_BAD_ARG, "in-place scan needs n_out == n");
+  PR_REQUIRE(X && Y && A && aligned16(X) && aligned16(Y), PR_ERR_BAD_ARG, "null or misaligned pointer");
+  PR_REQUIRE(h <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "h and b must be <= 65535");
+  PR_CUDA(cudaSetDevice(device));
+  dim3 grid((unsigned)((E / 8 + kScanThreads - 1) / kScanThreads), h, b);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    scan_fwd_kernel<__nv_bfloat16><<<grid, kScanThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(X),
+                                                                static_cast<__nv_bfloat16*>(Y), A, carry_in, carry_out,
+                                                                n, n_out, h, (size_t)E);
+  else if (dtype == PR_FP16)
+    scan_fwd_kernel<__half><<<grid, kScanThreads, 0, s>>>(static_cast<const __half*>(X), static_cast<__half*>(Y), A,
+                                                         carry_in, carry_out, n, n_out, h, (size_t)E);
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+extern "C" int pr_discumsum_bwd_blocks(long long E) { return (int)((E / 8 + pr::kScanThreads - 1) / pr::kScanThreads); }
+
+extern "C" int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, const void* dY, const void* Y, void* dX,
+                                const float* A, const float* carry_in, float* carry_out, float* dA_part, int row_len,
+                                int row_weights, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(b > 0 && n > 0 && h > 0 && E > 0 && E % 8 == 0, PR_ERR_BAD_ARG, "bad sizes b=%d n=%d h=%d E=%lld", b, n,
+             h, E);
+  PR_REQUIRE(dY && Y && dX && A && dA_part && aligned16(dY) && aligned16(Y) && aligned16(dX), PR_ERR_BAD_ARG,
+             "null or misaligned pointer");
+  PR_REQUIRE(!row_weights || (row_len > 0 && row_len % 8 == 0), PR_ERR_BAD_ARG, "row_len %d", row_len);
+  PR_CUDA(cudaSetDevice(device));
+  dim3 grid((unsigned)pr_discumsum_bwd_blocks(E), h, b);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    scan_bwd_kernel<__nv_bfloat16><<<grid, kScanThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(dY), static_cast<const __nv_bfloat16*>(Y), static_cast<__nv_bfloat16*>(dX),
+        A, carry_in, carry_out, dA_part, n, h, (size_t)E, row_len, row_weights);
+  else if (dtype == PR_FP16)
+    scan_bwd_kernel<__half><<<grid, kScanThreads, 0, s>>>(static_cast<const __half*>(dY),
+                                                         static_cast<const __half*>(Y), static_cast<__half*>(dX), A,
+                                                         carry_in, carry_out, dA_part, n, h, (size_t)E, row_len,
+                                                         row_weights);
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+extern "C" int pr_gram_scan_fwd(int dtype, int b, int n, int h, int d, const float* G, void* hi, void* lo,
+                                float* full, const float* A, const float* carry_in, float* carry_out, int device,
+                                void* stream) {
+  using namespace pr;
+  PR_REQUIRE(b > 0 && n > 0 && h > 0 && d > 0, PR_ERR_BAD_ARG, "bad sizes");
+  PR_REQUIRE(G && hi && lo && A, PR_ERR_BAD_ARG, "null pointer");
+  PR_CUDA(cudaSetDevice(device));
+  const int E = d * d;
+  dim3 grid((E + 255) / 256, h, b);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    scan_gram_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(G, static_cast<__nv_bfloat16*>(hi),
+                                                            static_cast<__nv_bfloat16*>(lo), full, A, carry_in,
+                                                            carry_out, n, h, E);
+  else if (dtype == PR_FP16)
+    scan_gram_fwd_kernel<__half><<<grid, 256, 0, s>>>(G, static_cast<__half*>(hi), static_cast<__half*>(lo), full, A,
+                                                     carry_in, carry_out, n, h, E);
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+extern "C" int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const float* dZg, const float* Zg, void* hi,
+                                void* lo, const float* A, const float* carry_in, float* carry_out, float* dA_part,
+                                int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(b > 0 && n > 0 && h > 0 && d > 0 && d <= 128, PR_ERR_BAD_ARG, "bad sizes");
+  PR_REQUIRE(dZg && Zg && hi && lo && A && dA_part, PR_ERR_BAD_ARG, "null pointer");
+  PR_CUDA(cudaSetDevice(device));
+  dim3 grid(1, h, b);
+  const size_t smem = (size_t)d * d * 4;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16) {
+    PR_CUDA(cudaFuncSetAttribute(scan_gram_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    scan_gram_bwd_kernel<__nv_bfloat16><<<grid, 512, smem, s>>>(dZg, Zg, static_cast<__nv_bfloat16*>(hi),
+                                                               static_cast<__nv_bfloat16*>(lo), A, carry_in, carry_out,
+                                                               dA_part, n, h, d);
+  } else if (dtype == PR_FP16) {
+    PR_CUDA(cudaFuncSetAttribute(scan_gram_bwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    scan_gram_bwd_kernel<__half><<<grid, 512, smem, s>>>(dZg, Zg, static_cast<__half*>(hi), static_cast<__half*>(lo),
+                                                        A, carry_in, carry_out, dA_part, n, h, d);
+  } else {
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  }
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}

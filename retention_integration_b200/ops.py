@@ -1,0 +1,140 @@
+"""Thin Python wrappers over the C ABI of libpr_b200.so.
+
+Each function allocates its outputs with torch (device memory is torch's job here),
+passes raw device pointers and the current stream, and raises PRError on a non-zero
+status.  No function in this module computes anything itself.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, lib, ptr, stream_ptr
+
+
+def t2_dim(d: int) -> int:
+    """Rows of the internal pair-aligned expansion layout (2112 for d = 64)."""
+    return d * (d + 2) // 2
+
+
+def _dev(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise _lib.PRError("tensors must live on a CUDA device: there is no CPU path")
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, n: int, k: int) -> torch.Tensor:
+    out = torch.empty(128, n, device=a.device, dtype=torch.float32)
+    check(lib().pr_selftest_umma(c_int(variant), c_int(dtype_code(a.dtype)), c_int(n), c_int(k), ptr(a), ptr(b),
+                                 ptr(out), c_int(_dev(a)), stream_ptr(a.device)), "pr_selftest_umma")
+    return out
+
+
+def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.0, want_gates: bool = True):
+    """x [b,t,hx,d], log_g [b,t,h] fp32 or None ->
+    (a [b,t,h] fp32 or None, A [b,n,h] fp32, xT [b,n,hx,d,cp]) with cp = c rounded up to 64."""
+    b, t, hx, d = x.shape
+    h = log_g.shape[2] if log_g is not None else hx
+    n = t // c
+    cp = (c + 63) // 64 * 64
+    write = want_gates and not query_side
+    a = torch.empty(b, t, h, device=x.device, dtype=torch.float32) if (write and log_g is not None) else None
+    A = torch.empty(b, n, h, device=x.device, dtype=torch.float32) if write else None
+    xt = torch.empty(b, n, hx, d, cp, device=x.device, dtype=x.dtype)
+    check(lib().pr_gate_prep(c_int(dtype_code(x.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
+                             ptr(log_g), ptr(x), ptr(a), ptr(A), ptr(xt), c_int(1 if query_side else 0),
+                             c_float(mult), c_int(1 if write else 0), c_int(_dev(x)), stream_ptr(x.device)),
+          "pr_gate_prep")
+    return a, A, xt
+
+
+def chunk_state(xt: torch.Tensor, xts, v: torch.Tensor, c: int, nh: int, key_weights: bool, want_gram: bool):
+    """xt [b,n,hx,d,cp] (hx = nh*group), v [b,t,hx,d] -> (S [b,n,nh,D2,d], gram [b,n,nh,d,d] fp32 or None)."""
+    b, n, hx, d, cp = xt.shape
+    t = v.shape[1]
+    group = hx // nh
+    out = torch.empty(b, n, nh, t2_dim(d), d, device=xt.device, dtype=xt.dtype)
+    gram = torch.empty(b, n, nh, d, d, device=xt.device, dtype=torch.float32) if want_gram else None
+    if want_gram and xts is None:
+        xts = xt
+    check(lib().pr_chunk_state(c_int(dtype_code(xt.dtype)), c_int(b), c_int(t), c_int(nh), c_int(group), c_int(d),
+                               c_int(c), ptr(xt), ptr(xts), ptr(v), ptr(out), ptr(gram),
+                               c_int(1 if key_weights else 0), c_int(_dev(xt)), stream_ptr(xt.device)),
+          "pr_chunk_state")
+    return out, gram
+
+
+def discumsum_fwd(X: torch.Tensor, A: torch.Tensor, inplace: bool = False, carry_in=None, want_carry: bool = False):
+    """X [b,n,h,...] 16-bit, A [b,n,h] fp32.  inplace: X becomes the states entering each chunk
+    (n entries); otherwise returns Y [b,n+1,h,...] like the reference's discumsum."""
+    b, n, h = X.shape[:3]
+    E = X[0, 0, 0].numel()
+    n_out = n if inplace else n + 1
+    Y = X if inplace else torch.empty(b, n_out, *X.shape[2:], device=X.device, dtype=X.dtype)
+    carry_out = torch.empty(b, h, E, device=X.device, dtype=torch.float32) if want_carry else None
+    check(lib().pr_discumsum_fwd(c_int(dtype_code(X.dtype)), c_int(b), c_int(n), c_int(n_out), c_int(h),
+                                 c_longlong(E), ptr(X), ptr(Y), ptr(A), ptr(carry_in), ptr(carry_out),
+                                 c_int(_dev(X)), stream_ptr(X.device)), "pr_discumsum_fwd")
+    return (Y, carry_out) if want_carry else Y
+
+
+def discumsum_bwd(dY: torch.Tensor, Y: torch.Tensor, A: torch.Tensor, row_len: int = 0, row_weights: bool = False,
+                  inplace: bool = True, carry_in=None, want_carry: bool = False):
+    """Reverse scan.  dY, Y [b,n,h,...].  Returns (dX, dA [b,n,h] fp32[, carry_out])."""
+    b, n, h = dY.shape[:3]
+    E = dY[0, 0, 0].numel()
+    blocks = lib().pr_discumsum_bwd_blocks(c_longlong(E))
+    dX = dY if inplace else torch.empty_like(dY)
+    part = torch.empty(b, h, blocks, n, device=dY.device, dtype=torch.float32)
+    carry_out = torch.empty(b, h, E, device=dY.device, dtype=torch.float32) if want_carry else None
+    check(lib().pr_discumsum_bwd(c_int(dtype_code(dY.dtype)), c_int(b), c_int(n), c_int(h), c_longlong(E), ptr(dY),
+                                 ptr(Y), ptr(dX), ptr(A), ptr(carry_in), ptr(carry_out), ptr(part), c_int(row_len),
+                                 c_int(1 if row_weights else 0), c_int(_dev(dY)), stream_ptr(dY.device)),
+          "pr_discumsum_bwd")
+    dA = part.sum(dim=2).transpose(1, 2).contiguous()  # [b,n,h]
+    return (dX, dA, carry_out) if want_carry else (dX, dA)
+
+
+def gram_scan_fwd(G: torch.Tensor, A: torch.Tensor, dtype, want_full: bool, carry_in=None, want_carry=False):
+    """G [b,n,h,d,d] fp32 -> (hi, lo [b,n,h,d,d] 16-bit, full fp32 or None): Gram matrices entering each chunk."""
+    b, n, h, d, _ = G.shape
+    hi = torch.empty(b, n, h, d, d, device=G.device, dtype=dtype)
+    lo = torch.empty_like(hi)
+    full = torch.empty_like(G) if want_full else None
+    carry_out = torch.empty(b, h, d * d, device=G.device, dtype=torch.float32) if want_carry else None
+    check(lib().pr_gram_scan_fwd(c_int(dtype_code(dtype)), c_int(b), c_int(n), c_int(h), c_int(d), ptr(G), ptr(hi),
+                                 ptr(lo), ptr(full), ptr(A), ptr(carry_in), ptr(carry_out), c_int(_dev(G)),
+                                 stream_ptr(G.device)), "pr_gram_scan_fwd")
+    return (hi, lo, full, carry_out) if want_carry else (hi, lo, full)
+
+
+def gram_scan_bwd(dZg: torch.Tensor, Zg: torch.Tensor, A: torch.Tensor, dtype, carry_in=None, want_carry=False):
+    """dZg, Zg [b,n,h,d,d] fp32 -> (hi, lo of the symmetrised d(gram_m), dA [b,n,h])."""
+    b, n, h, d, _ = dZg.shape
+    hi = torch.empty(b, n, h, d, d, device=dZg.device, dtype=dtype)
+    lo = torch.empty_like(hi)
+    part = torch.empty(b, h, n, device=dZg.device, dtype=torch.float32)
+    carry_out = torch.empty(b, h, d * d, device=dZg.device, dtype=torch.float32) if want_carry else None
+    check(lib().pr_gram_scan_bwd(c_int(dtype_code(dtype)), c_int(b), c_int(n), c_int(h), c_int(d), ptr(dZg), ptr(Zg),
+                                 ptr(hi), ptr(lo), ptr(A), ptr(carry_in), ptr(carry_out), ptr(part), c_int(_dev(dZg)),
+                                 stream_ptr(dZg.device)), "pr_gram_scan_bwd")
+    dA = part.transpose(1, 2).contiguous()
+    return (hi, lo, dA, carry_out) if want_carry else (hi, lo, dA)
+
+
+def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, state_from_chunk: int, scale: float,
+              normalize: bool = True, q_gate_last: bool = False, want_l: bool = True):
+    """Fused attention + state read-out.  Q [b,n*cq,hq,d]; K,V [b,n*ck,h,d] or None; a [b,n*ck,h] or None;
+    Z [b,n,h,D2,d] or None.  Returns (O [b,n*cq,hq,d], l [b,n*cq,hq] fp32 or None)."""
+    b, tq, hq, d = Q.shape
+    h = K.shape[2] if K is not None else Z.shape[2]
+    O = torch.empty_like(Q)
+    l = torch.empty(b, tq, hq, device=Q.device, dtype=torch.float32) if want_l else None
+    check(lib().pr_chunk_out(c_int(dtype_code(Q.dtype)), c_int(b), c_int(n_chunks), c_int(cq), c_int(ck), c_int(hq),
+                             c_int(h), c_int(d), ptr(Q), ptr(K), ptr(V), ptr(a), ptr(Z), ptr(zg_hi), ptr(zg_lo),
+                             c_int(state_from_chunk), c_int(1 if q_gate_last else 0), c_int(1 if normalize else 0),
+                             c_float(scale), ptr(O), ptr(l), c_int(_dev(Q)), stream_ptr(Q.device)), "pr_chunk_out")
+    return O, l
