@@ -1,0 +1,411 @@
+// Backward of the intra-chunk attention with respect to keys and values, merged with the
+// state-path gradients (the reference's attn_bwd_dkdv, retention/_attention/triton.py:390-493,
+// and the dV part of retention/_update_state/reference.py:55-60).
+//
+// One CTA owns 128 key rows (tile J) of one (batch, chunk, kv head); thread = key row.  For
+// every query tile I >= J of every query head of the group:
+//     S^T = K_J Q_I^T,  dP^T = V_J dY_I^T                (tensor cores)
+//     p = (s S)^2 e^{a_i-a_j},  dp = dP + dl_i,  dS = 2 s^2 S e^{a_i-a_j} dp
+//     dV += P^T dY_I,   dK += dS^T Q_I                   (A operands from tensor memory)
+//     da_j -= sum_i p dp                                 (gate gradient, key side)
+// then the state path of the values, dV += phi(k~_j)^T (w (.) dS_m) with k~ the discounted
+// key (same expansion pipeline as the forward read-out).  The epilogue adds the state-path
+// key gradient (fp32, from the expansion-gradient kernel) and writes dK, dV.
+#include "host.cuh"
+#include "layout.cuh"
+#include "sm100.cuh"
+
+namespace pr {
+
+namespace dkv {
+constexpr int HD = 64;
+constexpr int NS = 4;
+constexpr int THREADS = 192;
+constexpr int TILE_BYTES = 128 * 128;
+constexpr int Z_BYTES = 64 * 128;
+constexpr int NBLK = t2_dim(HD) / 64;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_S = 0, COL_P = 0, COL_DP = 128, COL_DS = 128, COL_DV = 256, COL_DK = 320, COL_A = 0;
+}  // namespace dkv
+
+struct ChunkDkvParams {
+  int hq, h, n_chunks, c, tiles_per_chunk;
+  int state_chunk_hi;     // chunks <= this have a state-path dV term
+  float scale;
+  const float* a;         // [b, t, h] or null
+  const float* A;         // [b, n, h] or null
+  const float* dl;        // [b, t, hq]
+  const float* dk_state;  // [b, t, h, 64] fp32 or null
+  void* dK;
+  void* dV;
+  float* da_k;            // [b, t, h]
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(dkv::THREADS)
+chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_q,
+                 const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_ds) {
+  using namespace dkv;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t kv_full, qd_full, qd_empty, sp_full, pd_full, attn_done, acc_done;
+  __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ float sm_aq[2][128], sm_dl[2][128];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  uint8_t* smK = sm;
+  uint8_t* smV = smK + TILE_BYTES;
+  uint8_t* smQ = smV + TILE_BYTES;
+  uint8_t* smDY = smQ + TILE_BYTES;
+  uint8_t* smZ = smDY + TILE_BYTES;  // NS x Z_BYTES
+
+  const int tile_j = blockIdx.x % p.tiles_per_chunk;
+  const int chunk = blockIdx.x / p.tiles_per_chunk;
+  const int kvhead = blockIdx.y, batch = blockIdx.z;
+  const int ratio = p.hq / p.h;
+  const int row0 = tile_j * 128;
+  const int tok_chunk = chunk * p.c;
+  const int nI = p.tiles_per_chunk - tile_j;   // query tiles tile_j .. tiles_per_chunk-1
+  const int n_steps = nI * ratio;
+  const bool has_state = chunk <= p.state_chunk_hi;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&kv_full, 1);
+    mbar_init(&qd_full, 1);
+    mbar_init(&qd_empty, 1);
+    mbar_init(&sp_full, 1);
+    mbar_init(&pd_full, 4);
+    mbar_init(&attn_done, 1);
+    mbar_init(&acc_done, 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&z_full[s], 1);
+      mbar_init(&z_empty[s], 1);
+      mbar_init(&a_full[s], 4);
+      mbar_init(&a_empty[s], 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
+      tma_load_4d(smK, &tm_k, &kv_full, 0, kvhead, tok_chunk + row0, batch);
+      tma_load_4d(smV, &tm_v, &kv_full, 0, kvhead, tok_chunk + row0, batch);
+      for (int st = 0; st < n_steps && ok; ++st) {
+        const int I = tile_j + st / ratio, qh = kvhead * ratio + st % ratio;
+        ok = mbar_wait(&qd_empty, (st & 1) ^ 1, &abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(&qd_full, 2 * TILE_BYTES);
+        tma_load_4d(smQ, &tm_q, &qd_full, 0, qh, tok_chunk + I * 128, batch);
+        tma_load_4d(smDY, &tm_dy, &qd_full, 0, qh, tok_chunk + I * 128, batch);
+      }
+      if (ok && has_state) {
+        const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
+        for (int blk = 0; blk < NBLK; ++blk) {
+          const int s = blk % NS, ph = (blk / NS) & 1;
+          if (!mbar_wait(&z_empty[s], ph ^ 1, &abort_flag)) break;
+          mbar_expect_tx(&z_full[s], Z_BYTES);
+          tma_load_2d(smZ + s * Z_BYTES, &tm_ds, &z_full[s], 0, ch * t2_dim(HD) + blk * 64);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      bool ok = mbar_wait(&kv_full, 0, &abort_flag);
+      const uint32_t idesc_s = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
+      const uint32_t idesc_o = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
+      const uint32_t k_addr = smem_u32(smK), v_addr = smem_u32(smV), q_addr = smem_u32(smQ),
+                     dy_addr = smem_u32(smDY);
+      for (int st = 0; st < n_steps && ok; ++st) {
+        ok = mbar_wait(&qd_full, st & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + COL_S, umma_desc_sw128(k_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(q_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + COL_DP, umma_desc_sw128(v_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(dy_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(&sp_full);
+        ok = mbar_wait(&pd_full, st & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + COL_DV, tmem + COL_P + ks * 8, umma_desc_sw128(dy_addr + ks * 2048, 8192, 1024), idesc_o,
+                  (st > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + COL_DK, tmem + COL_DS + ks * 8, umma_desc_sw128(q_addr + ks * 2048, 8192, 1024), idesc_o,
+                  (st > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&qd_empty);
+        if (st == n_steps - 1) umma_commit(&attn_done);
+      }
+      if (ok && has_state) {
+        for (int it = 0; it < NBLK && ok; ++it) {
+          const int s = it % NS, ph = (it / NS) & 1;
+          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&z_full[s], ph, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t z_addr = smem_u32(smZ + s * Z_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ts(tmem + COL_DV, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(z_addr + ks * 2048, 8192, 1024),
+                    idesc_o, 1u);
+          umma_commit(&a_empty[s]);
+          umma_commit(&z_empty[s]);
+        }
+      }
+      if (ok) umma_commit(&acc_done);
+    }
+  } else {
+    const int row = row0 + tid;  // key index inside the chunk
+    const bool row_valid = row < p.c;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const bool gated = p.a != nullptr;
+    const size_t tok_base = (size_t)batch * p.n_chunks * p.c + tok_chunk;
+    const float* a_chunk = gated ? p.a + tok_base * p.h + kvhead : nullptr;
+    const float a_j = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
+    const float s2 = p.scale * p.scale;
+    float da = 0.f;
+    bool ok = true;
+    for (int st = 0; st < n_steps; ++st) {
+      const int I = tile_j + st / ratio, qh = kvhead * ratio + st % ratio;
+      const int qp0 = I * 128;
+      {
+        const int qp = qp0 + tid;
+        const bool v = qp < p.c;
+        sm_aq[st & 1][tid] = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
+        sm_dl[st & 1][tid] = v ? p.dl[(tok_base + qp) * p.hq + qh] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ok = mbar_wait(&sp_full, st & 1, &abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const float* aq = sm_aq[st & 1];
+      const float* dlq = sm_dl[st & 1];
+      const bool need_mask = (qp0 < row) || (qp0 + 127 >= p.c) || !row_valid;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t sv[32], pv[32];
+        tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+        tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
+        tmem_wait_ld();
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float pw[2], dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = q4 * 32 + j + u;
+            const float s = __uint_as_float(sv[j + u]);
+            float g = s2;
+            if (gated) g *= __expf(aq[col] - a_j);
+            const float dp = __uint_as_float(pv[j + u]) + dlq[col];
+            float sg = s * g;
+            if (need_mask) {
+              const int qp = qp0 + col;
+              if (qp < row || qp >= p.c || !row_valid) sg = 0.f;
+            }
+            const float pval = sg * s;
+            da = fmaf(pval, dp, da);
+            pw[u] = pval;
+            dsv[u] = 2.f * sg * dp;
+          }
+          pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
+          dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+        }
+        tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
+        tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, dk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&pd_full);
+    }
+
+    if (ok && has_state) {
+      ok = mbar_wait(&kv_full, 0, &abort_flag);
+      float f = 1.f;
+      if (gated) {
+        const float A = p.A[(batch * p.n_chunks + chunk) * p.h + kvhead];
+        f = __expf(0.5f * (A - a_j));
+      }
+      uint32_t k2[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(smK + swz128(tid, j));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = Pack2<T>::to_f32(w[k]);
+          k2[4 * j + k] = Pack2<T>::from_f32(x.x * f, x.y * f);
+        }
+      }
+      if (ok && n_steps > 0) ok = mbar_wait(&attn_done, 0, &abort_flag);
+      tc_fence_after();
+      uint32_t r[32];
+      int cnt = 0;
+#pragma unroll
+      for (int a = 0; a < HD; ++a) {
+        const uint32_t ka = (a & 1) ? dup_hi(k2[a >> 1]) : dup_lo(k2[a >> 1]);
+#pragma unroll
+        for (int j = a >> 1; j < HD / 2; ++j) {
+          r[cnt & 31] = Pack2<T>::mul(ka, k2[j]);
+          ++cnt;
+          if ((cnt & 31) == 0) {
+            const int it = (cnt >> 5) - 1;  // 0..NBLK-1
+            const int s = it % NS, ph = (it / NS) & 1;
+            if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+            if (ok) {
+              tc_fence_after();
+              tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+              tmem_wait_st();
+              tc_fence_before();
+            }
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(&a_full[s]);
+          }
+        }
+      }
+    }
+
+    if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
+    tc_fence_after();
+    if (ok) {
+      uint32_t acc[64];
+      const size_t tok = tok_base + row;
+      // dV
+      tmem_ld32(tmem + lane_addr + COL_DV, acc);
+      tmem_ld32(tmem + lane_addr + COL_DV + 32, acc + 32);
+      tmem_wait_ld();
+      if (row_valid) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.dV) + (tok * p.h + kvhead) * HD);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 v;
+          v.x = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 0]), __uint_as_float(acc[8 * j + 1]));
+          v.y = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 2]), __uint_as_float(acc[8 * j + 3]));
+          v.z = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 4]), __uint_as_float(acc[8 * j + 5]));
+          v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]), __uint_as_float(acc[8 * j + 7]));
+          dst[j] = v;
+        }
+      }
+      // dK
+      tmem_ld32(tmem + lane_addr + COL_DK, acc);
+      tmem_ld32(tmem + lane_addr + COL_DK + 32, acc + 32);
+      tmem_wait_ld();
+      if (row_valid) {
+        const float4* st = p.dk_state ? reinterpret_cast<const float4*>(p.dk_state + (tok * p.h + kvhead) * HD)
+                                      : nullptr;
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.dK) + (tok * p.h + kvhead) * HD);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+          if (st) {
+            s0 = st[2 * j];
+            s1 = st[2 * j + 1];
+          }
+          uint4 v;
+          v.x = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 0]) + s0.x, __uint_as_float(acc[8 * j + 1]) + s0.y);
+          v.y = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 2]) + s0.z, __uint_as_float(acc[8 * j + 3]) + s0.w);
+          v.z = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 4]) + s1.x, __uint_as_float(acc[8 * j + 5]) + s1.y);
+          v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
+          dst[j] = v;
+        }
+        p.da_k[tok * p.h + kvhead] = -da;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_flag) *p.status = ST_TIMEOUT;
+  if (warp == 0) tmem_dealloc(tmem, dkv::TMEM_COLS);
+}
+
+}  // namespace pr
+
+extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dY,
+                            const void* K, const void* V, const void* wdS, const float* a, const float* A,
+                            const float* dl, const float* dk_state, int state_chunk_hi, float scale, void* dK,
+                            void* dV, float* da_k, int device, void* stream) {
+  using namespace pr;
+  using namespace pr::dkv;
+  PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && t > 0 && hq > 0 && h > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
+             "bad sizes b=%d t=%d hq=%d h=%d c=%d", b, t, hq, h, c);
+  PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_REQUIRE(Q && dY && K && V && dl && dK && dV && da_k, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(Q) && aligned16(dY) && aligned16(K) && aligned16(V) && aligned16(dK) && aligned16(dV) &&
+                 aligned16(wdS) && aligned16(dk_state),
+             PR_ERR_BAD_ARG, "misaligned pointer");
+  PR_REQUIRE(!(wdS != nullptr && a != nullptr) || A != nullptr, PR_ERR_BAD_ARG,
+             "gated state path needs the chunk gate totals A");
+  PR_REQUIRE(h <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "h and b must be <= 65535");
+  PR_CUDA(cudaSetDevice(device));
+  ChunkDkvParams p;
+  p.hq = hq;
+  p.h = h;
+  p.n_chunks = t / c;
+  p.c = c;
+  p.tiles_per_chunk = (c + 127) / 128;
+  p.state_chunk_hi = wdS ? state_chunk_hi : -1;
+  p.scale = scale;
+  p.a = a;
+  p.A = A;
+  p.dl = dl;
+  p.dk_state = dk_state;
+  p.dK = dK;
+  p.dV = dV;
+  p.da_k = da_k;
+  int rc = status_word(device, &p.status, nullptr);
+  if (rc) return rc;
+  CUtensorMap tm_q, tm_dy, tm_k, tm_v, tm_ds;
+  uint64_t dq_[4] = {(uint64_t)d, (uint64_t)hq, (uint64_t)t, (uint64_t)b};
+  uint64_t sq[4] = {0, (uint64_t)d * 2, (uint64_t)hq * d * 2, (uint64_t)t * hq * d * 2};
+  uint64_t dk[4] = {(uint64_t)d, (uint64_t)h, (uint64_t)t, (uint64_t)b};
+  uint64_t sk[4] = {0, (uint64_t)d * 2, (uint64_t)h * d * 2, (uint64_t)t * h * d * 2};
+  uint32_t box[4] = {64, 1, 128, 1};
+  if ((rc = make_tmap(&tm_q, Q, 2, 4, dq_, sq, box, true))) return rc;
+  if ((rc = make_tmap(&tm_dy, dY, 2, 4, dq_, sq, box, true))) return rc;
+  if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
+  if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
+  if (wdS) {
+    uint64_t dz[2] = {64, (uint64_t)b * p.n_chunks * h * t2_dim(d)};
+    uint64_t st[2] = {0, 128};
+    uint32_t bz[2] = {64, 64};
+    if ((rc = make_tmap(&tm_ds, wdS, 2, 2, dz, st, bz, true))) return rc;
+  } else {
+    tm_ds = tm_q;
+  }
+  const size_t smem = 1024 + 4 * TILE_BYTES + NS * Z_BYTES;
+  dim3 grid(p.tiles_per_chunk * p.n_chunks, h, b);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16) {
+    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    chunk_dkv_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);
+  } else {
+    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    chunk_dkv_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);
+  }
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}

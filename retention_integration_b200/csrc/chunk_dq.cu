@@ -1,0 +1,273 @@
+// Backward of the intra-chunk attention with respect to the queries, merged with the
+// state-path query gradient (the reference's attn_bwd_dq, retention/_attention/triton.py:496-603,
+// for deg = 2 without the division by the score).
+//
+// One CTA owns 128 query rows of one (batch, chunk, query head); thread = row.  For every
+// key tile J up to the diagonal:
+//     S  = Q K_J^T,  dP = dY V_J^T                      (tensor cores, fp32 in tensor memory)
+//     p  = (s S)^2 e^{a_i-a_j},  dp = dP + dl_i,  e = p dp,  dS = 2 s^2 S e^{a_i-a_j} dp
+//     dQ += dS K_J                                      (A = dS from tensor memory)
+//     da_i += sum_j e_ij                                (gate gradient, query side)
+// with dY = dO / l and dl = -<O, dO> / l from the backward prologue.  The epilogue adds the
+// state-path gradient (fp32, from the expansion-gradient kernel) and writes dQ.
+#include "host.cuh"
+#include "sm100.cuh"
+
+namespace pr {
+
+namespace dq {
+constexpr int HD = 64;
+constexpr int THREADS = 192;
+constexpr int TILE_BYTES = 128 * 128;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_S = 0, COL_DS = 0, COL_DP = 128, COL_ACC = 256;
+}  // namespace dq
+
+struct ChunkDqParams {
+  int hq, h, n_chunks, c, tiles_per_chunk;
+  float scale;
+  const float* a;         // [b, t, h] or null
+  const float* dl;        // [b, t, hq]
+  const float* dq_state;  // [b, t, hq, 64] fp32 or null
+  void* dQ;               // [b, t, hq, 64]
+  float* da_q;            // [b, t, hq]
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(dq::THREADS)
+chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
+                const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v) {
+  using namespace dq;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t q_full, kv_full, kv_empty, sp_full, ds_full, acc_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ float sm_ak[2][128];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  uint8_t* smQ = sm;
+  uint8_t* smDY = smQ + TILE_BYTES;
+  uint8_t* smK = smDY + TILE_BYTES;
+  uint8_t* smV = smK + TILE_BYTES;
+
+  const int tile_i = blockIdx.x % p.tiles_per_chunk;
+  const int chunk = blockIdx.x / p.tiles_per_chunk;
+  const int qhead = blockIdx.y, batch = blockIdx.z;
+  const int kvhead = qhead / (p.hq / p.h);
+  const int row0 = tile_i * 128;
+  const int nJ = min(p.c - 1, row0 + 127) / 128 + 1;
+  const int tok_chunk = chunk * p.c;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&q_full, 1);
+    mbar_init(&kv_full, 1);
+    mbar_init(&kv_empty, 1);
+    mbar_init(&sp_full, 1);
+    mbar_init(&ds_full, 4);
+    mbar_init(&acc_done, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, 2 * TILE_BYTES);
+      tma_load_4d(smQ, &tm_q, &q_full, 0, qhead, tok_chunk + row0, batch);
+      tma_load_4d(smDY, &tm_dy, &q_full, 0, qhead, tok_chunk + row0, batch);
+      for (int J = 0; J < nJ; ++J) {
+        if (!mbar_wait(&kv_empty, (J & 1) ^ 1, &abort_flag)) break;
+        mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
+        tma_load_4d(smK, &tm_k, &kv_full, 0, kvhead, tok_chunk + J * 128, batch);
+        tma_load_4d(smV, &tm_v, &kv_full, 0, kvhead, tok_chunk + J * 128, batch);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      bool ok = mbar_wait(&q_full, 0, &abort_flag);
+      const uint32_t idesc_s = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
+      const uint32_t idesc_q = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
+      const uint32_t q_addr = smem_u32(smQ), dy_addr = smem_u32(smDY), k_addr = smem_u32(smK),
+                     v_addr = smem_u32(smV);
+      for (int J = 0; J < nJ && ok; ++J) {
+        ok = mbar_wait(&kv_full, J & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + COL_S, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(k_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + COL_DP, umma_desc_sw128(dy_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(v_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(&sp_full);
+        ok = mbar_wait(&ds_full, J & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + COL_ACC, tmem + COL_DS + ks * 8, umma_desc_sw128(k_addr + ks * 2048, 8192, 1024), idesc_q,
+                  (J > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&kv_empty);
+      }
+      if (ok) umma_commit(&acc_done);
+    }
+  } else {
+    const int row = row0 + tid;
+    const bool row_valid = row < p.c;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const bool gated = p.a != nullptr;
+    const size_t tok = (size_t)batch * p.n_chunks * p.c + tok_chunk + row;
+    const float* a_chunk = gated ? p.a + ((size_t)batch * p.n_chunks * p.c + tok_chunk) * p.h + kvhead : nullptr;
+    const float a_i = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
+    const float dl_i = row_valid ? p.dl[tok * p.hq + qhead] : 0.f;
+    const float s2 = p.scale * p.scale;
+    float da = 0.f;
+    bool ok = true;
+    for (int J = 0; J < nJ; ++J) {
+      const int kp0 = J * 128;
+      {
+        const int kp = kp0 + tid;
+        sm_ak[J & 1][tid] = (gated && kp < p.c) ? a_chunk[(size_t)kp * p.h] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ok = mbar_wait(&sp_full, J & 1, &abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const float* ak = sm_ak[J & 1];
+      const bool need_mask = (kp0 + 127 > row) || (kp0 + 127 >= p.c);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t sv[32], pv[32];
+        tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+        tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = q4 * 32 + j + u;
+            const float s = __uint_as_float(sv[j + u]);
+            float g = s2;
+            if (gated) g *= __expf(a_i - ak[col]);
+            const float dp = __uint_as_float(pv[j + u]) + dl_i;
+            float sg = s * g;  // s^2 S e^{a_i-a_j}
+            if (need_mask) {
+              const int kp = kp0 + col;
+              if (kp > row || kp >= p.c) sg = 0.f;
+            }
+            da = fmaf(sg * s, dp, da);
+            dsv[u] = 2.f * sg * dp;
+          }
+          pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+        }
+        tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_full);
+    }
+    if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
+    tc_fence_after();
+    if (ok) {
+      uint32_t acc[64];
+      tmem_ld32(tmem + lane_addr + COL_ACC, acc);
+      tmem_ld32(tmem + lane_addr + COL_ACC + 32, acc + 32);
+      tmem_wait_ld();
+      if (row_valid) {
+        const float4* st = p.dq_state ? reinterpret_cast<const float4*>(p.dq_state + (tok * p.hq + qhead) * HD)
+                                      : nullptr;
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.dQ) + (tok * p.hq + qhead) * HD);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+          if (st) {
+            s0 = st[2 * j];
+            s1 = st[2 * j + 1];
+          }
+          uint4 v;
+          v.x = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 0]) + s0.x, __uint_as_float(acc[8 * j + 1]) + s0.y);
+          v.y = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 2]) + s0.z, __uint_as_float(acc[8 * j + 3]) + s0.w);
+          v.z = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 4]) + s1.x, __uint_as_float(acc[8 * j + 5]) + s1.y);
+          v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
+          dst[j] = v;
+        }
+        p.da_q[tok * p.hq + qhead] = da;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_flag) *p.status = ST_TIMEOUT;
+  if (warp == 0) tmem_dealloc(tmem, dq::TMEM_COLS);
+}
+
+}  // namespace pr
+
+extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dY,
+                           const void* K, const void* V, const float* a, const float* dl, const float* dq_state,
+                           float scale, void* dQ, float* da_q, int device, void* stream) {
+  using namespace pr;
+  using namespace pr::dq;
+  PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && t > 0 && hq > 0 && h > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
+             "bad sizes b=%d t=%d hq=%d h=%d c=%d", b, t, hq, h, c);
+  PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_REQUIRE(Q && dY && K && V && dl && dQ && da_q, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(Q) && aligned16(dY) && aligned16(K) && aligned16(V) && aligned16(dQ) && aligned16(dq_state),
+             PR_ERR_BAD_ARG, "misaligned pointer");
+  PR_REQUIRE(hq <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "hq and b must be <= 65535");
+  PR_CUDA(cudaSetDevice(device));
+  ChunkDqParams p;
+  p.hq = hq;
+  p.h = h;
+  p.n_chunks = t / c;
+  p.c = c;
+  p.tiles_per_chunk = (c + 127) / 128;
+  p.scale = scale;
+  p.a = a;
+  p.dl = dl;
+  p.dq_state = dq_state;
+  p.dQ = dQ;
+  p.da_q = da_q;
+  int rc = status_word(device, &p.status, nullptr);
+  if (rc) return rc;
+  CUtensorMap tm_q, tm_dy, tm_k, tm_v;
+  uint64_t dq_[4] = {(uint64_t)d, (uint64_t)hq, (uint64_t)t, (uint64_t)b};
+  uint64_t sq[4] = {0, (uint64_t)d * 2, (uint64_t)hq * d * 2, (uint64_t)t * hq * d * 2};
+  uint64_t dk[4] = {(uint64_t)d, (uint64_t)h, (uint64_t)t, (uint64_t)b};
+  uint64_t sk[4] = {0, (uint64_t)d * 2, (uint64_t)h * d * 2, (uint64_t)t * h * d * 2};
+  uint32_t box[4] = {64, 1, 128, 1};
+  if ((rc = make_tmap(&tm_q, Q, 2, 4, dq_, sq, box, true))) return rc;
+  if ((rc = make_tmap(&tm_dy, dY, 2, 4, dq_, sq, box, true))) return rc;
+  if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
+  if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
+  const size_t smem = 1024 + 4 * TILE_BYTES;
+  dim3 grid(p.tiles_per_chunk * p.n_chunks, hq, b);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16) {
+    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    chunk_dq_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v);
+  } else {
+    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    chunk_dq_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v);
+  }
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}

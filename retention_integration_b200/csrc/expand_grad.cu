@@ -1,0 +1,380 @@
+// Gradient of the symmetric-power expansion with respect to its argument:
+//     dphi_i[(a,b)] = sum_e W[i,e] * State[(a,b), e]         (tensor cores, K = 64)
+//     dx~_i[a] += dphi_i[(a,b)] * x~_i[b],  dx~_i[b] += dphi_i[(a,b)] * x~_i[a]   (CUDA cores)
+//     dx~_i    += g_i * mult * Gs x~_i                        (Gram part: tensor cores)
+// and the chain rule through the gate factor f_i (x~ = round(x f_i)):
+//     dX_i = dx~_i * f_i,     gdot_i = <x~_i, dx~_i> / 2      (the gate-gradient term).
+//
+// Query side (gradient of the state read-out, retention/_query_state/triton.py:181-325):
+//   W = dO / l, State = Z_m (state entering the chunk), Gs = Zg_m, g_i = dl_i, mult = 2,
+//   f_i = s * exp(a_i / 2).
+// Key side (gradient of the chunk state, retention/_update_state/reference.py:55-83):
+//   W = V, State = w (.) dS_m, Gs = dG_m + dG_m^T, g_i = 1, mult = 1, f_i = exp((A_m - a_i)/2).
+//
+// One CTA owns 128 tokens of one (batch, chunk, head).  The expansion gradient dphi is
+// never written to memory: tiles of 128 expanded rows are produced in tensor memory
+// (double buffered) and drained by two groups of four warps, each thread owning one
+// token row and keeping x~ and its partial dx~ in registers; the triangle's (a, b)
+// pattern is resolved at compile time, so the drain is two FMAs per entry.
+#include <type_traits>
+
+#include "host.cuh"
+#include "layout.cuh"
+#include "sm100.cuh"
+
+namespace pr {
+
+namespace eg {
+constexpr int HD = 64;
+constexpr int D2 = t2_dim(HD);           // 2112
+constexpr int NT = (D2 + 127) / 128;     // 17 tiles, the last one 64 rows wide
+constexpr int THREADS = 320;             // warps 0-3 / 4-7 drain groups, 8 TMA, 9 MMA
+constexpr int TILE_BYTES = 128 * 128;
+constexpr int G_BYTES = 64 * 128;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t COL_D = 0;            // 2 x 128 columns
+constexpr uint32_t COL_U = 256, COL_XA = 320;
+
+__host__ __device__ constexpr int t2_a(int idx) {
+  int p = 0;
+  while (p + 1 <= HD / 2 && 2 * (p + 1) * (HD - (p + 1) + 1) <= idx) ++p;
+  const int rem = idx - 2 * p * (HD - p + 1);
+  return rem < HD - 2 * p ? 2 * p : 2 * p + 1;
+}
+__host__ __device__ constexpr int t2_b(int idx) {
+  int p = 0;
+  while (p + 1 <= HD / 2 && 2 * (p + 1) * (HD - (p + 1) + 1) <= idx) ++p;
+  const int rem = idx - 2 * p * (HD - p + 1);
+  return rem < HD - 2 * p ? 2 * p + rem : 2 * p + rem - (HD - 2 * p);
+}
+
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+}  // namespace eg
+
+struct ExpandGradParams {
+  int h, hx;             // gate/state heads, operand heads (hx = h * ratio)
+  int n_chunks, c;
+  int tiles_per_chunk;
+  int chunk_lo, chunk_hi;  // chunks in [lo, hi] have a state term; the others get zeros
+  int query_side;
+  float scale;           // s (query side only)
+  float gram_mult;
+  const float* a;        // [b, t, h] or null
+  const float* A;        // [b, n, h] or null
+  const float* row_g;    // [b, t, hx] (query side: dl) or null (= 1)
+  float* dX;             // [b, t, hx, 64] fp32
+  float* gdot;           // [b, t, hx]
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(eg::THREADS, 1)
+expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap tm_w,
+                   const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_s,
+                   const __grid_constant__ CUtensorMap tm_ghi, const __grid_constant__ CUtensorMap tm_glo) {
+  using namespace eg;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t w_full, g_full, xa_full, u_full, s_full[2], s_empty[2], d_full[2], d_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile_i = blockIdx.x % p.tiles_per_chunk;
+  const int chunk = blockIdx.x / p.tiles_per_chunk;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int gh = head / (p.hx / p.h);
+  const int row0 = tile_i * 128;
+  const size_t tok0 = (size_t)batch * p.n_chunks * p.c + (size_t)chunk * p.c;
+
+  if (chunk < p.chunk_lo || chunk > p.chunk_hi) {
+    // no state term for this chunk: zero gradient
+    if (tid < 128) {
+      const int row = row0 + tid;
+      if (row < p.c) {
+        float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) dst[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        p.gdot[(tok0 + row) * p.hx + head] = 0.f;
+      }
+    }
+    return;
+  }
+
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  uint8_t* smW = sm;
+  uint8_t* smX = smW + TILE_BYTES;
+  uint8_t* smS = smX + TILE_BYTES;              // 2 x TILE_BYTES
+  uint8_t* smG = smS + 2 * TILE_BYTES;          // hi, lo
+  float* smR = reinterpret_cast<float*>(smG + 2 * G_BYTES);  // [64][128] partial exchange
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&w_full, 1);
+    mbar_init(&g_full, 1);
+    mbar_init(&xa_full, 4);
+    mbar_init(&u_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 1);
+      mbar_init(&d_full[s], 1);
+      mbar_init(&d_empty[s], 4);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const int ch = (batch * p.n_chunks + chunk) * p.h + gh;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      mbar_expect_tx(&w_full, 2 * TILE_BYTES);
+      tma_load_4d(smW, &tm_w, &w_full, 0, head, chunk * p.c + row0, batch);
+      tma_load_4d(smX, &tm_x, &w_full, 0, head, chunk * p.c + row0, batch);
+      mbar_expect_tx(&g_full, 2 * G_BYTES);
+      tma_load_2d(smG, &tm_ghi, &g_full, 0, ch * HD);
+      tma_load_2d(smG + G_BYTES, &tm_glo, &g_full, 0, ch * HD);
+      for (int nt = 0; nt < NT; ++nt) {
+        const int s = nt & 1, ph = (nt >> 1) & 1;
+        if (!mbar_wait(&s_empty[s], ph ^ 1, &abort_flag)) break;
+        mbar_expect_tx(&s_full[s], TILE_BYTES);
+        tma_load_2d(smS + s * TILE_BYTES, &tm_s, &s_full[s], 0, ch * D2 + nt * 128);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      bool ok = mbar_wait(&w_full, 0, &abort_flag);
+      const uint32_t w_addr = smem_u32(smW);
+      for (int nt = 0; nt < NT && ok; ++nt) {
+        const int s = nt & 1, ph = (nt >> 1) & 1;
+        ok = mbar_wait(&s_full[s], ph, &abort_flag) && mbar_wait(&d_empty[s], ph ^ 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t idesc = umma_idesc(128, nt == NT - 1 ? 64 : 128, Pack2<T>::is_bf16, false, false);
+        const uint32_t s_addr = smem_u32(smS + s * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + COL_D + s * 128, umma_desc_sw128(w_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(s_addr + ks * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
+        umma_commit(&d_full[s]);
+        umma_commit(&s_empty[s]);
+        if (nt == 0) {
+          // Gram part: u = x~ (Gs_hi + Gs_lo)
+          ok = mbar_wait(&xa_full, 0, &abort_flag) && mbar_wait(&g_full, 0, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t idesc_g = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
+          const uint32_t g_addr = smem_u32(smG);
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ts(tmem + COL_U, tmem + COL_XA + ks * 8, umma_desc_sw128(g_addr + half * G_BYTES + ks * 32, 16, 1024),
+                      idesc_g, (half > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&u_full);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ drain warps
+    const int group = warp >> 2;               // 0: even tiles + epilogue, 1: odd tiles
+    const int r = (warp & 3) * 32 + lane;      // token row inside the tile = TMEM lane
+    const int row = row0 + r;
+    const bool row_valid = row < p.c;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+
+    float f = p.query_side ? p.scale : 1.f;
+    if (p.a != nullptr) {
+      const float a_i = row_valid ? p.a[(tok0 + row) * p.h + gh] : 0.f;
+      f *= p.query_side ? __expf(0.5f * a_i) : __expf(0.5f * (p.A[ch] - a_i));
+    }
+    bool ok = mbar_wait(&w_full, 0, &abort_flag);
+    float x[HD], dx[HD];
+    {
+      uint32_t xp[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(smX + swz128(r, j));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 raw = Pack2<T>::to_f32(w[k]);
+          xp[4 * j + k] = Pack2<T>::from_f32(raw.x * f, raw.y * f);
+          const float2 rounded = Pack2<T>::to_f32(xp[4 * j + k]);
+          x[8 * j + 2 * k] = rounded.x;
+          x[8 * j + 2 * k + 1] = rounded.y;
+        }
+      }
+      if (group == 0 && ok) {
+        tmem_st32(tmem + lane_addr + COL_XA, xp);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&xa_full);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < HD; ++e) dx[e] = 0.f;
+
+    static_for<0, NT>([&](auto nt_c) {
+      constexpr int nt = decltype(nt_c)::value;
+      constexpr int ncols = (nt == NT - 1) ? D2 - 128 * (NT - 1) : 128;
+      if (group == (nt & 1)) {
+        const int s = nt & 1, ph = (nt >> 1) & 1;
+        if (ok) ok = mbar_wait(&d_full[s], ph, &abort_flag);
+        tc_fence_after();
+        if (ok) {
+          static_for<0, ncols / 32>([&](auto q_c) {
+            constexpr int q = decltype(q_c)::value;
+            uint32_t v[32];
+            tmem_ld32(tmem + lane_addr + COL_D + s * 128 + q * 32, v);
+            tmem_wait_ld();
+            if constexpr (q == ncols / 32 - 1) {
+              // all of this thread's reads of the buffer are done
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&d_empty[s]);
+            }
+            float ra0 = 0.f, ra1 = 0.f;
+            static_for<0, 32>([&](auto j_c) {
+              constexpr int j = decltype(j_c)::value;
+              constexpr int D = nt * 128 + q * 32 + j;
+              constexpr int a = t2_a(D), b = t2_b(D);
+              const float val = __uint_as_float(v[j]);
+              dx[b] = fmaf(val, x[a], dx[b]);
+              if constexpr (j & 1)
+                ra1 = fmaf(val, x[b], ra1);
+              else
+                ra0 = fmaf(val, x[b], ra0);
+              constexpr bool row_ends = (j == 31) || (t2_a(D + 1) != a);
+              if constexpr (row_ends) {
+                dx[a] += ra0 + ra1;
+                ra0 = 0.f;
+                ra1 = 0.f;
+              }
+            });
+          });
+        }
+      }
+    });
+
+    // combine the two groups' partial sums
+    if (group == 1) {
+#pragma unroll
+      for (int e = 0; e < HD; ++e) smR[e * 128 + r] = dx[e];
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (group == 0) {
+#pragma unroll
+      for (int e = 0; e < HD; ++e) dx[e] += smR[e * 128 + r];
+      if (ok) ok = mbar_wait(&u_full, 0, &abort_flag);
+      tc_fence_after();
+      if (ok) {
+        uint32_t u[64];
+        tmem_ld32(tmem + lane_addr + COL_U, u);
+        tmem_ld32(tmem + lane_addr + COL_U + 32, u + 32);
+        tmem_wait_ld();
+        float g = p.gram_mult;
+        if (p.row_g != nullptr) g *= row_valid ? p.row_g[(tok0 + row) * p.hx + head] : 0.f;
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+          dx[e] = fmaf(g, __uint_as_float(u[e]), dx[e]);
+          dot = fmaf(x[e], dx[e], dot);
+        }
+        if (row_valid) {
+          float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            dst[j] = make_float4(dx[4 * j] * f, dx[4 * j + 1] * f, dx[4 * j + 2] * f, dx[4 * j + 3] * f);
+          p.gdot[(tok0 + row) * p.hx + head] = 0.5f * dot;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_flag) *p.status = ST_TIMEOUT;
+  if (warp == 0) tmem_dealloc(tmem, eg::TMEM_COLS);
+}
+
+}  // namespace pr
+
+extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int c, const void* W, const void* X,
+                              const void* State, const void* g_hi, const void* g_lo, const float* a, const float* A,
+                              const float* row_g, int query_side, float scale, float gram_mult, int chunk_lo,
+                              int chunk_hi, float* dX, float* gdot, int device, void* stream) {
+  using namespace pr;
+  using namespace pr::eg;
+  PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && t > 0 && h > 0 && hx > 0 && hx % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
+             "bad sizes b=%d t=%d h=%d hx=%d c=%d", b, t, h, hx, c);
+  PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_REQUIRE(W && X && State && g_hi && g_lo && dX && gdot, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(W) && aligned16(X) && aligned16(State) && aligned16(g_hi) && aligned16(g_lo) && aligned16(dX),
+             PR_ERR_BAD_ARG, "misaligned pointer");
+  PR_REQUIRE((a == nullptr) == (A == nullptr), PR_ERR_BAD_ARG, "a and A must be given together");
+  PR_REQUIRE(hx <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "hx and b must be <= 65535");
+  PR_CUDA(cudaSetDevice(device));
+  const int n = t / c;
+  ExpandGradParams p;
+  p.h = h;
+  p.hx = hx;
+  p.n_chunks = n;
+  p.c = c;
+  p.tiles_per_chunk = (c + 127) / 128;
+  p.chunk_lo = chunk_lo;
+  p.chunk_hi = chunk_hi;
+  p.query_side = query_side;
+  p.scale = scale;
+  p.gram_mult = gram_mult;
+  p.a = a;
+  p.A = A;
+  p.row_g = row_g;
+  p.dX = dX;
+  p.gdot = gdot;
+  int rc = status_word(device, &p.status, nullptr);
+  if (rc) return rc;
+  CUtensorMap tm_w, tm_x, tm_s, tm_ghi, tm_glo;
+  {
+    uint64_t dims[4] = {(uint64_t)d, (uint64_t)hx, (uint64_t)t, (uint64_t)b};
+    uint64_t str[4] = {0, (uint64_t)d * 2, (uint64_t)hx * d * 2, (uint64_t)t * hx * d * 2};
+    uint32_t box[4] = {64, 1, 128, 1};
+    if ((rc = make_tmap(&tm_w, W, 2, 4, dims, str, box, true))) return rc;
+    if ((rc = make_tmap(&tm_x, X, 2, 4, dims, str, box, true))) return rc;
+  }
+  {
+    uint64_t ds[2] = {64, (uint64_t)b * n * h * D2};
+    uint64_t dg[2] = {64, (uint64_t)b * n * h * d};
+    uint64_t st[2] = {0, 128};
+    uint32_t box_s[2] = {64, 128}, box_g[2] = {64, 64};
+    if ((rc = make_tmap(&tm_s, State, 2, 2, ds, st, box_s, true))) return rc;
+    if ((rc = make_tmap(&tm_ghi, g_hi, 2, 2, dg, st, box_g, true))) return rc;
+    if ((rc = make_tmap(&tm_glo, g_lo, 2, 2, dg, st, box_g, true))) return rc;
+  }
+  const size_t smem = 1024 + 4 * TILE_BYTES + 2 * G_BYTES + 64 * 128 * 4;
+  dim3 grid(p.tiles_per_chunk * n, hx, b);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16) {
+    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    expand_grad_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
+  } else {
+    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    expand_grad_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
+  }
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}

@@ -15,11 +15,13 @@ constexpr int kPrepThreads = 256;
 template <typename T>
 __global__ void __launch_bounds__(kPrepThreads)
 gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float* __restrict__ a_out,
-                 float* __restrict__ A_out, T* __restrict__ xt, int t, int h, int hx, int d, int c, int cp,
-                 int query_side, float mult, int write_a) {
+                 float* __restrict__ A_out, T* __restrict__ xt, const float* __restrict__ row_scale,
+                 T* __restrict__ xts, int t, int h, int hx, int d, int c, int cp, int query_side, float mult,
+                 int write_a) {
   extern __shared__ float sm_f[];
   float* sm_a = sm_f;                                    // [c] cumulative gates
   T* tile = reinterpret_cast<T*>(sm_f + ((c + 3) & ~3)); // [64][d + 2]
+  T* tile2 = tile + 64 * (d + 2);                        // same, times row_scale
   __shared__ float warp_tot[kPrepThreads / 32];
   __shared__ float carry_s;
 
@@ -69,25 +71,35 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
   const int ld = d + 2;
   const int vec_per_row = d / 8;
   T* out_base = xt + ((size_t)(batch * n + chunk) * hx + head) * (size_t)d * cp;
+  T* out2_base = xts ? xts + ((size_t)(batch * n + chunk) * hx + head) * (size_t)d * cp : nullptr;
   for (int tb = 0; tb < cp; tb += 64) {
     __syncthreads();
     for (int idx = tid; idx < 64 * vec_per_row; idx += kPrepThreads) {
       const int r = idx / vec_per_row, v = idx % vec_per_row;
       const int i = tb + r;
       uint4 raw = make_uint4(0, 0, 0, 0);
-      float f = 0.f;
+      float f = 0.f, rs = 0.f;
       if (i < c) {
         raw = *reinterpret_cast<const uint4*>(x + ((tok0 + i) * hx + head) * (size_t)d + v * 8);
         f = query_side ? mult * __expf(0.5f * sm_a[i]) : mult * __expf(0.5f * (A - sm_a[i]));
+        if (xts != nullptr) rs = row_scale[(tok0 + i) * hx + head];
       }
       uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t w2[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float2 p = Pack2<T>::to_f32(w[k]);
         w[k] = Pack2<T>::from_f32(p.x * f, p.y * f);
+        // the scaled copy multiplies the ROUNDED gated value, so that both copies describe the same x~
+        float2 pr_ = Pack2<T>::to_f32(w[k]);
+        w2[k] = Pack2<T>::from_f32(pr_.x * rs, pr_.y * rs);
       }
       uint32_t* dst = reinterpret_cast<uint32_t*>(tile + r * ld + v * 8);
       dst[0] = w[0]; dst[1] = w[1]; dst[2] = w[2]; dst[3] = w[3];
+      if (xts != nullptr) {
+        uint32_t* dst2 = reinterpret_cast<uint32_t*>(tile2 + r * ld + v * 8);
+        dst2[0] = w2[0]; dst2[1] = w2[1]; dst2[2] = w2[2]; dst2[3] = w2[3];
+      }
     }
     __syncthreads();
     // each thread writes 8 consecutive tokens of one feature row
@@ -97,15 +109,147 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
 #pragma unroll
       for (int k = 0; k < 8; ++k) vals[k] = tile[(tv * 8 + k) * ld + row];
       *reinterpret_cast<uint4*>(out_base + (size_t)row * cp + tb + tv * 8) = *reinterpret_cast<uint4*>(vals);
+      if (xts != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) vals[k] = tile2[(tv * 8 + k) * ld + row];
+        *reinterpret_cast<uint4*>(out2_base + (size_t)row * cp + tb + tv * 8) = *reinterpret_cast<uint4*>(vals);
+      }
     }
+  }
+}
+
+// Backward prologue per output row: delta = <O, dO>, dy = dO / l (16-bit), dl = -delta / l.
+// (O = y / l, so dL/dy = dO / l and dL/dl = -<dO, y> / l^2 = -delta / l.)
+template <typename T>
+__global__ void dout_prep_kernel(const T* __restrict__ O, const T* __restrict__ dO, const float* __restrict__ l,
+                                 T* __restrict__ dy, float* __restrict__ dl, size_t rows, int d) {
+  const int lanes_per_row = d / 8;  // 4, 8 or 16 threads share a row
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t row = gid / lanes_per_row;
+  const int sub = (int)(gid % lanes_per_row);
+  const bool active = row < rows;
+  float part = 0.f, inv = 0.f;
+  uint4 g = make_uint4(0, 0, 0, 0);
+  if (active) {
+    const uint4 o = *reinterpret_cast<const uint4*>(O + row * d + sub * 8);
+    g = *reinterpret_cast<const uint4*>(dO + row * d + sub * 8);
+    inv = 1.f / fmaxf(l[row], 1e-37f);
+    const uint32_t ow[4] = {o.x, o.y, o.z, o.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = Pack2<T>::to_f32(ow[k]), b = Pack2<T>::to_f32(gw[k]);
+      part = fmaf(a.x, b.x, fmaf(a.y, b.y, part));
+    }
+  }
+  for (int off = lanes_per_row >> 1; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+  if (active) {
+    uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 b = Pack2<T>::to_f32(gw[k]);
+      gw[k] = Pack2<T>::from_f32(b.x * inv, b.y * inv);
+    }
+    *reinterpret_cast<uint4*>(dy + row * d + sub * 8) = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+    if (sub == 0) dl[row] = -part * inv;
+  }
+}
+
+
+// Gate gradient assembly.  With a_i the inclusive cumulative log-gate inside a chunk and
+// A the chunk total, dlog_G[u] = sum_{i >= u in chunk} da_i + dA, where
+//   da_i = sum over the group's query heads of (attention term + state read-out term)
+//          + key-side attention term - key discount term,
+//   dA   = scan terms (state and Gram) + sum_i key discount term.
+__global__ void __launch_bounds__(kPrepThreads)
+gate_grad_kernel(const float* __restrict__ da_q, const float* __restrict__ gq, const float* __restrict__ da_k,
+                 const float* __restrict__ wk, const float* __restrict__ dA_scan, const float* __restrict__ dA_gram,
+                 float* __restrict__ dlog_g, int t, int h, int hq, int c) {
+  __shared__ float warp_tot[kPrepThreads / 32];
+  __shared__ float carry_s, wk_sum_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n = t / c, ratio = hq / h;
+  const int head = blockIdx.x % h;
+  const int chunk = (blockIdx.x / h) % n;
+  const int batch = blockIdx.x / (h * n);
+  const size_t tok0 = (size_t)batch * t + (size_t)chunk * c;
+
+  // sum of the key discount terms over the chunk
+  float part = 0.f;
+  if (wk != nullptr)
+    for (int i = tid; i < c; i += kPrepThreads) part += wk[(tok0 + i) * h + head];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+  if (lane == 0) warp_tot[warp] = part;
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.f;
+    for (int w = 0; w < kPrepThreads / 32; ++w) s += warp_tot[w];
+    const size_t ci = ((size_t)batch * n + chunk) * h + head;
+    wk_sum_s = s + (dA_scan ? dA_scan[ci] : 0.f) + (dA_gram ? dA_gram[ci] : 0.f);
+    carry_s = 0.f;
+  }
+  __syncthreads();
+  const float dA = wk_sum_s;
+
+  // reverse inclusive scan: walk the chunk from its end
+  for (int base = 0; base < c; base += kPrepThreads) {
+    const int ri = base + tid;     // distance from the end
+    const int i = c - 1 - ri;
+    float v = 0.f;
+    if (ri < c) {
+      const size_t tk = (tok0 + i) * h + head;
+      v = da_k[tk] - (wk ? wk[tk] : 0.f);
+      for (int r = 0; r < ratio; ++r) {
+        const size_t tq = (tok0 + i) * hq + head * ratio + r;
+        v += da_q[tq] + (gq ? gq[tq] : 0.f);
+      }
+    }
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float o = __shfl_up_sync(0xffffffffu, v, off);
+      if (lane >= off) v += o;
+    }
+    __syncthreads();
+    if (lane == 31) warp_tot[warp] = v;
+    __syncthreads();
+    float pre = carry_s;
+    for (int w = 0; w < warp; ++w) pre += warp_tot[w];
+    v += pre;
+    if (ri < c) dlog_g[(tok0 + i) * h + head] = v + dA;
+    __syncthreads();
+    if (tid == kPrepThreads - 1) carry_s = v;
+    __syncthreads();
   }
 }
 
 }  // namespace pr
 
+extern "C" int pr_dout_prep(int dtype, long long rows, int d, const void* O, const void* dO, const float* l, void* dy,
+                            float* dl, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(rows > 0 && (d == 32 || d == 64 || d == 128), PR_ERR_BAD_ARG, "rows=%lld d=%d", rows, d);
+  PR_REQUIRE(O && dO && l && dy && dl && aligned16(O) && aligned16(dO) && aligned16(dy), PR_ERR_BAD_ARG,
+             "null or misaligned pointer");
+  PR_CUDA(cudaSetDevice(device));
+  const size_t threads = (size_t)rows * (d / 8);
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    dout_prep_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(O),
+                                                        static_cast<const __nv_bfloat16*>(dO), l,
+                                                        static_cast<__nv_bfloat16*>(dy), dl, (size_t)rows, d);
+  else if (dtype == PR_FP16)
+    dout_prep_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(O), static_cast<const __half*>(dO), l,
+                                                 static_cast<__half*>(dy), dl, (size_t)rows, d);
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
 extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c, const float* log_g, const void* x,
-                            float* a_out, float* A_out, void* xt, int query_side, float mult, int write_a, int device,
-                            void* stream) {
+                            float* a_out, float* A_out, void* xt, const float* row_scale, void* xts, int query_side,
+                            float mult, int write_a, int device, void* stream) {
   using namespace pr;
   PR_REQUIRE(b > 0 && t > 0 && h > 0 && hx > 0 && hx % h == 0, PR_ERR_BAD_ARG, "bad sizes b=%d t=%d h=%d hx=%d", b, t,
              h, hx);
@@ -115,23 +259,40 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
   PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_REQUIRE(xt == nullptr || (x != nullptr && aligned16(x) && aligned16(xt)), PR_ERR_BAD_ARG,
              "x / xt null or misaligned");
+  PR_REQUIRE(xts == nullptr || (xt != nullptr && row_scale != nullptr && aligned16(xts)), PR_ERR_BAD_ARG,
+             "scaled copy requested without xt or row_scale");
   PR_CUDA(cudaSetDevice(device));
   const int cp = (c + 63) / 64 * 64;
-  const size_t smem = (size_t)((c + 3) & ~3) * 4 + (size_t)64 * (d + 2) * 2;
+  const size_t smem = (size_t)((c + 3) & ~3) * 4 + (size_t)2 * 64 * (d + 2) * 2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = b * (t / c) * hx;
   if (dtype == PR_BF16) {
     PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
     gate_prep_kernel<__nv_bfloat16><<<grid, kPrepThreads, smem, s>>>(
-        log_g, static_cast<const __nv_bfloat16*>(x), a_out, A_out, static_cast<__nv_bfloat16*>(xt), t, h, hx, d, c, cp,
-        query_side, mult, write_a);
+        log_g, static_cast<const __nv_bfloat16*>(x), a_out, A_out, static_cast<__nv_bfloat16*>(xt), row_scale,
+        static_cast<__nv_bfloat16*>(xts), t, h, hx, d, c, cp, query_side, mult, write_a);
   } else {
     PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     gate_prep_kernel<__half><<<grid, kPrepThreads, smem, s>>>(log_g, static_cast<const __half*>(x), a_out, A_out,
-                                                              static_cast<__half*>(xt), t, h, hx, d, c, cp, query_side,
-                                                              mult, write_a);
+                                                              static_cast<__half*>(xt), row_scale,
+                                                              static_cast<__half*>(xts), t, h, hx, d, c, cp,
+                                                              query_side, mult, write_a);
   }
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+extern "C" int pr_gate_grad(int b, int t, int h, int hq, int c, const float* da_q, const float* gq, const float* da_k,
+                            const float* wk, const float* dA_scan, const float* dA_gram, float* dlog_g, int device,
+                            void* stream) {
+  using namespace pr;
+  PR_REQUIRE(b > 0 && t > 0 && h > 0 && hq > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
+             "bad sizes b=%d t=%d h=%d hq=%d c=%d", b, t, h, hq, c);
+  PR_REQUIRE(da_q && da_k && dlog_g, PR_ERR_BAD_ARG, "null pointer");
+  PR_CUDA(cudaSetDevice(device));
+  gate_grad_kernel<<<b * (t / c) * h, kPrepThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      da_q, gq, da_k, wk, dA_scan, dA_gram, dlog_g, t, h, hq, c);
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }

@@ -33,9 +33,11 @@ def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, n: int, k: int
     return out
 
 
-def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.0, want_gates: bool = True):
+def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.0, want_gates: bool = True,
+              row_scale=None, want_xt: bool = True):
     """x [b,t,hx,d], log_g [b,t,h] fp32 or None ->
-    (a [b,t,h] fp32 or None, A [b,n,h] fp32, xT [b,n,hx,d,cp]) with cp = c rounded up to 64."""
+    (a [b,t,h] fp32 or None, A [b,n,h] fp32, xT [b,n,hx,d,cp]) with cp = c rounded up to 64.
+    With row_scale [b,t,hx] fp32 a fourth result is the copy of xT scaled per token."""
     b, t, hx, d = x.shape
     h = log_g.shape[2] if log_g is not None else hx
     n = t // c
@@ -43,12 +45,26 @@ def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.
     write = want_gates and not query_side
     a = torch.empty(b, t, h, device=x.device, dtype=torch.float32) if (write and log_g is not None) else None
     A = torch.empty(b, n, h, device=x.device, dtype=torch.float32) if write else None
-    xt = torch.empty(b, n, hx, d, cp, device=x.device, dtype=x.dtype)
+    xt = torch.empty(b, n, hx, d, cp, device=x.device, dtype=x.dtype) if want_xt else None
+    xts = torch.empty_like(xt) if (row_scale is not None and want_xt) else None
     check(lib().pr_gate_prep(c_int(dtype_code(x.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
-                             ptr(log_g), ptr(x), ptr(a), ptr(A), ptr(xt), c_int(1 if query_side else 0),
-                             c_float(mult), c_int(1 if write else 0), c_int(_dev(x)), stream_ptr(x.device)),
-          "pr_gate_prep")
+                             ptr(log_g), ptr(x), ptr(a), ptr(A), ptr(xt), ptr(row_scale), ptr(xts),
+                             c_int(1 if query_side else 0), c_float(mult), c_int(1 if write else 0), c_int(_dev(x)),
+                             stream_ptr(x.device)), "pr_gate_prep")
+    if row_scale is not None:
+        return a, A, xt, xts
     return a, A, xt
+
+
+def dout_prep(O: torch.Tensor, dO: torch.Tensor, l: torch.Tensor):
+    """O, dO [..., d] 16-bit, l [...] fp32 -> (dy = dO / l (16-bit), dl = -<O, dO> / l fp32)."""
+    d = O.shape[-1]
+    rows = O.numel() // d
+    dy = torch.empty_like(O)
+    dl = torch.empty_like(l)
+    check(lib().pr_dout_prep(c_int(dtype_code(O.dtype)), c_longlong(rows), c_int(d), ptr(O), ptr(dO), ptr(l), ptr(dy),
+                             ptr(dl), c_int(_dev(O)), stream_ptr(O.device)), "pr_dout_prep")
+    return dy, dl
 
 
 def chunk_state(xt: torch.Tensor, xts, v: torch.Tensor, c: int, nh: int, key_weights: bool, want_gram: bool):
@@ -138,3 +154,54 @@ def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, stat
                              c_int(state_from_chunk), c_int(1 if q_gate_last else 0), c_int(1 if normalize else 0),
                              c_float(scale), ptr(O), ptr(l), c_int(_dev(Q)), stream_ptr(Q.device)), "pr_chunk_out")
     return O, l
+
+
+def expand_grad(W, X, State, g_hi, g_lo, a, A, row_g, c: int, h: int, query_side: bool, scale: float,
+                gram_mult: float, chunk_lo: int, chunk_hi: int):
+    """Gradient through the expansion.  W, X [b,t,hx,d]; State [b,n,h,D2,d]; g_hi/g_lo [b,n,h,d,d].
+    Returns (dX [b,t,hx,d] fp32, gdot [b,t,hx] fp32)."""
+    b, t, hx, d = X.shape
+    dX = torch.empty(b, t, hx, d, device=X.device, dtype=torch.float32)
+    gdot = torch.empty(b, t, hx, device=X.device, dtype=torch.float32)
+    check(lib().pr_expand_grad(c_int(dtype_code(X.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
+                               ptr(W), ptr(X), ptr(State), ptr(g_hi), ptr(g_lo), ptr(a), ptr(A), ptr(row_g),
+                               c_int(1 if query_side else 0), c_float(scale), c_float(gram_mult), c_int(chunk_lo),
+                               c_int(chunk_hi), ptr(dX), ptr(gdot), c_int(_dev(X)), stream_ptr(X.device)),
+          "pr_expand_grad")
+    return dX, gdot
+
+
+def chunk_dq(Q, dY, K, V, a, dl, dq_state, c: int, scale: float):
+    """Returns (dQ [b,t,hq,d], da_q [b,t,hq] fp32)."""
+    b, t, hq, d = Q.shape
+    h = K.shape[2]
+    dQ = torch.empty_like(Q)
+    da_q = torch.empty(b, t, hq, device=Q.device, dtype=torch.float32)
+    check(lib().pr_chunk_dq(c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
+                            ptr(Q), ptr(dY), ptr(K), ptr(V), ptr(a), ptr(dl), ptr(dq_state), c_float(scale), ptr(dQ),
+                            ptr(da_q), c_int(_dev(Q)), stream_ptr(Q.device)), "pr_chunk_dq")
+    return dQ, da_q
+
+
+def chunk_dkv(Q, dY, K, V, wdS, a, A, dl, dk_state, c: int, state_chunk_hi: int, scale: float):
+    """Returns (dK, dV [b,t,h,d], da_k [b,t,h] fp32)."""
+    b, t, hq, d = Q.shape
+    h = K.shape[2]
+    dK, dV = torch.empty_like(K), torch.empty_like(V)
+    da_k = torch.empty(b, t, h, device=Q.device, dtype=torch.float32)
+    check(lib().pr_chunk_dkv(c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
+                             ptr(Q), ptr(dY), ptr(K), ptr(V), ptr(wdS), ptr(a), ptr(A), ptr(dl), ptr(dk_state),
+                             c_int(state_chunk_hi), c_float(scale), ptr(dK), ptr(dV), ptr(da_k), c_int(_dev(Q)),
+                             stream_ptr(Q.device)), "pr_chunk_dkv")
+    return dK, dV, da_k
+
+
+def gate_grad(da_q, gq, da_k, wk, dA_scan, dA_gram, c: int):
+    """Assembles dlog_G [b,t,h] from the per-token and per-chunk gate-gradient terms."""
+    b, t, hq = da_q.shape
+    h = da_k.shape[2]
+    out = torch.empty(b, t, h, device=da_q.device, dtype=torch.float32)
+    check(lib().pr_gate_grad(c_int(b), c_int(t), c_int(h), c_int(hq), c_int(c), ptr(da_q), ptr(gq), ptr(da_k),
+                             ptr(wk), ptr(dA_scan), ptr(dA_gram), ptr(out), c_int(_dev(da_q)),
+                             stream_ptr(da_q.device)), "pr_gate_grad")
+    return out

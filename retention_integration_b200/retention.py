@@ -1,0 +1,147 @@
+"""`power_retention` and `power_retention_inference` with the reference's signatures
+(retention/power_retention_maker.py:72-73 and :287-288), running on libpr_b200.so.
+
+The host side only validates arguments, pads, allocates and sequences kernel launches;
+every arithmetic step of the path is a kernel of the C-ABI library.  There is no
+PyTorch or CPU fallback: inputs must be CUDA tensors of dtype bfloat16 or float16.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import layout, ops
+from ._lib import PRError
+
+_SUPPORTED_D = (64,)
+
+
+def _check_inputs(Q, K, V, log_G, deg):
+    if deg != 2:
+        raise PRError(f"deg={deg}: the state kernels implement deg=2 (as the reference's state operators do)")
+    if not (Q.is_cuda and K.is_cuda and V.is_cuda):
+        raise PRError("Q, K, V must be CUDA tensors: this package has no CPU path")
+    assert Q.dtype == K.dtype == V.dtype, f"dtypes of inputs must match: {Q.dtype=}, {K.dtype=}, {V.dtype=}"
+    if Q.dtype not in (torch.bfloat16, torch.float16):
+        raise PRError(f"dtype {Q.dtype} unsupported: use bfloat16 or float16")
+    b, t, hq, d = Q.shape
+    h = K.shape[2]
+    assert hq % h == 0, f"Q heads must be a multiple of KV heads: {hq=} {h=}"
+    if d not in _SUPPORTED_D:
+        raise PRError(f"head dim {d} unsupported by this build (supported: {_SUPPORTED_D})")
+    if log_G is not None:
+        assert log_G.shape == K.shape[:3], "log_G must be [batch, seq_len, kv_heads]"
+
+
+class _ChunkedRetention(torch.autograd.Function):
+    """Chunked forward/backward.  Sequence length is a multiple of the chunk size here."""
+
+    @staticmethod
+    def forward(ctx, Q, K, V, log_G, c, scale):
+        b, t, hq, d = Q.shape
+        h = K.shape[2]
+        n = t // c
+        a, A, KT = ops.gate_prep(K, log_G, c, query_side=False)
+        S, gram = ops.chunk_state(KT, None, V, c, h, key_weights=True, want_gram=True)
+        del KT
+        Z = ops.discumsum_fwd(S, A, inplace=True)
+        zhi, zlo, zfull = ops.gram_scan_fwd(gram, A, Q.dtype, want_full=True)
+        O, l = ops.chunk_out(Q, K, V, a, Z, zhi, zlo, n, c, c, 1, scale)
+        ctx.save_for_backward(Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull)
+        ctx.c, ctx.scale = c, scale
+        return O
+
+    @staticmethod
+    def backward(ctx, dO):
+        Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull = ctx.saved_tensors
+        c, scale = ctx.c, ctx.scale
+        b, t, hq, d = Q.shape
+        h = K.shape[2]
+        n = t // c
+        dO = dO.contiguous()
+        dy, dl = ops.dout_prep(O, dO, l)
+        # state read-out: dZ_m = sum_i phi(q~_i) dy_i^T, dZg_m = sum_i dl_i q~_i q~_i^T
+        _, _, QT, QTs = ops.gate_prep(Q, log_G, c, query_side=True, mult=scale, row_scale=dl)
+        dZ, dZg = ops.chunk_state(QT, QTs, dy, c, h, key_weights=False, want_gram=True)
+        del QT, QTs
+        # reverse scans: dS_m (with key weights folded in) and the chunk-gate gradient
+        wdS, dA_state = ops.discumsum_bwd(dZ, Z, A, row_len=d, row_weights=True, inplace=True)
+        ghi, glo, dA_gram = ops.gram_scan_bwd(dZg, zfull, A, Q.dtype)
+        # gradients through the expansions
+        dq_state, gq = ops.expand_grad(dy, Q, Z, zhi, zlo, a, A if a is not None else None, dl, c, h, True, scale, 2.0,
+                                       1, n - 1)
+        dk_state, wk = ops.expand_grad(V, K, wdS, ghi, glo, a, A if a is not None else None, None, c, h, False, 1.0,
+                                       1.0, 0, n - 2)
+        # intra-chunk attention backward, merged with the state-path terms
+        dQ, da_q = ops.chunk_dq(Q, dy, K, V, a, dl, dq_state, c, scale)
+        dK, dV, da_k = ops.chunk_dkv(Q, dy, K, V, wdS, a, A if a is not None else None, dl, dk_state, c, n - 2, scale)
+        dlog_G = None
+        if log_G is not None:
+            dlog_G = ops.gate_grad(da_q, gq, da_k, wk, dA_state, dA_gram, c)
+        return dQ, dK, dV, dlog_G, None, None
+
+
+class _QuadraticRetention(torch.autograd.Function):
+    """Whole-sequence causal power attention (no state): the branch the reference takes for
+    t <= switch_over_seq_len (retention/power_retention_maker.py:128-132)."""
+
+    @staticmethod
+    def forward(ctx, Q, K, V, log_G, scale):
+        t = Q.shape[1]
+        a = None
+        if log_G is not None:
+            a, _, _ = ops.gate_prep(K, log_G, t, query_side=False, want_xt=False)
+        O, l = ops.chunk_out(Q, K, V, a, None, None, None, 1, t, t, 1, scale)
+        ctx.save_for_backward(Q, K, V, a, O, l)
+        ctx.scale = scale
+        ctx.gated = log_G is not None
+        return O
+
+    @staticmethod
+    def backward(ctx, dO):
+        Q, K, V, a, O, l = ctx.saved_tensors
+        t = Q.shape[1]
+        dy, dl = ops.dout_prep(O, dO.contiguous(), l)
+        dQ, da_q = ops.chunk_dq(Q, dy, K, V, a, dl, None, t, ctx.scale)
+        dK, dV, da_k = ops.chunk_dkv(Q, dy, K, V, None, a, None, dl, None, t, -1, ctx.scale)
+        dlog_G = ops.gate_grad(da_q, None, da_k, None, None, None, t) if ctx.gated else None
+        return dQ, dK, dV, dlog_G, None
+
+
+def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=False, deg=2, scale=None,
+                    chunk_size=None, switch_over_seq_len=None):
+    """Symmetric power retention, training forward (differentiable).
+
+    Same arguments as the reference (retention/power_retention_maker.py:72-73):
+    Q [b,t,hq,d]; K, V [b,t,h,d]; log_G [b,t,h] float32 or None; returns [b,t,hq,d].
+    `initial_state` / `return_final_state` are unfinished in the reference
+    (retention/power_retention_maker.py:43,158-160) and are rejected here.
+    """
+    assert deg % 2 == 0, f"deg must be even: {deg=}"
+    if initial_state is not None or return_final_state:
+        raise PRError("initial_state / return_final_state are not implemented (unfinished in the reference too)")
+    _check_inputs(Q, K, V, log_G, deg)
+    b, t, hq, d = Q.shape
+    if log_G is not None:
+        log_G = log_G.to(torch.float32).contiguous()
+    if not scale:
+        scale = 1.0 / math.sqrt(d)
+    if chunk_size is not None and switch_over_seq_len is None:
+        switch_over_seq_len = chunk_size
+    t_pad = 0
+    if chunk_size is not None and t % chunk_size != 0:
+        # pad with zero tokens whose gate is 1, as the reference does (:75-83)
+        t_pad = chunk_size - t % chunk_size
+        Q = torch.nn.functional.pad(Q, (0, 0, 0, 0, 0, t_pad))
+        K = torch.nn.functional.pad(K, (0, 0, 0, 0, 0, t_pad))
+        V = torch.nn.functional.pad(V, (0, 0, 0, 0, 0, t_pad))
+        if log_G is not None:
+            log_G = torch.nn.functional.pad(log_G, (0, 0, 0, t_pad))
+    Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
+    tt = t + t_pad
+    if switch_over_seq_len is None or tt <= switch_over_seq_len or chunk_size is None:
+        out = _QuadraticRetention.apply(Q, K, V, log_G, float(scale))
+    else:
+        out = _ChunkedRetention.apply(Q, K, V, log_G, int(chunk_size), float(scale))
+    return out[:, :t] if t_pad else out
