@@ -1,6 +1,14 @@
 /* C ABI of libpr_b200.so: power retention (chunked forward/backward and
  * inference) as hand-written sm_100a kernels.
  *
+ * The reference package has no FFI of its own for this path: its native module
+ * (`retention_cuda`, imported by retention/_attention/cuda.py:5,
+ * retention/_update_state/cuda.py:6, retention/_discumsum/cuda.py:12 and
+ * retention/_query_state/cuda.py:10) is absent from its tree.  The entry points below
+ * are what a binding for the reference's four-operator plugin interface
+ * (retention/power_retention_maker.py:92-104) needs; each one names the reference
+ * function it stands in for.
+ *
  * Conventions for every entry point
  *   - returns PR_OK (0) or a negative PR_ERR_* code; pr_last_error() gives a
  *     thread-local message for the last failure on the calling thread;
@@ -10,7 +18,13 @@
  *     the given device ordinal; the call sets that device current itself, so it
  *     may be called from any thread (autograd's backward thread included);
  *   - `dtype` is PR_BF16 or PR_FP16 for Q/K/V-like tensors; gates, row sums and
- *     sum-of-keys tensors are always fp32.
+ *     Gram matrices are fp32;
+ *   - tensors are dense and row-major in the stated shape;
+ *   - head dim d = 64 in this build; deg = 2.
+ *
+ * Shapes use b batch, t tokens, h kv heads, hq query heads (multiple of h), d head
+ * dim, c chunk length, n = t / c chunks, cp = c rounded up to 64, and
+ * D2 = d*(d+2)/2 rows of the internal expansion layout (see layout.cuh).
  */
 #ifndef PR_B200_H_
 #define PR_B200_H_
@@ -53,6 +67,99 @@ int pr_device_status(int device, int* status);
  * n in {64, 128, 256} (MN-major variants: n = 64). */
 int pr_selftest_umma(int variant, int dtype, int n, int k, const void* a, const void* b, float* out,
                      int device, void* stream);
+
+/* Gate glue of retention/power_retention_maker.py:143-155,183-186 in one pass.
+ * log_g [b,t,h] or NULL; x [b,t,hx,d].  Writes (when write_a) a [b,t,h] = inclusive
+ * cumulative log gate inside each chunk and A [b,n,h] = chunk totals; xt [b,n,hx,d,cp] =
+ * gated, transposed copy of x (keys: x*exp((A-a)/2); queries: x*mult*exp(a/2)), zero
+ * padded to cp; xts = xt scaled per token by row_scale [b,t,hx] (or NULL). */
+int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c, const float* log_g, const void* x,
+                 float* a_out, float* A_out, void* xt, const float* row_scale, void* xts, int query_side,
+                 float mult, int write_a, int device, void* stream);
+
+/* update_state (retention/_update_state/reference.py:31-53; the old binding
+ * compute_update_states, retention/_update_state/cuda.py:30).
+ * xt, xts [b,n,nh*group,d,cp] from pr_gate_prep; v [b,t,nh*group,d].
+ * out [b,n,nh,D2,d] = w (.) sum_i phi(x_i) v_i^T summed over the group's heads, with key
+ * weights {1,2,0} (key_weights=1) or {1,1,0}; gram [b,n,nh,d,d] fp32 = sum_i xs_i x_i^T
+ * (NULL to skip).  The Gram matrix of the discounted keys replaces the reference's
+ * sum_of_keys: N[(a,b)] = w(a,b) * gram[a][b]. */
+int pr_chunk_state(int dtype, int b, int t, int nh, int group, int d, int c, const void* xt, const void* xts,
+                   const void* v, void* out, float* gram, int key_weights, int device, void* stream);
+
+/* discumsum (retention/_discumsum/reference.py:3-15; old binding discumsum,
+ * retention/_discumsum/cuda.py:39-41).  X [b,n,h,E] 16-bit, A [b,n,h];
+ * Y[0] = carry_in (or 0), Y[m+1] = Y[m]*exp(A[m]) + X[m]; writes Y[0..n_out-1], n_out = n
+ * (may alias X) or n+1.  carry_in/out [b,h,E] fp32, optional (sequence-parallel hand-over). */
+int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long long E, const void* X, void* Y,
+                     const float* A, const float* carry_in, float* carry_out, int device, void* stream);
+
+/* discumsum backward (old binding discumsum_bwd, retention/_discumsum/cuda.py:75; gate
+ * index as autograd of the reference gives it).  dY, Y, dX [b,n,h,E]; dX may alias dY.
+ * dA_part [b,h,pr_discumsum_bwd_blocks(E),n]: per-block partial sums of the chunk-gate
+ * gradient.  row_weights=1 multiplies dX rows (row_len elements each) by the key
+ * weights of the expansion layout. */
+int pr_discumsum_bwd_blocks(long long E);
+int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, const void* dY, const void* Y, void* dX,
+                     const float* A, const float* carry_in, float* carry_out, float* dA_part, int row_len,
+                     int row_weights, int device, void* stream);
+
+/* The same scans for the d x d Gram matrices (fp32 in; hi + lo 16-bit halves out for the
+ * tensor cores; `full` fp32 copy optional).  Backward emits the symmetrised gradient. */
+int pr_gram_scan_fwd(int dtype, int b, int n, int h, int d, const float* G, void* hi, void* lo, float* full,
+                     const float* A, const float* carry_in, float* carry_out, int device, void* stream);
+int pr_gram_scan_bwd_blocks(int d);
+int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const float* dZg, const float* Zg, void* hi, void* lo,
+                     const float* A, const float* carry_in, float* carry_out, float* dA_part, int device,
+                     void* stream);
+
+/* attention + query_state fused (retention/_attention/reference.py:10-69 and
+ * retention/_query_state/reference.py:36-96; old bindings attention_fwd,
+ * retention/_attention/cuda.py:34, and compute_query_states, retention/_query_state/cuda.py:42-44).
+ * Q [b,n*cq,hq,d]; K,V [b,n*ck,h,d] or NULL (state only); a [b,n*ck,h] or NULL;
+ * Z [b,n,h,D2,d], zg_hi/zg_lo [b,n,h,d,d] or NULL.  Query i of a chunk sits at key
+ * position i + ck - cq.  Chunks >= state_from_chunk read the state.  O [b,n*cq,hq,d] =
+ * y / l (normalize=1) or y; l_out [b,n*cq,hq] or NULL. */
+int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int hq, int h, int d, const void* Q,
+                 const void* K, const void* V, const float* a, const void* Z, const void* zg_hi, const void* zg_lo,
+                 int state_from_chunk, int q_gate_last, int normalize, float scale, void* O, float* l_out,
+                 int device, void* stream);
+
+/* Backward prologue: dy = dO / l, dl = -<O, dO> / l over `rows` rows of d elements. */
+int pr_dout_prep(int dtype, long long rows, int d, const void* O, const void* dO, const float* l, void* dy,
+                 float* dl, int device, void* stream);
+
+/* Gradient through the expansion (query side: retention/_query_state/triton.py:181-325; key
+ * side: retention/_update_state/reference.py:55-83; old bindings query_states_bwd,
+ * retention/_query_state/cuda.py:86-87, and update_states_bwd, retention/_update_state/cuda.py:64).
+ * W, X [b,t,hx,d]; State [b,n,h,D2,d]; g_hi/g_lo [b,n,h,d,d]; a [b,t,h], A [b,n,h] or both
+ * NULL; row_g [b,t,hx] or NULL.  dX [b,t,hx,d] fp32 (gradient w.r.t. the ungated x),
+ * gdot [b,t,hx] = <x~, dx~>/2.  Chunks outside [chunk_lo, chunk_hi] get zeros. */
+int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int c, const void* W, const void* X,
+                   const void* State, const void* g_hi, const void* g_lo, const float* a, const float* A,
+                   const float* row_g, int query_side, float scale, float gram_mult, int chunk_lo, int chunk_hi,
+                   float* dX, float* gdot, int device, void* stream);
+
+/* attention backward (retention/_attention/triton.py:390-603; old binding attention_bwd,
+ * retention/_attention/cuda.py:75), split by output.  dO [b,t,hq,d] unscaled; l, dl [b,t,hq]
+ * from the forward and from pr_dout_prep.
+ * pr_chunk_dq : dQ [b,t,hq,d] (+ dq_state fp32 if given), da_q [b,t,hq].
+ * pr_chunk_dkv: dK, dV [b,t,h,d] (+ dk_state; + the state path of dV from wdS
+ *               [b,n,h,D2,d] for chunks <= state_chunk_hi), da_k [b,t,h]. */
+int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO, const void* K,
+                const void* V, const float* a, const float* dl, const float* l, const float* dq_state, float scale,
+                void* dQ, float* da_q, int device, void* stream);
+int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO, const void* K,
+                 const void* V, const void* wdS, const float* a, const float* A, const float* dl, const float* l,
+                 const float* dk_state, int state_chunk_hi, float scale, void* dK, void* dV, float* da_k,
+                 int device, void* stream);
+
+/* Assembles dlog_G [b,t,h] (the autograd of the cumsum / exp glue of
+ * retention/power_retention_maker.py:143-186): reverse cumulative sum inside each chunk of
+ * the per-token terms plus the chunk-gate gradient.  gq, wk, dA_scan, dA_gram may be NULL. */
+int pr_gate_grad(int b, int t, int h, int hq, int c, const float* da_q, const float* gq, const float* da_k,
+                 const float* wk, const float* dA_scan, int scan_blocks, const float* dA_gram, int gram_blocks,
+                 float* dlog_g, int device, void* stream);
 
 #ifdef __cplusplus
 }

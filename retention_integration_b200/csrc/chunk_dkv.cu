@@ -4,9 +4,9 @@
 //
 // One CTA owns 128 key rows (tile J) of one (batch, chunk, kv head); thread = key row.  For
 // every query tile I >= J of every query head of the group:
-//     S^T = K_J Q_I^T,  dP^T = V_J dY_I^T                (tensor cores)
-//     p = (s S)^2 e^{a_i-a_j},  dp = dP + dl_i,  dS = 2 s^2 S e^{a_i-a_j} dp
-//     dV += P^T dY_I,   dK += dS^T Q_I                   (A operands from tensor memory)
+//     S^T = K_J Q_I^T,  dP^T = V_J dO_I^T                (tensor cores)
+//     p = (s S)^2 e^{a_i-a_j},  dp = dP / l_i + dl_i,  dS = 2 s^2 S e^{a_i-a_j} dp
+//     dV += (P / l)^T dO_I,   dK += dS^T Q_I             (A operands from tensor memory)
 //     da_j -= sum_i p dp                                 (gate gradient, key side)
 // then the state path of the values, dV += phi(k~_j)^T (w (.) dS_m) with k~ the discounted
 // key (same expansion pipeline as the forward read-out).  The epilogue adds the state-path
@@ -35,6 +35,7 @@ struct ChunkDkvParams {
   const float* a;         // [b, t, h] or null
   const float* A;         // [b, n, h] or null
   const float* dl;        // [b, t, hq]
+  const float* l;         // [b, t, hq] row sums saved by the forward
   const float* dk_state;  // [b, t, h, 64] fp32 or null
   void* dK;
   void* dV;
@@ -53,7 +54,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
   __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float sm_aq[2][128], sm_dl[2][128];
+  __shared__ float sm_aq[2][128], sm_dl[2][128], sm_il[2][128];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -194,6 +195,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         const bool v = qp < p.c;
         sm_aq[st & 1][tid] = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
         sm_dl[st & 1][tid] = v ? p.dl[(tok_base + qp) * p.hq + qh] : 0.f;
+        sm_il[st & 1][tid] = v ? 1.f / fmaxf(p.l[(tok_base + qp) * p.hq + qh], 1e-37f) : 0.f;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = mbar_wait(&sp_full, st & 1, &abort_flag);
@@ -201,6 +203,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
       tc_fence_after();
       const float* aq = sm_aq[st & 1];
       const float* dlq = sm_dl[st & 1];
+      const float* ilq = sm_il[st & 1];
       const bool need_mask = (qp0 < row) || (qp0 + 127 >= p.c) || !row_valid;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
@@ -218,7 +221,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
             const float s = __uint_as_float(sv[j + u]);
             float g = s2;
             if (gated) g *= __expf(aq[col] - a_j);
-            const float dp = __uint_as_float(pv[j + u]) + dlq[col];
+            const float dp = fmaf(__uint_as_float(pv[j + u]), ilq[col], dlq[col]);
             float sg = s * g;
             if (need_mask) {
               const int qp = qp0 + col;
@@ -226,7 +229,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
             }
             const float pval = sg * s;
             da = fmaf(pval, dp, da);
-            pw[u] = pval;
+            pw[u] = pval * ilq[col];
             dsv[u] = 2.f * sg * dp;
           }
           pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
@@ -342,9 +345,10 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
 
 }  // namespace pr
 
-extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dY,
+extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO,
                             const void* K, const void* V, const void* wdS, const float* a, const float* A,
-                            const float* dl, const float* dk_state, int state_chunk_hi, float scale, void* dK,
+                            const float* dl, const float* l, const float* dk_state, int state_chunk_hi, float scale,
+                            void* dK,
                             void* dV, float* da_k, int device, void* stream) {
   using namespace pr;
   using namespace pr::dkv;
@@ -352,8 +356,8 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   PR_REQUIRE(b > 0 && t > 0 && hq > 0 && h > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
              "bad sizes b=%d t=%d hq=%d h=%d c=%d", b, t, hq, h, c);
   PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
-  PR_REQUIRE(Q && dY && K && V && dl && dK && dV && da_k, PR_ERR_BAD_ARG, "null pointer");
-  PR_REQUIRE(aligned16(Q) && aligned16(dY) && aligned16(K) && aligned16(V) && aligned16(dK) && aligned16(dV) &&
+  PR_REQUIRE(Q && dO && K && V && dl && l && dK && dV && da_k, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(Q) && aligned16(dO) && aligned16(K) && aligned16(V) && aligned16(dK) && aligned16(dV) &&
                  aligned16(wdS) && aligned16(dk_state),
              PR_ERR_BAD_ARG, "misaligned pointer");
   PR_REQUIRE(!(wdS != nullptr && a != nullptr) || A != nullptr, PR_ERR_BAD_ARG,
@@ -371,6 +375,7 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   p.a = a;
   p.A = A;
   p.dl = dl;
+  p.l = l;
   p.dk_state = dk_state;
   p.dK = dK;
   p.dV = dV;
@@ -384,7 +389,7 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   uint64_t sk[4] = {0, (uint64_t)d * 2, (uint64_t)h * d * 2, (uint64_t)t * h * d * 2};
   uint32_t box[4] = {64, 1, 128, 1};
   if ((rc = make_tmap(&tm_q, Q, 2, 4, dq_, sq, box, true))) return rc;
-  if ((rc = make_tmap(&tm_dy, dY, 2, 4, dq_, sq, box, true))) return rc;
+  if ((rc = make_tmap(&tm_dy, dO, 2, 4, dq_, sq, box, true))) return rc;
   if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
   if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
   if (wdS) {

@@ -4,11 +4,13 @@
 //
 // One CTA owns 128 query rows of one (batch, chunk, query head); thread = row.  For every
 // key tile J up to the diagonal:
-//     S  = Q K_J^T,  dP = dY V_J^T                      (tensor cores, fp32 in tensor memory)
-//     p  = (s S)^2 e^{a_i-a_j},  dp = dP + dl_i,  e = p dp,  dS = 2 s^2 S e^{a_i-a_j} dp
+//     S  = Q K_J^T,  dP = dO V_J^T                      (tensor cores, fp32 in tensor memory)
+//     p  = (s S)^2 e^{a_i-a_j},  dp = dP / l_i + dl_i,  e = p dp,  dS = 2 s^2 S e^{a_i-a_j} dp
 //     dQ += dS K_J                                      (A = dS from tensor memory)
 //     da_i += sum_j e_ij                                (gate gradient, query side)
-// with dY = dO / l and dl = -<O, dO> / l from the backward prologue.  The epilogue adds the
+// with dl = -<O, dO> / l from the backward prologue.  dO enters the tensor cores unscaled and
+// 1/l_i is applied in fp32, so the cancellation between dP / l and dl (exact for a row with a
+// single key) is not spoiled by a 16-bit rounding of dO / l.  The epilogue adds the
 // state-path gradient (fp32, from the expansion-gradient kernel) and writes dQ.
 #include "host.cuh"
 #include "sm100.cuh"
@@ -28,6 +30,7 @@ struct ChunkDqParams {
   float scale;
   const float* a;         // [b, t, h] or null
   const float* dl;        // [b, t, hq]
+  const float* l;         // [b, t, hq] row sums saved by the forward
   const float* dq_state;  // [b, t, hq, 64] fp32 or null
   void* dQ;               // [b, t, hq, 64]
   float* da_q;            // [b, t, hq]
@@ -133,6 +136,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
     const float* a_chunk = gated ? p.a + ((size_t)batch * p.n_chunks * p.c + tok_chunk) * p.h + kvhead : nullptr;
     const float a_i = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
     const float dl_i = row_valid ? p.dl[tok * p.hq + qhead] : 0.f;
+    const float inv_l = row_valid ? 1.f / fmaxf(p.l[tok * p.hq + qhead], 1e-37f) : 0.f;
     const float s2 = p.scale * p.scale;
     float da = 0.f;
     bool ok = true;
@@ -164,7 +168,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
             const float s = __uint_as_float(sv[j + u]);
             float g = s2;
             if (gated) g *= __expf(a_i - ak[col]);
-            const float dp = __uint_as_float(pv[j + u]) + dl_i;
+            const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
             float sg = s * g;  // s^2 S e^{a_i-a_j}
             if (need_mask) {
               const int kp = kp0 + col;
@@ -219,17 +223,17 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
 
 }  // namespace pr
 
-extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dY,
-                           const void* K, const void* V, const float* a, const float* dl, const float* dq_state,
-                           float scale, void* dQ, float* da_q, int device, void* stream) {
+extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO,
+                           const void* K, const void* V, const float* a, const float* dl, const float* l,
+                           const float* dq_state, float scale, void* dQ, float* da_q, int device, void* stream) {
   using namespace pr;
   using namespace pr::dq;
   PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && t > 0 && hq > 0 && h > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
              "bad sizes b=%d t=%d hq=%d h=%d c=%d", b, t, hq, h, c);
   PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
-  PR_REQUIRE(Q && dY && K && V && dl && dQ && da_q, PR_ERR_BAD_ARG, "null pointer");
-  PR_REQUIRE(aligned16(Q) && aligned16(dY) && aligned16(K) && aligned16(V) && aligned16(dQ) && aligned16(dq_state),
+  PR_REQUIRE(Q && dO && K && V && dl && l && dQ && da_q, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(Q) && aligned16(dO) && aligned16(K) && aligned16(V) && aligned16(dQ) && aligned16(dq_state),
              PR_ERR_BAD_ARG, "misaligned pointer");
   PR_REQUIRE(hq <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "hq and b must be <= 65535");
   PR_CUDA(cudaSetDevice(device));
@@ -242,6 +246,7 @@ extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c,
   p.scale = scale;
   p.a = a;
   p.dl = dl;
+  p.l = l;
   p.dq_state = dq_state;
   p.dQ = dQ;
   p.da_q = da_q;
@@ -254,7 +259,7 @@ extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c,
   uint64_t sk[4] = {0, (uint64_t)d * 2, (uint64_t)h * d * 2, (uint64_t)t * h * d * 2};
   uint32_t box[4] = {64, 1, 128, 1};
   if ((rc = make_tmap(&tm_q, Q, 2, 4, dq_, sq, box, true))) return rc;
-  if ((rc = make_tmap(&tm_dy, dY, 2, 4, dq_, sq, box, true))) return rc;
+  if ((rc = make_tmap(&tm_dy, dO, 2, 4, dq_, sq, box, true))) return rc;
   if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
   if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
   const size_t smem = 1024 + 4 * TILE_BYTES;

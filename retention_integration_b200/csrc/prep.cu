@@ -162,8 +162,9 @@ __global__ void dout_prep_kernel(const T* __restrict__ O, const T* __restrict__ 
 //   dA   = scan terms (state and Gram) + sum_i key discount term.
 __global__ void __launch_bounds__(kPrepThreads)
 gate_grad_kernel(const float* __restrict__ da_q, const float* __restrict__ gq, const float* __restrict__ da_k,
-                 const float* __restrict__ wk, const float* __restrict__ dA_scan, const float* __restrict__ dA_gram,
-                 float* __restrict__ dlog_g, int t, int h, int hq, int c) {
+                 const float* __restrict__ wk, const float* __restrict__ dA_scan, int scan_blocks,
+                 const float* __restrict__ dA_gram, int gram_blocks, float* __restrict__ dlog_g, int t, int h, int hq,
+                 int c) {
   __shared__ float warp_tot[kPrepThreads / 32];
   __shared__ float carry_s, wk_sum_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -184,8 +185,16 @@ gate_grad_kernel(const float* __restrict__ da_q, const float* __restrict__ gq, c
   if (tid == 0) {
     float s = 0.f;
     for (int w = 0; w < kPrepThreads / 32; ++w) s += warp_tot[w];
-    const size_t ci = ((size_t)batch * n + chunk) * h + head;
-    wk_sum_s = s + (dA_scan ? dA_scan[ci] : 0.f) + (dA_gram ? dA_gram[ci] : 0.f);
+    // per-block partial sums of the reverse scans: [b, h, scan_blocks, n] and [b, h, n]
+    if (dA_scan != nullptr) {
+      const float* ps = dA_scan + ((size_t)batch * h + head) * scan_blocks * n + chunk;
+      for (int k = 0; k < scan_blocks; ++k) s += ps[(size_t)k * n];
+    }
+    if (dA_gram != nullptr) {
+      const float* pg = dA_gram + ((size_t)batch * h + head) * gram_blocks * n + chunk;
+      for (int k = 0; k < gram_blocks; ++k) s += pg[(size_t)k * n];
+    }
+    wk_sum_s = s;
     carry_s = 0.f;
   }
   __syncthreads();
@@ -284,15 +293,15 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
 }
 
 extern "C" int pr_gate_grad(int b, int t, int h, int hq, int c, const float* da_q, const float* gq, const float* da_k,
-                            const float* wk, const float* dA_scan, const float* dA_gram, float* dlog_g, int device,
-                            void* stream) {
+                            const float* wk, const float* dA_scan, int scan_blocks, const float* dA_gram,
+                            int gram_blocks, float* dlog_g, int device, void* stream) {
   using namespace pr;
   PR_REQUIRE(b > 0 && t > 0 && h > 0 && hq > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
              "bad sizes b=%d t=%d h=%d hq=%d c=%d", b, t, h, hq, c);
   PR_REQUIRE(da_q && da_k && dlog_g, PR_ERR_BAD_ARG, "null pointer");
   PR_CUDA(cudaSetDevice(device));
   gate_grad_kernel<<<b * (t / c) * h, kPrepThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      da_q, gq, da_k, wk, dA_scan, dA_gram, dlog_g, t, h, hq, c);
+      da_q, gq, da_k, wk, dA_scan, scan_blocks, dA_gram, gram_blocks, dlog_g, t, h, hq, c);
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }

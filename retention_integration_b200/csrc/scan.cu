@@ -200,48 +200,50 @@ __global__ void scan_gram_fwd_kernel(const float* __restrict__ G, T* __restrict_
 }
 
 // backward: dG[m] = Gamma[m+1] (+ its transpose: the consumer needs the symmetrised
-// matrix) as hi + lo halves, and the gate-gradient partial sums.
+// matrix) as hi + lo halves, and the gate-gradient partial sums.  One thread per matrix
+// element; it carries the running gradient of its own element and of the mirrored one.
 template <typename T>
-__global__ void scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg, T* __restrict__ hi,
-                                     T* __restrict__ lo, const float* __restrict__ A,
-                                     const float* __restrict__ carry_in, float* __restrict__ carry_out,
-                                     float* __restrict__ dA_part, int n, int h, int d) {
-  // one block per (head, batch), d*d threads' worth of work strided over the block
-  extern __shared__ float sm_run[];  // [d*d] running gradient, then scratch for the reduction
-  __shared__ float red[32];
+__global__ void __launch_bounds__(256)
+scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg, T* __restrict__ hi,
+                     T* __restrict__ lo, const float* __restrict__ A, const float* __restrict__ carry_in,
+                     float* __restrict__ carry_out, float* __restrict__ dA_part, int n, int h, int d) {
+  __shared__ float red[8];
   const int E = d * d;
+  const int e = blockIdx.x * 256 + threadIdx.x;
+  const bool active = e < E;
   const int head = blockIdx.y, batch = blockIdx.z;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int e = tid; e < E; e += blockDim.x) sm_run[e] = carry_in ? carry_in[((size_t)batch * h + head) * E + e] : 0.f;
-  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int et = active ? (e % d) * d + e / d : 0;  // mirrored element
+  const size_t cbase = ((size_t)batch * h + head) * E;
+  float run = (active && carry_in) ? carry_in[cbase + e] : 0.f;
+  float run_t = (active && carry_in) ? carry_in[cbase + et] : 0.f;
+  float* part = dA_part + (((size_t)batch * h + head) * gridDim.x + blockIdx.x) * n;
   for (int m = n - 1; m >= 0; --m) {
     const size_t base = (((size_t)batch * n + m) * h + head) * E;
     const float g = __expf(A[((size_t)batch * n + m) * h + head]);
     float dot = 0.f;
-    for (int e = tid; e < E; e += blockDim.x) {
-      const int r = e / d, cc = e % d;
-      const float sym = sm_run[e] + sm_run[cc * d + r];
+    if (active) {
+      const float sym = run + run_t;
       const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(sym)) : T(__float2half_rn(sym));
       hi[base + e] = hv;
       lo[base + e] = T(sym - float(hv));
-      dot = fmaf(Zg[base + e], sm_run[e], dot);
+      dot = Zg[base + e] * run * g;
+      run = fmaf(run, g, dZg[base + e]);
+      run_t = fmaf(run_t, g, dZg[base + et]);
     }
-    __syncthreads();
-    for (int e = tid; e < E; e += blockDim.x) sm_run[e] = fmaf(sm_run[e], g, dZg[base + e]);
-    dot *= g;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
     if (lane == 0) red[warp] = dot;
     __syncthreads();
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
       float s = 0.f;
-      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[w];
-      dA_part[((size_t)batch * h + head) * n + m] = s;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += red[w];
+      part[m] = s;
     }
     __syncthreads();
   }
-  if (carry_out)
-    for (int e = tid; e < E; e += blockDim.x) carry_out[((size_t)batch * h + head) * E + e] = sm_run[e];
+  if (active && carry_out) carry_out[cbase + e] = run;
 }
 
 }  // namespace pr
@@ -323,6 +325,8 @@ extern "C" int pr_gram_scan_fwd(int dtype, int b, int n, int h, int d, const flo
   return PR_OK;
 }
 
+extern "C" int pr_gram_scan_bwd_blocks(int d) { return (d * d + 255) / 256; }
+
 extern "C" int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const float* dZg, const float* Zg, void* hi,
                                 void* lo, const float* A, const float* carry_in, float* carry_out, float* dA_part,
                                 int device, void* stream) {
@@ -330,23 +334,17 @@ extern "C" int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const flo
   PR_REQUIRE(b > 0 && n > 0 && h > 0 && d > 0 && d <= 128, PR_ERR_BAD_ARG, "bad sizes");
   PR_REQUIRE(dZg && Zg && hi && lo && A && dA_part, PR_ERR_BAD_ARG, "null pointer");
   PR_CUDA(cudaSetDevice(device));
-  dim3 grid(1, h, b);
-  const size_t smem = (size_t)d * d * 4;
+  dim3 grid(pr_gram_scan_bwd_blocks(d), h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PR_BF16) {
-    PR_CUDA(cudaFuncSetAttribute(scan_gram_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    scan_gram_bwd_kernel<__nv_bfloat16><<<grid, 512, smem, s>>>(dZg, Zg, static_cast<__nv_bfloat16*>(hi),
-                                                               static_cast<__nv_bfloat16*>(lo), A, carry_in, carry_out,
-                                                               dA_part, n, h, d);
-  } else if (dtype == PR_FP16) {
-    PR_CUDA(cudaFuncSetAttribute(scan_gram_bwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    scan_gram_bwd_kernel<__half><<<grid, 512, smem, s>>>(dZg, Zg, static_cast<__half*>(hi), static_cast<__half*>(lo),
-                                                        A, carry_in, carry_out, dA_part, n, h, d);
-  } else {
+  if (dtype == PR_BF16)
+    scan_gram_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(dZg, Zg, static_cast<__nv_bfloat16*>(hi),
+                                                            static_cast<__nv_bfloat16*>(lo), A, carry_in, carry_out,
+                                                            dA_part, n, h, d);
+  else if (dtype == PR_FP16)
+    scan_gram_bwd_kernel<__half><<<grid, 256, 0, s>>>(dZg, Zg, static_cast<__half*>(hi), static_cast<__half*>(lo), A,
+                                                     carry_in, carry_out, dA_part, n, h, d);
+  else
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
-  }
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }

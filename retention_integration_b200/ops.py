@@ -15,6 +15,49 @@ from . import _lib
 from ._lib import check, dtype_code, lib, ptr, stream_ptr
 
 
+class LaunchLog:
+    """Counts kernel launches and, when `timing` is on, brackets every launch with CUDA
+    events on the launching stream (used by bench.py for the per-kernel breakdown)."""
+
+    def __init__(self):
+        self.count = 0
+        self.timing = False
+        self.events = []  # (name, start, end)
+
+    def reset(self, timing: bool = False):
+        self.count = 0
+        self.timing = timing
+        self.events = []
+
+    def summary(self):
+        """name -> (launches, total ms).  Synchronise before calling."""
+        out = {}
+        for name, s, e in self.events:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + s.elapsed_time(e))
+        return out
+
+
+launch_log = LaunchLog()
+
+# kernels launched per entry point (for the launch count reported by bench.py)
+_KERNELS_PER_CALL = {}
+
+
+def _call(name: str, *args):
+    fn = getattr(lib(), name)
+    if launch_log.timing:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        rc = fn(*args)
+        e.record()
+        launch_log.events.append((name, s, e))
+    else:
+        rc = fn(*args)
+    check(rc, name)
+    launch_log.count += 1
+
+
 def t2_dim(d: int) -> int:
     """Rows of the internal pair-aligned expansion layout (2112 for d = 64)."""
     return d * (d + 2) // 2
@@ -28,8 +71,8 @@ def _dev(t: torch.Tensor) -> int:
 
 def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, n: int, k: int) -> torch.Tensor:
     out = torch.empty(128, n, device=a.device, dtype=torch.float32)
-    check(lib().pr_selftest_umma(c_int(variant), c_int(dtype_code(a.dtype)), c_int(n), c_int(k), ptr(a), ptr(b),
-                                 ptr(out), c_int(_dev(a)), stream_ptr(a.device)), "pr_selftest_umma")
+    _call("pr_selftest_umma", c_int(variant), c_int(dtype_code(a.dtype)), c_int(n), c_int(k), ptr(a), ptr(b),
+                                 ptr(out), c_int(_dev(a)), stream_ptr(a.device))
     return out
 
 
@@ -47,10 +90,10 @@ def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.
     A = torch.empty(b, n, h, device=x.device, dtype=torch.float32) if write else None
     xt = torch.empty(b, n, hx, d, cp, device=x.device, dtype=x.dtype) if want_xt else None
     xts = torch.empty_like(xt) if (row_scale is not None and want_xt) else None
-    check(lib().pr_gate_prep(c_int(dtype_code(x.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
+    _call("pr_gate_prep", c_int(dtype_code(x.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
                              ptr(log_g), ptr(x), ptr(a), ptr(A), ptr(xt), ptr(row_scale), ptr(xts),
                              c_int(1 if query_side else 0), c_float(mult), c_int(1 if write else 0), c_int(_dev(x)),
-                             stream_ptr(x.device)), "pr_gate_prep")
+                             stream_ptr(x.device))
     if row_scale is not None:
         return a, A, xt, xts
     return a, A, xt
@@ -62,8 +105,8 @@ def dout_prep(O: torch.Tensor, dO: torch.Tensor, l: torch.Tensor):
     rows = O.numel() // d
     dy = torch.empty_like(O)
     dl = torch.empty_like(l)
-    check(lib().pr_dout_prep(c_int(dtype_code(O.dtype)), c_longlong(rows), c_int(d), ptr(O), ptr(dO), ptr(l), ptr(dy),
-                             ptr(dl), c_int(_dev(O)), stream_ptr(O.device)), "pr_dout_prep")
+    _call("pr_dout_prep", c_int(dtype_code(O.dtype)), c_longlong(rows), c_int(d), ptr(O), ptr(dO), ptr(l), ptr(dy),
+                             ptr(dl), c_int(_dev(O)), stream_ptr(O.device))
     return dy, dl
 
 
@@ -76,10 +119,9 @@ def chunk_state(xt: torch.Tensor, xts, v: torch.Tensor, c: int, nh: int, key_wei
     gram = torch.empty(b, n, nh, d, d, device=xt.device, dtype=torch.float32) if want_gram else None
     if want_gram and xts is None:
         xts = xt
-    check(lib().pr_chunk_state(c_int(dtype_code(xt.dtype)), c_int(b), c_int(t), c_int(nh), c_int(group), c_int(d),
+    _call("pr_chunk_state", c_int(dtype_code(xt.dtype)), c_int(b), c_int(t), c_int(nh), c_int(group), c_int(d),
                                c_int(c), ptr(xt), ptr(xts), ptr(v), ptr(out), ptr(gram),
-                               c_int(1 if key_weights else 0), c_int(_dev(xt)), stream_ptr(xt.device)),
-          "pr_chunk_state")
+                               c_int(1 if key_weights else 0), c_int(_dev(xt)), stream_ptr(xt.device))
     return out, gram
 
 
@@ -91,27 +133,26 @@ def discumsum_fwd(X: torch.Tensor, A: torch.Tensor, inplace: bool = False, carry
     n_out = n if inplace else n + 1
     Y = X if inplace else torch.empty(b, n_out, *X.shape[2:], device=X.device, dtype=X.dtype)
     carry_out = torch.empty(b, h, E, device=X.device, dtype=torch.float32) if want_carry else None
-    check(lib().pr_discumsum_fwd(c_int(dtype_code(X.dtype)), c_int(b), c_int(n), c_int(n_out), c_int(h),
+    _call("pr_discumsum_fwd", c_int(dtype_code(X.dtype)), c_int(b), c_int(n), c_int(n_out), c_int(h),
                                  c_longlong(E), ptr(X), ptr(Y), ptr(A), ptr(carry_in), ptr(carry_out),
-                                 c_int(_dev(X)), stream_ptr(X.device)), "pr_discumsum_fwd")
+                                 c_int(_dev(X)), stream_ptr(X.device))
     return (Y, carry_out) if want_carry else Y
 
 
 def discumsum_bwd(dY: torch.Tensor, Y: torch.Tensor, A: torch.Tensor, row_len: int = 0, row_weights: bool = False,
                   inplace: bool = True, carry_in=None, want_carry: bool = False):
-    """Reverse scan.  dY, Y [b,n,h,...].  Returns (dX, dA [b,n,h] fp32[, carry_out])."""
+    """Reverse scan.  dY, Y [b,n,h,...].  Returns (dX, dA_part [b,h,blocks,n] fp32[, carry_out]):
+    the chunk-gate gradient is left as per-block partial sums, which gate_grad() adds up."""
     b, n, h = dY.shape[:3]
     E = dY[0, 0, 0].numel()
     blocks = lib().pr_discumsum_bwd_blocks(c_longlong(E))
     dX = dY if inplace else torch.empty_like(dY)
     part = torch.empty(b, h, blocks, n, device=dY.device, dtype=torch.float32)
     carry_out = torch.empty(b, h, E, device=dY.device, dtype=torch.float32) if want_carry else None
-    check(lib().pr_discumsum_bwd(c_int(dtype_code(dY.dtype)), c_int(b), c_int(n), c_int(h), c_longlong(E), ptr(dY),
+    _call("pr_discumsum_bwd", c_int(dtype_code(dY.dtype)), c_int(b), c_int(n), c_int(h), c_longlong(E), ptr(dY),
                                  ptr(Y), ptr(dX), ptr(A), ptr(carry_in), ptr(carry_out), ptr(part), c_int(row_len),
-                                 c_int(1 if row_weights else 0), c_int(_dev(dY)), stream_ptr(dY.device)),
-          "pr_discumsum_bwd")
-    dA = part.sum(dim=2).transpose(1, 2).contiguous()  # [b,n,h]
-    return (dX, dA, carry_out) if want_carry else (dX, dA)
+                                 c_int(1 if row_weights else 0), c_int(_dev(dY)), stream_ptr(dY.device))
+    return (dX, part, carry_out) if want_carry else (dX, part)
 
 
 def gram_scan_fwd(G: torch.Tensor, A: torch.Tensor, dtype, want_full: bool, carry_in=None, want_carry=False):
@@ -121,24 +162,24 @@ def gram_scan_fwd(G: torch.Tensor, A: torch.Tensor, dtype, want_full: bool, carr
     lo = torch.empty_like(hi)
     full = torch.empty_like(G) if want_full else None
     carry_out = torch.empty(b, h, d * d, device=G.device, dtype=torch.float32) if want_carry else None
-    check(lib().pr_gram_scan_fwd(c_int(dtype_code(dtype)), c_int(b), c_int(n), c_int(h), c_int(d), ptr(G), ptr(hi),
+    _call("pr_gram_scan_fwd", c_int(dtype_code(dtype)), c_int(b), c_int(n), c_int(h), c_int(d), ptr(G), ptr(hi),
                                  ptr(lo), ptr(full), ptr(A), ptr(carry_in), ptr(carry_out), c_int(_dev(G)),
-                                 stream_ptr(G.device)), "pr_gram_scan_fwd")
+                                 stream_ptr(G.device))
     return (hi, lo, full, carry_out) if want_carry else (hi, lo, full)
 
 
 def gram_scan_bwd(dZg: torch.Tensor, Zg: torch.Tensor, A: torch.Tensor, dtype, carry_in=None, want_carry=False):
-    """dZg, Zg [b,n,h,d,d] fp32 -> (hi, lo of the symmetrised d(gram_m), dA [b,n,h])."""
+    """dZg, Zg [b,n,h,d,d] fp32 -> (hi, lo of the symmetrised d(gram_m), dA partial sums [b,h,blocks,n])."""
     b, n, h, d, _ = dZg.shape
     hi = torch.empty(b, n, h, d, d, device=dZg.device, dtype=dtype)
     lo = torch.empty_like(hi)
-    part = torch.empty(b, h, n, device=dZg.device, dtype=torch.float32)
+    blocks = lib().pr_gram_scan_bwd_blocks(c_int(d))
+    part = torch.empty(b, h, blocks, n, device=dZg.device, dtype=torch.float32)
     carry_out = torch.empty(b, h, d * d, device=dZg.device, dtype=torch.float32) if want_carry else None
-    check(lib().pr_gram_scan_bwd(c_int(dtype_code(dtype)), c_int(b), c_int(n), c_int(h), c_int(d), ptr(dZg), ptr(Zg),
+    _call("pr_gram_scan_bwd", c_int(dtype_code(dtype)), c_int(b), c_int(n), c_int(h), c_int(d), ptr(dZg), ptr(Zg),
                                  ptr(hi), ptr(lo), ptr(A), ptr(carry_in), ptr(carry_out), ptr(part), c_int(_dev(dZg)),
-                                 stream_ptr(dZg.device)), "pr_gram_scan_bwd")
-    dA = part.transpose(1, 2).contiguous()
-    return (hi, lo, dA, carry_out) if want_carry else (hi, lo, dA)
+                                 stream_ptr(dZg.device))
+    return (hi, lo, part, carry_out) if want_carry else (hi, lo, part)
 
 
 def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, state_from_chunk: int, scale: float,
@@ -149,10 +190,10 @@ def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, stat
     h = K.shape[2] if K is not None else Z.shape[2]
     O = torch.empty_like(Q)
     l = torch.empty(b, tq, hq, device=Q.device, dtype=torch.float32) if want_l else None
-    check(lib().pr_chunk_out(c_int(dtype_code(Q.dtype)), c_int(b), c_int(n_chunks), c_int(cq), c_int(ck), c_int(hq),
+    _call("pr_chunk_out", c_int(dtype_code(Q.dtype)), c_int(b), c_int(n_chunks), c_int(cq), c_int(ck), c_int(hq),
                              c_int(h), c_int(d), ptr(Q), ptr(K), ptr(V), ptr(a), ptr(Z), ptr(zg_hi), ptr(zg_lo),
                              c_int(state_from_chunk), c_int(1 if q_gate_last else 0), c_int(1 if normalize else 0),
-                             c_float(scale), ptr(O), ptr(l), c_int(_dev(Q)), stream_ptr(Q.device)), "pr_chunk_out")
+                             c_float(scale), ptr(O), ptr(l), c_int(_dev(Q)), stream_ptr(Q.device))
     return O, l
 
 
@@ -163,45 +204,47 @@ def expand_grad(W, X, State, g_hi, g_lo, a, A, row_g, c: int, h: int, query_side
     b, t, hx, d = X.shape
     dX = torch.empty(b, t, hx, d, device=X.device, dtype=torch.float32)
     gdot = torch.empty(b, t, hx, device=X.device, dtype=torch.float32)
-    check(lib().pr_expand_grad(c_int(dtype_code(X.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
+    _call("pr_expand_grad", c_int(dtype_code(X.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
                                ptr(W), ptr(X), ptr(State), ptr(g_hi), ptr(g_lo), ptr(a), ptr(A), ptr(row_g),
                                c_int(1 if query_side else 0), c_float(scale), c_float(gram_mult), c_int(chunk_lo),
-                               c_int(chunk_hi), ptr(dX), ptr(gdot), c_int(_dev(X)), stream_ptr(X.device)),
-          "pr_expand_grad")
+                               c_int(chunk_hi), ptr(dX), ptr(gdot), c_int(_dev(X)), stream_ptr(X.device))
     return dX, gdot
 
 
-def chunk_dq(Q, dY, K, V, a, dl, dq_state, c: int, scale: float):
+def chunk_dq(Q, dO, K, V, a, dl, l, dq_state, c: int, scale: float):
     """Returns (dQ [b,t,hq,d], da_q [b,t,hq] fp32)."""
     b, t, hq, d = Q.shape
     h = K.shape[2]
     dQ = torch.empty_like(Q)
     da_q = torch.empty(b, t, hq, device=Q.device, dtype=torch.float32)
-    check(lib().pr_chunk_dq(c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
-                            ptr(Q), ptr(dY), ptr(K), ptr(V), ptr(a), ptr(dl), ptr(dq_state), c_float(scale), ptr(dQ),
-                            ptr(da_q), c_int(_dev(Q)), stream_ptr(Q.device)), "pr_chunk_dq")
+    _call("pr_chunk_dq", c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
+                            ptr(Q), ptr(dO), ptr(K), ptr(V), ptr(a), ptr(dl), ptr(l), ptr(dq_state), c_float(scale), ptr(dQ),
+                            ptr(da_q), c_int(_dev(Q)), stream_ptr(Q.device))
     return dQ, da_q
 
 
-def chunk_dkv(Q, dY, K, V, wdS, a, A, dl, dk_state, c: int, state_chunk_hi: int, scale: float):
+def chunk_dkv(Q, dO, K, V, wdS, a, A, dl, l, dk_state, c: int, state_chunk_hi: int, scale: float):
     """Returns (dK, dV [b,t,h,d], da_k [b,t,h] fp32)."""
     b, t, hq, d = Q.shape
     h = K.shape[2]
     dK, dV = torch.empty_like(K), torch.empty_like(V)
     da_k = torch.empty(b, t, h, device=Q.device, dtype=torch.float32)
-    check(lib().pr_chunk_dkv(c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
-                             ptr(Q), ptr(dY), ptr(K), ptr(V), ptr(wdS), ptr(a), ptr(A), ptr(dl), ptr(dk_state),
+    _call("pr_chunk_dkv", c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
+                             ptr(Q), ptr(dO), ptr(K), ptr(V), ptr(wdS), ptr(a), ptr(A), ptr(dl), ptr(l), ptr(dk_state),
                              c_int(state_chunk_hi), c_float(scale), ptr(dK), ptr(dV), ptr(da_k), c_int(_dev(Q)),
-                             stream_ptr(Q.device)), "pr_chunk_dkv")
+                             stream_ptr(Q.device))
     return dK, dV, da_k
 
 
 def gate_grad(da_q, gq, da_k, wk, dA_scan, dA_gram, c: int):
-    """Assembles dlog_G [b,t,h] from the per-token and per-chunk gate-gradient terms."""
+    """Assembles dlog_G [b,t,h] from the per-token terms and the reverse scans' partial sums
+    (dA_scan [b,h,blocks,n], dA_gram [b,h,blocks2,n])."""
     b, t, hq = da_q.shape
     h = da_k.shape[2]
     out = torch.empty(b, t, h, device=da_q.device, dtype=torch.float32)
-    check(lib().pr_gate_grad(c_int(b), c_int(t), c_int(h), c_int(hq), c_int(c), ptr(da_q), ptr(gq), ptr(da_k),
-                             ptr(wk), ptr(dA_scan), ptr(dA_gram), ptr(out), c_int(_dev(da_q)),
-                             stream_ptr(da_q.device)), "pr_gate_grad")
+    blocks = dA_scan.shape[2] if dA_scan is not None else 0
+    gblocks = dA_gram.shape[2] if dA_gram is not None else 0
+    _call("pr_gate_grad", c_int(b), c_int(t), c_int(h), c_int(hq), c_int(c), ptr(da_q), ptr(gq), ptr(da_k),
+                             ptr(wk), ptr(dA_scan), c_int(blocks), ptr(dA_gram), c_int(gblocks), ptr(out), c_int(_dev(da_q)),
+                             stream_ptr(da_q.device))
     return out

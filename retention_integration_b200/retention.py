@@ -74,8 +74,9 @@ class _ChunkedRetention(torch.autograd.Function):
         dk_state, wk = ops.expand_grad(V, K, wdS, ghi, glo, a, A if a is not None else None, None, c, h, False, 1.0,
                                        1.0, 0, n - 2)
         # intra-chunk attention backward, merged with the state-path terms
-        dQ, da_q = ops.chunk_dq(Q, dy, K, V, a, dl, dq_state, c, scale)
-        dK, dV, da_k = ops.chunk_dkv(Q, dy, K, V, wdS, a, A if a is not None else None, dl, dk_state, c, n - 2, scale)
+        dQ, da_q = ops.chunk_dq(Q, dO, K, V, a, dl, l, dq_state, c, scale)
+        dK, dV, da_k = ops.chunk_dkv(Q, dO, K, V, wdS, a, A if a is not None else None, dl, l, dk_state, c, n - 2,
+                                     scale)
         dlog_G = None
         if log_G is not None:
             dlog_G = ops.gate_grad(da_q, gq, da_k, wk, dA_state, dA_gram, c)
@@ -102,9 +103,10 @@ class _QuadraticRetention(torch.autograd.Function):
     def backward(ctx, dO):
         Q, K, V, a, O, l = ctx.saved_tensors
         t = Q.shape[1]
-        dy, dl = ops.dout_prep(O, dO.contiguous(), l)
-        dQ, da_q = ops.chunk_dq(Q, dy, K, V, a, dl, None, t, ctx.scale)
-        dK, dV, da_k = ops.chunk_dkv(Q, dy, K, V, None, a, None, dl, None, t, -1, ctx.scale)
+        dO = dO.contiguous()
+        _, dl = ops.dout_prep(O, dO, l)
+        dQ, da_q = ops.chunk_dq(Q, dO, K, V, a, dl, l, None, t, ctx.scale)
+        dK, dV, da_k = ops.chunk_dkv(Q, dO, K, V, None, a, None, dl, l, None, t, -1, ctx.scale)
         dlog_G = ops.gate_grad(da_q, None, da_k, None, None, None, t) if ctx.gated else None
         return dQ, dK, dV, dlog_G, None
 

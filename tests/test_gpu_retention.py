@@ -1,0 +1,166 @@
+"""Parity of power_retention (forward and backward) on a B200 against the CPU oracle, the
+reference's golden fixtures, and size-independent properties at the benchmark size.
+
+Tolerance (stated by the task): relative L2 <= 2e-2 against an fp32 run of the reference
+for bf16/fp16 inputs, and at least as close as the reference's own 16-bit path, which is
+measured here by running the oracle in bf16 on the same inputs.
+"""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import power_retention_oracle as oracle
+from tests._golden import load, rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def _run_ours(dev, Q, K, V, lg, dO, chunk, **kw):
+    import retention_integration_b200 as prb
+    from retention_integration_b200 import _lib
+
+    leaves = [x.to(dev).requires_grad_(True) for x in (Q, K, V)]
+    g = lg.to(dev).requires_grad_(True) if lg is not None else None
+    O = prb.power_retention(leaves[0], leaves[1], leaves[2], g, deg=2, chunk_size=chunk, **kw)
+    O.backward(dO.to(dev))
+    torch.cuda.synchronize()
+    assert _lib.device_status(dev.index or 0) == 0
+    out = {"O": O, "dQ": leaves[0].grad, "dK": leaves[1].grad, "dV": leaves[2].grad}
+    if g is not None:
+        out["dlog_G"] = g.grad
+    return {k: v.detach().float().cpu() for k, v in out.items()}
+
+
+def _run_oracle(Q, K, V, lg, dO, chunk, dtype):
+    leaves = [x.to(dtype).requires_grad_(True) for x in (Q, K, V)]
+    g = lg.clone().requires_grad_(True) if lg is not None else None
+    O = oracle.power_retention(leaves[0], leaves[1], leaves[2], g, deg=2, chunk_size=chunk)
+    O.backward(dO.to(dtype))
+    out = {"O": O, "dQ": leaves[0].grad, "dK": leaves[1].grad, "dV": leaves[2].grad}
+    if g is not None:
+        out["dlog_G"] = g.grad
+    return {k: v.detach().float() for k, v in out.items()}
+
+
+def _case(b, t, h, r, d, gated, shift, seed, dtype=torch.bfloat16, in_scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    Q = (torch.randn(b, t, h * r, d, generator=g) * in_scale).to(dtype)
+    K = (torch.randn(b, t, h, d, generator=g) * in_scale).to(dtype)
+    V = (torch.randn(b, t, h, d, generator=g) * in_scale).to(dtype)
+    lg = F.logsigmoid(torch.randn(b, t, h, generator=g) + shift) if gated else None
+    dO = torch.randn(b, t, h * r, d, generator=g).to(dtype)
+    return Q, K, V, lg, dO
+
+
+# grid modelled on the reference's own (perf/tests/test_list.py:248-259): t in {31,128,1024,2000},
+# chunk in {None,128}, gated or not; plus GQA, a long chunk and slow/fast decay.
+CASES = [
+    # b, t, h, r, gated, shift, chunk
+    (1, 31, 2, 1, True, 0.0, None),
+    (1, 128, 2, 1, False, 0.0, None),
+    (1, 128, 2, 1, True, 0.0, 128),
+    (1, 1024, 2, 1, True, 0.0, 128),
+    (1, 1024, 2, 1, False, 0.0, 128),
+    (1, 2000, 2, 1, True, 2.0, 128),   # padding
+    (2, 512, 2, 2, True, 4.0, 256),    # GQA + slow decay
+    (1, 600, 1, 8, False, 0.0, 128),   # GQA ratio 8 + padding
+    (1, 2048, 1, 1, True, 0.0, 1024),  # the benchmark's chunk size
+    (1, 300, 2, 1, True, 2.0, None),   # quadratic branch, ragged length
+]
+
+
+@pytest.mark.parametrize("b,t,h,r,gated,shift,chunk", CASES)
+def test_forward_backward_vs_fp32_oracle(cuda_device, b, t, h, r, gated, shift, chunk):
+    Q, K, V, lg, dO = _case(b, t, h, r, 64, gated, shift, seed=t + h)
+    ours = _run_ours(cuda_device, Q, K, V, lg, dO, chunk)
+    gold = _run_oracle(Q, K, V, lg, dO, chunk, torch.float32)
+    ref16 = _run_oracle(Q, K, V, lg, dO, chunk, torch.bfloat16)
+    for key in gold:
+        err, err16 = rel_l2(ours[key], gold[key]), rel_l2(ref16[key], gold[key])
+        assert err < TOL, (key, err)
+        assert err < 1.5 * err16 + 1e-3, (key, err, err16)  # as close as the 16-bit reference path
+
+
+def test_fp16_inputs(cuda_device):
+    Q, K, V, lg, dO = _case(1, 512, 2, 1, 64, True, 2.0, seed=77, dtype=torch.float16, in_scale=0.5)
+    ours = _run_ours(cuda_device, Q, K, V, lg, dO, 128)
+    gold = _run_oracle(Q, K, V, lg, dO, 128, torch.float32)
+    for key in gold:
+        assert rel_l2(ours[key], gold[key]) < TOL, key
+
+
+@pytest.mark.parametrize("name", ["train_gated_fp32", "train_slow_decay_fp32", "train_gated_bf16"])
+def test_against_reference_golden_outputs(cuda_device, name):
+    """Same seeded inputs as the reference run that produced the fixture (inputs are bf16-exact)."""
+    g = load(name)
+    b, t, h, d, r, gated, chunk, stride = g["meta"]
+    ours = _run_ours(cuda_device, g["Q"].bfloat16(), g["K"].bfloat16(), g["V"].bfloat16(),
+                     g["log_G"] if gated else None, g["dO"].bfloat16(), chunk or None)
+    tol = TOL if name.endswith("fp32") else 2.5e-2  # bf16 fixture: both sides carry 16-bit noise
+    for key in ("O", "dQ", "dK", "dV", "dlog_G"):
+        assert rel_l2(ours[key][:, ::stride], g[key]) < tol, key
+
+
+def test_cfg1_shape_against_reference_golden(cuda_device):
+    g = load("train_cfg1_fp32")  # b1 t1024 h4 d64 c128 gated: the reference's CPU-runnable case
+    ours = _run_ours(cuda_device, g["Q"].bfloat16(), g["K"].bfloat16(), g["V"].bfloat16(), g["log_G"],
+                     g["dO"].bfloat16(), 128)
+    for key in ("O", "dQ", "dK", "dV", "dlog_G"):
+        assert rel_l2(ours[key][:, ::8], g[key]) < TOL, key
+
+
+def test_chunk_size_invariance_and_determinism(cuda_device):
+    """Chunked == quadratic, as in the reference's chunk-consistency test
+    (perf/tests/chunk_consistency_tests.py:22-45); two runs are bitwise identical."""
+    Q, K, V, lg, dO = _case(1, 1024, 2, 1, 64, True, 3.0, seed=5)
+    a = _run_ours(cuda_device, Q, K, V, lg, dO, 128)
+    a2 = _run_ours(cuda_device, Q, K, V, lg, dO, 128)
+    bq = _run_ours(cuda_device, Q, K, V, lg, dO, None)
+    c = _run_ours(cuda_device, Q, K, V, lg, dO, 256)
+    for key in a:
+        assert torch.equal(a[key], a2[key]), key
+        assert rel_l2(a[key], bq[key]) < 1e-2, key
+        assert rel_l2(a[key], c[key]) < 1e-2, key
+
+
+def test_gqa_equals_repeated_heads(cuda_device):
+    """GQA == MHA with the kv heads repeated (perf/tests/gqa_tests.py:44-66)."""
+    Q, K, V, lg, dO = _case(1, 512, 2, 4, 64, True, 2.0, seed=8)
+    gq = _run_ours(cuda_device, Q, K, V, lg, dO, 128)
+    Kr, Vr, lgr = K.repeat_interleave(4, 2), V.repeat_interleave(4, 2), lg.repeat_interleave(4, 2)
+    mha = _run_ours(cuda_device, Q, Kr, Vr, lgr, dO, 128)
+    assert rel_l2(gq["O"], mha["O"]) < 1e-3
+    assert rel_l2(gq["dQ"], mha["dQ"]) < 5e-3
+    assert rel_l2(gq["dK"], mha["dK"].view(1, 512, 2, 4, 64).sum(3)) < 1e-2
+    assert rel_l2(gq["dV"], mha["dV"].view(1, 512, 2, 4, 64).sum(3)) < 1e-2
+
+
+def test_full_benchmark_size_properties(cuda_device):
+    """At b1 t65536 h8 d64 c1024 (too large for the oracle): no NaN, output invariant to the
+    chunk size, and a 2048-token prefix agrees with the fp32 oracle (causality)."""
+    import retention_integration_b200 as prb
+
+    g = torch.Generator().manual_seed(0)
+    b, t, h, d = 1, 65536, 8, 64
+    Q, K, V = (torch.randn(b, t, h, d, generator=g).bfloat16().to(cuda_device) for _ in range(3))
+    lg = F.logsigmoid(torch.randn(b, t, h, generator=g)).to(cuda_device)
+    O1 = prb.power_retention(Q, K, V, lg, chunk_size=1024)
+    O2 = prb.power_retention(Q, K, V, lg, chunk_size=512)
+    torch.cuda.synchronize()
+    assert torch.isfinite(O1).all()
+    assert rel_l2(O1.float().cpu(), O2.float().cpu()) < 1e-2
+    pre = slice(0, 2048)
+    O_ref = oracle.power_retention(Q[:, pre, :2].float().cpu(), K[:, pre, :2].float().cpu(),
+                                   V[:, pre, :2].float().cpu(), lg[:, pre, :2].cpu(), chunk_size=1024)
+    assert rel_l2(O1[:, pre, :2].float().cpu(), O_ref) < TOL
+
+
+def test_rejects_what_the_reference_leaves_unfinished(cuda_device):
+    import retention_integration_b200 as prb
+
+    q = torch.zeros(1, 128, 1, 64, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(prb.PRError):
+        prb.power_retention(q, q, q, None, return_final_state=True, chunk_size=64)
+    with pytest.raises(AssertionError):
+        prb.power_retention(q, q, q, None, deg=3)
