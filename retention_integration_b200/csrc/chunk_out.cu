@@ -57,7 +57,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(co::THREADS)
+__global__ void __launch_bounds__(co::THREADS, 2)
 chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                  const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_ghi,
@@ -444,9 +444,11 @@ extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int 
   if (dtype == PR_BF16) {
     PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     chunk_out_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);
   } else {
     PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     chunk_out_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);
   }
   PR_CUDA(cudaGetLastError());

@@ -46,7 +46,7 @@ struct ChunkStateParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(cs::THREADS)
+__global__ void __launch_bounds__(cs::THREADS, 2)
 chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap tm_xt,
                    const __grid_constant__ CUtensorMap tm_xs, const __grid_constant__ CUtensorMap tm_w) {
   using namespace cs;
@@ -60,7 +60,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smX = sm;                          // NS x XT_BYTES (rows = features, 64 tokens)
   uint8_t* smW = sm + NS * XT_BYTES;          // NS x W_BYTES  (rows = tokens, 64 features)
-  uint8_t* smG = smW + NS * W_BYTES;          // NS x GA_BYTES (Gram CTA only)
+  uint8_t* smG = smW;                         // Gram CTA only: 2 x GA_BYTES over the (unused) value ring
 
   const int tile = blockIdx.x;
   const bool gram_cta = (tile == p.n_tiles);
@@ -75,7 +75,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
       mbar_init(&x_full[s], 1);
-      mbar_init(&x_empty[s], gram_cta ? 1 : 4);
+      mbar_init(&x_empty[s], 4);
       mbar_init(&w_full[s], 1);
       mbar_init(&w_empty[s], 1);
       mbar_init(&a_full[s], 4);
@@ -101,11 +101,14 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         const int g = it / kblocks, kb = it % kblocks;
         const int xhead = head * p.group + g;
         const int xrow = ((batch * p.n_chunks + chunk) * (p.nh * p.group) + xhead) * HD;
-        if (!mbar_wait(&x_empty[s], ph ^ 1, &abort_flag)) break;
+        if (!gram_cta && !mbar_wait(&x_empty[s], ph ^ 1, &abort_flag)) break;
         if (gram_cta) {
-          mbar_expect_tx(&x_full[s], 2 * XT_BYTES);
-          tma_load_2d(smX + s * XT_BYTES, &tm_xt, &x_full[s], kb * TOK, xrow);
-          tma_load_2d(smG + s * GA_BYTES, &tm_xs, &x_full[s], kb * TOK, xrow);
+          // two stages only: the padded A operand is twice the size of a value stage
+          const int gs = it & 1, gph = (it >> 1) & 1;
+          if (!mbar_wait(&w_empty[gs], gph ^ 1, &abort_flag)) break;
+          mbar_expect_tx(&w_full[gs], 2 * XT_BYTES);
+          tma_load_2d(smX + gs * XT_BYTES, &tm_xt, &w_full[gs], kb * TOK, xrow);
+          tma_load_2d(smG + gs * GA_BYTES, &tm_xs, &w_full[gs], kb * TOK, xrow);
         } else {
           mbar_expect_tx(&x_full[s], XT_BYTES);
           tma_load_2d(smX + s * XT_BYTES, &tm_xt, &x_full[s], kb * TOK, xrow);
@@ -122,16 +125,16 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
       if (gram_cta) {
         const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
         for (int it = 0; it < total && ok; ++it) {
-          const int s = it % NS, ph = (it / NS) & 1;
-          ok = mbar_wait(&x_full[s], ph, &abort_flag);
+          const int gs = it & 1, gph = (it >> 1) & 1;
+          ok = mbar_wait(&w_full[gs], gph, &abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smG + s * GA_BYTES), b_addr = smem_u32(smX + s * XT_BYTES);
+          const uint32_t a_addr = smem_u32(smG + gs * GA_BYTES), b_addr = smem_u32(smX + gs * XT_BYTES);
 #pragma unroll
           for (int ks = 0; ks < TOK / 16; ++ks)
             umma_ss(tmem + COL_ACC, umma_desc_sw128(a_addr + ks * 32, 16, 1024),
                     umma_desc_sw128(b_addr + ks * 32, 16, 1024), idesc, (it > 0 || ks > 0) ? 1u : 0u);
-          umma_commit(&x_empty[s]);
+          umma_commit(&w_empty[gs]);
         }
       } else {
         const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
@@ -230,8 +233,10 @@ template <typename T>
 static int launch_chunk_state(const ChunkStateParams& p, int b, const CUtensorMap& tm_xt, const CUtensorMap& tm_xs,
                               const CUtensorMap& tm_w, cudaStream_t stream) {
   using namespace cs;
-  const size_t smem = 1024 + NS * (XT_BYTES + W_BYTES) + (p.gram ? NS * GA_BYTES : 0);
+  const size_t smem = 1024 + NS * (XT_BYTES + W_BYTES);
+  static_assert(2 * GA_BYTES <= NS * W_BYTES, "Gram stages must fit in the value ring");
   PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
   dim3 grid(p.n_tiles + (p.gram ? 1 : 0), b * p.n_chunks * p.nh);
   chunk_state_kernel<T><<<grid, THREADS, smem, stream>>>(p, tm_xt, tm_xs, tm_w);
   PR_CUDA(cudaGetLastError());

@@ -11,11 +11,12 @@
 // Key side (gradient of the chunk state, retention/_update_state/reference.py:55-83):
 //   W = V, State = w (.) dS_m, Gs = dG_m + dG_m^T, g_i = 1, mult = 1, f_i = exp((A_m - a_i)/2).
 //
-// One CTA owns 128 tokens of one (batch, chunk, head).  The expansion gradient dphi is
-// never written to memory: tiles of 128 expanded rows are produced in tensor memory
-// (double buffered) and drained by two groups of four warps, each thread owning one
-// token row and keeping x~ and its partial dx~ in registers; the triangle's (a, b)
-// pattern is resolved at compile time, so the drain is two FMAs per entry.
+// One CTA owns 256 tokens (two row tiles of 128) of one (batch, chunk, head), so that each
+// state tile fetched from L2 feeds two products.  The expansion gradient dphi is never
+// written to memory: tiles of 128 expanded rows are produced in tensor memory, one buffer
+// per row tile, and drained by the row tile's four warps while the tensor core fills the
+// other buffer.  Each thread owns one token row and keeps x~ and dx~ in registers; the
+// triangle's (a, b) pattern is resolved at compile time, so the drain is two FMAs per entry.
 #include <type_traits>
 
 #include "host.cuh"
@@ -28,12 +29,14 @@ namespace eg {
 constexpr int HD = 64;
 constexpr int D2 = t2_dim(HD);           // 2112
 constexpr int NT = (D2 + 127) / 128;     // 17 tiles, the last one 64 rows wide
-constexpr int THREADS = 320;             // warps 0-3 / 4-7 drain groups, 8 TMA, 9 MMA
+constexpr int THREADS = 320;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9 MMA
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int G_BYTES = 64 * 128;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t COL_D = 0;            // 2 x 128 columns
-constexpr uint32_t COL_U = 256, COL_XA = 320;
+constexpr int ROWS = 256;                // token rows per CTA: two row tiles of 128
+constexpr uint32_t COL_D = 0;            // 2 x 128 columns (one buffer per row tile)
+constexpr uint32_t COL_U = 256;          // 2 x 64
+constexpr uint32_t COL_XA = 384;         // 2 x 32
 
 __host__ __device__ constexpr int t2_a(int idx) {
   int p = 0;
@@ -80,7 +83,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
                    const __grid_constant__ CUtensorMap tm_ghi, const __grid_constant__ CUtensorMap tm_glo) {
   using namespace eg;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t w_full, g_full, xa_full, u_full, s_full[2], s_empty[2], d_full[2], d_empty[2];
+  __shared__ uint64_t w_full, g_full, xa_full[2], u_full[2], s_full[2], s_empty[2], d_full[2], d_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -89,12 +92,12 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
   const int chunk = blockIdx.x / p.tiles_per_chunk;
   const int head = blockIdx.y, batch = blockIdx.z;
   const int gh = head / (p.hx / p.h);
-  const int row0 = tile_i * 128;
+  const int row0 = tile_i * ROWS;
   const size_t tok0 = (size_t)batch * p.n_chunks * p.c + (size_t)chunk * p.c;
 
   if (chunk < p.chunk_lo || chunk > p.chunk_hi) {
     // no state term for this chunk: zero gradient
-    if (tid < 128) {
+    if (tid < ROWS) {
       const int row = row0 + tid;
       if (row < p.c) {
         float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
@@ -108,19 +111,18 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
 
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
-  uint8_t* smW = sm;
-  uint8_t* smX = smW + TILE_BYTES;
-  uint8_t* smS = smX + TILE_BYTES;              // 2 x TILE_BYTES
+  uint8_t* smW = sm;                            // 2 x TILE_BYTES (one per row tile)
+  uint8_t* smX = smW + 2 * TILE_BYTES;          // 2 x TILE_BYTES
+  uint8_t* smS = smX + 2 * TILE_BYTES;          // 2 x TILE_BYTES (ring of state tiles)
   uint8_t* smG = smS + 2 * TILE_BYTES;          // hi, lo
-  float* smR = reinterpret_cast<float*>(smG + 2 * G_BYTES);  // [64][128] partial exchange
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&w_full, 1);
     mbar_init(&g_full, 1);
-    mbar_init(&xa_full, 4);
-    mbar_init(&u_full, 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&xa_full[s], 4);
+      mbar_init(&u_full[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 1);
       mbar_init(&d_full[s], 1);
@@ -140,9 +142,11 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
 
   if (warp == 8) {
     if (lane == 0) {
-      mbar_expect_tx(&w_full, 2 * TILE_BYTES);
-      tma_load_4d(smW, &tm_w, &w_full, 0, head, chunk * p.c + row0, batch);
-      tma_load_4d(smX, &tm_x, &w_full, 0, head, chunk * p.c + row0, batch);
+      mbar_expect_tx(&w_full, 4 * TILE_BYTES);
+      for (int rt = 0; rt < 2; ++rt) {
+        tma_load_4d(smW + rt * TILE_BYTES, &tm_w, &w_full, 0, head, chunk * p.c + row0 + rt * 128, batch);
+        tma_load_4d(smX + rt * TILE_BYTES, &tm_x, &w_full, 0, head, chunk * p.c + row0 + rt * 128, batch);
+      }
       mbar_expect_tx(&g_full, 2 * G_BYTES);
       tma_load_2d(smG, &tm_ghi, &g_full, 0, ch * HD);
       tma_load_2d(smG + G_BYTES, &tm_glo, &g_full, 0, ch * HD);
@@ -159,41 +163,51 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
       const uint32_t w_addr = smem_u32(smW);
       for (int nt = 0; nt < NT && ok; ++nt) {
         const int s = nt & 1, ph = (nt >> 1) & 1;
-        ok = mbar_wait(&s_full[s], ph, &abort_flag) && mbar_wait(&d_empty[s], ph ^ 1, &abort_flag);
+        ok = mbar_wait(&s_full[s], ph, &abort_flag);
         if (!ok) break;
-        tc_fence_after();
         const uint32_t idesc = umma_idesc(128, nt == NT - 1 ? 64 : 128, Pack2<T>::is_bf16, false, false);
         const uint32_t s_addr = smem_u32(smS + s * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + COL_D + s * 128, umma_desc_sw128(w_addr + ks * 32, 16, 1024),
-                  umma_desc_sw128(s_addr + ks * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
-        umma_commit(&d_full[s]);
-        umma_commit(&s_empty[s]);
-        if (nt == 0) {
-          // Gram part: u = x~ (Gs_hi + Gs_lo)
-          ok = mbar_wait(&xa_full, 0, &abort_flag) && mbar_wait(&g_full, 0, &abort_flag);
+        for (int rt = 0; rt < 2 && ok; ++rt) {
+          ok = mbar_wait(&d_empty[rt], (nt & 1) ^ 1, &abort_flag);
           if (!ok) break;
           tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ss(tmem + COL_D + rt * 128, umma_desc_sw128(w_addr + rt * TILE_BYTES + ks * 32, 16, 1024),
+                    umma_desc_sw128(s_addr + ks * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
+          umma_commit(&d_full[rt]);
+        }
+        if (!ok) break;
+        umma_commit(&s_empty[s]);
+        if (nt == 0) {
+          // Gram part: u = x~ (Gs_hi + Gs_lo), once per row tile
+          ok = mbar_wait(&g_full, 0, &abort_flag);
           const uint32_t idesc_g = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
           const uint32_t g_addr = smem_u32(smG);
+          for (int rt = 0; rt < 2 && ok; ++rt) {
+            ok = mbar_wait(&xa_full[rt], 0, &abort_flag);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-          for (int half = 0; half < 2; ++half)
+            for (int half = 0; half < 2; ++half)
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_ts(tmem + COL_U, tmem + COL_XA + ks * 8, umma_desc_sw128(g_addr + half * G_BYTES + ks * 32, 16, 1024),
-                      idesc_g, (half > 0 || ks > 0) ? 1u : 0u);
-          umma_commit(&u_full);
+              for (int ks = 0; ks < 4; ++ks)
+                umma_ts(tmem + COL_U + rt * 64, tmem + COL_XA + rt * 32 + ks * 8,
+                        umma_desc_sw128(g_addr + half * G_BYTES + ks * 32, 16, 1024), idesc_g,
+                        (half > 0 || ks > 0) ? 1u : 0u);
+            umma_commit(&u_full[rt]);
+          }
         }
       }
     }
   } else {
     // ------------------------------------------------------------ drain warps
-    const int group = warp >> 2;               // 0: even tiles + epilogue, 1: odd tiles
+    const int rt = warp >> 2;                  // row tile owned by this warp group
     const int r = (warp & 3) * 32 + lane;      // token row inside the tile = TMEM lane
-    const int row = row0 + r;
+    const int row = row0 + rt * 128 + r;
     const bool row_valid = row < p.c;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t col_d = COL_D + rt * 128;
 
     float f = p.query_side ? p.scale : 1.f;
     if (p.a != nullptr) {
@@ -204,9 +218,10 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     float x[HD], dx[HD];
     {
       uint32_t xp[32];
+      const uint8_t* xs = smX + rt * TILE_BYTES;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint4 v = *reinterpret_cast<const uint4*>(smX + swz128(r, j));
+        const uint4 v = *reinterpret_cast<const uint4*>(xs + swz128(r, j));
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -217,12 +232,12 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
           x[8 * j + 2 * k + 1] = rounded.y;
         }
       }
-      if (group == 0 && ok) {
-        tmem_st32(tmem + lane_addr + COL_XA, xp);
+      if (ok) {
+        tmem_st32(tmem + lane_addr + COL_XA + rt * 32, xp);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&xa_full);
+        if (lane == 0) mbar_arrive(&xa_full[rt]);
       }
     }
 #pragma unroll
@@ -231,76 +246,63 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     static_for<0, NT>([&](auto nt_c) {
       constexpr int nt = decltype(nt_c)::value;
       constexpr int ncols = (nt == NT - 1) ? D2 - 128 * (NT - 1) : 128;
-      if (group == (nt & 1)) {
-        const int s = nt & 1, ph = (nt >> 1) & 1;
-        if (ok) ok = mbar_wait(&d_full[s], ph, &abort_flag);
-        tc_fence_after();
-        if (ok) {
-          static_for<0, ncols / 32>([&](auto q_c) {
-            constexpr int q = decltype(q_c)::value;
-            uint32_t v[32];
-            tmem_ld32(tmem + lane_addr + COL_D + s * 128 + q * 32, v);
-            tmem_wait_ld();
-            if constexpr (q == ncols / 32 - 1) {
-              // all of this thread's reads of the buffer are done
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&d_empty[s]);
+      if (ok) ok = mbar_wait(&d_full[rt], nt & 1, &abort_flag);
+      tc_fence_after();
+      if (ok) {
+        static_for<0, ncols / 32>([&](auto q_c) {
+          constexpr int q = decltype(q_c)::value;
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_addr + col_d + q * 32, v);
+          tmem_wait_ld();
+          if constexpr (q == ncols / 32 - 1) {
+            // all of this thread's reads of the buffer are done
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&d_empty[rt]);
+          }
+          float ra0 = 0.f, ra1 = 0.f;
+          static_for<0, 32>([&](auto j_c) {
+            constexpr int j = decltype(j_c)::value;
+            constexpr int D = nt * 128 + q * 32 + j;
+            constexpr int a = t2_a(D), b = t2_b(D);
+            const float val = __uint_as_float(v[j]);
+            dx[b] = fmaf(val, x[a], dx[b]);
+            if constexpr (j & 1)
+              ra1 = fmaf(val, x[b], ra1);
+            else
+              ra0 = fmaf(val, x[b], ra0);
+            constexpr bool row_ends = (j == 31) || (t2_a(D + 1) != a);
+            if constexpr (row_ends) {
+              dx[a] += ra0 + ra1;
+              ra0 = 0.f;
+              ra1 = 0.f;
             }
-            float ra0 = 0.f, ra1 = 0.f;
-            static_for<0, 32>([&](auto j_c) {
-              constexpr int j = decltype(j_c)::value;
-              constexpr int D = nt * 128 + q * 32 + j;
-              constexpr int a = t2_a(D), b = t2_b(D);
-              const float val = __uint_as_float(v[j]);
-              dx[b] = fmaf(val, x[a], dx[b]);
-              if constexpr (j & 1)
-                ra1 = fmaf(val, x[b], ra1);
-              else
-                ra0 = fmaf(val, x[b], ra0);
-              constexpr bool row_ends = (j == 31) || (t2_a(D + 1) != a);
-              if constexpr (row_ends) {
-                dx[a] += ra0 + ra1;
-                ra0 = 0.f;
-                ra1 = 0.f;
-              }
-            });
           });
-        }
+        });
       }
     });
 
-    // combine the two groups' partial sums
-    if (group == 1) {
+    if (ok) ok = mbar_wait(&u_full[rt], 0, &abort_flag);
+    tc_fence_after();
+    if (ok) {
+      uint32_t u[64];
+      tmem_ld32(tmem + lane_addr + COL_U + rt * 64, u);
+      tmem_ld32(tmem + lane_addr + COL_U + rt * 64 + 32, u + 32);
+      tmem_wait_ld();
+      float g = p.gram_mult;
+      if (p.row_g != nullptr) g *= row_valid ? p.row_g[(tok0 + row) * p.hx + head] : 0.f;
+      float dot = 0.f;
 #pragma unroll
-      for (int e = 0; e < HD; ++e) smR[e * 128 + r] = dx[e];
-    }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (group == 0) {
+      for (int e = 0; e < HD; ++e) {
+        dx[e] = fmaf(g, __uint_as_float(u[e]), dx[e]);
+        dot = fmaf(x[e], dx[e], dot);
+      }
+      if (row_valid) {
+        float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
 #pragma unroll
-      for (int e = 0; e < HD; ++e) dx[e] += smR[e * 128 + r];
-      if (ok) ok = mbar_wait(&u_full, 0, &abort_flag);
-      tc_fence_after();
-      if (ok) {
-        uint32_t u[64];
-        tmem_ld32(tmem + lane_addr + COL_U, u);
-        tmem_ld32(tmem + lane_addr + COL_U + 32, u + 32);
-        tmem_wait_ld();
-        float g = p.gram_mult;
-        if (p.row_g != nullptr) g *= row_valid ? p.row_g[(tok0 + row) * p.hx + head] : 0.f;
-        float dot = 0.f;
-#pragma unroll
-        for (int e = 0; e < HD; ++e) {
-          dx[e] = fmaf(g, __uint_as_float(u[e]), dx[e]);
-          dot = fmaf(x[e], dx[e], dot);
-        }
-        if (row_valid) {
-          float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            dst[j] = make_float4(dx[4 * j] * f, dx[4 * j + 1] * f, dx[4 * j + 2] * f, dx[4 * j + 3] * f);
-          p.gdot[(tok0 + row) * p.hx + head] = 0.5f * dot;
-        }
+        for (int j = 0; j < 16; ++j)
+          dst[j] = make_float4(dx[4 * j] * f, dx[4 * j + 1] * f, dx[4 * j + 2] * f, dx[4 * j + 3] * f);
+        p.gdot[(tok0 + row) * p.hx + head] = 0.5f * dot;
       }
     }
   }
@@ -334,7 +336,7 @@ extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int
   p.hx = hx;
   p.n_chunks = n;
   p.c = c;
-  p.tiles_per_chunk = (c + 127) / 128;
+  p.tiles_per_chunk = (c + ROWS - 1) / ROWS;
   p.chunk_lo = chunk_lo;
   p.chunk_hi = chunk_hi;
   p.query_side = query_side;
@@ -364,7 +366,7 @@ extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int
     if ((rc = make_tmap(&tm_ghi, g_hi, 2, 2, dg, st, box_g, true))) return rc;
     if ((rc = make_tmap(&tm_glo, g_lo, 2, 2, dg, st, box_g, true))) return rc;
   }
-  const size_t smem = 1024 + 4 * TILE_BYTES + 2 * G_BYTES + 64 * 128 * 4;
+  const size_t smem = 1024 + 6 * TILE_BYTES + 2 * G_BYTES;
   dim3 grid(p.tiles_per_chunk * n, hx, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {

@@ -64,9 +64,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA.  The slow
+// path is kept out of line so that heavily unrolled callers stay small.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
@@ -78,6 +78,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
 }
 
 // --------------------------------------------------------------------- TMA
