@@ -3,7 +3,8 @@
 // and the dV part of retention/_update_state/reference.py:55-60).
 //
 // One CTA owns 128 key rows (tile J) of one (batch, chunk, kv head); thread = key row.  For
-// every query tile I >= J of every query head of the group:
+// every tile of 64 queries at or after the key tile, of every query head of the group (tiles
+// double-buffered in shared memory; 256 tensor memory columns, two CTAs per SM):
 //     S^T = K_J Q_I^T,  dP^T = V_J dO_I^T                (tensor cores)
 //     p = (s S)^2 e^{a_i-a_j},  dp = dP / l_i + dl_i,  dS = 2 s^2 S e^{a_i-a_j} dp
 //     dV += (P / l)^T dO_I,   dK += dS^T Q_I             (A operands from tensor memory)
@@ -21,11 +22,13 @@ namespace dkv {
 constexpr int HD = 64;
 constexpr int NS = 4;
 constexpr int THREADS = 192;
-constexpr int TILE_BYTES = 128 * 128;
+constexpr int TILE_BYTES = 128 * 128;   // 128 key rows x 64 features
+constexpr int TW = 64;                  // queries per step
+constexpr int QD_BYTES = TW * 128;      // one query or dO tile
 constexpr int Z_BYTES = 64 * 128;
 constexpr int NBLK = t2_dim(HD) / 64;
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t COL_S = 0, COL_P = 0, COL_DP = 128, COL_DS = 128, COL_DV = 256, COL_DK = 320, COL_A = 0;
+constexpr uint32_t TMEM_COLS = 256;     // two CTAs per SM
+constexpr uint32_t COL_S = 0, COL_P = 0, COL_DP = 64, COL_DS = 64, COL_DV = 128, COL_DK = 192, COL_A = 0;
 }  // namespace dkv
 
 struct ChunkDkvParams {
@@ -44,26 +47,26 @@ struct ChunkDkvParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(dkv::THREADS)
+__global__ void __launch_bounds__(dkv::THREADS, 2)
 chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_ds) {
   using namespace dkv;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t kv_full, qd_full, qd_empty, sp_full, pd_full, attn_done, acc_done;
+  __shared__ uint64_t kv_full, qd_full[2], qd_empty[2], sp_full, pd_full, attn_done, acc_done;
   __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float sm_aq[2][128], sm_dl[2][128], sm_il[2][128];
+  __shared__ float sm_aq[2][TW], sm_dl[2][TW], sm_il[2][TW];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smK = sm;
   uint8_t* smV = smK + TILE_BYTES;
-  uint8_t* smQ = smV + TILE_BYTES;
-  uint8_t* smDY = smQ + TILE_BYTES;
-  uint8_t* smZ = smDY + TILE_BYTES;  // NS x Z_BYTES
+  uint8_t* smQ = smV + TILE_BYTES;       // 2 stages x QD_BYTES
+  uint8_t* smDY = smQ + 2 * QD_BYTES;    // 2 stages x QD_BYTES
+  uint8_t* smZ = smDY + 2 * QD_BYTES;    // NS x Z_BYTES
 
   const int tile_j = blockIdx.x % p.tiles_per_chunk;
   const int chunk = blockIdx.x / p.tiles_per_chunk;
@@ -71,15 +74,19 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
   const int ratio = p.hq / p.h;
   const int row0 = tile_j * 128;
   const int tok_chunk = chunk * p.c;
-  const int nI = p.tiles_per_chunk - tile_j;   // query tiles tile_j .. tiles_per_chunk-1
+  const int q_tiles = (p.c + TW - 1) / TW;      // query tiles of TW rows in the chunk
+  const int qt0 = row0 / TW;                    // first query tile that can see this key tile
+  const int nI = q_tiles - qt0;
   const int n_steps = nI * ratio;
   const bool has_state = chunk <= p.state_chunk_hi;
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&kv_full, 1);
-    mbar_init(&qd_full, 1);
-    mbar_init(&qd_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qd_full[s], 1);
+      mbar_init(&qd_empty[s], 1);
+    }
     mbar_init(&sp_full, 1);
     mbar_init(&pd_full, 4);
     mbar_init(&attn_done, 1);
@@ -108,12 +115,13 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
       tma_load_4d(smK, &tm_k, &kv_full, 0, kvhead, tok_chunk + row0, batch);
       tma_load_4d(smV, &tm_v, &kv_full, 0, kvhead, tok_chunk + row0, batch);
       for (int st = 0; st < n_steps && ok; ++st) {
-        const int I = tile_j + st / ratio, qh = kvhead * ratio + st % ratio;
-        ok = mbar_wait(&qd_empty, (st & 1) ^ 1, &abort_flag);
+        const int I = qt0 + st / ratio, qh = kvhead * ratio + st % ratio;
+        const int s = st & 1, ph = (st >> 1) & 1;
+        ok = mbar_wait(&qd_empty[s], ph ^ 1, &abort_flag);
         if (!ok) break;
-        mbar_expect_tx(&qd_full, 2 * TILE_BYTES);
-        tma_load_4d(smQ, &tm_q, &qd_full, 0, qh, tok_chunk + I * 128, batch);
-        tma_load_4d(smDY, &tm_dy, &qd_full, 0, qh, tok_chunk + I * 128, batch);
+        mbar_expect_tx(&qd_full[s], 2 * QD_BYTES);
+        tma_load_4d(smQ + s * QD_BYTES, &tm_q, &qd_full[s], 0, qh, tok_chunk + I * TW, batch);
+        tma_load_4d(smDY + s * QD_BYTES, &tm_dy, &qd_full[s], 0, qh, tok_chunk + I * TW, batch);
       }
       if (ok && has_state) {
         const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
@@ -128,14 +136,15 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
   } else if (warp == 5) {
     if (lane == 0) {
       bool ok = mbar_wait(&kv_full, 0, &abort_flag);
-      const uint32_t idesc_s = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
+      const uint32_t idesc_s = umma_idesc(128, TW, Pack2<T>::is_bf16, false, false);
       const uint32_t idesc_o = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
-      const uint32_t k_addr = smem_u32(smK), v_addr = smem_u32(smV), q_addr = smem_u32(smQ),
-                     dy_addr = smem_u32(smDY);
+      const uint32_t k_addr = smem_u32(smK), v_addr = smem_u32(smV);
       for (int st = 0; st < n_steps && ok; ++st) {
-        ok = mbar_wait(&qd_full, st & 1, &abort_flag);
+        const int sg = st & 1;
+        ok = mbar_wait(&qd_full[sg], (st >> 1) & 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t q_addr = smem_u32(smQ + sg * QD_BYTES), dy_addr = smem_u32(smDY + sg * QD_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_ss(tmem + COL_S, umma_desc_sw128(k_addr + ks * 32, 16, 1024),
@@ -149,14 +158,14 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
+        for (int ks = 0; ks < TW / 16; ++ks)
           umma_ts(tmem + COL_DV, tmem + COL_P + ks * 8, umma_desc_sw128(dy_addr + ks * 2048, 8192, 1024), idesc_o,
                   (st > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
+        for (int ks = 0; ks < TW / 16; ++ks)
           umma_ts(tmem + COL_DK, tmem + COL_DS + ks * 8, umma_desc_sw128(q_addr + ks * 2048, 8192, 1024), idesc_o,
                   (st > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&qd_empty);
+        umma_commit(&qd_empty[sg]);
         if (st == n_steps - 1) umma_commit(&attn_done);
       }
       if (ok && has_state) {
@@ -188,9 +197,9 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
     float da = 0.f;
     bool ok = true;
     for (int st = 0; st < n_steps; ++st) {
-      const int I = tile_j + st / ratio, qh = kvhead * ratio + st % ratio;
-      const int qp0 = I * 128;
-      {
+      const int I = qt0 + st / ratio, qh = kvhead * ratio + st % ratio;
+      const int qp0 = I * TW;
+      if (tid < TW) {
         const int qp = qp0 + tid;
         const bool v = qp < p.c;
         sm_aq[st & 1][tid] = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
@@ -204,9 +213,9 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
       const float* aq = sm_aq[st & 1];
       const float* dlq = sm_dl[st & 1];
       const float* ilq = sm_il[st & 1];
-      const bool need_mask = (qp0 < row) || (qp0 + 127 >= p.c) || !row_valid;
+      const bool need_mask = (qp0 < row) || (qp0 + TW - 1 >= p.c) || !row_valid;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < TW / 32; ++q4) {
         uint32_t sv[32], pv[32];
         tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
         tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
@@ -388,8 +397,9 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   uint64_t dk[4] = {(uint64_t)d, (uint64_t)h, (uint64_t)t, (uint64_t)b};
   uint64_t sk[4] = {0, (uint64_t)d * 2, (uint64_t)h * d * 2, (uint64_t)t * h * d * 2};
   uint32_t box[4] = {64, 1, 128, 1};
-  if ((rc = make_tmap(&tm_q, Q, 2, 4, dq_, sq, box, true))) return rc;
-  if ((rc = make_tmap(&tm_dy, dO, 2, 4, dq_, sq, box, true))) return rc;
+  uint32_t box_q[4] = {64, 1, (uint32_t)TW, 1};
+  if ((rc = make_tmap(&tm_q, Q, 2, 4, dq_, sq, box_q, true))) return rc;
+  if ((rc = make_tmap(&tm_dy, dO, 2, 4, dq_, sq, box_q, true))) return rc;
   if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
   if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
   if (wdS) {
@@ -400,15 +410,17 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   } else {
     tm_ds = tm_q;
   }
-  const size_t smem = 1024 + 4 * TILE_BYTES + NS * Z_BYTES;
+  const size_t smem = 1024 + 2 * TILE_BYTES + 4 * QD_BYTES + NS * Z_BYTES;
   dim3 grid(p.tiles_per_chunk * p.n_chunks, h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
     PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     chunk_dkv_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);
   } else {
     PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     chunk_dkv_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);
   }
   PR_CUDA(cudaGetLastError());

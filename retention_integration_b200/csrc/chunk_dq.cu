@@ -3,7 +3,8 @@
 // for deg = 2 without the division by the score).
 //
 // One CTA owns 128 query rows of one (batch, chunk, query head); thread = row.  For every
-// key tile J up to the diagonal:
+// tile of 64 keys up to the diagonal (tiles double-buffered in shared memory; 256 tensor
+// memory columns, so two CTAs share an SM and hide each other's waits):
 //     S  = Q K_J^T,  dP = dO V_J^T                      (tensor cores, fp32 in tensor memory)
 //     p  = (s S)^2 e^{a_i-a_j},  dp = dP / l_i + dl_i,  e = p dp,  dS = 2 s^2 S e^{a_i-a_j} dp
 //     dQ += dS K_J                                      (A = dS from tensor memory)
@@ -20,9 +21,11 @@ namespace pr {
 namespace dq {
 constexpr int HD = 64;
 constexpr int THREADS = 192;
-constexpr int TILE_BYTES = 128 * 128;
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t COL_S = 0, COL_DS = 0, COL_DP = 128, COL_ACC = 256;
+constexpr int TILE_BYTES = 128 * 128;   // 128 query rows x 64 features
+constexpr int TW = 64;                  // keys per step
+constexpr int KV_BYTES = TW * 128;      // one key or value tile
+constexpr uint32_t TMEM_COLS = 256;     // two CTAs per SM
+constexpr uint32_t COL_S = 0, COL_DS = 0, COL_DP = 64, COL_ACC = 128;
 }  // namespace dq
 
 struct ChunkDqParams {
@@ -38,38 +41,40 @@ struct ChunkDqParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(dq::THREADS)
+__global__ void __launch_bounds__(dq::THREADS, 2)
 chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v) {
   using namespace dq;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, kv_full, kv_empty, sp_full, ds_full, acc_done;
+  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], sp_full, ds_full, acc_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float sm_ak[2][128];
+  __shared__ float sm_ak[2][TW];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smQ = sm;
   uint8_t* smDY = smQ + TILE_BYTES;
-  uint8_t* smK = smDY + TILE_BYTES;
-  uint8_t* smV = smK + TILE_BYTES;
+  uint8_t* smK = smDY + TILE_BYTES;      // 2 stages x KV_BYTES
+  uint8_t* smV = smK + 2 * KV_BYTES;     // 2 stages x KV_BYTES
 
   const int tile_i = blockIdx.x % p.tiles_per_chunk;
   const int chunk = blockIdx.x / p.tiles_per_chunk;
   const int qhead = blockIdx.y, batch = blockIdx.z;
   const int kvhead = qhead / (p.hq / p.h);
   const int row0 = tile_i * 128;
-  const int nJ = min(p.c - 1, row0 + 127) / 128 + 1;
+  const int nJ = min(p.c - 1, row0 + 127) / TW + 1;
   const int tok_chunk = chunk * p.c;
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&q_full, 1);
-    mbar_init(&kv_full, 1);
-    mbar_init(&kv_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
     mbar_init(&sp_full, 1);
     mbar_init(&ds_full, 4);
     mbar_init(&acc_done, 1);
@@ -90,23 +95,25 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
       tma_load_4d(smQ, &tm_q, &q_full, 0, qhead, tok_chunk + row0, batch);
       tma_load_4d(smDY, &tm_dy, &q_full, 0, qhead, tok_chunk + row0, batch);
       for (int J = 0; J < nJ; ++J) {
-        if (!mbar_wait(&kv_empty, (J & 1) ^ 1, &abort_flag)) break;
-        mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
-        tma_load_4d(smK, &tm_k, &kv_full, 0, kvhead, tok_chunk + J * 128, batch);
-        tma_load_4d(smV, &tm_v, &kv_full, 0, kvhead, tok_chunk + J * 128, batch);
+        const int s = J & 1, ph = (J >> 1) & 1;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1, &abort_flag)) break;
+        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+        tma_load_4d(smK + s * KV_BYTES, &tm_k, &kv_full[s], 0, kvhead, tok_chunk + J * TW, batch);
+        tma_load_4d(smV + s * KV_BYTES, &tm_v, &kv_full[s], 0, kvhead, tok_chunk + J * TW, batch);
       }
     }
   } else if (warp == 5) {
     if (lane == 0) {
       bool ok = mbar_wait(&q_full, 0, &abort_flag);
-      const uint32_t idesc_s = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
+      const uint32_t idesc_s = umma_idesc(128, TW, Pack2<T>::is_bf16, false, false);
       const uint32_t idesc_q = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
-      const uint32_t q_addr = smem_u32(smQ), dy_addr = smem_u32(smDY), k_addr = smem_u32(smK),
-                     v_addr = smem_u32(smV);
+      const uint32_t q_addr = smem_u32(smQ), dy_addr = smem_u32(smDY);
       for (int J = 0; J < nJ && ok; ++J) {
-        ok = mbar_wait(&kv_full, J & 1, &abort_flag);
+        const int st = J & 1;
+        ok = mbar_wait(&kv_full[st], (J >> 1) & 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t k_addr = smem_u32(smK + st * KV_BYTES), v_addr = smem_u32(smV + st * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_ss(tmem + COL_S, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
@@ -120,10 +127,10 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
+        for (int ks = 0; ks < TW / 16; ++ks)
           umma_ts(tmem + COL_ACC, tmem + COL_DS + ks * 8, umma_desc_sw128(k_addr + ks * 2048, 8192, 1024), idesc_q,
                   (J > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&kv_empty);
+        umma_commit(&kv_empty[st]);
       }
       if (ok) umma_commit(&acc_done);
     }
@@ -141,8 +148,8 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
     float da = 0.f;
     bool ok = true;
     for (int J = 0; J < nJ; ++J) {
-      const int kp0 = J * 128;
-      {
+      const int kp0 = J * TW;
+      if (tid < TW) {
         const int kp = kp0 + tid;
         sm_ak[J & 1][tid] = (gated && kp < p.c) ? a_chunk[(size_t)kp * p.h] : 0.f;
       }
@@ -151,9 +158,9 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
       if (!ok) break;
       tc_fence_after();
       const float* ak = sm_ak[J & 1];
-      const bool need_mask = (kp0 + 127 > row) || (kp0 + 127 >= p.c);
+      const bool need_mask = (kp0 + TW - 1 > row) || (kp0 + TW - 1 >= p.c);
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < TW / 32; ++q4) {
         uint32_t sv[32], pv[32];
         tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
         tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
@@ -260,17 +267,20 @@ extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c,
   uint32_t box[4] = {64, 1, 128, 1};
   if ((rc = make_tmap(&tm_q, Q, 2, 4, dq_, sq, box, true))) return rc;
   if ((rc = make_tmap(&tm_dy, dO, 2, 4, dq_, sq, box, true))) return rc;
-  if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
-  if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
-  const size_t smem = 1024 + 4 * TILE_BYTES;
+  uint32_t box_kv[4] = {64, 1, (uint32_t)TW, 1};
+  if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box_kv, true))) return rc;
+  if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box_kv, true))) return rc;
+  const size_t smem = 1024 + 2 * TILE_BYTES + 4 * KV_BYTES;
   dim3 grid(p.tiles_per_chunk * p.n_chunks, hq, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
     PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     chunk_dq_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v);
   } else {
     PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
     chunk_dq_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v);
   }
   PR_CUDA(cudaGetLastError());
