@@ -30,10 +30,12 @@ constexpr int HD = 64;
 constexpr int NS = 4;                 // stages of the expansion / Z ring
 constexpr int THREADS = 192;
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows x 64 16-bit features
+constexpr int TW = 64;                 // keys per attention step
+constexpr int KV_BYTES = TW * 128;     // one key or value tile
 constexpr int Z_BYTES = 64 * 128;      // 64 expanded rows x 64 features
 constexpr int NBLK = t2_dim(HD) / 64;  // 33 blocks of 64 expanded rows
 constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t COL_ACC = 0, COL_U = 64, COL_S = 128, COL_P = 128, COL_A = 128;
+constexpr uint32_t COL_ACC = 0, COL_U = 64, COL_S = 128, COL_A = 128;  // S: 2 buffers x 64 columns, P aliased
 }  // namespace co
 
 struct ChunkOutParams {
@@ -64,19 +66,19 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
                  const __grid_constant__ CUtensorMap tm_glo) {
   using namespace co;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, attn_done, g_full, acc_done;
+  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2], attn_done, g_full, acc_done;
   __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float sm_ak[2][128];
+  __shared__ float sm_ak[2][TW];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smQ = sm;
-  uint8_t* smK = smQ + TILE_BYTES;
-  uint8_t* smV = smK + TILE_BYTES;
-  uint8_t* smZ = smV + TILE_BYTES;        // NS x Z_BYTES
+  uint8_t* smK = smQ + TILE_BYTES;        // 2 stages x KV_BYTES
+  uint8_t* smV = smK + 2 * KV_BYTES;      // 2 stages x KV_BYTES
+  uint8_t* smZ = smV + 2 * KV_BYTES;      // NS x Z_BYTES
   uint8_t* smG = smZ + NS * Z_BYTES;      // hi, lo: 2 x Z_BYTES
 
   const int tile_i = blockIdx.x % p.tiles_per_chunk;
@@ -86,19 +88,19 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
   const int q_off = p.ck - p.cq;
   const int row0 = tile_i * 128;
   const int last_key = min(p.ck - 1, row0 + 127 + q_off);
-  const int nJ = p.has_attn ? last_key / 128 + 1 : 0;
+  const int nJ = p.has_attn ? last_key / TW + 1 : 0;
   const bool has_state = chunk >= p.state_from_chunk;
   const int n_items = has_state ? NBLK + 1 : 0;
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&q_full, 1);
-    mbar_init(&k_full, 1);
-    mbar_init(&k_empty, 1);
-    mbar_init(&v_full, 1);
-    mbar_init(&v_empty, 1);
-    mbar_init(&s_full, 1);
-    mbar_init(&p_full, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);
+    }
     mbar_init(&attn_done, 1);
     mbar_init(&g_full, 1);
     mbar_init(&acc_done, 1);
@@ -126,14 +128,12 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
       mbar_expect_tx(&q_full, TILE_BYTES);
       tma_load_4d(smQ, &tm_q, &q_full, 0, qhead, chunk * p.cq + row0, batch);
       for (int J = 0; J < nJ && ok; ++J) {
-        ok = mbar_wait(&k_empty, (J & 1) ^ 1, &abort_flag);
+        const int s = J & 1, ph = (J >> 1) & 1;
+        ok = mbar_wait(&kv_empty[s], ph ^ 1, &abort_flag);
         if (!ok) break;
-        mbar_expect_tx(&k_full, TILE_BYTES);
-        tma_load_4d(smK, &tm_k, &k_full, 0, kvhead, chunk * p.ck + J * 128, batch);
-        ok = mbar_wait(&v_empty, (J & 1) ^ 1, &abort_flag);
-        if (!ok) break;
-        mbar_expect_tx(&v_full, TILE_BYTES);
-        tma_load_4d(smV, &tm_v, &v_full, 0, kvhead, chunk * p.ck + J * 128, batch);
+        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+        tma_load_4d(smK + s * KV_BYTES, &tm_k, &kv_full[s], 0, kvhead, chunk * p.ck + J * TW, batch);
+        tma_load_4d(smV + s * KV_BYTES, &tm_v, &kv_full[s], 0, kvhead, chunk * p.ck + J * TW, batch);
       }
       if (ok && has_state) {
         const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
@@ -152,28 +152,38 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       bool ok = mbar_wait(&q_full, 0, &abort_flag);
-      const uint32_t idesc_s = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
+      const uint32_t idesc_s = umma_idesc(128, TW, Pack2<T>::is_bf16, false, false);
       const uint32_t idesc_v = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
       const uint32_t idesc_g = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
-      const uint32_t q_addr = smem_u32(smQ), k_addr = smem_u32(smK), v_addr = smem_u32(smV);
-      for (int J = 0; J < nJ && ok; ++J) {
-        ok = mbar_wait(&k_full, J & 1, &abort_flag);
-        if (!ok) break;
+      const uint32_t q_addr = smem_u32(smQ);
+      // scores of tile J+1 are issued before the P V product of tile J, so the row threads
+      // always have the next tile waiting (two score buffers, two key/value stages)
+      auto issue_scores = [&](int J) -> bool {
+        const int s = J & 1;
+        if (!mbar_wait(&kv_full[s], (J >> 1) & 1, &abort_flag)) return false;
         tc_fence_after();
+        const uint32_t k_addr = smem_u32(smK + s * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + COL_S, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
+          umma_ss(tmem + COL_S + s * TW, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
                   umma_desc_sw128(k_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(&s_full);
-        umma_commit(&k_empty);
-        ok = mbar_wait(&p_full, J & 1, &abort_flag) && mbar_wait(&v_full, J & 1, &abort_flag);
+        umma_commit(&s_full[s]);
+        return true;
+      };
+      if (ok && nJ > 0) ok = issue_scores(0);
+      for (int J = 0; J < nJ && ok; ++J) {
+        const int s = J & 1;
+        if (J + 1 < nJ) ok = issue_scores(J + 1);
+        if (!ok) break;
+        ok = mbar_wait(&p_full[s], (J >> 1) & 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t v_addr = smem_u32(smV + s * KV_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tmem + COL_ACC, tmem + COL_P + ks * 8, umma_desc_sw128(v_addr + ks * 2048, 8192, 1024), idesc_v,
-                  (J > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&v_empty);
+        for (int ks = 0; ks < TW / 16; ++ks)
+          umma_ts(tmem + COL_ACC, tmem + COL_S + s * TW + ks * 8, umma_desc_sw128(v_addr + ks * 2048, 8192, 1024),
+                  idesc_v, (J > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&kv_empty[s]);
         if (J == nJ - 1) umma_commit(&attn_done);
       }
       if (ok && has_state) {
@@ -223,21 +233,23 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
     bool ok = true;
 
     for (int J = 0; J < nJ; ++J) {
-      const int kp0 = J * 128;
-      {
+      const int kp0 = J * TW;
+      const int sb = J & 1;
+      if (tid < TW) {
         const int kp = kp0 + tid;
-        sm_ak[J & 1][tid] = (gated && kp < p.ck) ? a_chunk[(size_t)kp * p.h] : 0.f;
+        sm_ak[sb][tid] = (gated && kp < p.ck) ? a_chunk[(size_t)kp * p.h] : 0.f;
       }
       named_bar_sync(1, 128);
-      ok = mbar_wait(&s_full, J & 1, &abort_flag);
+      ok = mbar_wait(&s_full[sb], (J >> 1) & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const float* ak = sm_ak[J & 1];
-      const bool need_mask = (kp0 + 127 > qpos) || (kp0 + 127 >= p.ck);
+      const float* ak = sm_ak[sb];
+      const uint32_t col_s = COL_S + sb * TW;
+      const bool need_mask = (kp0 + TW - 1 > qpos) || (kp0 + TW - 1 >= p.ck);
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < TW / 32; ++q4) {
         uint32_t sv[32];
-        tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+        tmem_ld32(tmem + lane_addr + col_s + q4 * 32, sv);
         tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
@@ -256,15 +268,14 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
             pv[u] = w;
           }
           pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
-          const float2 back = Pack2<T>::to_f32(pk[j >> 1]);
-          l_acc += back.x + back.y;
+          l_acc += pv[0] + pv[1];
         }
-        tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
+        tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
+      if (lane == 0) mbar_arrive(&p_full[sb]);
     }
 
     // gated, scaled query row as 32 packed pairs
@@ -416,10 +427,11 @@ extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int 
     uint64_t dk[4] = {(uint64_t)d, (uint64_t)h, tk, (uint64_t)b};
     uint64_t sk[4] = {0, (uint64_t)d * 2, (uint64_t)h * d * 2, tk * h * d * 2};
     uint32_t box[4] = {64, 1, 128, 1};
+    uint32_t box_kv[4] = {64, 1, (uint32_t)TW, 1};
     if ((rc = make_tmap(&tm_q, Q, 2, 4, dq, sq, box, true))) return rc;
     if (has_attn) {
-      if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
-      if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
+      if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box_kv, true))) return rc;
+      if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box_kv, true))) return rc;
     } else {
       tm_k = tm_q;
       tm_v = tm_q;
@@ -438,7 +450,7 @@ extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int 
     tm_ghi = tm_q;
     tm_glo = tm_q;
   }
-  const size_t smem = 1024 + 3 * TILE_BYTES + NS * Z_BYTES + 2 * Z_BYTES;
+  const size_t smem = 1024 + TILE_BYTES + 4 * KV_BYTES + NS * Z_BYTES + 2 * Z_BYTES;
   dim3 grid(p.tiles_per_chunk * n_chunks, hq, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
