@@ -161,6 +161,30 @@ int pr_gate_grad(int b, int t, int h, int hq, int c, const float* da_q, const fl
                  const float* wk, const float* dA_scan, int scan_blocks, const float* dA_gram, int gram_blocks,
                  float* dlog_g, int device, void* stream);
 
+/* Inference (retention/power_retention_maker.py:287-390).  States use the exact layout:
+ * state [b,h,D,d] 16-bit, sum_of_keys [b,h,D] fp32, D = d*(d+1)/2, pair (a<=b) at
+ * a*d - a*(a-1)/2 + (b-a), weight 2 on a != b.
+ *
+ * pr_decode_state: one query token per sequence against the state (query_state of the
+ * reference, retention/_query_state/reference.py:36-96, for tq = 1): Q [b,1,hq,d];
+ * a_last [b,h] = cumulative log gate at the last cached key, or NULL.  Writes partial sums
+ * part_y [b,hq,pr_decode_nsplit(),d] and part_l [b,hq,pr_decode_nsplit()].
+ * pr_decode_finish: attention over the tk cached tokens (K,V [b,tk,h,d], a [b,tk,h]; may be
+ * absent) + the partials (may be absent) -> O [b,1,hq,d].
+ * pr_state_merge: the switch-over of :366-382: new_state = state*exp(a_last) + S, with
+ * S [b,1,h,D2,d] and gram [b,1,h,d,d] from pr_chunk_state over the cached tokens; state and
+ * sum_of_keys may be NULL (first compression). */
+int pr_decode_nsplit(void);
+int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
+                    const float* sum_of_keys, const float* a_last, float scale, float* part_y, float* part_l,
+                    int device, void* stream);
+int pr_decode_finish(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
+                     const float* a, float scale, const float* part_y, const float* part_l, void* O, int device,
+                     void* stream);
+int pr_state_merge(int dtype, int b, int h, int d, const void* state, const float* sum_of_keys, const void* S,
+                   const float* gram, const float* a_last, void* new_state, float* new_sum_of_keys, int device,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -204,7 +204,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         const bool v = qp < p.c;
         sm_aq[st & 1][tid] = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
         sm_dl[st & 1][tid] = v ? p.dl[(tok_base + qp) * p.hq + qh] : 0.f;
-        sm_il[st & 1][tid] = v ? 1.f / fmaxf(p.l[(tok_base + qp) * p.hq + qh], 1e-37f) : 0.f;
+        sm_il[st & 1][tid] = v ? safe_recip(p.l[(tok_base + qp) * p.hq + qh]) : 0.f;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = mbar_wait(&sp_full, st & 1, &abort_flag);

@@ -143,7 +143,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
     const float* a_chunk = gated ? p.a + ((size_t)batch * p.n_chunks * p.c + tok_chunk) * p.h + kvhead : nullptr;
     const float a_i = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
     const float dl_i = row_valid ? p.dl[tok * p.hq + qhead] : 0.f;
-    const float inv_l = row_valid ? 1.f / fmaxf(p.l[tok * p.hq + qhead], 1e-37f) : 0.f;
+    const float inv_l = row_valid ? safe_recip(p.l[tok * p.hq + qhead]) : 0.f;
     const float s2 = p.scale * p.scale;
     float da = 0.f;
     bool ok = true;

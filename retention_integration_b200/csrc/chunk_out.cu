@@ -360,7 +360,7 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
       }
       if (row_valid) {
         const size_t tok = (size_t)batch * p.n_chunks * p.cq + (size_t)chunk * p.cq + row;
-        const float inv = p.normalize ? 1.f / fmaxf(l, 1e-37f) : 1.f;
+        const float inv = p.normalize ? safe_recip(l) : 1.f;
         uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.O) + (tok * p.hq + qhead) * HD);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {

@@ -1,0 +1,347 @@
+// Inference kernels (the reference's _power_retention_inference,
+// retention/power_retention_maker.py:287-390, for a single query token per sequence):
+//
+//   pr_decode_state : reads the recurrent state once.  For every (batch, kv head) the
+//                     state S [D, 64] and sum_of_keys s [D] (exact layout, D = C(d+1,2)) are
+//                     contracted with phi(q~) of the group's query heads, q~ = s*q*exp(a_last/2):
+//                     y = sum_D phi(q~)[D] S[D,:],  l = sum_D phi(q~)[D] s[D].
+//                     HBM bound: 128-bit loads, each 128-byte state row read by 8 threads,
+//                     D split over several CTAs; partial sums go to a small workspace.
+//   pr_decode_finish: adds the attention over the tokens cached since the last
+//                     switch-over, sums the partials, normalises and writes the output.
+//   pr_state_merge  : prefill-to-state switch-over: new_state = state*exp(a_last) + S_chunk,
+//                     converting the chunk state from the kernels' internal layout to the
+//                     exact layout on the fly; same for sum_of_keys from the Gram matrix.
+#include "host.cuh"
+#include "layout.cuh"
+#include "sm100.cuh"
+
+namespace pr {
+
+namespace dec {
+constexpr int HD = 64;
+constexpr int DEX = HD * (HD + 1) / 2;  // 2080
+constexpr int THREADS = 256;
+constexpr int ROWS_PER_ITER = THREADS / 8;  // 32 state rows per iteration
+constexpr int RG = 4;                       // query heads handled per CTA
+}  // namespace dec
+
+// exact-layout row -> (a, b), a <= b
+__device__ __forceinline__ void exact_decode(int D, int* a, int* b) {
+  int aa = 0, off = 0;
+  while (off + (dec::HD - aa) <= D) {
+    off += dec::HD - aa;
+    ++aa;
+  }
+  *a = aa;
+  *b = aa + (D - off);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(dec::THREADS)
+decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const float* __restrict__ sok,
+                    const float* __restrict__ a_last, float scale, int h, int hq, int nsplit,
+                    float* __restrict__ part_y, float* __restrict__ part_l) {
+  using namespace dec;
+  __shared__ float sq[RG][HD];
+  __shared__ float red_y[THREADS / 32][RG][HD];
+  __shared__ float red_l[THREADS / 32][RG];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int bh = blockIdx.x, split = blockIdx.y, grp = blockIdx.z;
+  const int batch = bh / h, head = bh % h;
+  const int ratio = hq / h;
+  const int r0 = grp * RG, nr = min(RG, ratio - r0);
+
+  // gated, scaled, rounded queries of this group (as the reference rounds Q*exp(.) to Q's dtype)
+  float f = scale;
+  if (a_last != nullptr) f *= __expf(0.5f * a_last[bh]);
+  for (int i = tid; i < nr * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    const float q = float(Q[((size_t)batch * hq + head * ratio + r0 + r) * HD + e]);
+    sq[r][e] = float(T(q * f));
+  }
+  __syncthreads();
+
+  const int rows_per_split = (DEX + nsplit - 1) / nsplit;
+  const int d_begin = split * rows_per_split, d_end = min(DEX, d_begin + rows_per_split);
+  const int sub = tid & 7;
+  int D = d_begin + (tid >> 3);
+  int a = 0, b = 0;
+  if (D < DEX) exact_decode(D, &a, &b);
+
+  float acc[RG][8];
+  float accl[RG];
+#pragma unroll
+  for (int r = 0; r < RG; ++r) {
+    accl[r] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[r][k] = 0.f;
+  }
+  const T* sbase = state + (size_t)bh * DEX * HD;
+  const float* kbase = sok + (size_t)bh * DEX;
+  for (; D < d_end; D += ROWS_PER_ITER) {
+    const uint4 v = *reinterpret_cast<const uint4*>(sbase + (size_t)D * HD + sub * 8);
+    const float sk = kbase[D];
+    float x[8];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 p2 = Pack2<T>::to_f32(w[k]);
+      x[2 * k] = p2.x;
+      x[2 * k + 1] = p2.y;
+    }
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+      if (r < nr) {
+        const float phi = float(T(sq[r][a] * sq[r][b]));  // product rounded to the input dtype
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(phi, x[k], acc[r][k]);
+        accl[r] = fmaf(phi, sk, accl[r]);
+      }
+    }
+    // advance (a, b) by ROWS_PER_ITER rows of the triangle
+    b += ROWS_PER_ITER;
+    while (b >= HD && a < HD) {
+      b = b - HD + a + 1;
+      ++a;
+    }
+  }
+  // reduce the 4 rows a warp covers (lanes with equal sub), then the 8 warps
+#pragma unroll
+  for (int r = 0; r < RG; ++r) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float t = acc[r][k];
+      t += __shfl_xor_sync(0xffffffffu, t, 8);
+      t += __shfl_xor_sync(0xffffffffu, t, 16);
+      acc[r][k] = t;
+    }
+    float t = accl[r];  // every lane of a row holds the same l term: count it once (sub == 0)
+    t = (sub == 0) ? t : 0.f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+    accl[r] = t;
+  }
+  if (lane < 8) {
+#pragma unroll
+    for (int r = 0; r < RG; ++r)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) red_y[warp][r][lane * 8 + k] = acc[r][k];
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < RG; ++r) red_l[warp][r] = accl[r];
+  }
+  __syncthreads();
+  for (int i = tid; i < nr * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) t += red_y[w][r][e];
+    part_y[(((size_t)batch * hq + head * ratio + r0 + r) * nsplit + split) * HD + e] = t;
+  }
+  if (tid < nr) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) t += red_l[w][tid];
+    part_l[((size_t)batch * hq + head * ratio + r0 + tid) * nsplit + split] = t;
+  }
+}
+
+// One CTA per (batch, query head): attention over the tk cached tokens + merge + normalise.
+template <typename T>
+__global__ void __launch_bounds__(128)
+decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
+                     const float* __restrict__ a, float scale, int tk, int h, int hq, int nsplit,
+                     const float* __restrict__ part_y, const float* __restrict__ part_l, T* __restrict__ O) {
+  constexpr int HD = dec::HD;
+  __shared__ float sq[HD];
+  __shared__ float red[4][HD + 1];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int batch = blockIdx.x / hq, qh = blockIdx.x % hq;
+  const int kvh = qh / (hq / h);
+  if (tid < HD) sq[tid] = float(Q[((size_t)batch * hq + qh) * HD + tid]);
+  __syncthreads();
+  float y[HD];
+#pragma unroll
+  for (int e = 0; e < HD; ++e) y[e] = 0.f;
+  float l = 0.f;
+  if (K != nullptr && tk > 0) {
+    const float a_q = a ? a[((size_t)batch * tk + tk - 1) * h + kvh] : 0.f;
+    const float s2 = scale * scale;
+    for (int j = tid; j < tk; j += 128) {
+      const uint4* kr = reinterpret_cast<const uint4*>(K + (((size_t)batch * tk + j) * h + kvh) * HD);
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = kr[c];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 p2 = Pack2<T>::to_f32(w[k]);
+          s = fmaf(p2.x, sq[c * 8 + 2 * k], s);
+          s = fmaf(p2.y, sq[c * 8 + 2 * k + 1], s);
+        }
+      }
+      float wgt = s2 * s * s;
+      if (a) wgt *= __expf(a_q - a[((size_t)batch * tk + j) * h + kvh]);
+      l += wgt;
+      const uint4* vr = reinterpret_cast<const uint4*>(V + (((size_t)batch * tk + j) * h + kvh) * HD);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = vr[c];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 p2 = Pack2<T>::to_f32(w[k]);
+          y[c * 8 + 2 * k] = fmaf(wgt, p2.x, y[c * 8 + 2 * k]);
+          y[c * 8 + 2 * k + 1] = fmaf(wgt, p2.y, y[c * 8 + 2 * k + 1]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < HD; ++e) {
+    float t = y[e];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+    if (lane == 0) red[warp][e] = t;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+  if (lane == 0) red[warp][HD] = l;
+  __syncthreads();
+  if (tid < HD) {
+    float yt = red[0][tid] + red[1][tid] + red[2][tid] + red[3][tid];
+    float lt = red[0][HD] + red[1][HD] + red[2][HD] + red[3][HD];
+    if (part_y != nullptr) {
+      const size_t base = ((size_t)batch * hq + qh) * nsplit;
+      for (int sp = 0; sp < nsplit; ++sp) {
+        yt += part_y[(base + sp) * HD + tid];
+        lt += part_l[base + sp];
+      }
+    }
+    O[((size_t)batch * hq + qh) * HD + tid] = T(yt * safe_recip(lt));
+  }
+}
+
+// new_state (exact layout) = decay * state + S (internal layout); new_sok = decay * sok + w * gram.
+template <typename T>
+__global__ void state_merge_kernel(const T* __restrict__ state, const float* __restrict__ sok,
+                                   const T* __restrict__ S, const float* __restrict__ gram,
+                                   const float* __restrict__ a_last, T* __restrict__ new_state,
+                                   float* __restrict__ new_sok, int bh_total) {
+  constexpr int HD = dec::HD, DEX = dec::DEX, D2 = t2_dim(HD);
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 elements
+  const size_t total = (size_t)bh_total * DEX * 8;
+  if (gid >= total) return;
+  const int sub = (int)(gid & 7);
+  const size_t rowg = gid >> 3;
+  const int D = (int)(rowg % DEX);
+  const int bh = (int)(rowg / DEX);
+  int a, b;
+  exact_decode(D, &a, &b);
+  const int row_t2 = t2_row_offset(HD, a) + (b - 2 * (a >> 1));
+  const float decay = (state != nullptr) ? (a_last ? __expf(a_last[bh]) : 1.f) : 0.f;
+  const uint4 sv = *reinterpret_cast<const uint4*>(S + ((size_t)bh * D2 + row_t2) * HD + sub * 8);
+  uint4 ov = make_uint4(0, 0, 0, 0);
+  if (state != nullptr) ov = *reinterpret_cast<const uint4*>(state + ((size_t)bh * DEX + D) * HD + sub * 8);
+  const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w}, ow[4] = {ov.x, ov.y, ov.z, ov.w};
+  uint32_t rw[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 s2 = Pack2<T>::to_f32(sw[k]), o2 = Pack2<T>::to_f32(ow[k]);
+    // the reference rounds state*decay to the state dtype before adding (:374-382)
+    const float2 od = Pack2<T>::to_f32(Pack2<T>::from_f32(o2.x * decay, o2.y * decay));
+    rw[k] = Pack2<T>::from_f32(od.x + s2.x, od.y + s2.y);
+  }
+  *reinterpret_cast<uint4*>(new_state + ((size_t)bh * DEX + D) * HD + sub * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+  if (sub == 0) {
+    const float g = gram[((size_t)bh * HD + a) * HD + b] * (a == b ? 1.f : 2.f);
+    new_sok[(size_t)bh * DEX + D] = (sok != nullptr ? sok[(size_t)bh * DEX + D] * decay : 0.f) + g;
+  }
+}
+
+}  // namespace pr
+
+extern "C" int pr_decode_nsplit(void) { return 5; }
+
+extern "C" int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
+                               const float* sum_of_keys, const float* a_last, float scale, float* part_y,
+                               float* part_l, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0, PR_ERR_BAD_ARG, "bad sizes b=%d h=%d hq=%d", b, h, hq);
+  PR_REQUIRE(Q && state && sum_of_keys && part_y && part_l && aligned16(state) && aligned16(Q), PR_ERR_BAD_ARG,
+             "null or misaligned pointer");
+  PR_CUDA(cudaSetDevice(device));
+  const int nsplit = pr_decode_nsplit();
+  dim3 grid(b * h, nsplit, (hq / h + dec::RG - 1) / dec::RG);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    decode_state_kernel<__nv_bfloat16><<<grid, dec::THREADS, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(state), sum_of_keys, a_last, scale, h,
+        hq, nsplit, part_y, part_l);
+  else if (dtype == PR_FP16)
+    decode_state_kernel<__half><<<grid, dec::THREADS, 0, s>>>(static_cast<const __half*>(Q),
+                                                              static_cast<const __half*>(state), sum_of_keys, a_last,
+                                                              scale, h, hq, nsplit, part_y, part_l);
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+extern "C" int pr_decode_finish(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K,
+                                const void* V, const float* a, float scale, const float* part_y, const float* part_l,
+                                void* O, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0 && tk >= 0, PR_ERR_BAD_ARG, "bad sizes");
+  PR_REQUIRE(Q && O && aligned16(K) && aligned16(V), PR_ERR_BAD_ARG, "null or misaligned pointer");
+  PR_REQUIRE((part_y == nullptr) == (part_l == nullptr), PR_ERR_BAD_ARG, "partials must come together");
+  PR_REQUIRE(part_y != nullptr || (K != nullptr && tk > 0), PR_ERR_BAD_ARG, "neither a state nor cached tokens");
+  PR_CUDA(cudaSetDevice(device));
+  const int nsplit = pr_decode_nsplit();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    decode_finish_kernel<__nv_bfloat16><<<b * hq, 128, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
+        static_cast<const __nv_bfloat16*>(V), a, scale, tk, h, hq, nsplit, part_y, part_l,
+        static_cast<__nv_bfloat16*>(O));
+  else if (dtype == PR_FP16)
+    decode_finish_kernel<__half><<<b * hq, 128, 0, s>>>(static_cast<const __half*>(Q), static_cast<const __half*>(K),
+                                                        static_cast<const __half*>(V), a, scale, tk, h, hq, nsplit,
+                                                        part_y, part_l, static_cast<__half*>(O));
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+extern "C" int pr_state_merge(int dtype, int b, int h, int d, const void* state, const float* sum_of_keys,
+                              const void* S, const float* gram, const float* a_last, void* new_state,
+                              float* new_sum_of_keys, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && h > 0, PR_ERR_BAD_ARG, "bad sizes");
+  PR_REQUIRE(S && gram && new_state && new_sum_of_keys && aligned16(S) && aligned16(new_state) && aligned16(state),
+             PR_ERR_BAD_ARG, "null or misaligned pointer");
+  PR_REQUIRE((state == nullptr) == (sum_of_keys == nullptr), PR_ERR_BAD_ARG, "state and sum_of_keys come together");
+  PR_CUDA(cudaSetDevice(device));
+  const size_t threads = (size_t)b * h * dec::DEX * 8;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    state_merge_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(state), sum_of_keys, static_cast<const __nv_bfloat16*>(S), gram, a_last,
+        static_cast<__nv_bfloat16*>(new_state), new_sum_of_keys, b * h);
+  else if (dtype == PR_FP16)
+    state_merge_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(state), sum_of_keys,
+                                                    static_cast<const __half*>(S), gram, a_last,
+                                                    static_cast<__half*>(new_state), new_sum_of_keys, b * h);
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}

@@ -133,7 +133,7 @@ __global__ void dout_prep_kernel(const T* __restrict__ O, const T* __restrict__ 
   if (active) {
     const uint4 o = *reinterpret_cast<const uint4*>(O + row * d + sub * 8);
     g = *reinterpret_cast<const uint4*>(dO + row * d + sub * 8);
-    inv = 1.f / fmaxf(l[row], 1e-37f);
+    inv = safe_recip(l[row]);
     const uint32_t ow[4] = {o.x, o.y, o.z, o.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {

@@ -233,6 +233,12 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// 1 / l guarded against an exact zero only.  Row sums of real states are positive, but a
+// caller may hand over any state, and the reference divides by negative sums too.
+__device__ __forceinline__ float safe_recip(float l) {
+  return 1.f / (fabsf(l) < 1e-37f ? copysignf(1e-37f, l) : l);
+}
+
 // ------------------------------------------------------------------ packing
 template <typename T>
 struct Pack2;

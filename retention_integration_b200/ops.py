@@ -248,3 +248,38 @@ def gate_grad(da_q, gq, da_k, wk, dA_scan, dA_gram, c: int):
                              ptr(wk), ptr(dA_scan), c_int(blocks), ptr(dA_gram), c_int(gblocks), ptr(out), c_int(_dev(da_q)),
                              stream_ptr(da_q.device))
     return out
+
+
+def decode_state(Q, state, sum_of_keys, a_last, scale: float):
+    """Q [b,1,hq,d]; state [b,h,D,d]; sum_of_keys [b,h,D]; a_last [b,h] or None -> partial sums."""
+    b, _, hq, d = Q.shape
+    h = state.shape[1]
+    ns = lib().pr_decode_nsplit()
+    part_y = torch.empty(b, hq, ns, d, device=Q.device, dtype=torch.float32)
+    part_l = torch.empty(b, hq, ns, device=Q.device, dtype=torch.float32)
+    _call("pr_decode_state", c_int(dtype_code(Q.dtype)), c_int(b), c_int(h), c_int(hq), c_int(d), ptr(Q), ptr(state),
+          ptr(sum_of_keys), ptr(a_last), c_float(scale), ptr(part_y), ptr(part_l), c_int(_dev(Q)),
+          stream_ptr(Q.device))
+    return part_y, part_l
+
+
+def decode_finish(Q, K, V, a, scale: float, part_y, part_l, h: int):
+    """Attention over the cached tokens + state partials -> O [b,1,hq,d]."""
+    b, _, hq, d = Q.shape
+    tk = K.shape[1] if K is not None else 0
+    O = torch.empty_like(Q)
+    _call("pr_decode_finish", c_int(dtype_code(Q.dtype)), c_int(b), c_int(tk), c_int(h), c_int(hq), c_int(d), ptr(Q),
+          ptr(K), ptr(V), ptr(a), c_float(scale), ptr(part_y), ptr(part_l), ptr(O), c_int(_dev(Q)),
+          stream_ptr(Q.device))
+    return O
+
+
+def state_merge(state, sum_of_keys, S, gram, a_last):
+    """new_state = state*exp(a_last) + S (internal -> exact layout); S [b,1,h,D2,d], gram [b,1,h,d,d]."""
+    b, _, h, _, d = S.shape
+    D = d * (d + 1) // 2
+    new_state = torch.empty(b, h, D, d, device=S.device, dtype=S.dtype)
+    new_sok = torch.empty(b, h, D, device=S.device, dtype=torch.float32)
+    _call("pr_state_merge", c_int(dtype_code(S.dtype)), c_int(b), c_int(h), c_int(d), ptr(state), ptr(sum_of_keys),
+          ptr(S), ptr(gram), ptr(a_last), ptr(new_state), ptr(new_sok), c_int(_dev(S)), stream_ptr(S.device))
+    return new_state, new_sok

@@ -147,3 +147,76 @@ def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=
     else:
         out = _ChunkedRetention.apply(Q, K, V, log_G, int(chunk_size), float(scale))
     return out[:, :t] if t_pad else out
+
+
+def power_retention_inference(Q, K, V, log_G=None, initial_state=None, sum_of_keys=None, deg=2, scale=None,
+                              switch_over_seq_len=512):
+    """Decode / prefill-to-state step with the reference's signature and semantics
+    (retention/power_retention_maker.py:287-390, the variant with an explicit sum_of_keys).
+
+    Q [b,tq,hq,d]; K, V [b,tk,h,d] or None (the tokens cached since the last switch-over);
+    log_G [b,tk,h] or None; initial_state [b,h,D,d], sum_of_keys [b,h,D] fp32 or None.
+    Returns (Y [b,tq,hq,d], state, sum_of_keys); when tk >= switch_over_seq_len the cache is
+    compressed into a new state, otherwise the very same state objects come back.
+
+    States use the exact expansion layout, D = d*(d+1)/2 (2080 at d = 64); the reference's
+    padded layout (2560) converts with layout.to_reference_layout / from_reference_layout.
+    """
+    has_cache = K is not None and V is not None
+    assert has_cache or initial_state is not None, "initial_state or cache must be provided for inference"
+    assert (initial_state is None) == (sum_of_keys is None), "initial_state and sum_of_keys come together"
+    if deg != 2:
+        raise PRError(f"deg={deg}: the state kernels implement deg=2")
+    if not Q.is_cuda:
+        raise PRError("tensors must be CUDA tensors: this package has no CPU path")
+    b, tq, hq, d = Q.shape
+    if d not in _SUPPORTED_D:
+        raise PRError(f"head dim {d} unsupported by this build (supported: {_SUPPORTED_D})")
+    if has_cache:
+        assert Q.dtype == K.dtype == V.dtype, "dtypes of inputs must match"
+        assert K.shape[1] == V.shape[1], "key and value must have the same seq_len"
+        tk, h = K.shape[1], K.shape[2]
+        K, V = K.contiguous(), V.contiguous()
+    else:
+        tk, h = 0, initial_state.shape[1]
+    assert hq % h == 0
+    if initial_state is not None:
+        D = layout.exact_dim(d)
+        assert initial_state.shape == (b, h, D, d), f"state must be [b,h,{D},{d}] (exact layout)"
+        assert sum_of_keys.shape == (b, h, D) and sum_of_keys.dtype == torch.float32
+    Q = Q.contiguous()
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    gated = has_cache and log_G is not None
+    a = None
+    if gated:
+        assert log_G.shape == K.shape[:3]
+        a, _, _ = ops.gate_prep(K, log_G.to(torch.float32).contiguous(), tk, query_side=False, want_xt=False)
+    a_last = a[:, -1, :].contiguous() if a is not None else None
+
+    # ---- read-out
+    if initial_state is None:
+        Y, _ = ops.chunk_out(Q, K, V, a, None, None, None, 1, tq, tk, 1, scale, want_l=False)
+    elif tq == 1:
+        part_y, part_l = ops.decode_state(Q, initial_state.contiguous(), sum_of_keys.contiguous(), a_last, scale)
+        Y = ops.decode_finish(Q, K if tk > 0 else None, V if tk > 0 else None, a, scale, part_y, part_l, h)
+    else:
+        # several query tokens against a state: the tensor-core path, state converted to its layout
+        Z = layout.exact_to_t2(initial_state, d, dim=-2).unsqueeze(1).contiguous()
+        zg = layout.exact_sum_of_keys_to_gram(sum_of_keys, d)
+        zhi = zg.to(Q.dtype)
+        zlo = (zg - zhi.float()).to(Q.dtype)
+        if tk > 0:
+            Y, _ = ops.chunk_out(Q, K, V, a, Z, zhi.unsqueeze(1).contiguous(), zlo.unsqueeze(1).contiguous(), 1, tq,
+                                 tk, 0, scale, q_gate_last=True, want_l=False)
+        else:
+            Y, _ = ops.chunk_out(Q, None, None, None, Z, zhi.unsqueeze(1).contiguous(), zlo.unsqueeze(1).contiguous(),
+                                 1, tq, tq, 0, scale, want_l=False)
+
+    # ---- optionally compress the cache into the state
+    if switch_over_seq_len is not None and tk >= switch_over_seq_len:
+        lg = log_G.to(torch.float32).contiguous() if gated else None
+        _, _, KT = ops.gate_prep(K, lg, tk, query_side=False, want_gates=False)
+        S, gram = ops.chunk_state(KT, None, V, tk, h, key_weights=True, want_gram=True)
+        new_state, new_sok = ops.state_merge(initial_state, sum_of_keys, S, gram, a_last)
+        return Y, new_state, new_sok
+    return Y, initial_state, sum_of_keys

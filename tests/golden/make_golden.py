@@ -110,17 +110,26 @@ def inference_cases(ref):
     Dref = {32: 768, 64: 2560}
     for name, seed, b, tq, tk, h, r, d, with_state, sw in [
         ("infer_decode_state", 11, 1, 1, 48, 1, 1, 64, True, 512),
-        ("infer_switch_over", 12, 1, 1, 64, 2, 2, 32, True, 64),
-        ("infer_no_state_switch", 13, 1, 5, 64, 2, 1, 32, False, 64),
-        ("infer_state_only", 14, 1, 1, 0, 2, 4, 32, True, 512),
+        ("infer_switch_over", 12, 1, 1, 64, 1, 2, 64, True, 64),
+        ("infer_no_state_switch", 13, 1, 5, 64, 2, 1, 64, False, 64),
+        ("infer_state_only", 14, 1, 1, 0, 1, 4, 64, True, 512),
+        ("infer_prefill_with_state", 15, 1, 63, 128, 1, 2, 64, True, 512),
     ]:
         g = torch.Generator().manual_seed(seed)
         Q = rb(torch.randn(b, tq, h * r, d, generator=g) / math.sqrt(d))
         K = rb(torch.randn(b, tk, h, d, generator=g) / math.sqrt(d)) if tk else None
         V = rb(torch.randn(b, tk, h, d, generator=g) / math.sqrt(d)) if tk else None
         log_G = F.logsigmoid(2.0 + torch.randn(b, tk, h, generator=g)) if tk else None
-        state = rb(torch.randn(b, h, Dref[d], d, generator=g)) if with_state else None
-        sk = torch.randn(b, h, Dref[d], generator=g).abs() + 1.0 if with_state else None
+        state = sk = None
+        if with_state:
+            # a realistic state: the reference's own update_state over 96 earlier tokens, so that the
+            # normaliser phi(q).sum_of_keys is a sum of squares (a random state makes it cancel)
+            upd = sys.modules["retention._update_state.reference"].update_state
+            K0 = rb(torch.randn(b, 96, h, d, generator=g) / math.sqrt(d))
+            V0 = rb(torch.randn(b, 96, h, d, generator=g) / math.sqrt(d))
+            state, sk = upd(K0, V0, 2)
+            state = rb(state)
+            assert state.shape == (b, h, Dref[d], d)
         Y, ns, nk = ref.power_retention_inference(Q, K, V, log_G, state, sk, deg=2, switch_over_seq_len=sw)
         switched = tk >= sw
         save(name, Q__bf16=bits(Q), K__bf16=bits(K), V__bf16=bits(V), log_G=npy(log_G), state__bf16=bits(state),

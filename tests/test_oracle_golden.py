@@ -62,7 +62,7 @@ def test_operators_match_reference():
 
 
 @pytest.mark.parametrize("name", ["infer_decode_state", "infer_switch_over", "infer_no_state_switch",
-                                  "infer_state_only"])
+                                  "infer_state_only", "infer_prefill_with_state"])
 def test_inference_matches_reference(name):
     g = load(name)
     b, tq, tk, h, r, d, with_state, sw = g["meta"]
