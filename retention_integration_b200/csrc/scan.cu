@@ -60,7 +60,7 @@ scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restr
   }
   const size_t in_stride = (size_t)h * E;
   const T* xin = X + ((size_t)batch * n * h + head) * E + e0;
-  T* yout = Y + ((size_t)batch * n_out * h + head) * E + e0;
+  T* yout = Y ? Y + ((size_t)batch * n_out * h + head) * E + e0 : nullptr;
   const float* Ap = A + (size_t)batch * n * h + head;
   for (int m0 = 0; m0 < n; m0 += kScanUnroll) {
     uint4 xv[kScanUnroll];
@@ -75,7 +75,7 @@ scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restr
 #pragma unroll
     for (int u = 0; u < kScanUnroll; ++u) {
       if (m0 + u < n) {
-        *reinterpret_cast<uint4*>(yout + (size_t)(m0 + u) * in_stride) = pack8<T>(run);
+        if (yout) *reinterpret_cast<uint4*>(yout + (size_t)(m0 + u) * in_stride) = pack8<T>(run);
         float x[8];
         unpack8<T>(xv[u], x);
 #pragma unroll
@@ -83,7 +83,7 @@ scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restr
       }
     }
   }
-  if (n_out > n) *reinterpret_cast<uint4*>(yout + (size_t)n * in_stride) = pack8<T>(run);
+  if (yout && n_out > n) *reinterpret_cast<uint4*>(yout + (size_t)n * in_stride) = pack8<T>(run);
   if (carry_out != nullptr) {
     float4* co = reinterpret_cast<float4*>(carry_out + ((size_t)batch * h + head) * E + e0);
     co[0] = make_float4(run[0], run[1], run[2], run[3]);
@@ -122,7 +122,8 @@ scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict
   const size_t stride = (size_t)h * E;
   const size_t base = ((size_t)batch * n * h + head) * E + e0;
   const float* Ap = A + (size_t)batch * n * h + head;
-  float* part = dA_part + (((size_t)batch * h + head) * gridDim.x + blockIdx.x) * n;
+  const bool reduce_only = (dX == nullptr);
+  float* part = reduce_only ? nullptr : dA_part + (((size_t)batch * h + head) * gridDim.x + blockIdx.x) * n;
   for (int m0 = n - 1; m0 >= 0; m0 -= kScanUnroll) {
     uint4 gv[kScanUnroll], yv[kScanUnroll];
     float g[kScanUnroll];
@@ -131,7 +132,7 @@ scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict
       const int m = m0 - u;
       if (m >= 0 && active) {
         gv[u] = *reinterpret_cast<const uint4*>(dY + base + (size_t)m * stride);
-        yv[u] = *reinterpret_cast<const uint4*>(Y + base + (size_t)m * stride);
+        if (!reduce_only) yv[u] = *reinterpret_cast<const uint4*>(Y + base + (size_t)m * stride);
       }
       if (m >= 0) g[u] = __expf(Ap[(size_t)m * h]);
     }
@@ -139,6 +140,16 @@ scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict
     for (int u = 0; u < kScanUnroll; ++u) {
       const int m = m0 - u;
       if (m < 0) continue;
+      if (reduce_only) {
+        // only the carry leaving this block of chunks is wanted
+        if (active) {
+          float dy[8];
+          unpack8<T>(gv[u], dy);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) run[k] = fmaf(run[k], g[u], dy[k]);
+        }
+        continue;
+      }
       float dot = 0.f;
       if (active) {
         float o[8], y[8], dy[8];
@@ -255,7 +266,8 @@ extern "C" int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long 
              h, E);
   PR_REQUIRE(n_out == n || n_out == n + 1, PR_ERR_BAD_ARG, "n_out=%d must be n or n+1", n_out);
   PR_REQUIRE(n_out == n || X != Y, PR_ERR_BAD_ARG, "in-place scan needs n_out == n");
-  PR_REQUIRE(X && Y && A && aligned16(X) && aligned16(Y), PR_ERR_BAD_ARG, "null or misaligned pointer");
+  PR_REQUIRE(X && A && aligned16(X) && aligned16(Y), PR_ERR_BAD_ARG, "null or misaligned pointer");
+  PR_REQUIRE(Y != nullptr || carry_out != nullptr, PR_ERR_BAD_ARG, "neither an output nor a carry was requested");
   PR_REQUIRE(h <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "h and b must be <= 65535");
   PR_CUDA(cudaSetDevice(device));
   dim3 grid((unsigned)((E / 8 + kScanThreads - 1) / kScanThreads), h, b);
@@ -281,8 +293,10 @@ extern "C" int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, con
   using namespace pr;
   PR_REQUIRE(b > 0 && n > 0 && h > 0 && E > 0 && E % 8 == 0, PR_ERR_BAD_ARG, "bad sizes b=%d n=%d h=%d E=%lld", b, n,
              h, E);
-  PR_REQUIRE(dY && Y && dX && A && dA_part && aligned16(dY) && aligned16(Y) && aligned16(dX), PR_ERR_BAD_ARG,
+  PR_REQUIRE(dY && A && aligned16(dY) && aligned16(Y) && aligned16(dX), PR_ERR_BAD_ARG,
              "null or misaligned pointer");
+  PR_REQUIRE((dX == nullptr && carry_out != nullptr) || (dX != nullptr && Y != nullptr && dA_part != nullptr),
+             PR_ERR_BAD_ARG, "give dX, Y and dA_part together, or none of them and a carry_out");
   PR_REQUIRE(!row_weights || (row_len > 0 && row_len % 8 == 0), PR_ERR_BAD_ARG, "row_len %d", row_len);
   PR_CUDA(cudaSetDevice(device));
   dim3 grid((unsigned)pr_discumsum_bwd_blocks(E), h, b);

@@ -125,18 +125,34 @@ def chunk_state(xt: torch.Tensor, xts, v: torch.Tensor, c: int, nh: int, key_wei
     return out, gram
 
 
-def discumsum_fwd(X: torch.Tensor, A: torch.Tensor, inplace: bool = False, carry_in=None, want_carry: bool = False):
+def discumsum_fwd(X: torch.Tensor, A: torch.Tensor, inplace: bool = False, carry_in=None, want_carry: bool = False,
+                  carry_only: bool = False):
     """X [b,n,h,...] 16-bit, A [b,n,h] fp32.  inplace: X becomes the states entering each chunk
-    (n entries); otherwise returns Y [b,n+1,h,...] like the reference's discumsum."""
+    (n entries); otherwise returns Y [b,n+1,h,...] like the reference's discumsum.
+    carry_only: nothing is written but the fp32 carry leaving the last chunk (returned alone)."""
     b, n, h = X.shape[:3]
     E = X[0, 0, 0].numel()
-    n_out = n if inplace else n + 1
-    Y = X if inplace else torch.empty(b, n_out, *X.shape[2:], device=X.device, dtype=X.dtype)
+    n_out = n if (inplace or carry_only) else n + 1
+    Y = None if carry_only else (X if inplace else torch.empty(b, n_out, *X.shape[2:], device=X.device, dtype=X.dtype))
+    want_carry = want_carry or carry_only
     carry_out = torch.empty(b, h, E, device=X.device, dtype=torch.float32) if want_carry else None
     _call("pr_discumsum_fwd", c_int(dtype_code(X.dtype)), c_int(b), c_int(n), c_int(n_out), c_int(h),
                                  c_longlong(E), ptr(X), ptr(Y), ptr(A), ptr(carry_in), ptr(carry_out),
                                  c_int(_dev(X)), stream_ptr(X.device))
+    if carry_only:
+        return carry_out
     return (Y, carry_out) if want_carry else Y
+
+
+def discumsum_bwd_carry(dY: torch.Tensor, A: torch.Tensor, carry_in=None):
+    """Reverse scan reduced to its carry: G[0] for G[m] = dY[m] + exp(A[m]) G[m+1], G[n] = carry_in."""
+    b, n, h = dY.shape[:3]
+    E = dY[0, 0, 0].numel()
+    carry_out = torch.empty(b, h, E, device=dY.device, dtype=torch.float32)
+    _call("pr_discumsum_bwd", c_int(dtype_code(dY.dtype)), c_int(b), c_int(n), c_int(h), c_longlong(E), ptr(dY),
+          ptr(None), ptr(None), ptr(A), ptr(carry_in), ptr(carry_out), ptr(None), c_int(0), c_int(0),
+          c_int(_dev(dY)), stream_ptr(dY.device))
+    return carry_out
 
 
 def discumsum_bwd(dY: torch.Tensor, Y: torch.Tensor, A: torch.Tensor, row_len: int = 0, row_weights: bool = False,
