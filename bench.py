@@ -152,6 +152,79 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args):
+    """Inference workload: b=16, h=32, d=64 bf16 gated; a 2048-token prefill compressed into the
+    state (switch_over 1024), then 512 single-token steps whose cache grows from 1 to 512 tokens.
+    Reports decode tokens/s and the achieved HBM bandwidth of the state read."""
+    import retention_integration_b200 as prb
+    from retention_integration_b200 import _lib, ops
+
+    dev = torch.device("cuda", 0)
+    b, h, d, t0, steps = 16, 32, 64, 2048, 512
+    g = torch.Generator().manual_seed(0)
+    mk = lambda *s: torch.randn(*s, generator=g).bfloat16().to(dev)
+    Kp, Vp, qp = mk(b, t0, h, d), mk(b, t0, h, d), mk(b, 1, h, d)
+    lgp = F.logsigmoid(torch.randn(b, t0, h, generator=g)).to(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    prb.power_retention_inference(qp, Kp, Vp, lgp, switch_over_seq_len=1024)  # warm-up
+    torch.cuda.synchronize()
+    e0.record()
+    _, state, sk = prb.power_retention_inference(qp, Kp, Vp, lgp, switch_over_seq_len=1024)
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1)
+    Kc, Vc, Qs = mk(b, steps, h, d), mk(b, steps, h, d), mk(b, steps, h, d)
+    lgc = F.logsigmoid(torch.randn(b, steps, h, generator=g)).to(dev)
+
+    def decode_all():
+        for i in range(steps):
+            prb.power_retention_inference(Qs[:, i:i + 1], Kc[:, :i + 1], Vc[:, :i + 1], lgc[:, :i + 1], state, sk,
+                                          switch_over_seq_len=1024)
+
+    decode_all()
+    torch.cuda.synchronize()
+    ops.launch_log.reset(timing=True)
+    e0.record()
+    decode_all()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    kern = ops.launch_log.summary()
+    launches = ops.launch_log.count
+    ops.launch_log.reset()
+    # the state read timed alone, launches queued back to back (inside a decode step the GPU
+    # waits for the host between launches, so per-launch events there include that wait)
+    qd = Qs[:, :1].contiguous()
+    ops.decode_state(qd, state, sk, None, 0.125)
+    torch.cuda.synchronize()
+    n_state = 50
+    e0.record()
+    for _ in range(n_state):
+        ops.decode_state(qd, state, sk, None, 0.125)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_state = e0.elapsed_time(e1)
+    state_bytes = state.numel() * 2 + sk.numel() * 4
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    peak = peaks.get("hbm_gbs") or 6650.0
+    achieved = state_bytes / (ms_state / n_state * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "decode_tokens_per_sec", "value": b * steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "ms_per_step": ms / steps, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "power_retention_inference decode b16 h32 d64 gated, state [16,32,2080,64], cache 1..512"},
+        "prefill_to_state_ms": prefill_ms, "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "kernel": "pr_decode_state", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
+                     "traffic": None},
+        "kernels": {k: {"launches": n, "ms_total": t} for k, (n, t) in kern.items()},
+        "device_status": _lib.device_status(0)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -160,6 +233,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--t", type=int, default=CFG["t"], help="sequence length override (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="train", choices=["train", "decode"])
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -168,6 +242,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "decode":
+        run_decode(args)
         return
 
     import torch.distributed as dist
@@ -201,16 +278,25 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # clocks are sampled from before the warm-up to the end of the timed regions (nvidia-smi
+    # needs a few hundred ms to start, longer than a short timed region)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step(Q, K, V, G, dO)
     barrier()
     if _lib.device_status(local_rank) != 0:
         raise SystemExit("a kernel reported a timed-out wait during warm-up")
+    if rank == 0:
+        # keep the GPU busy until the sampler has delivered its first readings
+        t_wait = time.time()
+        while len(sampler.samples) < 3 and time.time() - t_wait < 5.0:
+            step(Q, K, V, G, dO)
+            torch.cuda.synchronize()
+    barrier()
 
     # ---- device-resident timed region (per-kernel CUDA events recorded on the launch stream)
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     ops.launch_log.reset(timing=True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -223,7 +309,6 @@ def main():
     launches = ops.launch_log.count
     kernels = ops.launch_log.summary()
     ops.launch_log.reset(timing=False)
-    clocks = sampler.stop() if rank == 0 else None
     status = _lib.device_status(local_rank)
     tms = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -254,6 +339,7 @@ def main():
     if world > 1:
         dist.all_reduce(tms2, op=dist.ReduceOp.MAX)
     e2e_ms = float(tms2.item()) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
     h2d = sum(x.numel() * x.element_size() for x in (Qh, Kh, Vh, Gh, dOh))
     d2h = sum(x.numel() * x.element_size() for x in outs_h)
 

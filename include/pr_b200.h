@@ -178,6 +178,16 @@ int pr_decode_nsplit(void);
 int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
                     const float* sum_of_keys, const float* a_last, float scale, float* part_y, float* part_l,
                     int device, void* stream);
+/* As pr_decode_state with a_last element (batch, head) at a_last[batch*a_batch_stride + head]. */
+int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
+                            const float* sum_of_keys, const float* a_last, long long a_batch_stride, float scale,
+                            float* part_y, float* part_l, int device, void* stream);
+/* One decode step in one call: cumulative gates of the tk cached tokens (into a_scratch
+ * [b,tk,h], needed when log_g is given), state read-out and attention over the cache, merged
+ * and normalised into O [b,1,hq,d].  K/V/log_g and state/sum_of_keys may each be absent. */
+int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
+                   const float* log_g, const void* state, const float* sum_of_keys, float scale, float* a_scratch,
+                   float* part_y, float* part_l, void* O, int device, void* stream);
 int pr_decode_finish(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
                      const float* a, float scale, const float* part_y, const float* part_l, void* O, int device,
                      void* stream);

@@ -23,7 +23,7 @@ constexpr int HD = 64;
 constexpr int DEX = HD * (HD + 1) / 2;  // 2080
 constexpr int THREADS = 256;
 constexpr int ROWS_PER_ITER = THREADS / 8;  // 32 state rows per iteration
-constexpr int RG = 4;                       // query heads handled per CTA
+constexpr int RG_MAX = 4;                   // query heads handled per CTA (template: 1 or 4)
 }  // namespace dec
 
 // exact-layout row -> (a, b), a <= b
@@ -37,11 +37,11 @@ __device__ __forceinline__ void exact_decode(int D, int* a, int* b) {
   *b = aa + (D - off);
 }
 
-template <typename T>
+template <typename T, int RG>
 __global__ void __launch_bounds__(dec::THREADS)
 decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const float* __restrict__ sok,
-                    const float* __restrict__ a_last, float scale, int h, int hq, int nsplit,
-                    float* __restrict__ part_y, float* __restrict__ part_l) {
+                    const float* __restrict__ a_last, long long a_batch_stride, float scale, int h, int hq,
+                    int nsplit, float* __restrict__ part_y, float* __restrict__ part_l) {
   using namespace dec;
   __shared__ float sq[RG][HD];
   __shared__ float red_y[THREADS / 32][RG][HD];
@@ -54,7 +54,7 @@ decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const 
 
   // gated, scaled, rounded queries of this group (as the reference rounds Q*exp(.) to Q's dtype)
   float f = scale;
-  if (a_last != nullptr) f *= __expf(0.5f * a_last[bh]);
+  if (a_last != nullptr) f *= __expf(0.5f * a_last[(size_t)batch * a_batch_stride + head]);
   for (int i = tid; i < nr * HD; i += THREADS) {
     const int r = i / HD, e = i % HD;
     const float q = float(Q[((size_t)batch * hq + head * ratio + r0 + r) * HD + e]);
@@ -79,31 +79,48 @@ decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const 
   }
   const T* sbase = state + (size_t)bh * DEX * HD;
   const float* kbase = sok + (size_t)bh * DEX;
-  for (; D < d_end; D += ROWS_PER_ITER) {
-    const uint4 v = *reinterpret_cast<const uint4*>(sbase + (size_t)D * HD + sub * 8);
-    const float sk = kbase[D];
-    float x[8];
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  // four rows per thread in flight: the loads are issued before any of them is used
+  constexpr int UN = 4;
+  for (; D < d_end; D += UN * ROWS_PER_ITER) {
+    uint4 v[UN];
+    float sk[UN];
+    int ra[UN], rb[UN];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float2 p2 = Pack2<T>::to_f32(w[k]);
-      x[2 * k] = p2.x;
-      x[2 * k + 1] = p2.y;
-    }
-#pragma unroll
-    for (int r = 0; r < RG; ++r) {
-      if (r < nr) {
-        const float phi = float(T(sq[r][a] * sq[r][b]));  // product rounded to the input dtype
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(phi, x[k], acc[r][k]);
-        accl[r] = fmaf(phi, sk, accl[r]);
+    for (int u = 0; u < UN; ++u) {
+      const int Du = D + u * ROWS_PER_ITER;
+      ra[u] = a;
+      rb[u] = b;
+      if (Du < d_end) {
+        v[u] = __ldg(reinterpret_cast<const uint4*>(sbase + (size_t)Du * HD + sub * 8));
+        sk[u] = __ldg(kbase + Du);
+      }
+      // advance (a, b) by ROWS_PER_ITER rows of the triangle
+      b += ROWS_PER_ITER;
+      while (b >= HD && a < HD) {
+        b = b - HD + a + 1;
+        ++a;
       }
     }
-    // advance (a, b) by ROWS_PER_ITER rows of the triangle
-    b += ROWS_PER_ITER;
-    while (b >= HD && a < HD) {
-      b = b - HD + a + 1;
-      ++a;
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      if (D + u * ROWS_PER_ITER >= d_end) break;
+      float x[8];
+      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 p2 = Pack2<T>::to_f32(w[k]);
+        x[2 * k] = p2.x;
+        x[2 * k + 1] = p2.y;
+      }
+#pragma unroll
+      for (int r = 0; r < RG; ++r) {
+        if (r < nr) {
+          const float phi = float(T(sq[r][min(ra[u], HD - 1)] * sq[r][min(rb[u], HD - 1)]));  // rounded like the inputs
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(phi, x[k], acc[r][k]);
+          accl[r] = fmaf(phi, sk[u], accl[r]);
+        }
+      }
     }
   }
   // reduce the 4 rows a warp covers (lanes with equal sub), then the 8 warps
@@ -269,6 +286,13 @@ extern "C" int pr_decode_nsplit(void) { return 5; }
 extern "C" int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
                                const float* sum_of_keys, const float* a_last, float scale, float* part_y,
                                float* part_l, int device, void* stream) {
+  return pr_decode_state_strided(dtype, b, h, hq, d, Q, state, sum_of_keys, a_last, h, scale, part_y, part_l, device,
+                                 stream);
+}
+
+extern "C" int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
+                                       const float* sum_of_keys, const float* a_last, long long a_batch_stride,
+                                       float scale, float* part_y, float* part_l, int device, void* stream) {
   using namespace pr;
   PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0, PR_ERR_BAD_ARG, "bad sizes b=%d h=%d hq=%d", b, h, hq);
@@ -276,18 +300,22 @@ extern "C" int pr_decode_state(int dtype, int b, int h, int hq, int d, const voi
              "null or misaligned pointer");
   PR_CUDA(cudaSetDevice(device));
   const int nsplit = pr_decode_nsplit();
-  dim3 grid(b * h, nsplit, (hq / h + dec::RG - 1) / dec::RG);
+  const int ratio = hq / h;
+  const int rg = ratio == 1 ? 1 : dec::RG_MAX;
+  dim3 grid(b * h, nsplit, (ratio + rg - 1) / rg);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PR_BF16)
-    decode_state_kernel<__nv_bfloat16><<<grid, dec::THREADS, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(state), sum_of_keys, a_last, scale, h,
-        hq, nsplit, part_y, part_l);
-  else if (dtype == PR_FP16)
-    decode_state_kernel<__half><<<grid, dec::THREADS, 0, s>>>(static_cast<const __half*>(Q),
-                                                              static_cast<const __half*>(state), sum_of_keys, a_last,
-                                                              scale, h, hq, nsplit, part_y, part_l);
-  else
+#define PR_LAUNCH_DECODE(TT, RGV)                                                                              \
+  decode_state_kernel<TT, RGV><<<grid, dec::THREADS, 0, s>>>(static_cast<const TT*>(Q), static_cast<const TT*>(state), \
+                                                             sum_of_keys, a_last, a_batch_stride, scale, h, hq,      \
+                                                             nsplit, part_y, part_l)
+  if (dtype == PR_BF16) {
+    if (rg == 1) PR_LAUNCH_DECODE(__nv_bfloat16, 1); else PR_LAUNCH_DECODE(__nv_bfloat16, 4);
+  } else if (dtype == PR_FP16) {
+    if (rg == 1) PR_LAUNCH_DECODE(__half, 1); else PR_LAUNCH_DECODE(__half, 4);
+  } else {
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  }
+#undef PR_LAUNCH_DECODE
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }
@@ -344,4 +372,36 @@ extern "C" int pr_state_merge(int dtype, int b, int h, int d, const void* state,
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_CUDA(cudaGetLastError());
   return PR_OK;
+}
+
+// One decode step in a single call: cumulative gates of the cached tokens, state read-out,
+// attention over the cache, merge.  a_scratch [b,tk,h] fp32 (only when log_g is given),
+// part_y / part_l as for pr_decode_state (only when a state is given).
+extern "C" int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K,
+                              const void* V, const float* log_g, const void* state, const float* sum_of_keys,
+                              float scale, float* a_scratch, float* part_y, float* part_l, void* O, int device,
+                              void* stream) {
+  using namespace pr;
+  const bool has_cache = (K != nullptr && V != nullptr && tk > 0);
+  const bool gated = has_cache && log_g != nullptr;
+  PR_REQUIRE(!gated || a_scratch != nullptr, PR_ERR_BAD_ARG, "gated decode needs a_scratch");
+  PR_REQUIRE(state == nullptr || (part_y != nullptr && part_l != nullptr && sum_of_keys != nullptr), PR_ERR_BAD_ARG,
+             "a state needs sum_of_keys and the partial-sum workspace");
+  int rc = PR_OK;
+  if (gated) {
+    rc = pr_gate_prep(dtype, b, tk, h, h, d, tk, log_g, nullptr, a_scratch, nullptr, nullptr, nullptr, nullptr, 0, 1.f,
+                      1, device, stream);
+    if (rc) return rc;
+  }
+  if (state != nullptr) {
+    // a_last[b,h] is the last row of a_scratch: element (batch, tk-1, head); the kernel indexes
+    // it as a_last[batch*h + head], so hand it a pointer with the batch stride folded in when b == 1,
+    // else use the strided variant below
+    rc = pr_decode_state_strided(dtype, b, h, hq, d, Q, state, sum_of_keys, gated ? a_scratch + (size_t)(tk - 1) * h : nullptr,
+                                 gated ? (long long)tk * h : 0, scale, part_y, part_l, device, stream);
+    if (rc) return rc;
+  }
+  return pr_decode_finish(dtype, b, has_cache ? tk : 0, h, hq, d, Q, has_cache ? K : nullptr, has_cache ? V : nullptr,
+                          gated ? a_scratch : nullptr, scale, state ? part_y : nullptr, state ? part_l : nullptr, O,
+                          device, stream);
 }

@@ -299,3 +299,26 @@ def state_merge(state, sum_of_keys, S, gram, a_last):
     _call("pr_state_merge", c_int(dtype_code(S.dtype)), c_int(b), c_int(h), c_int(d), ptr(state), ptr(sum_of_keys),
           ptr(S), ptr(gram), ptr(a_last), ptr(new_state), ptr(new_sok), c_int(_dev(S)), stream_ptr(S.device))
     return new_state, new_sok
+
+
+_decode_ws = {}
+
+
+def decode_step(Q, K, V, log_g, state, sum_of_keys, scale: float, h: int):
+    """One decode step (tq = 1) in a single library call.  Returns O [b,1,hq,d]."""
+    b, _, hq, d = Q.shape
+    tk = K.shape[1] if K is not None else 0
+    O = torch.empty_like(Q)
+    a = torch.empty(b, tk, h, device=Q.device, dtype=torch.float32) if (log_g is not None and tk > 0) else None
+    part_y = part_l = None
+    if state is not None:
+        key = (Q.device, b, hq, d)
+        if key not in _decode_ws:
+            ns = lib().pr_decode_nsplit()
+            _decode_ws[key] = (torch.empty(b, hq, ns, d, device=Q.device, dtype=torch.float32),
+                               torch.empty(b, hq, ns, device=Q.device, dtype=torch.float32))
+        part_y, part_l = _decode_ws[key]
+    _call("pr_decode_step", c_int(dtype_code(Q.dtype)), c_int(b), c_int(tk), c_int(h), c_int(hq), c_int(d), ptr(Q),
+          ptr(K), ptr(V), ptr(log_g), ptr(state), ptr(sum_of_keys), c_float(scale), ptr(a), ptr(part_y), ptr(part_l),
+          ptr(O), c_int(_dev(Q)), stream_ptr(Q.device))
+    return O

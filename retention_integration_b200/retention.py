@@ -187,35 +187,39 @@ def power_retention_inference(Q, K, V, log_G=None, initial_state=None, sum_of_ke
     Q = Q.contiguous()
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     gated = has_cache and log_G is not None
-    a = None
     if gated:
         assert log_G.shape == K.shape[:3]
-        a, _, _ = ops.gate_prep(K, log_G.to(torch.float32).contiguous(), tk, query_side=False, want_xt=False)
-    a_last = a[:, -1, :].contiguous() if a is not None else None
+        log_G = log_G.to(torch.float32).contiguous()
+    switch = switch_over_seq_len is not None and tk >= switch_over_seq_len
 
     # ---- read-out
-    if initial_state is None:
-        Y, _ = ops.chunk_out(Q, K, V, a, None, None, None, 1, tq, tk, 1, scale, want_l=False)
-    elif tq == 1:
-        part_y, part_l = ops.decode_state(Q, initial_state.contiguous(), sum_of_keys.contiguous(), a_last, scale)
-        Y = ops.decode_finish(Q, K if tk > 0 else None, V if tk > 0 else None, a, scale, part_y, part_l, h)
+    a = None
+    if tq == 1 and initial_state is not None:
+        # the decode step proper: one library call (gate cumsum, state read, cache attention)
+        Y = ops.decode_step(Q, K if tk > 0 else None, V if tk > 0 else None, log_G if gated else None,
+                            initial_state.contiguous(), sum_of_keys.contiguous(), scale, h)
     else:
-        # several query tokens against a state: the tensor-core path, state converted to its layout
-        Z = layout.exact_to_t2(initial_state, d, dim=-2).unsqueeze(1).contiguous()
-        zg = layout.exact_sum_of_keys_to_gram(sum_of_keys, d)
-        zhi = zg.to(Q.dtype)
-        zlo = (zg - zhi.float()).to(Q.dtype)
-        if tk > 0:
-            Y, _ = ops.chunk_out(Q, K, V, a, Z, zhi.unsqueeze(1).contiguous(), zlo.unsqueeze(1).contiguous(), 1, tq,
-                                 tk, 0, scale, q_gate_last=True, want_l=False)
+        if gated:
+            a, _, _ = ops.gate_prep(K, log_G, tk, query_side=False, want_xt=False)
+        if initial_state is None:
+            Y, _ = ops.chunk_out(Q, K, V, a, None, None, None, 1, tq, tk, 1, scale, want_l=False)
         else:
-            Y, _ = ops.chunk_out(Q, None, None, None, Z, zhi.unsqueeze(1).contiguous(), zlo.unsqueeze(1).contiguous(),
-                                 1, tq, tq, 0, scale, want_l=False)
+            # several query tokens against a state: the tensor-core path, state converted to its layout
+            Z = layout.exact_to_t2(initial_state, d, dim=-2).unsqueeze(1).contiguous()
+            zg = layout.exact_sum_of_keys_to_gram(sum_of_keys, d)
+            zhi = zg.to(Q.dtype)
+            zlo = (zg - zhi.float()).to(Q.dtype)
+            if tk > 0:
+                Y, _ = ops.chunk_out(Q, K, V, a, Z, zhi.unsqueeze(1).contiguous(), zlo.unsqueeze(1).contiguous(), 1,
+                                     tq, tk, 0, scale, q_gate_last=True, want_l=False)
+            else:
+                Y, _ = ops.chunk_out(Q, None, None, None, Z, zhi.unsqueeze(1).contiguous(),
+                                     zlo.unsqueeze(1).contiguous(), 1, tq, tq, 0, scale, want_l=False)
 
     # ---- optionally compress the cache into the state
-    if switch_over_seq_len is not None and tk >= switch_over_seq_len:
-        lg = log_G.to(torch.float32).contiguous() if gated else None
-        _, _, KT = ops.gate_prep(K, lg, tk, query_side=False, want_gates=False)
+    if switch:
+        a2, _, KT = ops.gate_prep(K, log_G if gated else None, tk, query_side=False)
+        a_last = a2[:, -1, :].contiguous() if a2 is not None else None
         S, gram = ops.chunk_state(KT, None, V, tk, h, key_weights=True, want_gram=True)
         new_state, new_sok = ops.state_merge(initial_state, sum_of_keys, S, gram, a_last)
         return Y, new_state, new_sok

@@ -46,3 +46,60 @@ def test_sequence_parallel_equals_single_device(cuda_device, world, gated):
             continue
         got = torch.cat([locs[rk][i].grad for rk in range(world)], 1).float()
         assert rel_l2(got, ref_in[i].grad.float()) < 5e-3, name
+
+
+def _nccl_worker(rank, world, port, t, c, ret):
+    import os
+
+    import torch.distributed as dist
+
+    import retention_integration_b200 as prb
+    from retention_integration_b200 import parallel
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        g = torch.Generator().manual_seed(11)
+        b, h, d = 1, 2, 64
+        Q, K, V, dO = (torch.randn(b, t, h, d, generator=g).bfloat16().to(dev) for _ in range(4))
+        lg = F.logsigmoid(torch.randn(b, t, h, generator=g) + 4.0).to(dev)
+        tl = t // world
+        sl = slice(rank * tl, (rank + 1) * tl)
+        ins = [x[:, sl].clone().requires_grad_(True) for x in (Q, K, V, lg)]
+        O = parallel.power_retention_sequence_parallel(*ins, deg=2, chunk_size=c)
+        O.backward(dO[:, sl])
+        full = [x.clone().requires_grad_(True) for x in (Q, K, V, lg)]
+        O_ref = prb.power_retention(*full, deg=2, chunk_size=c)
+        O_ref.backward(dO)
+        errs = [rel_l2(O.float(), O_ref[:, sl].float())]
+        errs += [rel_l2(a.grad.float(), f.grad[:, sl].float()) for a, f in zip(ins, full)]
+        torch.cuda.synchronize()
+        ret[rank] = errs
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_parallel_over_nccl():
+    """Real ranks, one per GPU, boundary states exchanged with NCCL send/recv."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, 4096, 256, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for r in range(world):
+        assert max(ret[r]) < 5e-3, (r, ret[r])
