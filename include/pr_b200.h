@@ -188,6 +188,16 @@ int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, const void* 
 int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
                    const float* log_g, const void* state, const float* sum_of_keys, float scale, float* a_scratch,
                    float* part_y, float* part_l, void* O, int device, void* stream);
+/* No counterpart in the reference.  pr_decode_step for hosts that cannot hand over scratch
+ * memory (a frozen memory pool, a stream callback, a stream capture in progress): the gate and
+ * partial-sum scratch sits in a fixed device array of about 2.4 MB that the library carries on
+ * every GPU.  Limits: b*hq <= 1024 and b*tk*h <= 262144, beyond which PR_ERR_BAD_ARG is
+ * returned.  The array is shared by all calls on a device, so calls that overlap on the GPU
+ * race; nothing in it needs zeroing between calls.  The first call on a device looks up the
+ * array's device address and should be made outside any stream capture. */
+int pr_decode_step_static(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K,
+                          const void* V, const float* log_g, const void* state, const float* sum_of_keys,
+                          float scale, void* O, int device, void* stream);
 int pr_decode_finish(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
                      const float* a, float scale, const float* part_y, const float* part_l, void* O, int device,
                      void* stream);

@@ -12,6 +12,8 @@
 //   pr_state_merge  : prefill-to-state switch-over: new_state = state*exp(a_last) + S_chunk,
 //                     converting the chunk state from the kernels' internal layout to the
 //                     exact layout on the fly; same for sum_of_keys from the Gram matrix.
+#include <mutex>
+
 #include "host.cuh"
 #include "layout.cuh"
 #include "sm100.cuh"
@@ -404,4 +406,78 @@ extern "C" int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, co
   return pr_decode_finish(dtype, b, has_cache ? tk : 0, h, hq, d, Q, has_cache ? K : nullptr, has_cache ? V : nullptr,
                           gated ? a_scratch : nullptr, scale, state ? part_y : nullptr, state ? part_l : nullptr, O,
                           device, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode step for callers that must not allocate.
+//
+// pr_decode_step needs two pieces of scratch memory from its caller: the cumulative gates
+// of the cached tokens and the partial sums of the split state read.  Some hosts of this
+// library cannot provide them: a serving loop that froze its memory pool after start-up, a
+// plugin running inside another runtime's stream callback, or code between
+// cudaStreamBeginCapture and EndCapture, where cudaMalloc is an error.  For them the same
+// step is offered with its scratch in the fixed device array below, which every GPU that
+// loads this library carries until the process exits (kStaticScratchBytes, about 2.4 MB).
+//
+// Limits: batch * query_heads <= kStaticMaxRows and batch * cached_tokens * kv_heads <=
+// kStaticMaxGates; larger problems are refused with PR_ERR_BAD_ARG.  All calls on a device
+// share the one array: two calls whose kernels overlap on the GPU (different streams, or
+// different threads) race on it, so keep such calls on one stream.  Nothing in the array has
+// to start at zero - each call overwrites every word it later reads - so stale contents of the
+// previous call are harmless.  The device address of the array is looked up the first time
+// the entry point runs on a device; make that first call outside any stream capture.
+namespace pr {
+namespace {
+constexpr int kStaticMaxRows = 1024;                                       // batch * query heads
+constexpr int kStaticMaxGates = 1 << 18;                                   // batch * cached tokens * kv heads
+constexpr int kStaticSplit = 5;                                            // == pr_decode_nsplit()
+constexpr size_t kStaticPartY = (size_t)kStaticMaxRows * kStaticSplit * dec::HD;  // floats
+constexpr size_t kStaticPartL = (size_t)kStaticMaxRows * kStaticSplit;
+constexpr size_t kStaticFloats = kStaticPartY + kStaticPartL + kStaticMaxGates;
+constexpr size_t kStaticScratchBytes = kStaticFloats * sizeof(float);
+
+static __device__ __align__(256) float g_decode_scratch[kStaticFloats];
+
+constexpr int kStaticMaxDevices = 64;
+float* g_scratch_addr[kStaticMaxDevices] = {nullptr};  // device address of the array, per device
+std::mutex g_scratch_mu;
+
+// In host code `g_decode_scratch` names a host-side shadow, not device memory; the address a
+// kernel may use has to be asked for, with the target device current.
+int static_scratch(int device, float** out) {
+  PR_REQUIRE(device >= 0 && device < kStaticMaxDevices, PR_ERR_BAD_ARG, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_addr[device] == nullptr) {
+    void* p = nullptr;
+    PR_CUDA(cudaGetSymbolAddress(&p, g_decode_scratch));
+    PR_REQUIRE(p != nullptr, PR_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_scratch_addr[device] = static_cast<float*>(p);
+  }
+  *out = g_scratch_addr[device];
+  return PR_OK;
+}
+}  // namespace
+}  // namespace pr
+
+extern "C" int pr_decode_step_static(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K,
+                                     const void* V, const float* log_g, const void* state, const float* sum_of_keys,
+                                     float scale, void* O, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(b > 0 && h > 0 && hq > 0 && tk >= 0, PR_ERR_BAD_ARG, "bad sizes b=%d h=%d hq=%d tk=%d", b, h, hq, tk);
+  PR_REQUIRE(pr_decode_nsplit() == kStaticSplit, PR_ERR_BAD_ARG, "static scratch was sized for another split count");
+  PR_REQUIRE((long long)b * hq <= kStaticMaxRows, PR_ERR_BAD_ARG,
+             "batch * query heads = %lld exceeds the static scratch limit of %d rows", (long long)b * hq,
+             kStaticMaxRows);
+  PR_REQUIRE((long long)b * tk * h <= kStaticMaxGates, PR_ERR_BAD_ARG,
+             "batch * cached tokens * kv heads = %lld exceeds the static scratch limit of %d gates",
+             (long long)b * tk * h, kStaticMaxGates);
+  PR_CUDA(cudaSetDevice(device));
+  float* scratch = nullptr;
+  int rc = static_scratch(device, &scratch);
+  if (rc) return rc;
+  float* part_y = scratch;
+  float* part_l = scratch + kStaticPartY;
+  float* gates = scratch + kStaticPartY + kStaticPartL;
+  return pr_decode_step(dtype, b, tk, h, hq, d, Q, K, V, log_g, state, sum_of_keys, scale, gates, part_y, part_l, O,
+                        device, stream);
 }
