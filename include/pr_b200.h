@@ -189,7 +189,7 @@ int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q
                    const float* log_g, const void* state, const float* sum_of_keys, float scale, float* a_scratch,
                    float* part_y, float* part_l, void* O, int device, void* stream);
 /* No counterpart in the reference.  pr_decode_step for hosts that cannot hand over scratch
- * memory (a frozen memory pool, a stream callback, a stream capture in progress): the gate and
+ * memory (a frozen memory pool, a stream callback, an allocator owned by another component): the gate and
  * partial-sum scratch sits in a fixed device array of about 2.4 MB that the library carries on
  * every GPU.  Limits: b*hq <= 1024 and b*tk*h <= 262144, beyond which PR_ERR_BAD_ARG is
  * returned.  The array is shared by all calls on a device, so calls that overlap on the GPU

@@ -414,8 +414,9 @@ extern "C" int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, co
 // pr_decode_step needs two pieces of scratch memory from its caller: the cumulative gates
 // of the cached tokens and the partial sums of the split state read.  Some hosts of this
 // library cannot provide them: a serving loop that froze its memory pool after start-up, a
-// plugin running inside another runtime's stream callback, or code between
-// cudaStreamBeginCapture and EndCapture, where cudaMalloc is an error.  For them the same
+// plugin running inside another runtime's stream callback (no CUDA API calls allowed there
+// beyond launches), or a process whose device allocator belongs to a different component and
+// hands out nothing at request time.  For them the same
 // step is offered with its scratch in the fixed device array below, which every GPU that
 // loads this library carries until the process exits (kStaticScratchBytes, about 2.4 MB).
 //

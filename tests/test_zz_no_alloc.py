@@ -1,7 +1,7 @@
 """The allocation-free decode entry point (pr_decode_step_static) against pr_decode_step.
 
 For hosts that cannot allocate device memory while serving (fixed pools, stream callbacks,
-stream capture) the library keeps the decode scratch in a fixed device array.  This test calls
+allocators owned by another component) the library keeps the decode scratch in a fixed device array.  This test calls
 both entry points through the C ABI on the same inputs, twice in a row with different cache
 lengths (the second call finds the first call's leftovers in the array), and wants the same
 output.  It sits in a file that pytest collects last, and passes on its own as well.
