@@ -8,8 +8,9 @@
 // Backward use (gradient of the state read-out, retention/_query_state/triton.py:337-448):
 //   x = gated queries, v = dO / l, weights off -> dZ_m; xs = x * dl -> gram = d(gram of Z).
 //
-// One CTA owns a tile of 128 expanded rows.  The expansion is never written to shared
-// or global memory: each of 128 threads owns one expanded row (a, b), multiplies rows a
+// One CTA owns two tiles of 128 expanded rows (one group of four warps each), so every
+// operand stage fetched from L2 feeds two products.  The expansion is never written to shared
+// or global memory: each thread owns one expanded row (a, b), multiplies rows a
 // and b of the transposed operand (TMA-loaded, 128-byte swizzled) with packed 16-bit
 // multiplies and stores the products straight into tensor memory as the A operand of
 // tcgen05.mma; the values come in by TMA as the MN-major B operand; fp32 accumulation in
@@ -23,18 +24,21 @@ namespace pr {
 
 namespace cs {
 constexpr int HD = 64;          // head dim handled by this build of the kernel
-constexpr int NS = 4;           // pipeline stages
+constexpr int NS = 4;           // shared-memory pipeline stages
+constexpr int NSA = 2;          // tensor-memory stages of each group's expansion ring
+constexpr int NG = 2;           // row tiles (groups of 4 warps) per CTA: each loaded stage feeds both
 constexpr int TOK = 64;         // tokens per stage
-constexpr int THREADS = 192;    // warps 0-3 expand + epilogue, 4 TMA, 5 MMA
+constexpr int THREADS = 320;    // warps 0-3 / 4-7 expand + epilogue (one group per row tile), 8 TMA, 9 MMA
 constexpr int XT_BYTES = HD * TOK * 2;   // 8 KB
 constexpr int W_BYTES = TOK * HD * 2;    // 8 KB
 constexpr int GA_BYTES = 128 * TOK * 2;  // Gram A operand padded to 128 rows
 constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t COL_ACC = 0, COL_A = 64;  // A ring: NS x 32 columns
+constexpr uint32_t COL_ACC = 0;    // NG x 64 columns
+constexpr uint32_t COL_A = 128;    // NG rings of NSA x 32 columns
 }  // namespace cs
 
 struct ChunkStateParams {
-  int n_tiles;      // tiles of 128 expanded rows; grid.x = n_tiles + (gram ? 1 : 0)
+  int n_tiles;      // tiles of 128 expanded rows; grid.x = ceil(n_tiles / 2) + (gram ? 1 : 0)
   int nh;           // kv heads of the output
   int group;        // operand heads summed into one output head (GQA ratio in backward)
   int c, cp;        // chunk length, padded to 64
@@ -46,12 +50,12 @@ struct ChunkStateParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(cs::THREADS, 2)
+__global__ void __maxnreg__(80)
 chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap tm_xt,
                    const __grid_constant__ CUtensorMap tm_xs, const __grid_constant__ CUtensorMap tm_w) {
   using namespace cs;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t x_full[NS], x_empty[NS], w_full[NS], w_empty[NS], a_full[NS], a_empty[NS], acc_done;
+  __shared__ uint64_t x_full[NS], x_empty[NS], w_full[NS], w_empty[NS], a_full[NG][NSA], a_empty[NG][NSA], acc_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -62,8 +66,8 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
   uint8_t* smW = sm + NS * XT_BYTES;          // NS x W_BYTES  (rows = tokens, 64 features)
   uint8_t* smG = smW;                         // Gram CTA only: 2 x GA_BYTES over the (unused) value ring
 
-  const int tile = blockIdx.x;
-  const bool gram_cta = (tile == p.n_tiles);
+  const int n_tile_ctas = (p.n_tiles + NG - 1) / NG;
+  const bool gram_cta = ((int)blockIdx.x == n_tile_ctas);
   const int ch = blockIdx.y;  // (batch * n + chunk) * nh + head
   const int head = ch % p.nh;
   const int chunk = (ch / p.nh) % p.n_chunks;
@@ -75,12 +79,15 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
       mbar_init(&x_full[s], 1);
-      mbar_init(&x_empty[s], 4);
+      mbar_init(&x_empty[s], 4 * NG);
       mbar_init(&w_full[s], 1);
       mbar_init(&w_empty[s], 1);
-      mbar_init(&a_full[s], 4);
-      mbar_init(&a_empty[s], 1);
     }
+    for (int g = 0; g < NG; ++g)
+      for (int s = 0; s < NSA; ++s) {
+        mbar_init(&a_full[g][s], 4);
+        mbar_init(&a_empty[g][s], 1);
+      }
     mbar_init(&acc_done, 1);
     fence_mbar_init();
   }
@@ -93,7 +100,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
 
-  if (warp == 4) {
+  if (warp == 4 * NG) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int it = 0; it < total; ++it) {
@@ -118,7 +125,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 4 * NG + 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       bool ok = true;
@@ -140,15 +147,20 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
         for (int it = 0; it < total && ok; ++it) {
           const int s = it % NS, ph = (it / NS) & 1;
-          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&w_full[s], ph, &abort_flag);
-          if (!ok) break;
-          tc_fence_after();
+          const int sa = it % NSA, pha = (it / NSA) & 1;
+          ok = mbar_wait(&w_full[s], ph, &abort_flag);
           const uint32_t b_addr = smem_u32(smW + s * W_BYTES);
+          for (int g = 0; g < NG && ok; ++g) {
+            ok = mbar_wait(&a_full[g][sa], pha, &abort_flag);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-          for (int ks = 0; ks < TOK / 16; ++ks)
-            umma_ts(tmem + COL_ACC, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(b_addr + ks * 2048, 8192, 1024),
-                    idesc, (it > 0 || ks > 0) ? 1u : 0u);
-          umma_commit(&a_empty[s]);
+            for (int ks = 0; ks < TOK / 16; ++ks)
+              umma_ts(tmem + COL_ACC + g * 64, tmem + COL_A + (g * NSA + sa) * 32 + ks * 8,
+                      umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc, (it > 0 || ks > 0) ? 1u : 0u);
+            umma_commit(&a_empty[g][sa]);
+          }
+          if (!ok) break;
           umma_commit(&w_empty[s]);
         }
       }
@@ -156,11 +168,13 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     }
   } else {
     // ------------------------------------------------- expansion + epilogue warps
-    const int row_in_tile = warp * 32 + lane;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const int grp = warp >> 2;
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int D2 = t2_dim(HD);
+    const int tile = (int)blockIdx.x * NG + grp;
     int drow = tile * 128 + row_in_tile;
-    const bool valid = !gram_cta && drow < D2;
+    const bool valid = !gram_cta && drow < D2;  // rows past the end still take part in the pipeline
     int a = 0, b = 0;
     if (valid) t2_decode(HD, drow, &a, &b);
     bool ok = true;
@@ -182,25 +196,26 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&x_empty[s]);
-        ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+        const int sa = it % NSA, pha = (it / NSA) & 1;
+        ok = mbar_wait(&a_empty[grp][sa], pha ^ 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
-        tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+        tmem_st32(tmem + lane_addr + COL_A + (grp * NSA + sa) * 32, r);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[s]);
+        if (lane == 0) mbar_arrive(&a_full[grp][sa]);
       }
     }
     if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
     tc_fence_after();
     if (ok) {
       uint32_t acc[64];
-      tmem_ld32(tmem + lane_addr + COL_ACC, acc);
-      tmem_ld32(tmem + lane_addr + COL_ACC + 32, acc + 32);
+      tmem_ld32(tmem + lane_addr + COL_ACC + grp * 64, acc);
+      tmem_ld32(tmem + lane_addr + COL_ACC + grp * 64 + 32, acc + 32);
       tmem_wait_ld();
       if (gram_cta) {
-        if (row_in_tile < HD && p.gram != nullptr) {
+        if (grp == 0 && row_in_tile < HD && p.gram != nullptr) {
           float4* dst = reinterpret_cast<float4*>(p.gram + ((size_t)ch * HD + row_in_tile) * HD);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -237,7 +252,7 @@ static int launch_chunk_state(const ChunkStateParams& p, int b, const CUtensorMa
   static_assert(2 * GA_BYTES <= NS * W_BYTES, "Gram stages must fit in the value ring");
   PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-  dim3 grid(p.n_tiles + (p.gram ? 1 : 0), b * p.n_chunks * p.nh);
+  dim3 grid((p.n_tiles + NG - 1) / NG + (p.gram ? 1 : 0), b * p.n_chunks * p.nh);
   chunk_state_kernel<T><<<grid, THREADS, smem, stream>>>(p, tm_xt, tm_xs, tm_w);
   PR_CUDA(cudaGetLastError());
   return PR_OK;
