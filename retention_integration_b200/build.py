@@ -46,7 +46,7 @@ def _headers() -> list[str]:
 
 
 def _compile(src: str, obj: str, verbose: bool) -> None:
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+    cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("PR_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd), flush=True)

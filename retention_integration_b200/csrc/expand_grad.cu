@@ -32,6 +32,7 @@ constexpr int NT = (D2 + 127) / 128;     // 17 tiles, the last one 64 rows wide
 constexpr int THREADS = 320;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9 MMA
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int G_BYTES = 64 * 128;
+constexpr int NSS = 6;                   // state tiles in flight (TMA latency x L2 bandwidth needs ~100 KB per SM)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int ROWS = 256;                // token rows per CTA: two row tiles of 128
 constexpr uint32_t COL_D = 0;            // 2 x 128 columns (one buffer per row tile)
@@ -83,7 +84,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
                    const __grid_constant__ CUtensorMap tm_ghi, const __grid_constant__ CUtensorMap tm_glo) {
   using namespace eg;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t w_full, g_full, xa_full[2], u_full[2], s_full[2], s_empty[2], d_full[2], d_empty[2];
+  __shared__ uint64_t w_full, g_full, xa_full[2], u_full[2], s_full[NSS], s_empty[NSS], d_full[2], d_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -113,8 +114,8 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smW = sm;                            // 2 x TILE_BYTES (one per row tile)
   uint8_t* smX = smW + 2 * TILE_BYTES;          // 2 x TILE_BYTES
-  uint8_t* smS = smX + 2 * TILE_BYTES;          // 2 x TILE_BYTES (ring of state tiles)
-  uint8_t* smG = smS + 2 * TILE_BYTES;          // hi, lo
+  uint8_t* smS = smX + 2 * TILE_BYTES;          // NSS x TILE_BYTES (ring of state tiles)
+  uint8_t* smG = smS + NSS * TILE_BYTES;        // hi, lo
 
   if (tid == 0) {
     abort_flag = 0;
@@ -123,10 +124,12 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     for (int s = 0; s < 2; ++s) {
       mbar_init(&xa_full[s], 4);
       mbar_init(&u_full[s], 1);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 1);
       mbar_init(&d_full[s], 1);
       mbar_init(&d_empty[s], 4);
+    }
+    for (int s = 0; s < NSS; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 1);
     }
     fence_mbar_init();
   }
@@ -151,7 +154,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
       tma_load_2d(smG, &tm_ghi, &g_full, 0, ch * HD);
       tma_load_2d(smG + G_BYTES, &tm_glo, &g_full, 0, ch * HD);
       for (int nt = 0; nt < NT; ++nt) {
-        const int s = nt & 1, ph = (nt >> 1) & 1;
+        const int s = nt % NSS, ph = (nt / NSS) & 1;
         if (!mbar_wait(&s_empty[s], ph ^ 1, &abort_flag)) break;
         mbar_expect_tx(&s_full[s], TILE_BYTES);
         tma_load_2d(smS + s * TILE_BYTES, &tm_s, &s_full[s], 0, ch * D2 + nt * 128);
@@ -162,7 +165,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
       bool ok = mbar_wait(&w_full, 0, &abort_flag);
       const uint32_t w_addr = smem_u32(smW);
       for (int nt = 0; nt < NT && ok; ++nt) {
-        const int s = nt & 1, ph = (nt >> 1) & 1;
+        const int s = nt % NSS, ph = (nt / NSS) & 1;
         ok = mbar_wait(&s_full[s], ph, &abort_flag);
         if (!ok) break;
         const uint32_t idesc = umma_idesc(128, nt == NT - 1 ? 64 : 128, Pack2<T>::is_bf16, false, false);
@@ -366,7 +369,7 @@ extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int
     if ((rc = make_tmap(&tm_ghi, g_hi, 2, 2, dg, st, box_g, true))) return rc;
     if ((rc = make_tmap(&tm_glo, g_lo, 2, 2, dg, st, box_g, true))) return rc;
   }
-  const size_t smem = 1024 + 6 * TILE_BYTES + 2 * G_BYTES;
+  const size_t smem = 1024 + (4 + NSS) * TILE_BYTES + 2 * G_BYTES;
   dim3 grid(p.tiles_per_chunk * n, hx, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
