@@ -315,30 +315,27 @@ def main():
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
     ms_per_step = float(tms.item()) / args.steps
 
-    # ---- end to end: pinned host inputs in, results out, every step
-    outs_h = None
+    # ---- end to end: pinned host inputs in, results out, every step (the library's host-tensor
+    # call: head slices pipelined over copy-in / compute / copy-out streams)
+    from retention_integration_b200.host import HostPipeline
+
+    n_slices = 4 if hl % 4 == 0 else (2 if hl % 2 == 0 else 1)
+    pipe = HostPipeline(b, t, hl, d, torch.bfloat16, dev, c, n_slices=n_slices)
+    outs_h = {k: torch.empty(b, t, hl, d, dtype=torch.bfloat16).pin_memory() for k in ("O", "dQ", "dK", "dV")}
+    outs_h["dlog_G"] = torch.empty(b, t, hl).pin_memory()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-
-    def e2e_step():
-        nonlocal outs_h
-        dq, dk, dv, dg, ddo = (x.to(dev, non_blocking=True) for x in (Qh, Kh, Vh, Gh, dOh))
-        res = step(dq, dk, dv, dg, ddo)
-        if outs_h is None:
-            outs_h = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in res]
-        for dst, src in zip(outs_h, res):
-            dst.copy_(src, non_blocking=True)
-
-    e2e_step()
+    pipe.fwd_bwd(Qh, Kh, Vh, Gh, dOh, outs_h)
     barrier()
     e2.record()
     for _ in range(args.steps):
-        e2e_step()
+        pipe.fwd_bwd(Qh, Kh, Vh, Gh, dOh, outs_h)
     e3.record()
     barrier()
     tms2 = torch.tensor([e2.elapsed_time(e3)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tms2, op=dist.ReduceOp.MAX)
     e2e_ms = float(tms2.item()) / args.steps
+    outs_h = list(outs_h.values())
     clocks = sampler.stop() if rank == 0 else None
     h2d = sum(x.numel() * x.element_size() for x in (Qh, Kh, Vh, Gh, dOh))
     d2h = sum(x.numel() * x.element_size() for x in outs_h)

@@ -56,6 +56,13 @@ const char* pr_last_error(void);
  * *status is 0 when nothing failed. */
 int pr_device_status(int device, int* status);
 
+/* Strided copy of `rows` rows of `width_bytes` between pinned host memory and device memory
+ * (to_device = 1: host -> device), e.g. one slice of heads of a [b,t,h,d] tensor; the host-buffer
+ * variant of the public call pipelines such slices.  No counterpart in the reference, whose
+ * operators take device tensors only. */
+int pr_copy_2d(void* dst, long long dst_pitch, const void* src, long long src_pitch, long long width_bytes,
+               long long rows, int to_device, int device, void* stream);
+
 /* Self-test of the tensor-core building blocks on a 128 x N x K product:
  *   variant 0: A, B K-major in shared memory (manual swizzled stores)
  *   variant 1: A K-major, B MN-major in shared memory

@@ -93,3 +93,17 @@ extern "C" int pr_device_status(int device, int* status) {
   *h = 0;
   return PR_OK;
 }
+
+// Strided host<->device copy of a [rows, width_bytes] window (cudaMemcpy2DAsync): used to move a
+// slice of heads of a [b, t, h, d] tensor between pinned host memory and a dense device buffer.
+extern "C" int pr_copy_2d(void* dst, long long dst_pitch, const void* src, long long src_pitch,
+                          long long width_bytes, long long rows, int to_device, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(dst && src && width_bytes > 0 && rows > 0 && dst_pitch >= width_bytes && src_pitch >= width_bytes,
+             PR_ERR_BAD_ARG, "bad 2-D copy arguments");
+  PR_CUDA(cudaSetDevice(device));
+  PR_CUDA(cudaMemcpy2DAsync(dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width_bytes, (size_t)rows,
+                            to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost,
+                            static_cast<cudaStream_t>(stream)));
+  return PR_OK;
+}

@@ -1,0 +1,95 @@
+"""Forward + backward of power retention for tensors that live in (pinned) host memory.
+
+The layer is independent across kv heads, so the heads are cut into slices and the slices are
+pipelined over three streams: while slice i computes, slice i+1 is copied in and the results
+of slice i-1 are copied out.  PCIe is full duplex, so the step costs about
+max(copy in, copy out, compute) instead of their sum.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .retention import power_retention
+
+
+def _copy2d(dst, dst_off_bytes, dst_pitch, src, src_off_bytes, src_pitch, width, rows, to_device, dev_index, stream):
+    _lib.check(_lib.lib().pr_copy_2d(ctypes.c_void_p(dst.data_ptr() + dst_off_bytes), ctypes.c_longlong(dst_pitch),
+                                     ctypes.c_void_p(src.data_ptr() + src_off_bytes), ctypes.c_longlong(src_pitch),
+                                     ctypes.c_longlong(width), ctypes.c_longlong(rows), ctypes.c_int(to_device),
+                                     ctypes.c_int(dev_index), ctypes.c_void_p(stream.cuda_stream)), "pr_copy_2d")
+
+
+class HostPipeline:
+    """Reusable buffers and streams for `fwd_bwd` on host tensors of one fixed shape."""
+
+    def __init__(self, b, t, h, d, dtype, device, chunk_size, n_slices=4, gated=True, ratio=1):
+        assert h % n_slices == 0
+        self.b, self.t, self.h, self.d, self.ratio = b, t, h, d, ratio
+        self.hs = h // n_slices
+        self.n_slices, self.chunk, self.gated = n_slices, chunk_size, gated
+        self.dev = torch.device(device)
+        self.idx = self.dev.index if self.dev.index is not None else torch.cuda.current_device()
+        self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
+        mk = lambda hh: [torch.empty(b, t, hh, d, device=self.dev, dtype=dtype) for _ in range(2)]
+        self.Q, self.dO = mk(self.hs * ratio), mk(self.hs * ratio)
+        self.K, self.V = mk(self.hs), mk(self.hs)
+        self.G = torch.empty(b, t, h, device=self.dev, dtype=torch.float32) if gated else None
+        self.dG = torch.empty(b, t, h, device=self.dev, dtype=torch.float32) if gated else None
+        self.res = [None, None]  # results of the slice in flight per parity (kept alive until copied out)
+        self.ev_in = [torch.cuda.Event() for _ in range(n_slices)]
+        self.ev_cmp = [torch.cuda.Event() for _ in range(n_slices)]
+        self.ev_out = [torch.cuda.Event() for _ in range(n_slices)]
+
+    def fwd_bwd(self, Qh, Kh, Vh, Gh, dOh, out):
+        """Qh, dOh [b,t,h*ratio,d], Kh, Vh [b,t,h,d], Gh [b,t,h] pinned host tensors; `out` = dict of
+        pinned host tensors O, dQ, dK, dV (and dlog_G) that receive the results.  Returns after
+        everything has been enqueued; synchronise the device (or `self.s_out`) before reading `out`."""
+        b, t, h, d, hs, r = self.b, self.t, self.h, self.d, self.hs, self.ratio
+        es = Qh.element_size()
+        rows = b * t
+        cur = torch.cuda.current_stream(self.dev)
+        for s in (self.s_in, self.s_cmp, self.s_out):
+            s.wait_stream(cur)
+        if self.gated:
+            with torch.cuda.stream(self.s_in):
+                self.G.copy_(Gh, non_blocking=True)
+        for i in range(self.n_slices):
+            p = i & 1
+            if i >= 2:  # the buffers of this parity are free once slice i-2 has been computed
+                self.s_in.wait_event(self.ev_cmp[i - 2])
+            for host, devbuf, heads in ((Qh, self.Q[p], hs * r), (Kh, self.K[p], hs), (Vh, self.V[p], hs),
+                                        (dOh, self.dO[p], hs * r)):
+                full = heads * self.n_slices
+                _copy2d(devbuf, 0, heads * d * es, host, i * heads * d * es, full * d * es, heads * d * es, rows, 1,
+                        self.idx, self.s_in)
+            self.ev_in[i].record(self.s_in)
+            self.s_cmp.wait_event(self.ev_in[i])
+            if i >= 2:  # results of slice i-2 must have left before their tensors are dropped
+                self.s_cmp.wait_event(self.ev_out[i - 2])
+            with torch.cuda.stream(self.s_cmp):
+                q, k, v = (x.detach().requires_grad_(True) for x in (self.Q[p], self.K[p], self.V[p]))
+                g = None
+                if self.gated:
+                    g = self.G[:, :, i * hs:(i + 1) * hs].contiguous().requires_grad_(True)
+                O = power_retention(q, k, v, g, deg=2, chunk_size=self.chunk)
+                O.backward(self.dO[p])
+                if self.gated:
+                    self.dG[:, :, i * hs:(i + 1) * hs].copy_(g.grad)
+                self.res[p] = (O.detach(), q.grad, k.grad, v.grad)
+            self.ev_cmp[i].record(self.s_cmp)
+            self.s_out.wait_event(self.ev_cmp[i])
+            for name, src, heads in (("O", self.res[p][0], hs * r), ("dQ", self.res[p][1], hs * r),
+                                     ("dK", self.res[p][2], hs), ("dV", self.res[p][3], hs)):
+                full = heads * self.n_slices
+                _copy2d(out[name], i * heads * d * es, full * d * es, src, 0, heads * d * es, heads * d * es, rows, 0,
+                        self.idx, self.s_out)
+            self.ev_out[i].record(self.s_out)
+        if self.gated:
+            self.s_out.wait_event(self.ev_cmp[self.n_slices - 1])
+            with torch.cuda.stream(self.s_out):
+                out["dlog_G"].copy_(self.dG, non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_cmp)
