@@ -26,7 +26,8 @@ constexpr int TILE_BYTES = 128 * 128;   // 128 key rows x 64 features
 constexpr int TW = 64;                  // queries per step
 constexpr int QD_BYTES = TW * 128;      // one query or dO tile
 constexpr int Z_BYTES = 64 * 128;
-constexpr int NBLK = t2_dim(HD) / 64;
+constexpr int DR = ref_dim(HD);
+constexpr int NBLK = DR / 64;           // 40 stages of 64 expanded rows
 constexpr uint32_t TMEM_COLS = 256;     // two CTAs per SM
 constexpr uint32_t COL_S = 0, COL_P = 0, COL_DP = 64, COL_DS = 64, COL_DV = 128, COL_DK = 192, COL_A = 0;
 }  // namespace dkv
@@ -129,7 +130,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
           const int s = blk % NS, ph = (blk / NS) & 1;
           if (!mbar_wait(&z_empty[s], ph ^ 1, &abort_flag)) break;
           mbar_expect_tx(&z_full[s], Z_BYTES);
-          tma_load_2d(smZ + s * Z_BYTES, &tm_ds, &z_full[s], 0, ch * t2_dim(HD) + blk * 64);
+          tma_load_2d(smZ + s * Z_BYTES, &tm_ds, &z_full[s], 0, ch * DR + blk * 64);
         }
       }
     }
@@ -273,30 +274,32 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
       }
       if (ok && n_steps > 0) ok = mbar_wait(&attn_done, 0, &abort_flag);
       tc_fence_after();
-      uint32_t r[32];
-      int cnt = 0;
+      // the discounted row goes back to its own slot of the key tile (first factors are fetched
+      // by a runtime index); the attention products that read the tile have completed
+      if (ok) {
 #pragma unroll
-      for (int a = 0; a < HD; ++a) {
-        const uint32_t ka = (a & 1) ? dup_hi(k2[a >> 1]) : dup_lo(k2[a >> 1]);
-#pragma unroll
-        for (int j = a >> 1; j < HD / 2; ++j) {
-          r[cnt & 31] = Pack2<T>::mul(ka, k2[j]);
-          ++cnt;
-          if ((cnt & 31) == 0) {
-            const int it = (cnt >> 5) - 1;  // 0..NBLK-1
-            const int s = it % NS, ph = (it / NS) & 1;
-            if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
-            if (ok) {
-              tc_fence_after();
-              tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
-              tmem_wait_st();
-              tc_fence_before();
-            }
-            __syncwarp();
-            if (ok && lane == 0) mbar_arrive(&a_full[s]);
-          }
-        }
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(smK + swz128(tid, j)) = make_uint4(k2[4 * j], k2[4 * j + 1], k2[4 * j + 2], k2[4 * j + 3]);
       }
+      int it = 0;
+      static_for<0, HD / 16>([&](auto yc) {
+        constexpr int Y = decltype(yc)::value;
+#pragma unroll 1
+        for (int a0 = 0; a0 < 16 * (Y + 1); a0 += 4, ++it) {
+          uint32_t r[32];
+          expand_stage<T, Y>(smK, tid, a0, k2, r);
+          const int s = it % NS, ph = (it / NS) & 1;
+          if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+          if (ok) {
+            tc_fence_after();
+            tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+            tmem_wait_st();
+            tc_fence_before();
+          }
+          __syncwarp();
+          if (ok && lane == 0) mbar_arrive(&a_full[s]);
+        }
+      });
     }
 
     if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
@@ -403,7 +406,7 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box, true))) return rc;
   if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box, true))) return rc;
   if (wdS) {
-    uint64_t dz[2] = {64, (uint64_t)b * p.n_chunks * h * t2_dim(d)};
+    uint64_t dz[2] = {64, (uint64_t)b * p.n_chunks * h * ref_dim(d)};
     uint64_t st[2] = {0, 128};
     uint32_t bz[2] = {64, 64};
     if ((rc = make_tmap(&tm_ds, wdS, 2, 2, dz, st, bz, true))) return rc;

@@ -33,7 +33,8 @@ constexpr int TILE_BYTES = 128 * 128;  // 128 rows x 64 16-bit features
 constexpr int TW = 64;                 // keys per attention step
 constexpr int KV_BYTES = TW * 128;     // one key or value tile
 constexpr int Z_BYTES = 64 * 128;      // 64 expanded rows x 64 features
-constexpr int NBLK = t2_dim(HD) / 64;  // 33 blocks of 64 expanded rows
+constexpr int DR = ref_dim(HD);        // 2560 expanded rows
+constexpr int NBLK = DR / 64;          // 40 stages of 64 expanded rows (4 first factors x 16)
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t COL_ACC = 0, COL_U = 64, COL_S = 128, COL_A = 128;  // S: 2 buffers x 64 columns, P aliased
 }  // namespace co
@@ -144,7 +145,7 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
           const int s = blk % NS, ph = (blk / NS) & 1;
           if (!mbar_wait(&z_empty[s], ph ^ 1, &abort_flag)) break;
           mbar_expect_tx(&z_full[s], Z_BYTES);
-          tma_load_2d(smZ + s * Z_BYTES, &tm_z, &z_full[s], 0, ch * t2_dim(HD) + blk * 64);
+          tma_load_2d(smZ + s * Z_BYTES, &tm_z, &z_full[s], 0, ch * DR + blk * 64);
         }
       }
     }
@@ -308,31 +309,33 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_full[0]);
       }
-      // items 1..NBLK: 64 expanded entries (32 packed products) each
-      uint32_t r[32];
-      int cnt = 0;
+      // items 1..NBLK: 64 expanded entries (32 packed products) each.  The gated row goes back
+      // to its own slot of the query tile so that the first factor can be fetched by a runtime
+      // index; the loop over first factors then has a body of 32 multiplies per stage.
+      if (ok) {
 #pragma unroll
-      for (int a = 0; a < HD; ++a) {
-        const uint32_t qa = (a & 1) ? dup_hi(q2[a >> 1]) : dup_lo(q2[a >> 1]);
-#pragma unroll
-        for (int j = a >> 1; j < HD / 2; ++j) {
-          r[cnt & 31] = Pack2<T>::mul(qa, q2[j]);
-          ++cnt;
-          if ((cnt & 31) == 0) {
-            const int it = cnt >> 5;  // 1..NBLK
-            const int s = it % NS, ph = (it / NS) & 1;
-            if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
-            if (ok) {
-              tc_fence_after();
-              tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
-              tmem_wait_st();
-              tc_fence_before();
-            }
-            __syncwarp();
-            if (ok && lane == 0) mbar_arrive(&a_full[s]);
-          }
-        }
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(smQ + swz128(tid, j)) = make_uint4(q2[4 * j], q2[4 * j + 1], q2[4 * j + 2], q2[4 * j + 3]);
       }
+      int it = 1;
+      static_for<0, HD / 16>([&](auto yc) {
+        constexpr int Y = decltype(yc)::value;
+#pragma unroll 1
+        for (int a0 = 0; a0 < 16 * (Y + 1); a0 += 4, ++it) {
+          uint32_t r[32];
+          expand_stage<T, Y>(smQ, tid, a0, q2, r);
+          const int s = it % NS, ph = (it / NS) & 1;
+          if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+          if (ok) {
+            tc_fence_after();
+            tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+            tmem_wait_st();
+            tc_fence_before();
+          }
+          __syncwarp();
+          if (ok && lane == 0) mbar_arrive(&a_full[s]);
+        }
+      });
     }
 
     if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
@@ -438,7 +441,7 @@ extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int 
     }
   }
   if (with_state) {
-    uint64_t dz[2] = {64, (uint64_t)b * n_chunks * h * t2_dim(d)};
+    uint64_t dz[2] = {64, (uint64_t)b * n_chunks * h * ref_dim(d)};
     uint64_t dg[2] = {64, (uint64_t)b * n_chunks * h * d};
     uint64_t st[2] = {0, 128};
     uint32_t box[2] = {64, 64};

@@ -43,7 +43,7 @@ struct ChunkStateParams {
   int group;        // operand heads summed into one output head (GQA ratio in backward)
   int c, cp;        // chunk length, padded to 64
   int n_chunks;     // chunks per batch element
-  int key_weights;  // 1: weights {1,2,0}; 0: weights {1,1,0}
+  int key_weights;  // 1: weight 2 on pairs from different 16-blocks; 0: all weights 1
   void* out;        // [b, n, nh, D2, 64]
   float* gram;      // [b, n, nh, 64, 64] or null
   int* status;
@@ -171,12 +171,12 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     const int grp = warp >> 2;
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const int D2 = t2_dim(HD);
+    const int D2 = ref_dim(HD);
     const int tile = (int)blockIdx.x * NG + grp;
     int drow = tile * 128 + row_in_tile;
     const bool valid = !gram_cta && drow < D2;  // rows past the end still take part in the pipeline
     int a = 0, b = 0;
-    if (valid) t2_decode(HD, drow, &a, &b);
+    if (valid) ref_decode(drow, &a, &b);
     bool ok = true;
     if (!gram_cta) {
       for (int it = 0; it < total; ++it) {
@@ -223,7 +223,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
                                  __uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3]));
         }
       } else if (valid) {
-        const float wgt = p.key_weights ? t2_key_weight(a, b) : (b < a ? 0.f : 1.f);
+        const float wgt = p.key_weights ? ref_key_weight(a, b) : 1.f;
         uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.out) + ((size_t)ch * D2 + drow) * HD);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -273,7 +273,7 @@ extern "C" int pr_chunk_state(int dtype, int b, int t, int nh, int group, int d,
              "gram requested without a scaled operand");
   PR_CUDA(cudaSetDevice(device));
   ChunkStateParams p;
-  p.n_tiles = (t2_dim(d) + 127) / 128;
+  p.n_tiles = (ref_dim(d) + 127) / 128;
   p.nh = nh;
   p.group = group;
   p.c = c;

@@ -244,13 +244,13 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
   }
 }
 
-// new_state (exact layout) = decay * state + S (internal layout); new_sok = decay * sok + w * gram.
+// new_state (exact layout) = decay * state + S (chunk-state layout); new_sok = decay * sok + w * gram.
 template <typename T>
 __global__ void state_merge_kernel(const T* __restrict__ state, const float* __restrict__ sok,
                                    const T* __restrict__ S, const float* __restrict__ gram,
                                    const float* __restrict__ a_last, T* __restrict__ new_state,
                                    float* __restrict__ new_sok, int bh_total) {
-  constexpr int HD = dec::HD, DEX = dec::DEX, D2 = t2_dim(HD);
+  constexpr int HD = dec::HD, DEX = dec::DEX, DR = ref_dim(HD);
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 elements
   const size_t total = (size_t)bh_total * DEX * 8;
   if (gid >= total) return;
@@ -260,19 +260,27 @@ __global__ void state_merge_kernel(const T* __restrict__ state, const float* __r
   const int bh = (int)(rowg / DEX);
   int a, b;
   exact_decode(D, &a, &b);
-  const int row_t2 = t2_row_offset(HD, a) + (b - 2 * (a >> 1));
+  // chunk-state rows of the pair: (a, b) always exists (a <= b); inside a 16-block the mirrored
+  // entry (b, a) holds the other half of the pair's weight
+  const int yb = b >> 4;
+  const int row1 = ref_block_base(yb) + 16 * a + (b & 15);
+  const bool mirrored = (a != b) && ((a >> 4) == yb);
+  const int row2 = ref_block_base(yb) + 16 * b + (a & 15);
   const float decay = (state != nullptr) ? (a_last ? __expf(a_last[bh]) : 1.f) : 0.f;
-  const uint4 sv = *reinterpret_cast<const uint4*>(S + ((size_t)bh * D2 + row_t2) * HD + sub * 8);
+  const uint4 sv = *reinterpret_cast<const uint4*>(S + ((size_t)bh * DR + row1) * HD + sub * 8);
+  uint4 sv2 = make_uint4(0, 0, 0, 0);
+  if (mirrored) sv2 = *reinterpret_cast<const uint4*>(S + ((size_t)bh * DR + row2) * HD + sub * 8);
   uint4 ov = make_uint4(0, 0, 0, 0);
   if (state != nullptr) ov = *reinterpret_cast<const uint4*>(state + ((size_t)bh * DEX + D) * HD + sub * 8);
-  const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w}, ow[4] = {ov.x, ov.y, ov.z, ov.w};
+  const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w}, sw2[4] = {sv2.x, sv2.y, sv2.z, sv2.w},
+                 ow[4] = {ov.x, ov.y, ov.z, ov.w};
   uint32_t rw[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    const float2 s2 = Pack2<T>::to_f32(sw[k]), o2 = Pack2<T>::to_f32(ow[k]);
+    const float2 s2 = Pack2<T>::to_f32(sw[k]), s3 = Pack2<T>::to_f32(sw2[k]), o2 = Pack2<T>::to_f32(ow[k]);
     // the reference rounds state*decay to the state dtype before adding (:374-382)
     const float2 od = Pack2<T>::to_f32(Pack2<T>::from_f32(o2.x * decay, o2.y * decay));
-    rw[k] = Pack2<T>::from_f32(od.x + s2.x, od.y + s2.y);
+    rw[k] = Pack2<T>::from_f32(od.x + s2.x + s3.x, od.y + s2.y + s3.y);
   }
   *reinterpret_cast<uint4*>(new_state + ((size_t)bh * DEX + D) * HD + sub * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
   if (sub == 0) {

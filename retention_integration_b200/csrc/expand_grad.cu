@@ -27,38 +27,18 @@ namespace pr {
 
 namespace eg {
 constexpr int HD = 64;
-constexpr int D2 = t2_dim(HD);           // 2112
-constexpr int NT = (D2 + 127) / 128;     // 17 tiles, the last one 64 rows wide
+constexpr int D2 = ref_dim(HD);          // 2560 expanded rows (block layout, see layout.cuh)
+constexpr int NT = D2 / 128;             // 20 tiles of 128 rows = 8 first factors x 16
 constexpr int THREADS = 320;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9 MMA
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int G_BYTES = 64 * 128;
-constexpr int NSS = 6;                   // state tiles in flight (TMA latency x L2 bandwidth needs ~100 KB per SM)
+constexpr int NSS = 4;                   // state tiles in flight (TMA latency x L2 bandwidth needs ~100 KB per SM)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int ROWS = 256;                // token rows per CTA: two row tiles of 128
 constexpr uint32_t COL_D = 0;            // 2 x 128 columns (one buffer per row tile)
 constexpr uint32_t COL_U = 256;          // 2 x 64
 constexpr uint32_t COL_XA = 384;         // 2 x 32
 
-__host__ __device__ constexpr int t2_a(int idx) {
-  int p = 0;
-  while (p + 1 <= HD / 2 && 2 * (p + 1) * (HD - (p + 1) + 1) <= idx) ++p;
-  const int rem = idx - 2 * p * (HD - p + 1);
-  return rem < HD - 2 * p ? 2 * p : 2 * p + 1;
-}
-__host__ __device__ constexpr int t2_b(int idx) {
-  int p = 0;
-  while (p + 1 <= HD / 2 && 2 * (p + 1) * (HD - (p + 1) + 1) <= idx) ++p;
-  const int rem = idx - 2 * p * (HD - p + 1);
-  return rem < HD - 2 * p ? 2 * p + rem : 2 * p + rem - (HD - 2 * p);
-}
-
-template <int I, int N, typename F>
-__device__ __forceinline__ void static_for(F&& f) {
-  if constexpr (I < N) {
-    f(std::integral_constant<int, I>{});
-    static_for<I + 1, N>(f);
-  }
-}
 }  // namespace eg
 
 struct ExpandGradParams {
@@ -116,6 +96,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
   uint8_t* smX = smW + 2 * TILE_BYTES;          // 2 x TILE_BYTES
   uint8_t* smS = smX + 2 * TILE_BYTES;          // NSS x TILE_BYTES (ring of state tiles)
   uint8_t* smG = smS + NSS * TILE_BYTES;        // hi, lo
+  float* smR = reinterpret_cast<float*>(smG + 2 * G_BYTES);  // 2 x [64][128] fp32: dx~ terms indexed at run time
 
   if (tid == 0) {
     abort_flag = 0;
@@ -168,7 +149,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         const int s = nt % NSS, ph = (nt / NSS) & 1;
         ok = mbar_wait(&s_full[s], ph, &abort_flag);
         if (!ok) break;
-        const uint32_t idesc = umma_idesc(128, nt == NT - 1 ? 64 : 128, Pack2<T>::is_bf16, false, false);
+        const uint32_t idesc = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
         const uint32_t s_addr = smem_u32(smS + s * TILE_BYTES);
         for (int rt = 0; rt < 2 && ok; ++rt) {
           ok = mbar_wait(&d_empty[rt], (nt & 1) ^ 1, &abort_flag);
@@ -221,7 +202,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     float x[HD], dx[HD];
     {
       uint32_t xp[32];
-      const uint8_t* xs = smX + rt * TILE_BYTES;
+      uint8_t* xs = smX + rt * TILE_BYTES;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const uint4 v = *reinterpret_cast<const uint4*>(xs + swz128(r, j));
@@ -235,6 +216,12 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
           x[8 * j + 2 * k + 1] = rounded.y;
         }
       }
+      // the gated row replaces the raw one in this thread's slot of the tile (fetched by a
+      // run-time index in the drain)
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(smX + rt * TILE_BYTES + swz128(r, j)) =
+            make_uint4(xp[4 * j], xp[4 * j + 1], xp[4 * j + 2], xp[4 * j + 3]);
       if (ok) {
         tmem_st32(tmem + lane_addr + COL_XA + rt * 32, xp);
         tmem_wait_st();
@@ -245,45 +232,58 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     }
 #pragma unroll
     for (int e = 0; e < HD; ++e) dx[e] = 0.f;
+    // dx~[a] for the first factor a (a run-time index in the loop below) is accumulated in this
+    // thread's private column of shared memory; dx~[b] for the second factor stays in registers
+    float* sdx = smR + rt * 64 * 128 + r;
+#pragma unroll
+    for (int e = 0; e < HD; ++e) sdx[e * 128] = 0.f;
+    const uint8_t* xrow = smX + rt * TILE_BYTES;  // holds the gated row again (written above)
 
-    static_for<0, NT>([&](auto nt_c) {
-      constexpr int nt = decltype(nt_c)::value;
-      constexpr int ncols = (nt == NT - 1) ? D2 - 128 * (NT - 1) : 128;
-      if (ok) ok = mbar_wait(&d_full[rt], nt & 1, &abort_flag);
-      tc_fence_after();
-      if (ok) {
-        static_for<0, ncols / 32>([&](auto q_c) {
-          constexpr int q = decltype(q_c)::value;
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_addr + col_d + q * 32, v);
+    int nt = 0;
+    static_for<0, HD / 16>([&](auto yc) {
+      constexpr int Y = decltype(yc)::value;
+#pragma unroll 1
+      for (int tt = 0; tt < 2 * (Y + 1); ++tt, ++nt) {
+        if (ok) ok = mbar_wait(&d_full[rt], nt & 1, &abort_flag);
+        tc_fence_after();
+        if (!ok) continue;
+        // two register buffers: the load of the next 32 columns is in flight while these are used
+        uint32_t v[2][32];
+        tmem_ld32(tmem + lane_addr + col_d, v[0]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
           tmem_wait_ld();
-          if constexpr (q == ncols / 32 - 1) {
+          if (q < 3) {
+            tmem_ld32(tmem + lane_addr + col_d + (q + 1) * 32, v[(q + 1) & 1]);
+          } else {
             // all of this thread's reads of the buffer are done
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&d_empty[rt]);
           }
-          float ra0 = 0.f, ra1 = 0.f;
-          static_for<0, 32>([&](auto j_c) {
-            constexpr int j = decltype(j_c)::value;
-            constexpr int D = nt * 128 + q * 32 + j;
-            constexpr int a = t2_a(D), b = t2_b(D);
-            const float val = __uint_as_float(v[j]);
-            dx[b] = fmaf(val, x[a], dx[b]);
-            if constexpr (j & 1)
-              ra1 = fmaf(val, x[b], ra1);
-            else
-              ra0 = fmaf(val, x[b], ra0);
-            constexpr bool row_ends = (j == 31) || (t2_a(D + 1) != a);
-            if constexpr (row_ends) {
-              dx[a] += ra0 + ra1;
-              ra0 = 0.f;
-              ra1 = 0.f;
+          const int a = 8 * tt + 2 * q;  // first factors a, a+1 (a even)
+          const float2 xa2 = Pack2<T>::to_f32(
+              *reinterpret_cast<const uint32_t*>(xrow + swz128(r, a >> 3) + ((a & 7) << 1)));
+#pragma unroll
+          for (int aa = 0; aa < 2; ++aa) {
+            const float xa = aa ? xa2.y : xa2.x;
+            float ra0 = 0.f, ra1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float val = __uint_as_float(v[q & 1][16 * aa + i]);
+              dx[16 * Y + i] = fmaf(val, xa, dx[16 * Y + i]);
+              if (i & 1)
+                ra1 = fmaf(val, x[16 * Y + i], ra1);
+              else
+                ra0 = fmaf(val, x[16 * Y + i], ra0);
             }
-          });
-        });
+            sdx[(a + aa) * 128] += ra0 + ra1;
+          }
+        }
       }
     });
+#pragma unroll
+    for (int e = 0; e < HD; ++e) dx[e] += sdx[e * 128];
 
     if (ok) ok = mbar_wait(&u_full[rt], 0, &abort_flag);
     tc_fence_after();
@@ -369,7 +369,7 @@ extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int
     if ((rc = make_tmap(&tm_ghi, g_hi, 2, 2, dg, st, box_g, true))) return rc;
     if ((rc = make_tmap(&tm_glo, g_lo, 2, 2, dg, st, box_g, true))) return rc;
   }
-  const size_t smem = 1024 + (4 + NSS) * TILE_BYTES + 2 * G_BYTES;
+  const size_t smem = 1024 + (4 + NSS) * TILE_BYTES + 2 * G_BYTES + 2 * 64 * 128 * 4;
   dim3 grid(p.tiles_per_chunk * n, hx, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {

@@ -1,45 +1,36 @@
-// Internal layout of the symmetric-power expansion for deg = 2 ("pair-aligned
-// triangle").  For head dim d (even) row a holds the products x[a]*x[b] for
-// b = 2*floor(a/2) .. d-1, rows stored one after another:
+// Layout of the symmetric-power expansion for deg = 2 used by every kernel and by the chunk
+// states in HBM: the reference package's own layout (retention/_update_state/reference.py:5-29,
+// retention/_query_state/reference.py:11-33).  With B = 16 and head dim d,
 //
-//     D2 = d*(d+2)/2            (2112 for d = 64; the exact C(d+1,2) is 2080)
+//     entry  I(y, a, i) = 256*y*(y+1)/2 + 16*a + i   holds  x[a] * x[16*y + i]
+//     for  y in [0, d/16),  a in [0, 16*(y+1)),  i in [0, 16);      DR = 2560 at d = 64.
 //
-// Every row starts at an even b and has even length, so two consecutive entries
-// always share `a` and form an aligned pair (x[b], x[b+1]) - the expansion is one
-// packed 16-bit multiply per two entries with no shuffling.  The d/2 entries with
-// b = a-1 (a odd) duplicate (a-1, a); they carry weight 0 on the key side, so the
-// states hold zeros there and the query side may leave its products in place.
-// Key-side weights: 1 for a == b, 2 for b > a, 0 for b < a.  (The reference's layout,
-// retention/_update_state/reference.py:5-29, pads whole 16x16 diagonal blocks
-// instead: 2560 at d = 64.)
+// Every group (y, a) is 16 consecutive entries with a fixed first factor x[a] and an aligned run
+// of second factors, so it is 8 packed 16-bit multiplies (x_a,x_a)*(x_b,x_{b+1}) and exactly one
+// K = 16 step of tcgen05.mma; the expansion and its gradient are short loops over a with the
+// register indices of the second factor known at compile time.  Pairs whose indices fall in the
+// same 16-block appear twice, (a,b) and (b,a), each with weight 1; pairs from different blocks
+// appear once and carry weight 2 on the key side.  The exact count C(d+1,2) = 2080 is what the
+// algorithmic FLOPs are quoted with; the padded layout costs 23 % more tensor work but lets the
+// CUDA-core side run from the instruction cache instead of streaming unrolled code.
 #pragma once
 #include <stdint.h>
 
 namespace pr {
 
-__host__ __device__ constexpr int t2_dim(int d) { return d * (d + 2) / 2; }
-
-// first entry of row a: rows 2p and 2p+1 both have length d - 2p
-__host__ __device__ constexpr int t2_row_offset(int d, int a) {
-  const int p = a >> 1;
-  return 2 * p * (d - p + 1) + ((a & 1) ? (d - 2 * p) : 0);
-}
+__host__ __device__ constexpr int ref_dim(int d) { return 128 * (d / 16) * (d / 16 + 1); }
+// first entry of b-block y
+__host__ __device__ constexpr int ref_block_base(int y) { return 128 * y * (y + 1); }
 
 // entry index -> (a, b)
-__host__ __device__ inline void t2_decode(int d, int idx, int* a, int* b) {
-  int p = 0;
-  while (p + 1 <= d / 2 && 2 * (p + 1) * (d - (p + 1) + 1) <= idx) ++p;
-  int rem = idx - 2 * p * (d - p + 1);
-  const int len = d - 2 * p;
-  if (rem < len) {
-    *a = 2 * p;
-    *b = 2 * p + rem;
-  } else {
-    *a = 2 * p + 1;
-    *b = 2 * p + rem - len;
-  }
+__host__ __device__ inline void ref_decode(int idx, int* a, int* b) {
+  int y = 0;
+  while (ref_block_base(y + 1) <= idx) ++y;
+  const int rem = idx - ref_block_base(y);
+  *a = rem >> 4;
+  *b = 16 * y + (rem & 15);
 }
-
-__host__ __device__ inline float t2_key_weight(int a, int b) { return a == b ? 1.f : (b > a ? 2.f : 0.f); }
+// key-side weight of entry (a, b): 2 when a lies left of b's 16-block
+__host__ __device__ inline float ref_key_weight(int a, int b) { return a < (b & ~15) ? 2.f : 1.f; }
 
 }  // namespace pr

@@ -93,7 +93,7 @@ scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restr
 
 // dY, dX: [b, n, h, E] (may alias); Y: [b, n, h, E] states entering each chunk;
 // dA_part: [b, h, gridDim.x, n] per-block partial sums of exp(A[m]) * <Y[m], G[m+1]>.
-// row_weights: apply the key-side weights {1,2,0} of expanded row (e / row_len) to dX.
+// row_weights: apply the key-side weight (1 or 2) of expanded row (e / row_len) to dX.
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
 scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict__ dX, const float* __restrict__ A,
@@ -116,8 +116,8 @@ scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict
   float wgt = 1.f;
   if (active && row_weights) {
     int a, b;
-    t2_decode(row_len, (int)(e0 / row_len), &a, &b);
-    wgt = t2_key_weight(a, b);
+    ref_decode((int)(e0 / row_len), &a, &b);
+    wgt = ref_key_weight(a, b);
   }
   const size_t stride = (size_t)h * E;
   const size_t base = ((size_t)batch * n * h + head) * E + e0;

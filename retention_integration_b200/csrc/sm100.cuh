@@ -12,7 +12,19 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace pr {
+
+// compile-time loop: f(std::integral_constant<int, I>{}) for I in [I0, N)
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+
 
 #ifndef PR_WAIT_BUDGET_NS
 #define PR_WAIT_BUDGET_NS 2000000000ull  // 2 s per wait, far above any kernel's run time
@@ -274,6 +286,22 @@ struct Pack2<__half> {
   }
   static constexpr bool is_bf16 = false;
 };
+// Expansion of one stage of the block layout (see layout.cuh): the 64 entries of four
+// consecutive first factors a0..a0+3 (a0 a multiple of 4) against the 16 second factors of
+// block Y, as 32 packed products.  `row` is the thread's own gated row in shared memory
+// (128 bytes, 128-byte swizzle, row index `r`), `x2` the same row as 32 packed registers.
+template <typename T, int Y>
+__device__ __forceinline__ void expand_stage(const uint8_t* tile, int r, int a0, const uint32_t (&x2)[32],
+                                             uint32_t (&out)[32]) {
+  const uint2 h = *reinterpret_cast<const uint2*>(tile + swz128(r, a0 >> 3) + ((a0 & 7) << 1));
+  const uint32_t xa[4] = {__byte_perm(h.x, h.x, 0x1010), __byte_perm(h.x, h.x, 0x3232),
+                          __byte_perm(h.y, h.y, 0x1010), __byte_perm(h.y, h.y, 0x3232)};
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[8 * k + j] = Pack2<T>::mul(xa[k], x2[8 * Y + j]);
+}
+
 // duplicate the low / high 16-bit half of a packed pair into both halves
 __device__ __forceinline__ uint32_t dup_lo(uint32_t x) { return __byte_perm(x, x, 0x1010); }
 __device__ __forceinline__ uint32_t dup_hi(uint32_t x) { return __byte_perm(x, x, 0x3232); }

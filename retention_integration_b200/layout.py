@@ -1,18 +1,16 @@
 """Layouts of the degree-2 symmetric-power expansion and converters between them.
 
-Three layouts of the expanded dimension exist for head dim d:
+Two layouts of the expanded dimension exist for head dim d:
 
 * ``exact``      C(d+1, 2) entries, pair (a <= b) at  a*d - a*(a-1)/2 + (b-a)
                  (2080 at d = 64).  States returned by ``power_retention_inference``.
-* ``t2``         the kernels' internal pair-aligned triangle, d*(d+2)/2 entries
-                 (2112 at d = 64): row a holds b = 2*floor(a/2) .. d-1; the d/2 entries
-                 with b = a-1 are zero in every state.
 * ``reference``  the reference package's padded layout (2560 at d = 64): entry
                  256*y*(y+1)/2 + 16*x + i  holds the pair (x, 16*y+i) for x < 16*(y+1)
-                 (retention/_update_state/reference.py:5-29).
+                 (retention/_update_state/reference.py:5-29).  The kernels and the chunk
+                 states of the training path use this layout too.
 
 States and sums of keys carry the key-side multiplicity: weight 2 on a pair a != b in
-``exact`` and ``t2``.  The reference stores weight 2 only on pairs whose two indices lie
+``exact``.  The reference stores weight 2 only on pairs whose two indices lie
 in different 16-blocks; inside a diagonal block it stores (a,b) and (b,a) separately with
 weight 1, so converting to the reference layout halves those entries and converting
 back adds the two halves.
@@ -28,10 +26,6 @@ def exact_dim(d: int) -> int:
     return d * (d + 1) // 2
 
 
-def t2_dim(d: int) -> int:
-    return d * (d + 2) // 2
-
-
 def reference_dim(d: int) -> int:
     nb = d // 16
     return 256 * nb * (nb + 1) // 2
@@ -41,19 +35,10 @@ def _exact_index(d: int, a: int, b: int) -> int:
     return a * d - a * (a - 1) // 2 + (b - a)
 
 
-def _t2_index(d: int, a: int, b: int) -> int:
-    p = a // 2
-    return 2 * p * (d - p + 1) + ((d - 2 * p) if a % 2 else 0) + (b - 2 * p)
-
-
 @lru_cache(maxsize=None)
 def _tables(d: int):
-    """(t2_from_exact [D2] with -1 at ghosts, ref_src_exact [Dref], ref_coef [Dref],
-    exact_from_ref_1 [Dex], exact_from_ref_2 [Dex] (-1 if single))."""
-    t2_from_exact = torch.full((t2_dim(d),), -1, dtype=torch.long)
-    for a in range(d):
-        for b in range(a, d):
-            t2_from_exact[_t2_index(d, a, b)] = _exact_index(d, a, b)
+    """(ref_src_exact [Dref], ref_coef [Dref], exact_from_ref_1 [Dex], exact_from_ref_2 [Dex]
+    (-1 if the pair has a single entry))."""
     ref_src = torch.empty(reference_dim(d), dtype=torch.long)
     ref_coef = torch.empty(reference_dim(d), dtype=torch.float32)
     ex1 = torch.full((exact_dim(d),), -1, dtype=torch.long)
@@ -73,32 +58,16 @@ def _tables(d: int):
                     ex1[e] = I
                 else:
                     ex2[e] = I
-    return t2_from_exact, ref_src, ref_coef, ex1, ex2
+    return ref_src, ref_coef, ex1, ex2
 
 
 def _move(x: torch.Tensor, dim: int):
     return x.movedim(dim, -1)
 
 
-def exact_to_t2(x: torch.Tensor, d: int, dim: int = -2) -> torch.Tensor:
-    """Insert the zero ghost entries.  `dim` is the expanded axis."""
-    t2_from_exact = _tables(d)[0].to(x.device)
-    xm = _move(x, dim)
-    out = xm.index_select(-1, t2_from_exact.clamp_min(0)) * (t2_from_exact >= 0).to(x.dtype)
-    return out.movedim(-1, dim).contiguous()
-
-
-def t2_to_exact(x: torch.Tensor, d: int, dim: int = -2) -> torch.Tensor:
-    t2_from_exact = _tables(d)[0]
-    keep = torch.nonzero(t2_from_exact >= 0).squeeze(-1)
-    order = torch.argsort(t2_from_exact[keep])
-    idx = keep[order].to(x.device)
-    return _move(x, dim).index_select(-1, idx).movedim(-1, dim).contiguous()
-
-
 def exact_to_reference(x: torch.Tensor, d: int, dim: int = -2) -> torch.Tensor:
     """State / sum-of-keys in the exact layout -> the reference package's layout."""
-    _, ref_src, ref_coef, _, _ = _tables(d)
+    ref_src, ref_coef, _, _ = _tables(d)
     xm = _move(x, dim)
     out = xm.index_select(-1, ref_src.to(x.device)) * ref_coef.to(device=x.device, dtype=x.dtype)
     return out.movedim(-1, dim).contiguous()
@@ -106,7 +75,7 @@ def exact_to_reference(x: torch.Tensor, d: int, dim: int = -2) -> torch.Tensor:
 
 def reference_to_exact(x: torch.Tensor, d: int, dim: int = -2) -> torch.Tensor:
     """The reference package's layout -> exact (the two halves of in-block pairs are added)."""
-    _, _, _, ex1, ex2 = _tables(d)
+    _, _, ex1, ex2 = _tables(d)
     xm = _move(x, dim)
     out = xm.index_select(-1, ex1.to(x.device))
     second = xm.index_select(-1, ex2.clamp_min(0).to(x.device)) * (ex2 >= 0).to(device=x.device, dtype=x.dtype)

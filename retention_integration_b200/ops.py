@@ -58,9 +58,9 @@ def _call(name: str, *args):
     launch_log.count += 1
 
 
-def t2_dim(d: int) -> int:
-    """Rows of the internal pair-aligned expansion layout (2112 for d = 64)."""
-    return d * (d + 2) // 2
+def state_rows(d: int) -> int:
+    """Rows of a chunk state: the reference package's expansion layout (2560 for d = 64)."""
+    return 128 * (d // 16) * (d // 16 + 1)
 
 
 def _dev(t: torch.Tensor) -> int:
@@ -111,11 +111,11 @@ def dout_prep(O: torch.Tensor, dO: torch.Tensor, l: torch.Tensor):
 
 
 def chunk_state(xt: torch.Tensor, xts, v: torch.Tensor, c: int, nh: int, key_weights: bool, want_gram: bool):
-    """xt [b,n,hx,d,cp] (hx = nh*group), v [b,t,hx,d] -> (S [b,n,nh,D2,d], gram [b,n,nh,d,d] fp32 or None)."""
+    """xt [b,n,hx,d,cp] (hx = nh*group), v [b,t,hx,d] -> (S [b,n,nh,DR,d], gram [b,n,nh,d,d] fp32 or None)."""
     b, n, hx, d, cp = xt.shape
     t = v.shape[1]
     group = hx // nh
-    out = torch.empty(b, n, nh, t2_dim(d), d, device=xt.device, dtype=xt.dtype)
+    out = torch.empty(b, n, nh, state_rows(d), d, device=xt.device, dtype=xt.dtype)
     gram = torch.empty(b, n, nh, d, d, device=xt.device, dtype=torch.float32) if want_gram else None
     if want_gram and xts is None:
         xts = xt
@@ -201,7 +201,7 @@ def gram_scan_bwd(dZg: torch.Tensor, Zg: torch.Tensor, A: torch.Tensor, dtype, c
 def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, state_from_chunk: int, scale: float,
               normalize: bool = True, q_gate_last: bool = False, want_l: bool = True):
     """Fused attention + state read-out.  Q [b,n*cq,hq,d]; K,V [b,n*ck,h,d] or None; a [b,n*ck,h] or None;
-    Z [b,n,h,D2,d] or None.  Returns (O [b,n*cq,hq,d], l [b,n*cq,hq] fp32 or None)."""
+    Z [b,n,h,DR,d] or None.  Returns (O [b,n*cq,hq,d], l [b,n*cq,hq] fp32 or None)."""
     b, tq, hq, d = Q.shape
     h = K.shape[2] if K is not None else Z.shape[2]
     O = torch.empty_like(Q)
@@ -215,7 +215,7 @@ def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, stat
 
 def expand_grad(W, X, State, g_hi, g_lo, a, A, row_g, c: int, h: int, query_side: bool, scale: float,
                 gram_mult: float, chunk_lo: int, chunk_hi: int):
-    """Gradient through the expansion.  W, X [b,t,hx,d]; State [b,n,h,D2,d]; g_hi/g_lo [b,n,h,d,d].
+    """Gradient through the expansion.  W, X [b,t,hx,d]; State [b,n,h,DR,d]; g_hi/g_lo [b,n,h,d,d].
     Returns (dX [b,t,hx,d] fp32, gdot [b,t,hx] fp32)."""
     b, t, hx, d = X.shape
     dX = torch.empty(b, t, hx, d, device=X.device, dtype=torch.float32)
@@ -291,7 +291,7 @@ def decode_finish(Q, K, V, a, scale: float, part_y, part_l, h: int):
 
 
 def state_merge(state, sum_of_keys, S, gram, a_last):
-    """new_state = state*exp(a_last) + S (internal -> exact layout); S [b,1,h,D2,d], gram [b,1,h,d,d]."""
+    """new_state = state*exp(a_last) + S (chunk-state -> exact layout); S [b,1,h,DR,d], gram [b,1,h,d,d]."""
     b, _, h, _, d = S.shape
     D = d * (d + 1) // 2
     new_state = torch.empty(b, h, D, d, device=S.device, dtype=S.dtype)

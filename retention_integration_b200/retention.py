@@ -205,7 +205,7 @@ def power_retention_inference(Q, K, V, log_G=None, initial_state=None, sum_of_ke
             Y, _ = ops.chunk_out(Q, K, V, a, None, None, None, 1, tq, tk, 1, scale, want_l=False)
         else:
             # several query tokens against a state: the tensor-core path, state converted to its layout
-            Z = layout.exact_to_t2(initial_state, d, dim=-2).unsqueeze(1).contiguous()
+            Z = layout.exact_to_reference(initial_state, d, dim=-2).unsqueeze(1).contiguous()
             zg = layout.exact_sum_of_keys_to_gram(sum_of_keys, d)
             zhi = zg.to(Q.dtype)
             zlo = (zg - zhi.float()).to(Q.dtype)

@@ -13,7 +13,7 @@ def _weighted_exact(k):
 
 
 def test_dims():
-    assert (layout.exact_dim(64), layout.t2_dim(64), layout.reference_dim(64)) == (2080, 2112, 2560)
+    assert (layout.exact_dim(64), layout.reference_dim(64)) == (2080, 2560)
     assert layout.reference_dim(32) == oracle.expanded_dim(32) == 768
     assert layout.reference_dim(128) == oracle.expanded_dim(128) == 9216
 
@@ -34,16 +34,6 @@ def test_query_key_inner_product_is_squared_dot():
     ia, ib = torch.triu_indices(d, d)
     phi_q = q[ia] * q[ib]
     assert torch.allclose((phi_q * _weighted_exact(k)).sum(), (q @ k) ** 2)
-
-
-def test_t2_roundtrip_and_ghosts():
-    d = 64
-    x = torch.randn(2, layout.exact_dim(d), 5)
-    t2 = layout.exact_to_t2(x, d, dim=-2)
-    assert t2.shape == (2, layout.t2_dim(d), 5)
-    ghosts = layout._tables(d)[0] < 0
-    assert int(ghosts.sum()) == d // 2 and torch.count_nonzero(t2[:, ghosts]) == 0
-    assert torch.equal(layout.t2_to_exact(t2, d, dim=-2), x)
 
 
 def test_gram_sum_of_keys_roundtrip():
