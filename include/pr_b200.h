@@ -75,6 +75,13 @@ int pr_copy_2d(void* dst, long long dst_pitch, const void* src, long long src_pi
 int pr_selftest_umma(int variant, int dtype, int n, int k, const void* a, const void* b, float* out,
                      int device, void* stream);
 
+/* Micro-benchmark of tensor-memory reads: nwarps (4, 8, 16) warps of one CTA each issue `iters`
+ * loads of 32 lanes x 32 columns; cycles[0] receives the SM clock cycles taken. */
+/* Micro-benchmark of the tcgen05.mma issue rate for the operand shapes used here (mode 0: smem x smem
+ * N=128; 1: smem x smem N=64; 2: tmem x smem N=64; 3: tmem x smem N=128); 4*reps MMAs of K=16. */
+int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int device, void* stream);
+int pr_selftest_tmem_bw(int nwarps, int iters, long long* cycles, float* sink, int device, void* stream);
+
 /* Gate glue of retention/power_retention_maker.py:143-155,183-186 in one pass.
  * log_g [b,t,h] or NULL; x [b,t,hx,d].  Writes (when write_a) a [b,t,h] = inclusive
  * cumulative log gate inside each chunk and A [b,n,h] = chunk totals; xt [b,n,hx,d,cp] =
@@ -103,7 +110,7 @@ int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long long E, con
 
 /* discumsum backward (old binding discumsum_bwd, retention/_discumsum/cuda.py:75; gate
  * index as autograd of the reference gives it).  dY, Y, dX [b,n,h,E]; dX may alias dY.
- * dA_part [b,h,pr_discumsum_bwd_blocks(E),n]: per-block partial sums of the chunk-gate
+ * dA_part [b,h,pr_discumsum_bwd_blocks(E),n]: per-warp partial sums of the chunk-gate
  * gradient.  row_weights=1 multiplies dX rows (row_len elements each) by the key
  * weights of the expansion layout. */
 int pr_discumsum_bwd_blocks(long long E);

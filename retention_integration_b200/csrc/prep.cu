@@ -60,7 +60,7 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
     __syncthreads();
   }
   const float A = sm_a[c - 1];
-  if (write_a) {
+  if (write_a && blockIdx.y == 0) {
     if (a_out != nullptr)
       for (int i = tid; i < c; i += kPrepThreads) a_out[(tok0 + i) * h + gh] = sm_a[i];
     if (tid == 0 && A_out != nullptr) A_out[((size_t)batch * n + chunk) * h + gh] = A;
@@ -72,7 +72,10 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
   const int vec_per_row = d / 8;
   T* out_base = xt + ((size_t)(batch * n + chunk) * hx + head) * (size_t)d * cp;
   T* out2_base = xts ? xts + ((size_t)(batch * n + chunk) * hx + head) * (size_t)d * cp : nullptr;
-  for (int tb = 0; tb < cp; tb += 64) {
+  // the chunk's 64-token tiles are split over gridDim.y blocks (each recomputes the cheap scan)
+  const int tiles = cp / 64, tiles_per = (tiles + gridDim.y - 1) / gridDim.y;
+  const int tb_end = min(cp, (int)(blockIdx.y + 1) * tiles_per * 64);
+  for (int tb = blockIdx.y * tiles_per * 64; tb < tb_end; tb += 64) {
     __syncthreads();
     for (int idx = tid; idx < 64 * vec_per_row; idx += kPrepThreads) {
       const int r = idx / vec_per_row, v = idx % vec_per_row;
@@ -174,10 +177,19 @@ gate_grad_kernel(const float* __restrict__ da_q, const float* __restrict__ gq, c
   const int batch = blockIdx.x / (h * n);
   const size_t tok0 = (size_t)batch * t + (size_t)chunk * c;
 
-  // sum of the key discount terms over the chunk
+  // chunk-gate gradient: key discount terms of the chunk + the reverse scans' partial sums
+  // ([b, h, scan_blocks, n] and [b, h, gram_blocks, n]), all reduced by the whole block
   float part = 0.f;
   if (wk != nullptr)
     for (int i = tid; i < c; i += kPrepThreads) part += wk[(tok0 + i) * h + head];
+  if (dA_scan != nullptr) {
+    const float* ps = dA_scan + ((size_t)batch * h + head) * scan_blocks * n + chunk;
+    for (int k = tid; k < scan_blocks; k += kPrepThreads) part += ps[(size_t)k * n];
+  }
+  if (dA_gram != nullptr) {
+    const float* pg = dA_gram + ((size_t)batch * h + head) * gram_blocks * n + chunk;
+    for (int k = tid; k < gram_blocks; k += kPrepThreads) part += pg[(size_t)k * n];
+  }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
   if (lane == 0) warp_tot[warp] = part;
@@ -185,15 +197,6 @@ gate_grad_kernel(const float* __restrict__ da_q, const float* __restrict__ gq, c
   if (tid == 0) {
     float s = 0.f;
     for (int w = 0; w < kPrepThreads / 32; ++w) s += warp_tot[w];
-    // per-block partial sums of the reverse scans: [b, h, scan_blocks, n] and [b, h, n]
-    if (dA_scan != nullptr) {
-      const float* ps = dA_scan + ((size_t)batch * h + head) * scan_blocks * n + chunk;
-      for (int k = 0; k < scan_blocks; ++k) s += ps[(size_t)k * n];
-    }
-    if (dA_gram != nullptr) {
-      const float* pg = dA_gram + ((size_t)batch * h + head) * gram_blocks * n + chunk;
-      for (int k = 0; k < gram_blocks; ++k) s += pg[(size_t)k * n];
-    }
     wk_sum_s = s;
     carry_s = 0.f;
   }
@@ -274,7 +277,8 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
   const int cp = (c + 63) / 64 * 64;
   const size_t smem = (size_t)((c + 3) & ~3) * 4 + (size_t)2 * 64 * (d + 2) * 2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = b * (t / c) * hx;
+  const int tiles = cp / 64;
+  const dim3 grid(b * (t / c) * hx, xt ? (tiles >= 8 ? 4 : (tiles >= 2 ? 2 : 1)) : 1);
   if (dtype == PR_BF16) {
     PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));

@@ -92,14 +92,13 @@ scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restr
 }
 
 // dY, dX: [b, n, h, E] (may alias); Y: [b, n, h, E] states entering each chunk;
-// dA_part: [b, h, gridDim.x, n] per-block partial sums of exp(A[m]) * <Y[m], G[m+1]>.
+// dA_part: [b, h, 8 * gridDim.x, n] per-warp partial sums of exp(A[m]) * <Y[m], G[m+1]>.
 // row_weights: apply the key-side weight (1 or 2) of expanded row (e / row_len) to dX.
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
 scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict__ dX, const float* __restrict__ A,
                 const float* __restrict__ carry_in, float* __restrict__ carry_out, float* __restrict__ dA_part, int n,
                 int h, size_t E, int row_len, int row_weights) {
-  __shared__ float red[kScanThreads / 32];
   const size_t e0 = ((size_t)blockIdx.x * kScanThreads + threadIdx.x) * 8;
   const bool active = e0 < E;
   const int head = blockIdx.y, batch = blockIdx.z;
@@ -123,7 +122,10 @@ scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict
   const size_t base = ((size_t)batch * n * h + head) * E + e0;
   const float* Ap = A + (size_t)batch * n * h + head;
   const bool reduce_only = (dX == nullptr);
-  float* part = reduce_only ? nullptr : dA_part + (((size_t)batch * h + head) * gridDim.x + blockIdx.x) * n;
+  // one partial per warp and chunk: no block-wide barrier inside the chunk loop
+  float* part = reduce_only ? nullptr
+                            : dA_part + (((size_t)batch * h + head) * gridDim.x * (kScanThreads / 32) +
+                                         blockIdx.x * (kScanThreads / 32) + warp) * n;
   for (int m0 = n - 1; m0 >= 0; m0 -= kScanUnroll) {
     uint4 gv[kScanUnroll], yv[kScanUnroll];
     float g[kScanUnroll];
@@ -167,15 +169,7 @@ scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict
       dot *= g[u];
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-      if (lane == 0) red[warp] = dot;
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < kScanThreads / 32; ++w) s += red[w];
-        part[m] = s;
-      }
-      __syncthreads();
+      if (lane == 0) part[m] = dot;
     }
   }
   if (active && carry_out != nullptr) {
@@ -218,7 +212,6 @@ __global__ void __launch_bounds__(256)
 scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg, T* __restrict__ hi,
                      T* __restrict__ lo, const float* __restrict__ A, const float* __restrict__ carry_in,
                      float* __restrict__ carry_out, float* __restrict__ dA_part, int n, int h, int d) {
-  __shared__ float red[8];
   const int E = d * d;
   const int e = blockIdx.x * 256 + threadIdx.x;
   const bool active = e < E;
@@ -228,7 +221,7 @@ scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg
   const size_t cbase = ((size_t)batch * h + head) * E;
   float run = (active && carry_in) ? carry_in[cbase + e] : 0.f;
   float run_t = (active && carry_in) ? carry_in[cbase + et] : 0.f;
-  float* part = dA_part + (((size_t)batch * h + head) * gridDim.x + blockIdx.x) * n;
+  float* part = dA_part + (((size_t)batch * h + head) * gridDim.x * 8 + blockIdx.x * 8 + warp) * n;
   for (int m = n - 1; m >= 0; --m) {
     const size_t base = (((size_t)batch * n + m) * h + head) * E;
     const float g = __expf(A[((size_t)batch * n + m) * h + head]);
@@ -244,15 +237,7 @@ scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    if (lane == 0) red[warp] = dot;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < 8; ++w) s += red[w];
-      part[m] = s;
-    }
-    __syncthreads();
+    if (lane == 0) part[m] = dot;
   }
   if (active && carry_out) carry_out[cbase + e] = run;
 }
@@ -285,7 +270,9 @@ extern "C" int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long 
   return PR_OK;
 }
 
-extern "C" int pr_discumsum_bwd_blocks(long long E) { return (int)((E / 8 + pr::kScanThreads - 1) / pr::kScanThreads); }
+extern "C" int pr_discumsum_bwd_blocks(long long E) {
+  return (int)((E / 8 + pr::kScanThreads - 1) / pr::kScanThreads) * (pr::kScanThreads / 32);
+}
 
 extern "C" int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, const void* dY, const void* Y, void* dX,
                                 const float* A, const float* carry_in, float* carry_out, float* dA_part, int row_len,
@@ -299,7 +286,7 @@ extern "C" int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, con
              PR_ERR_BAD_ARG, "give dX, Y and dA_part together, or none of them and a carry_out");
   PR_REQUIRE(!row_weights || (row_len > 0 && row_len % 8 == 0), PR_ERR_BAD_ARG, "row_len %d", row_len);
   PR_CUDA(cudaSetDevice(device));
-  dim3 grid((unsigned)pr_discumsum_bwd_blocks(E), h, b);
+  dim3 grid((unsigned)((E / 8 + kScanThreads - 1) / kScanThreads), h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
     scan_bwd_kernel<__nv_bfloat16><<<grid, kScanThreads, 0, s>>>(
@@ -339,7 +326,7 @@ extern "C" int pr_gram_scan_fwd(int dtype, int b, int n, int h, int d, const flo
   return PR_OK;
 }
 
-extern "C" int pr_gram_scan_bwd_blocks(int d) { return (d * d + 255) / 256; }
+extern "C" int pr_gram_scan_bwd_blocks(int d) { return (d * d + 255) / 256 * 8; }
 
 extern "C" int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const float* dZg, const float* Zg, void* hi,
                                 void* lo, const float* A, const float* carry_in, float* carry_out, float* dA_part,
@@ -348,7 +335,7 @@ extern "C" int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const flo
   PR_REQUIRE(b > 0 && n > 0 && h > 0 && d > 0 && d <= 128, PR_ERR_BAD_ARG, "bad sizes");
   PR_REQUIRE(dZg && Zg && hi && lo && A && dA_part, PR_ERR_BAD_ARG, "null pointer");
   PR_CUDA(cudaSetDevice(device));
-  dim3 grid(pr_gram_scan_bwd_blocks(d), h, b);
+  dim3 grid((d * d + 255) / 256, h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
     scan_gram_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(dZg, Zg, static_cast<__nv_bfloat16*>(hi),

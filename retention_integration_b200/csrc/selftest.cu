@@ -193,3 +193,140 @@ extern "C" int pr_selftest_umma(int variant, int dtype, int n, int k, const void
   return dtype == PR_BF16 ? launch_selftest<__nv_bfloat16>(variant, n, k, a, b, out, status, s)
                           : launch_selftest<__half>(variant, n, k, a, b, out, status, s);
 }
+
+// Micro-benchmark: tensor-memory read bandwidth.  `nwarps` warps (4, 8 or 16) each issue
+// `iters` loads of 32 lanes x 32 columns from an allocated region; returns SM clock cycles.
+namespace pr {
+// mode 0: x32 load then wait; 1: two x32 loads then one wait; 2: x16 loads; 3: x8 loads
+__global__ void tmem_bw_kernel(int iters, int mode, long long* cycles, float* sink) {
+  __shared__ uint32_t tmem_base_s;
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s + ((uint32_t)((warp & 3) * 32) << 16);
+  uint32_t v[64];
+  float acc = 0.f;
+  __syncthreads();
+  const long long t0 = clock64();
+  if (mode == 0) {
+    for (int it = 0; it < iters; ++it) {
+      tmem_ld32(tmem + ((it * 32) & 511), v);
+      tmem_wait_ld();
+      acc += __uint_as_float(v[it & 31]);
+    }
+  } else if (mode == 1) {
+    for (int it = 0; it < iters; it += 2) {
+      tmem_ld32(tmem + ((it * 32) & 511), v);
+      tmem_ld32(tmem + ((it * 32 + 32) & 511), v + 32);
+      tmem_wait_ld();
+      acc += __uint_as_float(v[it & 63]);
+    }
+  } else if (mode == 2) {
+    for (int it = 0; it < iters; ++it) {
+      tmem_ld16(tmem + ((it * 32) & 511), v);
+      tmem_ld16(tmem + ((it * 32 + 16) & 511), v + 16);
+      tmem_wait_ld();
+      acc += __uint_as_float(v[it & 31]);
+    }
+  } else {
+    for (int it = 0; it < iters; ++it) {
+      uint32_t w[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        tmem_ld8(tmem + ((it * 32 + 8 * k) & 511), w);
+        v[8 * k] = w[0] ^ w[7];
+      }
+      tmem_wait_ld();
+      acc += __uint_as_float(v[(it & 3) * 8]);
+    }
+  }
+  __syncthreads();
+  const long long t1 = clock64();
+  if (threadIdx.x == 0) cycles[blockIdx.x] = t1 - t0;
+  if (acc == 123.456f) sink[0] = acc;
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+}
+}  // namespace pr
+
+namespace pr {
+// Micro-benchmark: issue rate of tcgen05.mma for the operand shapes the kernels use.
+// mode 0: A,B in smem, N=128 (K-major); 1: A,B in smem, N=64; 2: A in TMEM, B MN-major smem, N=64;
+// 3: A in TMEM, B MN-major, N=128 (two 64-wide blocks).  `reps` groups of four K=16 steps.
+__global__ void mma_rate_kernel(int reps, int mode, long long* cycles) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  for (int i = tid; i < 49152 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(sm)[i] = 0;
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (tid == 0) {
+    const uint32_t a_addr = smem_u32(sm), b_addr = smem_u32(sm + 16384), tmem = tmem_base_s;
+    // modes 4-7 repeat 0-3 with two accumulators used alternately; mode 8: smem x smem, N=256
+    const int alt = (mode >= 4 && mode <= 7) ? 1 : 0;
+    const int m4 = mode & 3;
+    const int n = mode == 8 ? 256 : ((m4 == 0 || m4 == 3) ? 128 : 64);
+    const bool ts = mode != 8 && m4 >= 2;
+    const uint32_t idesc = umma_idesc(128, n, true, false, ts);
+    const long long t0 = clock64();
+    for (int r = 0; r < reps; ++r) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t dcol = tmem + (alt ? (ks & 1) * 128 : 0);
+        if (ts)
+          umma_ts(dcol, tmem + 256 + ks * 8, umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc, 1u);
+        else
+          umma_ss(dcol, umma_desc_sw128(a_addr + ks * 32, 16, 1024), umma_desc_sw128(b_addr + ks * 32, 16, 1024),
+                  idesc, 1u);
+      }
+    }
+    umma_commit(&bar);
+    mbar_wait(&bar, 0, &abort_flag);
+    cycles[0] = clock64() - t0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+}
+}  // namespace pr
+
+extern "C" int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(reps > 0 && mode >= 0 && mode <= 8 && cycles, PR_ERR_BAD_ARG, "bad arguments");
+  PR_CUDA(cudaSetDevice(device));
+  PR_CUDA(cudaFuncSetAttribute(mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 51200));
+  mma_rate_kernel<<<1, 128, 51200, static_cast<cudaStream_t>(stream)>>>(reps, mode, cycles);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+extern "C" int pr_selftest_tmem_bw(int nwarps, int iters, long long* cycles, float* sink, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(nwarps == 4 || nwarps == 8 || nwarps == 16, PR_ERR_BAD_ARG, "nwarps must be 4, 8 or 16");
+  PR_REQUIRE(cycles && sink && iters > 0, PR_ERR_BAD_ARG, "bad arguments");
+  PR_CUDA(cudaSetDevice(device));
+  tmem_bw_kernel<<<1, nwarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(iters & 0xffffff, iters >> 24, cycles, sink);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
