@@ -58,7 +58,11 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
   __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float sm_aq[2][TW], sm_dl[2][TW], sm_il[2][TW];
+  __shared__ __align__(16) float sm_aq[2][TW], sm_dl[2][TW], sm_il[2][TW];
+  __shared__ __align__(16) float sm_fq[2][TW];  // e^{a_i - r}, r = gate sum at the step's first query
+  __shared__ __align__(16) float sm_hl[2][TW];  // 1 / (2 l_i)
+  __shared__ float sm_r[2];
+  __shared__ int sm_wide[2][2];                 // a loader warp saw a_i - r > 80 (overflow guard)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -195,58 +199,110 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
     const float* a_chunk = gated ? p.a + tok_base * p.h + kvhead : nullptr;
     const float a_j = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
     const float s2 = p.scale * p.scale;
-    float da = 0.f;
+    float da = 0.f, da2 = 0.f;  // da2 collects twice the fast-path terms
     bool ok = true;
     for (int st = 0; st < n_steps; ++st) {
       const int I = qt0 + st / ratio, qh = kvhead * ratio + st % ratio;
       const int qp0 = I * TW;
+      const int sb = st & 1;
       if (tid < TW) {
         const int qp = qp0 + tid;
         const bool v = qp < p.c;
-        sm_aq[st & 1][tid] = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
-        sm_dl[st & 1][tid] = v ? p.dl[(tok_base + qp) * p.hq + qh] : 0.f;
-        sm_il[st & 1][tid] = v ? safe_recip(p.l[(tok_base + qp) * p.hq + qh]) : 0.f;
+        const float av = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
+        const float r = gated ? a_chunk[(size_t)qp0 * p.h] : 0.f;
+        const float il = v ? safe_recip(p.l[(tok_base + qp) * p.hq + qh]) : 0.f;
+        sm_aq[sb][tid] = av;
+        sm_dl[sb][tid] = v ? p.dl[(tok_base + qp) * p.hq + qh] : 0.f;
+        sm_il[sb][tid] = il;
+        sm_hl[sb][tid] = 0.5f * il;
+        sm_fq[sb][tid] = v ? __expf(av - r) : 0.f;
+        const bool wide = __any_sync(0xffffffffu, (av - r) > 80.f);
+        if (lane == 0) sm_wide[sb][warp] = wide;
+        if (tid == 0) sm_r[sb] = r;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = mbar_wait(&sp_full, st & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const float* aq = sm_aq[st & 1];
-      const float* dlq = sm_dl[st & 1];
-      const float* ilq = sm_il[st & 1];
-      const bool need_mask = (qp0 < row) || (qp0 + TW - 1 >= p.c) || !row_valid;
+      const float* aq = sm_aq[sb];
+      const float* dlq = sm_dl[sb];
+      const float* ilq = sm_il[sb];
+      // Steps whose queries all lie at or after every key of this warp need no mask, and their
+      // gate factor separates: e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}; one exponential per
+      // key and per query instead of one per pair.  Other steps take the exact per-pair form.
+      const float r = sm_r[sb];
+      const bool fast = (row0 + (warp << 5) + 31 <= qp0) && (qp0 + TW - 1 < p.c) &&
+                        !(sm_wide[sb][0] | sm_wide[sb][1]) &&
+                        !__any_sync(0xffffffffu, (r - a_j) > 80.f);
+      if (fast) {
+        const float c_j = 2.f * s2 * __expf(r - a_j);
+        const float4* fq4 = reinterpret_cast<const float4*>(sm_fq[sb]);
+        const float4* il4 = reinterpret_cast<const float4*>(sm_il[sb]);
+        const float4* hl4 = reinterpret_cast<const float4*>(sm_hl[sb]);
+        const float4* dl4 = reinterpret_cast<const float4*>(sm_dl[sb]);
 #pragma unroll
-      for (int q4 = 0; q4 < TW / 32; ++q4) {
-        uint32_t sv[32], pv[32];
-        tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
-        tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
-        tmem_wait_ld();
-        uint32_t pk[16], dk[16];
+        for (int q4 = 0; q4 < TW / 32; ++q4) {
+          uint32_t sv[32], pv[32];
+          tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+          tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
+          tmem_wait_ld();
+          uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float pw[2], dsv[2];
+          for (int j = 0; j < 32; j += 4) {
+            const float4 f = fq4[q4 * 8 + (j >> 2)], i4 = il4[q4 * 8 + (j >> 2)];
+            const float4 h4 = hl4[q4 * 8 + (j >> 2)], d4 = dl4[q4 * 8 + (j >> 2)];
+            const float fv[4] = {f.x, f.y, f.z, f.w}, iv[4] = {i4.x, i4.y, i4.z, i4.w};
+            const float hv[4] = {h4.x, h4.y, h4.z, h4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pw[4], dsv[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = q4 * 32 + j + u;
-            const float s = __uint_as_float(sv[j + u]);
-            float g = s2;
-            if (gated) g *= __expf(aq[col] - a_j);
-            const float dp = fmaf(__uint_as_float(pv[j + u]), ilq[col], dlq[col]);
-            float sg = s * g;
-            if (need_mask) {
+            for (int u = 0; u < 4; ++u) {
+              const float s = __uint_as_float(sv[j + u]);
+              const float sg2 = s * (c_j * fv[u]);  // 2 s^2 S e^{a_i-a_j}
+              const float dp = fmaf(__uint_as_float(pv[j + u]), iv[u], dv[u]);
+              dsv[u] = sg2 * dp;
+              da2 = fmaf(dsv[u], s, da2);
+              pw[u] = (sg2 * s) * hv[u];
+            }
+            pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
+            pk[(j >> 1) + 1] = Pack2<T>::from_f32(pw[2], pw[3]);
+            dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+            dk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
+          }
+          tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
+          tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, dk);
+        }
+      } else {
+#pragma unroll
+        for (int q4 = 0; q4 < TW / 32; ++q4) {
+          uint32_t sv[32], pv[32];
+          tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+          tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
+          tmem_wait_ld();
+          uint32_t pk[16], dk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float pw[2], dsv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = q4 * 32 + j + u;
+              const float s = __uint_as_float(sv[j + u]);
+              float g = s2;
+              if (gated) g *= __expf(aq[col] - a_j);
+              const float dp = fmaf(__uint_as_float(pv[j + u]), ilq[col], dlq[col]);
+              float sg = s * g;
               const int qp = qp0 + col;
               if (qp < row || qp >= p.c || !row_valid) sg = 0.f;
+              const float pval = sg * s;
+              da = fmaf(pval, dp, da);
+              pw[u] = pval * ilq[col];
+              dsv[u] = 2.f * sg * dp;
             }
-            const float pval = sg * s;
-            da = fmaf(pval, dp, da);
-            pw[u] = pval * ilq[col];
-            dsv[u] = 2.f * sg * dp;
+            pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
+            dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
           }
-          pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
-          dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+          tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
+          tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, dk);
         }
-        tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
-        tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, dk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -345,7 +401,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
           v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
           dst[j] = v;
         }
-        p.da_k[tok * p.h + kvhead] = -da;
+        p.da_k[tok * p.h + kvhead] = -fmaf(0.5f, da2, da);
       }
     }
   }

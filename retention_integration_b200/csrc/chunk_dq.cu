@@ -51,6 +51,9 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ float sm_ak[2][TW];
+  __shared__ __align__(16) float sm_fk[2][TW];  // e^{r - a_j}, r = gate sum at the step's last key
+  __shared__ float sm_r[2];
+  __shared__ int sm_wide[2][2];                 // a loader warp saw r - a_j > 80 (overflow guard)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -145,48 +148,89 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
     const float dl_i = row_valid ? p.dl[tok * p.hq + qhead] : 0.f;
     const float inv_l = row_valid ? safe_recip(p.l[tok * p.hq + qhead]) : 0.f;
     const float s2 = p.scale * p.scale;
-    float da = 0.f;
+    float da = 0.f, da2 = 0.f;  // da2 collects twice the fast-path terms
     bool ok = true;
     for (int J = 0; J < nJ; ++J) {
       const int kp0 = J * TW;
+      const int sb = J & 1;
       if (tid < TW) {
         const int kp = kp0 + tid;
-        sm_ak[J & 1][tid] = (gated && kp < p.c) ? a_chunk[(size_t)kp * p.h] : 0.f;
+        const float av = (gated && kp < p.c) ? a_chunk[(size_t)kp * p.h] : 0.f;
+        const float r = gated ? a_chunk[(size_t)min(kp0 + TW - 1, p.c - 1) * p.h] : 0.f;
+        sm_ak[sb][tid] = av;
+        sm_fk[sb][tid] = kp < p.c ? __expf(r - av) : 0.f;
+        const bool wide = __any_sync(0xffffffffu, (r - av) > 80.f);
+        if (lane == 0) sm_wide[sb][warp] = wide;
+        if (tid == 0) sm_r[sb] = r;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = mbar_wait(&sp_full, J & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const float* ak = sm_ak[J & 1];
-      const bool need_mask = (kp0 + TW - 1 > row) || (kp0 + TW - 1 >= p.c);
+      // Steps that lie wholly below the diagonal for every row of this warp need no mask, and
+      // their gate factor separates: e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}, both <= 1 for
+      // gates <= 0; one exponential per row and per key instead of one per pair.  Steps on the
+      // diagonal, ragged steps and out-of-range exponents take the exact per-pair form.
+      const float r = sm_r[sb];
+      const bool fast = (kp0 + TW - 1 <= row0 + (warp << 5)) && (kp0 + TW - 1 < p.c) &&
+                        !(sm_wide[sb][0] | sm_wide[sb][1]) &&
+                        !__any_sync(0xffffffffu, (a_i - r) > 80.f);
+      if (fast) {
+        const float c_i = 2.f * s2 * __expf(a_i - r);
+        const float4* fk4 = reinterpret_cast<const float4*>(sm_fk[sb]);
 #pragma unroll
-      for (int q4 = 0; q4 < TW / 32; ++q4) {
-        uint32_t sv[32], pv[32];
-        tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
-        tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
-        tmem_wait_ld();
-        uint32_t pk[16];
+        for (int q4 = 0; q4 < TW / 32; ++q4) {
+          uint32_t sv[32], pv[32];
+          tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+          tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
+          tmem_wait_ld();
+          uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float dsv[2];
+          for (int j = 0; j < 32; j += 4) {
+            const float4 f = fk4[q4 * 8 + (j >> 2)];
+            const float fv[4] = {f.x, f.y, f.z, f.w};
+            float dsv[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = q4 * 32 + j + u;
-            const float s = __uint_as_float(sv[j + u]);
-            float g = s2;
-            if (gated) g *= __expf(a_i - ak[col]);
-            const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
-            float sg = s * g;  // s^2 S e^{a_i-a_j}
-            if (need_mask) {
+            for (int u = 0; u < 4; ++u) {
+              const float s = __uint_as_float(sv[j + u]);
+              const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
+              dsv[u] = (s * (c_i * fv[u])) * dp;  // 2 s^2 S e^{a_i-a_j} dp
+              da2 = fmaf(dsv[u], s, da2);
+            }
+            pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+            pk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
+          }
+          tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, pk);
+        }
+      } else {
+        const float* ak = sm_ak[sb];
+#pragma unroll
+        for (int q4 = 0; q4 < TW / 32; ++q4) {
+          uint32_t sv[32], pv[32];
+          tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+          tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
+          tmem_wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float dsv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = q4 * 32 + j + u;
+              const float s = __uint_as_float(sv[j + u]);
+              float g = s2;
+              if (gated) g *= __expf(a_i - ak[col]);
+              const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
+              float sg = s * g;  // s^2 S e^{a_i-a_j}
               const int kp = kp0 + col;
               if (kp > row || kp >= p.c) sg = 0.f;
+              da = fmaf(sg * s, dp, da);
+              dsv[u] = 2.f * sg * dp;
             }
-            da = fmaf(sg * s, dp, da);
-            dsv[u] = 2.f * sg * dp;
+            pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
           }
-          pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+          tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, pk);
         }
-        tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -218,7 +262,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
           v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
           dst[j] = v;
         }
-        p.da_q[tok * p.hq + qhead] = da;
+        p.da_q[tok * p.hq + qhead] = fmaf(0.5f, da2, da);
       }
     }
   }

@@ -72,6 +72,9 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ float sm_ak[2][TW];
+  __shared__ __align__(16) float sm_fk[2][TW];  // e^{r - a_j}, r = gate sum at the step's last key
+  __shared__ float sm_r[2];
+  __shared__ int sm_wide[2][2];                 // a loader warp saw r - a_j > 80 (overflow guard)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -238,40 +241,78 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
       const int sb = J & 1;
       if (tid < TW) {
         const int kp = kp0 + tid;
-        sm_ak[sb][tid] = (gated && kp < p.ck) ? a_chunk[(size_t)kp * p.h] : 0.f;
+        const float av = (gated && kp < p.ck) ? a_chunk[(size_t)kp * p.h] : 0.f;
+        const float r = gated ? a_chunk[(size_t)min(kp0 + TW - 1, p.ck - 1) * p.h] : 0.f;
+        sm_ak[sb][tid] = av;
+        sm_fk[sb][tid] = kp < p.ck ? __expf(r - av) : 0.f;
+        const bool wide = __any_sync(0xffffffffu, (r - av) > 80.f);
+        if (lane == 0) sm_wide[sb][warp] = wide;
+        if (tid == 0) sm_r[sb] = r;
       }
       named_bar_sync(1, 128);
       ok = mbar_wait(&s_full[sb], (J >> 1) & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const float* ak = sm_ak[sb];
       const uint32_t col_s = COL_S + sb * TW;
-      const bool need_mask = (kp0 + TW - 1 > qpos) || (kp0 + TW - 1 >= p.ck);
+      // Steps that lie wholly below the diagonal for every row of this warp need no mask, and
+      // their gate factor separates: e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}; one exponential
+      // per row and per key instead of one per pair.  Steps on the diagonal, ragged steps and
+      // out-of-range exponents take the exact per-pair form.
+      const float r = sm_r[sb];
+      const bool fast = (kp0 + TW - 1 <= row0 + (warp << 5) + q_off) && (kp0 + TW - 1 < p.ck) &&
+                        !(sm_wide[sb][0] | sm_wide[sb][1]) &&
+                        !__any_sync(0xffffffffu, (a_i - r) > 80.f);
+      if (fast) {
+        const float c_i = s2 * __expf(a_i - r);
+        const float4* fk4 = reinterpret_cast<const float4*>(sm_fk[sb]);
 #pragma unroll
-      for (int q4 = 0; q4 < TW / 32; ++q4) {
-        uint32_t sv[32];
-        tmem_ld32(tmem + lane_addr + col_s + q4 * 32, sv);
-        tmem_wait_ld();
-        uint32_t pk[16];
+        for (int q4 = 0; q4 < TW / 32; ++q4) {
+          uint32_t sv[32];
+          tmem_ld32(tmem + lane_addr + col_s + q4 * 32, sv);
+          tmem_wait_ld();
+          uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float pv[2];
+          for (int j = 0; j < 32; j += 4) {
+            const float4 f = fk4[q4 * 8 + (j >> 2)];
+            const float fv[4] = {f.x, f.y, f.z, f.w};
+            float pv[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = q4 * 32 + j + u;
-            const float s = __uint_as_float(sv[j + u]);
-            float w = s2 * s * s;
-            if (gated) w *= __expf(a_i - ak[col]);
-            if (need_mask) {
+            for (int u = 0; u < 4; ++u) {
+              const float s = __uint_as_float(sv[j + u]);
+              pv[u] = (s * s) * (c_i * fv[u]);
+            }
+            pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
+            pk[(j >> 1) + 1] = Pack2<T>::from_f32(pv[2], pv[3]);
+            l_acc += (pv[0] + pv[1]) + (pv[2] + pv[3]);
+          }
+          tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
+        }
+      } else {
+        const float* ak = sm_ak[sb];
+#pragma unroll
+        for (int q4 = 0; q4 < TW / 32; ++q4) {
+          uint32_t sv[32];
+          tmem_ld32(tmem + lane_addr + col_s + q4 * 32, sv);
+          tmem_wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float pv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = q4 * 32 + j + u;
+              const float s = __uint_as_float(sv[j + u]);
+              float w = s2 * s * s;
+              if (gated) w *= __expf(a_i - ak[col]);
               const int kp = kp0 + col;
               if (kp > qpos || kp >= p.ck) w = 0.f;
+              pv[u] = w;
             }
-            pv[u] = w;
+            pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
+            l_acc += pv[0] + pv[1];
           }
-          pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
-          l_acc += pv[0] + pv[1];
+          tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
         }
-        tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
