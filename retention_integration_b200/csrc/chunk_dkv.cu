@@ -201,26 +201,38 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
     const float s2 = p.scale * p.scale;
     float da = 0.f, da2 = 0.f;  // da2 collects twice the fast-path terms
     bool ok = true;
+    // per-query values of the next step, loaded one step ahead by the first TW threads
+    float av_n = 0.f, r_n = 0.f, dl_n = 0.f, l_n = 1.f;
+    auto load_cols = [&](int st) {
+      if (tid < TW) {
+        const int qp0 = (qt0 + st / ratio) * TW, qh = kvhead * ratio + st % ratio;
+        const int qp = qp0 + tid;
+        const bool v = qp < p.c;
+        av_n = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
+        r_n = gated ? a_chunk[(size_t)qp0 * p.h] : 0.f;
+        dl_n = v ? p.dl[(tok_base + qp) * p.hq + qh] : 0.f;
+        l_n = v ? p.l[(tok_base + qp) * p.hq + qh] : 1.f;
+      }
+    };
+    if (n_steps > 0) load_cols(0);
     for (int st = 0; st < n_steps; ++st) {
       const int I = qt0 + st / ratio, qh = kvhead * ratio + st % ratio;
       const int qp0 = I * TW;
       const int sb = st & 1;
       if (tid < TW) {
-        const int qp = qp0 + tid;
-        const bool v = qp < p.c;
-        const float av = (gated && v) ? a_chunk[(size_t)qp * p.h] : 0.f;
-        const float r = gated ? a_chunk[(size_t)qp0 * p.h] : 0.f;
-        const float il = v ? safe_recip(p.l[(tok_base + qp) * p.hq + qh]) : 0.f;
-        sm_aq[sb][tid] = av;
-        sm_dl[sb][tid] = v ? p.dl[(tok_base + qp) * p.hq + qh] : 0.f;
+        const bool v = qp0 + tid < p.c;
+        const float il = v ? safe_recip(l_n) : 0.f;
+        sm_aq[sb][tid] = av_n;
+        sm_dl[sb][tid] = dl_n;
         sm_il[sb][tid] = il;
         sm_hl[sb][tid] = 0.5f * il;
-        sm_fq[sb][tid] = v ? __expf(av - r) : 0.f;
-        const bool wide = __any_sync(0xffffffffu, (av - r) > 80.f);
+        sm_fq[sb][tid] = v ? __expf(av_n - r_n) : 0.f;
+        const bool wide = __any_sync(0xffffffffu, (av_n - r_n) > 80.f);
         if (lane == 0) sm_wide[sb][warp] = wide;
-        if (tid == 0) sm_r[sb] = r;
+        if (tid == 0) sm_r[sb] = r_n;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (st + 1 < n_steps) load_cols(st + 1);  // in flight while this step is computed
       ok = mbar_wait(&sp_full, st & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();

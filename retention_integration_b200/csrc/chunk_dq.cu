@@ -24,8 +24,9 @@ constexpr int THREADS = 192;
 constexpr int TILE_BYTES = 128 * 128;   // 128 query rows x 64 features
 constexpr int TW = 64;                  // keys per step
 constexpr int KV_BYTES = TW * 128;      // one key or value tile
+constexpr int NKV = 4;                  // key/value tiles in flight
 constexpr uint32_t TMEM_COLS = 256;     // two CTAs per SM
-constexpr uint32_t COL_S = 0, COL_DS = 0, COL_DP = 64, COL_ACC = 128;
+constexpr uint32_t COL_S = 0, COL_DP = 128, COL_ACC = 192;  // S double-buffered (2 x 64); dS overwrites its S
 }  // namespace dq
 
 struct ChunkDqParams {
@@ -40,17 +41,44 @@ struct ChunkDqParams {
   int* status;
 };
 
+// One 32-column half of a step for one row: dS = 2 s^2 S g dp into `pk`, row sum of dS * S into da2.
+// SEP: the gate factor is c_i * fk[col] (c_i carries 2 s^2); otherwise 2 s^2 e^{a_i - ak[col]} per pair.
+// MASK: columns beyond `lim` (the row's own position, relative to the step) are dropped.
+template <typename T, bool SEP, bool MASK>
+__device__ __forceinline__ void dq_half(const uint32_t (&sv)[32], const uint32_t (&pv)[32], const float* __restrict__ fk,
+                                        float c_i, float a_i, float inv_l, float dl_i, int lim, uint32_t (&pk)[16],
+                                        float& da2) {
+  const float4* f4 = reinterpret_cast<const float4*>(fk);
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 f = f4[j >> 2];
+    const float fv[4] = {f.x, f.y, f.z, f.w};
+    float dsv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float s = __uint_as_float(sv[j + u]);
+      const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
+      float g = SEP ? c_i * fv[u] : c_i * __expf(a_i - fv[u]);
+      if (MASK) g = (j + u <= lim) ? g : 0.f;
+      dsv[u] = (s * g) * dp;
+      da2 = fmaf(dsv[u], s, da2);
+    }
+    pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+    pk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(dq::THREADS, 2)
 chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_st) {
   using namespace dq;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], sp_full, ds_full, acc_done;
+  __shared__ uint64_t q_full, kv_full[NKV], kv_empty[NKV], sp_full, ds_full, acc_done, qdy_free, st_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float sm_ak[2][TW];
+  __shared__ __align__(16) float sm_ak[2][TW];  // gate sums a_j of the step's keys
   __shared__ __align__(16) float sm_fk[2][TW];  // e^{r - a_j}, r = gate sum at the step's last key
   __shared__ float sm_r[2];
   __shared__ int sm_wide[2][2];                 // a loader warp saw r - a_j > 80 (overflow guard)
@@ -60,8 +88,8 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smQ = sm;
   uint8_t* smDY = smQ + TILE_BYTES;
-  uint8_t* smK = smDY + TILE_BYTES;      // 2 stages x KV_BYTES
-  uint8_t* smV = smK + 2 * KV_BYTES;     // 2 stages x KV_BYTES
+  uint8_t* smK = smDY + TILE_BYTES;      // NKV stages x KV_BYTES
+  uint8_t* smV = smK + NKV * KV_BYTES;   // NKV stages x KV_BYTES
 
   const int tile_i = blockIdx.x % p.tiles_per_chunk;
   const int chunk = blockIdx.x / p.tiles_per_chunk;
@@ -70,17 +98,20 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
   const int row0 = tile_i * 128;
   const int nJ = min(p.c - 1, row0 + 127) / TW + 1;
   const int tok_chunk = chunk * p.c;
+  const bool has_st = p.dq_state != nullptr;
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NKV; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(&sp_full, 1);
     mbar_init(&ds_full, 4);
     mbar_init(&acc_done, 1);
+    mbar_init(&qdy_free, 1);
+    mbar_init(&st_full, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -97,12 +128,20 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
       mbar_expect_tx(&q_full, 2 * TILE_BYTES);
       tma_load_4d(smQ, &tm_q, &q_full, 0, qhead, tok_chunk + row0, batch);
       tma_load_4d(smDY, &tm_dy, &q_full, 0, qhead, tok_chunk + row0, batch);
+      bool ok = true;
       for (int J = 0; J < nJ; ++J) {
-        const int s = J & 1, ph = (J >> 1) & 1;
-        if (!mbar_wait(&kv_empty[s], ph ^ 1, &abort_flag)) break;
+        const int s = J % NKV, ph = (J / NKV) & 1;
+        if (!(ok = mbar_wait(&kv_empty[s], ph ^ 1, &abort_flag))) break;
         mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
         tma_load_4d(smK + s * KV_BYTES, &tm_k, &kv_full[s], 0, kvhead, tok_chunk + J * TW, batch);
         tma_load_4d(smV + s * KV_BYTES, &tm_v, &kv_full[s], 0, kvhead, tok_chunk + J * TW, batch);
+      }
+      // The query and dO tiles are dead once the last S and dP are computed: the fp32
+      // state-path gradient of these rows (two 32-column halves) takes their place.
+      if (ok && has_st && mbar_wait(&qdy_free, 0, &abort_flag)) {
+        mbar_expect_tx(&st_full, 2 * TILE_BYTES);
+        tma_load_4d(smQ, &tm_st, &st_full, 0, qhead, tok_chunk + row0, batch);
+        tma_load_4d(smDY, &tm_st, &st_full, 32, qhead, tok_chunk + row0, batch);
       }
     }
   } else if (warp == 5) {
@@ -111,29 +150,47 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
       const uint32_t idesc_s = umma_idesc(128, TW, Pack2<T>::is_bf16, false, false);
       const uint32_t idesc_q = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
       const uint32_t q_addr = smem_u32(smQ), dy_addr = smem_u32(smDY);
-      for (int J = 0; J < nJ && ok; ++J) {
-        const int st = J & 1;
-        ok = mbar_wait(&kv_full[st], (J >> 1) & 1, &abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(smK + st * KV_BYTES), v_addr = smem_u32(smV + st * KV_BYTES);
+      // Issue order per step J: S(J+1) while the rows still work on step J, then, once dS(J) is
+      // in tensor memory, dP(J+1) (so the rows can go on) and only then dQ += dS(J) K_J.
+      auto issue_s = [&](int J) {
+        const uint32_t k_addr = smem_u32(smK + (J % NKV) * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + COL_S, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
+          umma_ss(tmem + COL_S + (J & 1) * TW, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
                   umma_desc_sw128(k_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+      };
+      auto issue_dp = [&](int J) {
+        const uint32_t v_addr = smem_u32(smV + (J % NKV) * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_ss(tmem + COL_DP, umma_desc_sw128(dy_addr + ks * 32, 16, 1024),
                   umma_desc_sw128(v_addr + ks * 32, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
         umma_commit(&sp_full);
+        if (J == nJ - 1) umma_commit(&qdy_free);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, &abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        issue_dp(0);
+      }
+      for (int J = 0; J < nJ && ok; ++J) {
+        if (J + 1 < nJ) {
+          ok = mbar_wait(&kv_full[(J + 1) % NKV], ((J + 1) / NKV) & 1, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(J + 1);
+        }
         ok = mbar_wait(&ds_full, J & 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
+        if (J + 1 < nJ) issue_dp(J + 1);
+        const uint32_t k_addr = smem_u32(smK + (J % NKV) * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < TW / 16; ++ks)
-          umma_ts(tmem + COL_ACC, tmem + COL_DS + ks * 8, umma_desc_sw128(k_addr + ks * 2048, 8192, 1024), idesc_q,
-                  (J > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&kv_empty[st]);
+          umma_ts(tmem + COL_ACC, tmem + COL_S + (J & 1) * TW + ks * 8,
+                  umma_desc_sw128(k_addr + ks * 2048, 8192, 1024), idesc_q, (J > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&kv_empty[J % NKV]);
       }
       if (ok) umma_commit(&acc_done);
     }
@@ -147,89 +204,67 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
     const float a_i = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
     const float dl_i = row_valid ? p.dl[tok * p.hq + qhead] : 0.f;
     const float inv_l = row_valid ? safe_recip(p.l[tok * p.hq + qhead]) : 0.f;
-    const float s2 = p.scale * p.scale;
-    float da = 0.f, da2 = 0.f;  // da2 collects twice the fast-path terms
+    const float s2x2 = 2.f * p.scale * p.scale;
+    const int wrow0 = row0 + (warp << 5);  // first row of this warp
+    float da2 = 0.f;                       // twice the row sum of p * dp
     bool ok = true;
+    // gate sums of the next step's keys, loaded one step ahead by the first TW threads
+    float av_n = 0.f, r_n = 0.f;
+    auto load_gates = [&](int J) {
+      if (tid < TW && gated) {
+        const int kp = J * TW + tid;
+        av_n = kp < p.c ? a_chunk[(size_t)kp * p.h] : 0.f;
+        r_n = a_chunk[(size_t)min(J * TW + TW - 1, p.c - 1) * p.h];
+      }
+    };
+    load_gates(0);
     for (int J = 0; J < nJ; ++J) {
       const int kp0 = J * TW;
       const int sb = J & 1;
+      const uint32_t col_s = COL_S + sb * TW;
       if (tid < TW) {
-        const int kp = kp0 + tid;
-        const float av = (gated && kp < p.c) ? a_chunk[(size_t)kp * p.h] : 0.f;
-        const float r = gated ? a_chunk[(size_t)min(kp0 + TW - 1, p.c - 1) * p.h] : 0.f;
-        sm_ak[sb][tid] = av;
-        sm_fk[sb][tid] = kp < p.c ? __expf(r - av) : 0.f;
-        const bool wide = __any_sync(0xffffffffu, (r - av) > 80.f);
+        sm_ak[sb][tid] = av_n;
+        sm_fk[sb][tid] = __expf(r_n - av_n);
+        const bool wide = __any_sync(0xffffffffu, (r_n - av_n) > 80.f);
         if (lane == 0) sm_wide[sb][warp] = wide;
-        if (tid == 0) sm_r[sb] = r;
+        if (tid == 0) sm_r[sb] = r_n;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (J + 1 < nJ) load_gates(J + 1);  // in flight while this step is computed
       ok = mbar_wait(&sp_full, J & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();
-      // Steps that lie wholly below the diagonal for every row of this warp need no mask, and
-      // their gate factor separates: e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}, both <= 1 for
-      // gates <= 0; one exponential per row and per key instead of one per pair.  Steps on the
-      // diagonal, ragged steps and out-of-range exponents take the exact per-pair form.
-      const float r = sm_r[sb];
-      const bool fast = (kp0 + TW - 1 <= row0 + (warp << 5)) && (kp0 + TW - 1 < p.c) &&
-                        !(sm_wide[sb][0] | sm_wide[sb][1]) &&
-                        !__any_sync(0xffffffffu, (a_i - r) > 80.f);
-      if (fast) {
-        const float c_i = 2.f * s2 * __expf(a_i - r);
-        const float4* fk4 = reinterpret_cast<const float4*>(sm_fk[sb]);
+      // The gate factor separates, e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}: one exponential
+      // per row and per key instead of one per pair.  Both exponents are <= 0 below the
+      // diagonal for gates <= 0; if one exceeds 80 (growing gates) the warp takes the per-pair
+      // form.  Steps wholly below the diagonal need no mask; a warp whose rows all precede the
+      // step's keys writes zeros without reading the scores.
+      const int lim = min(row, p.c - 1) - kp0;  // last column this row keeps
+      if (kp0 > min(wrow0 + 31, p.c - 1)) {
+        uint32_t z[16];
 #pragma unroll
-        for (int q4 = 0; q4 < TW / 32; ++q4) {
-          uint32_t sv[32], pv[32];
-          tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
-          tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
-          tmem_wait_ld();
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const float4 f = fk4[q4 * 8 + (j >> 2)];
-            const float fv[4] = {f.x, f.y, f.z, f.w};
-            float dsv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float s = __uint_as_float(sv[j + u]);
-              const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
-              dsv[u] = (s * (c_i * fv[u])) * dp;  // 2 s^2 S e^{a_i-a_j} dp
-              da2 = fmaf(dsv[u], s, da2);
-            }
-            pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
-            pk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
-          }
-          tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, pk);
-        }
+        for (int j = 0; j < 16; ++j) z[j] = 0u;
+        tmem_st16(tmem + lane_addr + col_s, z);
+        tmem_st16(tmem + lane_addr + col_s + 16, z);
       } else {
-        const float* ak = sm_ak[sb];
-#pragma unroll
+        const float r = sm_r[sb];
+        const bool mask = (kp0 + TW - 1 > wrow0) || (kp0 + TW - 1 >= p.c);
+        const bool sep = !(sm_wide[sb][0] | sm_wide[sb][1]) && !__any_sync(0xffffffffu, (a_i - r) > 80.f);
+        const float c_i = sep ? s2x2 * __expf(a_i - r) : s2x2;
+#pragma unroll 1
         for (int q4 = 0; q4 < TW / 32; ++q4) {
-          uint32_t sv[32], pv[32];
-          tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
+          uint32_t sv[32], pv[32], pk[16];
+          tmem_ld32(tmem + lane_addr + col_s + q4 * 32, sv);
           tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
           tmem_wait_ld();
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float dsv[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int col = q4 * 32 + j + u;
-              const float s = __uint_as_float(sv[j + u]);
-              float g = s2;
-              if (gated) g *= __expf(a_i - ak[col]);
-              const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
-              float sg = s * g;  // s^2 S e^{a_i-a_j}
-              const int kp = kp0 + col;
-              if (kp > row || kp >= p.c) sg = 0.f;
-              da = fmaf(sg * s, dp, da);
-              dsv[u] = 2.f * sg * dp;
-            }
-            pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+          const int lm = lim - q4 * 32;
+          if (sep) {
+            if (mask) dq_half<T, true, true>(sv, pv, sm_fk[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
+            else dq_half<T, true, false>(sv, pv, sm_fk[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
+          } else {
+            dq_half<T, false, true>(sv, pv, sm_ak[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
           }
-          tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, pk);
+          tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
         }
       }
       tmem_wait_st();
@@ -238,6 +273,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
       if (lane == 0) mbar_arrive(&ds_full);
     }
     if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
+    if (ok && has_st) ok = mbar_wait(&st_full, 0, &abort_flag);
     tc_fence_after();
     if (ok) {
       uint32_t acc[64];
@@ -245,15 +281,15 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
       tmem_ld32(tmem + lane_addr + COL_ACC + 32, acc + 32);
       tmem_wait_ld();
       if (row_valid) {
-        const float4* st = p.dq_state ? reinterpret_cast<const float4*>(p.dq_state + (tok * p.hq + qhead) * HD)
-                                      : nullptr;
         uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.dQ) + (tok * p.hq + qhead) * HD);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
-          if (st) {
-            s0 = st[2 * j];
-            s1 = st[2 * j + 1];
+          if (has_st) {
+            // columns 8j..8j+7: 16-byte chunks 2j, 2j+1 of the row in its 32-column half
+            const uint8_t* half = (j < 4) ? smQ : smDY;
+            s0 = *reinterpret_cast<const float4*>(half + swz128(tid, (2 * j) & 7));
+            s1 = *reinterpret_cast<const float4*>(half + swz128(tid, (2 * j + 1) & 7));
           }
           uint4 v;
           v.x = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 0]) + s0.x, __uint_as_float(acc[8 * j + 1]) + s0.y);
@@ -262,7 +298,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
           v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
           dst[j] = v;
         }
-        p.da_q[tok * p.hq + qhead] = fmaf(0.5f, da2, da);
+        p.da_q[tok * p.hq + qhead] = 0.5f * da2;
       }
     }
   }
@@ -303,7 +339,7 @@ extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c,
   p.da_q = da_q;
   int rc = status_word(device, &p.status, nullptr);
   if (rc) return rc;
-  CUtensorMap tm_q, tm_dy, tm_k, tm_v;
+  CUtensorMap tm_q, tm_dy, tm_k, tm_v, tm_st;
   uint64_t dq_[4] = {(uint64_t)d, (uint64_t)hq, (uint64_t)t, (uint64_t)b};
   uint64_t sq[4] = {0, (uint64_t)d * 2, (uint64_t)hq * d * 2, (uint64_t)t * hq * d * 2};
   uint64_t dk[4] = {(uint64_t)d, (uint64_t)h, (uint64_t)t, (uint64_t)b};
@@ -314,18 +350,24 @@ extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c,
   uint32_t box_kv[4] = {64, 1, (uint32_t)TW, 1};
   if ((rc = make_tmap(&tm_k, K, 2, 4, dk, sk, box_kv, true))) return rc;
   if ((rc = make_tmap(&tm_v, V, 2, 4, dk, sk, box_kv, true))) return rc;
-  const size_t smem = 1024 + 2 * TILE_BYTES + 4 * KV_BYTES;
+  tm_st = tm_q;  // unused without a state-path gradient
+  if (dq_state) {
+    uint64_t ss[4] = {0, (uint64_t)d * 4, (uint64_t)hq * d * 4, (uint64_t)t * hq * d * 4};
+    uint32_t box_st[4] = {32, 1, 128, 1};
+    if ((rc = make_tmap(&tm_st, dq_state, 4, 4, dq_, ss, box_st, true))) return rc;
+  }
+  const size_t smem = 1024 + 2 * TILE_BYTES + 2 * NKV * KV_BYTES;
   dim3 grid(p.tiles_per_chunk * p.n_chunks, hq, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
     PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
     PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_dq_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v);
+    chunk_dq_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v, tm_st);
   } else {
     PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_dq_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v);
+    chunk_dq_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v, tm_st);
   }
   PR_CUDA(cudaGetLastError());
   return PR_OK;

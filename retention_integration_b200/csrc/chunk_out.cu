@@ -235,21 +235,30 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
     const float s2 = p.scale * p.scale;
     float l_acc = 0.f;
     bool ok = true;
+    // gate sums of the next step's keys, loaded one step ahead by the first TW threads
+    float av_n = 0.f, r_n = 0.f;
+    auto load_gates = [&](int J) {
+      if (tid < TW && gated) {
+        const int kp = J * TW + tid;
+        av_n = kp < p.ck ? a_chunk[(size_t)kp * p.h] : 0.f;
+        r_n = a_chunk[(size_t)min(J * TW + TW - 1, p.ck - 1) * p.h];
+      }
+    };
+    if (nJ > 0) load_gates(0);
 
     for (int J = 0; J < nJ; ++J) {
       const int kp0 = J * TW;
       const int sb = J & 1;
       if (tid < TW) {
         const int kp = kp0 + tid;
-        const float av = (gated && kp < p.ck) ? a_chunk[(size_t)kp * p.h] : 0.f;
-        const float r = gated ? a_chunk[(size_t)min(kp0 + TW - 1, p.ck - 1) * p.h] : 0.f;
-        sm_ak[sb][tid] = av;
-        sm_fk[sb][tid] = kp < p.ck ? __expf(r - av) : 0.f;
-        const bool wide = __any_sync(0xffffffffu, (r - av) > 80.f);
+        sm_ak[sb][tid] = av_n;
+        sm_fk[sb][tid] = kp < p.ck ? __expf(r_n - av_n) : 0.f;
+        const bool wide = __any_sync(0xffffffffu, (r_n - av_n) > 80.f);
         if (lane == 0) sm_wide[sb][warp] = wide;
-        if (tid == 0) sm_r[sb] = r;
+        if (tid == 0) sm_r[sb] = r_n;
       }
       named_bar_sync(1, 128);
+      if (J + 1 < nJ) load_gates(J + 1);  // in flight while this step is computed
       ok = mbar_wait(&s_full[sb], (J >> 1) & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();
