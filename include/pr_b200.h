@@ -81,6 +81,11 @@ int pr_selftest_umma(int variant, int dtype, int n, int k, const void* a, const 
  * N=128; 1: smem x smem N=64; 2: tmem x smem N=64; 3: tmem x smem N=128); 4*reps MMAs of K=16. */
 int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int device, void* stream);
 int pr_selftest_tmem_bw(int nwarps, int iters, long long* cycles, float* sink, int device, void* stream);
+/* L2 -> shared memory streaming rate of TMA: `grid` CTAs each walk `tiles` 16 KB tiles `reps` times through a ring
+ * of `depth` stages (<= 12); CTAs with equal blockIdx.x / share read the same region; the regions must fit in
+ * buf_bytes.  cycles[grid] = SM clocks. */
+int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int grid, int tiles, int reps, int depth, int share,
+                           long long* cycles, int device, void* stream);
 
 /* Gate glue of retention/power_retention_maker.py:143-155,183-186 in one pass.
  * log_g [b,t,h] or NULL; x [b,t,hx,d].  Writes (when write_a) a [b,t,h] = inclusive

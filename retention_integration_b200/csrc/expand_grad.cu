@@ -35,9 +35,11 @@ constexpr int G_BYTES = 64 * 128;
 constexpr int NSS = 4;                   // state tiles in flight (TMA latency x L2 bandwidth needs ~100 KB per SM)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int ROWS = 256;                // token rows per CTA: two row tiles of 128
-constexpr uint32_t COL_D = 0;            // 2 x 128 columns (one buffer per row tile)
-constexpr uint32_t COL_U = 256;          // 2 x 64
-constexpr uint32_t COL_XA = 384;         // 2 x 32
+// Tensor memory: two 128-column buffers per row tile, buffer b of row tile rt at (2 rt + b) * 128.
+// Before the first use of buffer 1 its columns hold the Gram part: the gated row as A operand
+// (32 columns at +0) and u = x~ Gs (64 columns at +64), read into the accumulators' initial value.
+__device__ __forceinline__ constexpr uint32_t col_d(int rt, int b) { return (uint32_t)((2 * rt + b) * 128); }
+constexpr uint32_t OFF_XA = 0, OFF_U = 64;
 
 }  // namespace eg
 
@@ -64,7 +66,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
                    const __grid_constant__ CUtensorMap tm_ghi, const __grid_constant__ CUtensorMap tm_glo) {
   using namespace eg;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t w_full, g_full, xa_full[2], u_full[2], s_full[NSS], s_empty[NSS], d_full[2], d_empty[2];
+  __shared__ uint64_t w_full, g_full, xa_full[2], u_full[2], s_full[NSS], s_empty[NSS], d_full[2][2], d_empty[2][2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -105,8 +107,10 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     for (int s = 0; s < 2; ++s) {
       mbar_init(&xa_full[s], 4);
       mbar_init(&u_full[s], 1);
-      mbar_init(&d_full[s], 1);
-      mbar_init(&d_empty[s], 4);
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&d_full[s][b], 1);
+        mbar_init(&d_empty[s][b], 4);
+      }
     }
     for (int s = 0; s < NSS; ++s) {
       mbar_init(&s_full[s], 1);
@@ -151,15 +155,17 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         if (!ok) break;
         const uint32_t idesc = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
         const uint32_t s_addr = smem_u32(smS + s * TILE_BYTES);
+        const int b = nt & 1;
         for (int rt = 0; rt < 2 && ok; ++rt) {
-          ok = mbar_wait(&d_empty[rt], (nt & 1) ^ 1, &abort_flag);
+          // buffer 0 has been drained nt/2 times before tile nt; buffer 1 once more (the Gram part)
+          ok = mbar_wait(&d_empty[rt][b], ((nt >> 1) & 1) ^ (b ^ 1), &abort_flag);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tmem + COL_D + rt * 128, umma_desc_sw128(w_addr + rt * TILE_BYTES + ks * 32, 16, 1024),
+            umma_ss(tmem + col_d(rt, b), umma_desc_sw128(w_addr + rt * TILE_BYTES + ks * 32, 16, 1024),
                     umma_desc_sw128(s_addr + ks * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
-          umma_commit(&d_full[rt]);
+          umma_commit(&d_full[rt][b]);
         }
         if (!ok) break;
         umma_commit(&s_empty[s]);
@@ -176,7 +182,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
             for (int half = 0; half < 2; ++half)
 #pragma unroll
               for (int ks = 0; ks < 4; ++ks)
-                umma_ts(tmem + COL_U + rt * 64, tmem + COL_XA + rt * 32 + ks * 8,
+                umma_ts(tmem + col_d(rt, 1) + OFF_U, tmem + col_d(rt, 1) + OFF_XA + ks * 8,
                         umma_desc_sw128(g_addr + half * G_BYTES + ks * 32, 16, 1024), idesc_g,
                         (half > 0 || ks > 0) ? 1u : 0u);
             umma_commit(&u_full[rt]);
@@ -191,7 +197,6 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     const int row = row0 + rt * 128 + r;
     const bool row_valid = row < p.c;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t col_d = COL_D + rt * 128;
 
     float f = p.query_side ? p.scale : 1.f;
     if (p.a != nullptr) {
@@ -223,15 +228,31 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         *reinterpret_cast<uint4*>(smX + rt * TILE_BYTES + swz128(r, j)) =
             make_uint4(xp[4 * j], xp[4 * j + 1], xp[4 * j + 2], xp[4 * j + 3]);
       if (ok) {
-        tmem_st32(tmem + lane_addr + COL_XA + rt * 32, xp);
+        tmem_st32(tmem + lane_addr + col_d(rt, 1) + OFF_XA, xp);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&xa_full[rt]);
       }
     }
+    // Gram part first: dx~ starts at g_i * mult * (Gs x~)_i, which also frees buffer 1
+    {
+      float g = p.gram_mult;
+      if (p.row_g != nullptr) g *= row_valid ? p.row_g[(tok0 + row) * p.hx + head] : 0.f;
+      if (ok) ok = mbar_wait(&u_full[rt], 0, &abort_flag);
+      tc_fence_after();
+      uint32_t u[64];
+      if (ok) {
+        tmem_ld32(tmem + lane_addr + col_d(rt, 1) + OFF_U, u);
+        tmem_ld32(tmem + lane_addr + col_d(rt, 1) + OFF_U + 32, u + 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&d_empty[rt][1]);
+      }
 #pragma unroll
-    for (int e = 0; e < HD; ++e) dx[e] = 0.f;
+      for (int e = 0; e < HD; ++e) dx[e] = ok ? g * __uint_as_float(u[e]) : 0.f;
+    }
     // dx~[a] for the first factor a (a run-time index in the loop below) is accumulated in this
     // thread's private column of shared memory; dx~[b] for the second factor stays in registers
     float* sdx = smR + rt * 64 * 128 + r;
@@ -244,22 +265,24 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
       constexpr int Y = decltype(yc)::value;
 #pragma unroll 1
       for (int tt = 0; tt < 2 * (Y + 1); ++tt, ++nt) {
-        if (ok) ok = mbar_wait(&d_full[rt], nt & 1, &abort_flag);
+        const int b = nt & 1;
+        if (ok) ok = mbar_wait(&d_full[rt][b], (nt >> 1) & 1, &abort_flag);
         tc_fence_after();
         if (!ok) continue;
+        const uint32_t cd = tmem + lane_addr + col_d(rt, b);
         // two register buffers: the load of the next 32 columns is in flight while these are used
         uint32_t v[2][32];
-        tmem_ld32(tmem + lane_addr + col_d, v[0]);
+        tmem_ld32(cd, v[0]);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           tmem_wait_ld();
           if (q < 3) {
-            tmem_ld32(tmem + lane_addr + col_d + (q + 1) * 32, v[(q + 1) & 1]);
+            tmem_ld32(cd + (q + 1) * 32, v[(q + 1) & 1]);
           } else {
             // all of this thread's reads of the buffer are done
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&d_empty[rt]);
+            if (lane == 0) mbar_arrive(&d_empty[rt][b]);
           }
           const int a = 8 * tt + 2 * q;  // first factors a, a+1 (a even)
           const float2 xa2 = Pack2<T>::to_f32(
@@ -285,21 +308,10 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
 #pragma unroll
     for (int e = 0; e < HD; ++e) dx[e] += sdx[e * 128];
 
-    if (ok) ok = mbar_wait(&u_full[rt], 0, &abort_flag);
-    tc_fence_after();
     if (ok) {
-      uint32_t u[64];
-      tmem_ld32(tmem + lane_addr + COL_U + rt * 64, u);
-      tmem_ld32(tmem + lane_addr + COL_U + rt * 64 + 32, u + 32);
-      tmem_wait_ld();
-      float g = p.gram_mult;
-      if (p.row_g != nullptr) g *= row_valid ? p.row_g[(tok0 + row) * p.hx + head] : 0.f;
       float dot = 0.f;
 #pragma unroll
-      for (int e = 0; e < HD; ++e) {
-        dx[e] = fmaf(g, __uint_as_float(u[e]), dx[e]);
-        dot = fmaf(x[e], dx[e], dot);
-      }
+      for (int e = 0; e < HD; ++e) dot = fmaf(x[e], dx[e], dot);
       if (row_valid) {
         float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
 #pragma unroll

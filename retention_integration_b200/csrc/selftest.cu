@@ -321,6 +321,72 @@ extern "C" int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int d
   return PR_OK;
 }
 
+namespace pr {
+// Micro-benchmark: how fast the SMs can stream 16 KB tiles (128 rows x 128 B, swizzled) out of
+// L2 with TMA.  Every CTA walks `tiles` consecutive tiles of its region `reps` times through a
+// ring of `depth` stages; CTAs with the same blockIdx.x / share walk the same region.
+__global__ void __launch_bounds__(64)
+tma_stream_kernel(int tiles, int reps, int depth, int share, long long* cycles,
+                  const __grid_constant__ CUtensorMap tm) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full[12], empty[12];
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < depth; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const int region = blockIdx.x / share;
+  const int total = tiles * reps;
+  const long long t0 = clock64();
+  if (tid == 0) {
+    for (int i = 0; i < total; ++i) {
+      const int s = i % depth, ph = (i / depth) & 1;
+      if (!mbar_wait(&empty[s], ph ^ 1, &abort_flag)) break;
+      mbar_expect_tx(&full[s], 16384);
+      tma_load_2d(sm + s * 16384, &tm, &full[s], 0, (region * tiles + i % tiles) * 128);
+    }
+  } else if (tid == 32) {
+    for (int i = 0; i < total; ++i) {
+      const int s = i % depth, ph = (i / depth) & 1;
+      if (!mbar_wait(&full[s], ph, &abort_flag)) break;
+      mbar_arrive(&empty[s]);
+    }
+    cycles[blockIdx.x] = clock64() - t0;
+  }
+}
+}  // namespace pr
+
+// buf_bytes must cover ceil(grid / share) * tiles * 16384 bytes.  cycles: one entry per CTA.
+extern "C" int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int grid, int tiles, int reps, int depth,
+                                      int share, long long* cycles, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(buf && cycles && grid > 0 && tiles > 0 && reps > 0 && depth >= 1 && depth <= 12 && share >= 1,
+             PR_ERR_BAD_ARG, "bad arguments");
+  PR_REQUIRE((long long)((grid + share - 1) / share) * tiles * 16384 <= buf_bytes, PR_ERR_BAD_ARG,
+             "buffer of %lld bytes is smaller than the %d regions of %d tiles", buf_bytes, (grid + share - 1) / share,
+             tiles);
+  PR_CUDA(cudaSetDevice(device));
+  CUtensorMap tm;
+  uint64_t dims[2] = {64, (uint64_t)((grid + share - 1) / share) * tiles * 128};
+  uint64_t strides[2] = {0, 128};
+  uint32_t box[2] = {64, 128};
+  int rc = make_tmap(&tm, buf, 2, 2, dims, strides, box, true);
+  if (rc) return rc;
+  const int smem = 1024 + depth * 16384;
+  PR_CUDA(cudaFuncSetAttribute(tma_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  tma_stream_kernel<<<grid, 64, smem, static_cast<cudaStream_t>(stream)>>>(tiles, reps, depth, share, cycles, tm);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
 extern "C" int pr_selftest_tmem_bw(int nwarps, int iters, long long* cycles, float* sink, int device, void* stream) {
   using namespace pr;
   PR_REQUIRE(nwarps == 4 || nwarps == 8 || nwarps == 16, PR_ERR_BAD_ARG, "nwarps must be 4, 8 or 16");
