@@ -81,11 +81,19 @@ int pr_selftest_umma(int variant, int dtype, int n, int k, const void* a, const 
  * N=128; 1: smem x smem N=64; 2: tmem x smem N=64; 3: tmem x smem N=128); 4*reps MMAs of K=16. */
 int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int device, void* stream);
 int pr_selftest_tmem_bw(int nwarps, int iters, long long* cycles, float* sink, int device, void* stream);
+/* Round trip of a 32-lane x 32-column tensor-memory load seen by nwarps (4, 8, 16) reader warps while one more thread
+ * issues mma_reps groups of four M=128, N=mma_n, K=16 products (0 = idle tensor core).  cycles[0] = clocks of the slowest
+ * reader for `iters` loads, cycles[1] = clocks of the products.  burst > 0: mma_reps bursts of `burst` groups, each
+ * waited for, `gap` idle clocks apart; cycles[1] = clocks inside bursts, [2]/[3] = first/last burst, [4] = issuing (products and commit), [5] = products only;
+ * cycles holds 8 entries. */
+int pr_selftest_tmem_ld_contention(int nwarps, int iters, int mma_reps, int mma_n, int burst, int gap,
+                                   long long* cycles, float* sink, int device, void* stream);
 /* L2 -> shared memory streaming rate of TMA: `grid` CTAs each walk `tiles` 16 KB tiles `reps` times through a ring
  * of `depth` stages (<= 12); CTAs with equal blockIdx.x / share read the same region; the regions must fit in
- * buf_bytes.  cycles[grid] = SM clocks. */
+ * buf_bytes; min_smem (bytes of dynamic shared memory asked for at least) limits the CTAs per SM.
+ * cycles[grid] = SM clocks. */
 int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int grid, int tiles, int reps, int depth, int share,
-                           long long* cycles, int device, void* stream);
+                           int min_smem, long long* cycles, int device, void* stream);
 
 /* Gate glue of retention/power_retention_maker.py:143-155,183-186 in one pass.
  * log_g [b,t,h] or NULL; x [b,t,hx,d].  Writes (when write_a) a [b,t,h] = inclusive

@@ -47,6 +47,44 @@ struct ChunkDkvParams {
   int* status;
 };
 
+// One 32-column half of a step for one key row: P / l into `pk`, dS into `dk`, twice the row sum of
+// p * dp into da2.  SEP: the gate factor is c_j * fq[col] (c_j carries 2 s^2); otherwise
+// 2 s^2 e^{aq[col] - a_j} per pair, with columns beyond `hi` (past the chunk) dropped as well.
+// MASK: columns before `lo` (queries that precede this key) are dropped.
+template <typename T, bool SEP, bool MASK>
+__device__ __forceinline__ void dkv_half(const uint32_t (&sv)[32], const uint32_t (&pv)[32], const float* __restrict__ fq,
+                                         const float* __restrict__ il, const float* __restrict__ hl,
+                                         const float* __restrict__ dl, float c_j, float a_j, int lo, int hi,
+                                         uint32_t (&pk)[16], uint32_t (&dk)[16], float& da2) {
+  const float4* f4 = reinterpret_cast<const float4*>(fq);
+  const float4* i4 = reinterpret_cast<const float4*>(il);
+  const float4* h4 = reinterpret_cast<const float4*>(hl);
+  const float4* d4 = reinterpret_cast<const float4*>(dl);
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 f = f4[j >> 2], iq = i4[j >> 2], hq = h4[j >> 2], dq = d4[j >> 2];
+    const float fv[4] = {f.x, f.y, f.z, f.w}, iv[4] = {iq.x, iq.y, iq.z, iq.w};
+    const float hv[4] = {hq.x, hq.y, hq.z, hq.w}, dv[4] = {dq.x, dq.y, dq.z, dq.w};
+    float pw[4], dsv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float s = __uint_as_float(sv[j + u]);
+      float g = SEP ? c_j * fv[u] : c_j * __expf(fv[u] - a_j);
+      if (MASK) g = (j + u >= lo) ? g : 0.f;
+      if (!SEP) g = (j + u <= hi) ? g : 0.f;
+      const float sg2 = s * g;  // 2 s^2 S e^{a_i-a_j}
+      const float dp = fmaf(__uint_as_float(pv[j + u]), iv[u], dv[u]);
+      dsv[u] = sg2 * dp;
+      da2 = fmaf(dsv[u], s, da2);
+      pw[u] = (sg2 * s) * hv[u];
+    }
+    pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
+    pk[(j >> 1) + 1] = Pack2<T>::from_f32(pw[2], pw[3]);
+    dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+    dk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(dkv::THREADS, 2)
 chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_k,
@@ -199,7 +237,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
     const float* a_chunk = gated ? p.a + tok_base * p.h + kvhead : nullptr;
     const float a_j = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
     const float s2 = p.scale * p.scale;
-    float da = 0.f, da2 = 0.f;  // da2 collects twice the fast-path terms
+    float da2 = 0.f;  // twice the row sum of p * dp
     bool ok = true;
     // per-query values of the next step, loaded one step ahead by the first TW threads
     float av_n = 0.f, r_n = 0.f, dl_n = 0.f, l_n = 1.f;
@@ -236,81 +274,43 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
       ok = mbar_wait(&sp_full, st & 1, &abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const float* aq = sm_aq[sb];
-      const float* dlq = sm_dl[sb];
-      const float* ilq = sm_il[sb];
-      // Steps whose queries all lie at or after every key of this warp need no mask, and their
-      // gate factor separates: e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}; one exponential per
-      // key and per query instead of one per pair.  Other steps take the exact per-pair form.
-      const float r = sm_r[sb];
-      const bool fast = (row0 + (warp << 5) + 31 <= qp0) && (qp0 + TW - 1 < p.c) &&
-                        !(sm_wide[sb][0] | sm_wide[sb][1]) &&
-                        !__any_sync(0xffffffffu, (r - a_j) > 80.f);
-      if (fast) {
-        const float c_j = 2.f * s2 * __expf(r - a_j);
-        const float4* fq4 = reinterpret_cast<const float4*>(sm_fq[sb]);
-        const float4* il4 = reinterpret_cast<const float4*>(sm_il[sb]);
-        const float4* hl4 = reinterpret_cast<const float4*>(sm_hl[sb]);
-        const float4* dl4 = reinterpret_cast<const float4*>(sm_dl[sb]);
+      // The gate factor separates, e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}: one exponential per
+      // key and per query instead of one per pair (both exponents <= 0 off the diagonal for gates
+      // <= 0; a warp falls back to the per-pair form if one exceeds 80).  Steps whose queries all
+      // come after this warp's keys need no mask; a warp whose keys all come after the step's
+      // queries writes zeros without reading the scores.
+      const int wrow0 = row0 + (warp << 5);
+      if (qp0 + TW - 1 < wrow0 || wrow0 >= p.c) {
+        uint32_t z[16];
 #pragma unroll
-        for (int q4 = 0; q4 < TW / 32; ++q4) {
-          uint32_t sv[32], pv[32];
-          tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
-          tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
-          tmem_wait_ld();
-          uint32_t pk[16], dk[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const float4 f = fq4[q4 * 8 + (j >> 2)], i4 = il4[q4 * 8 + (j >> 2)];
-            const float4 h4 = hl4[q4 * 8 + (j >> 2)], d4 = dl4[q4 * 8 + (j >> 2)];
-            const float fv[4] = {f.x, f.y, f.z, f.w}, iv[4] = {i4.x, i4.y, i4.z, i4.w};
-            const float hv[4] = {h4.x, h4.y, h4.z, h4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pw[4], dsv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float s = __uint_as_float(sv[j + u]);
-              const float sg2 = s * (c_j * fv[u]);  // 2 s^2 S e^{a_i-a_j}
-              const float dp = fmaf(__uint_as_float(pv[j + u]), iv[u], dv[u]);
-              dsv[u] = sg2 * dp;
-              da2 = fmaf(dsv[u], s, da2);
-              pw[u] = (sg2 * s) * hv[u];
-            }
-            pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
-            pk[(j >> 1) + 1] = Pack2<T>::from_f32(pw[2], pw[3]);
-            dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
-            dk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
-          }
-          tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
-          tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, dk);
-        }
+        for (int j = 0; j < 16; ++j) z[j] = 0u;
+        tmem_st16(tmem + lane_addr + COL_P, z);
+        tmem_st16(tmem + lane_addr + COL_P + 16, z);
+        tmem_st16(tmem + lane_addr + COL_DS, z);
+        tmem_st16(tmem + lane_addr + COL_DS + 16, z);
       } else {
-#pragma unroll
+        const float r = sm_r[sb];
+        const bool mask = (wrow0 + 31 > qp0) || (wrow0 + 31 >= p.c);
+        const bool sep = (qp0 + TW - 1 < p.c) && !(sm_wide[sb][0] | sm_wide[sb][1]) &&
+                         !__any_sync(0xffffffffu, (r - a_j) > 80.f);
+        const float c_j = sep ? 2.f * s2 * __expf(r - a_j) : 2.f * s2;
+        const int lo = row_valid ? row - qp0 : TW;  // first query column this key keeps
+        const int hi = p.c - 1 - qp0;               // last column inside the chunk
+#pragma unroll 1
         for (int q4 = 0; q4 < TW / 32; ++q4) {
-          uint32_t sv[32], pv[32];
+          uint32_t sv[32], pv[32], pk[16], dk[16];
           tmem_ld32(tmem + lane_addr + COL_S + q4 * 32, sv);
           tmem_ld32(tmem + lane_addr + COL_DP + q4 * 32, pv);
           tmem_wait_ld();
-          uint32_t pk[16], dk[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float pw[2], dsv[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int col = q4 * 32 + j + u;
-              const float s = __uint_as_float(sv[j + u]);
-              float g = s2;
-              if (gated) g *= __expf(aq[col] - a_j);
-              const float dp = fmaf(__uint_as_float(pv[j + u]), ilq[col], dlq[col]);
-              float sg = s * g;
-              const int qp = qp0 + col;
-              if (qp < row || qp >= p.c || !row_valid) sg = 0.f;
-              const float pval = sg * s;
-              da = fmaf(pval, dp, da);
-              pw[u] = pval * ilq[col];
-              dsv[u] = 2.f * sg * dp;
-            }
-            pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
-            dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
+          const float* il = sm_il[sb] + q4 * 32;
+          const float* hl = sm_hl[sb] + q4 * 32;
+          const float* dl = sm_dl[sb] + q4 * 32;
+          const int lo4 = lo - q4 * 32, hi4 = hi - q4 * 32;
+          if (sep) {
+            if (mask) dkv_half<T, true, true>(sv, pv, sm_fq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
+            else dkv_half<T, true, false>(sv, pv, sm_fq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
+          } else {
+            dkv_half<T, false, true>(sv, pv, sm_aq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
           }
           tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
           tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, dk);
@@ -413,7 +413,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
           v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
           dst[j] = v;
         }
-        p.da_k[tok * p.h + kvhead] = -fmaf(0.5f, da2, da);
+        p.da_k[tok * p.h + kvhead] = -0.5f * da2;
       }
     }
   }

@@ -59,6 +59,31 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// One 32-column half of an attention step for one query row: p = s^2 S^2 g into `pk`, row sum into
+// l_acc.  SEP: the gate factor is c_i * fk[col] (c_i carries s^2); otherwise s^2 e^{a_i - ak[col]} per
+// pair.  MASK: columns beyond `lim` (the row's own key position, relative to the step) are dropped.
+template <typename T, bool SEP, bool MASK>
+__device__ __forceinline__ void out_half(const uint32_t (&sv)[32], const float* __restrict__ fk, float c_i, float a_i,
+                                         int lim, uint32_t (&pk)[16], float& l_acc) {
+  const float4* f4 = reinterpret_cast<const float4*>(fk);
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 f = f4[j >> 2];
+    const float fv[4] = {f.x, f.y, f.z, f.w};
+    float pv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float s = __uint_as_float(sv[j + u]);
+      float g = SEP ? c_i * fv[u] : c_i * __expf(a_i - fv[u]);
+      if (MASK) g = (j + u <= lim) ? g : 0.f;
+      pv[u] = (s * s) * g;
+    }
+    pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
+    pk[(j >> 1) + 1] = Pack2<T>::from_f32(pv[2], pv[3]);
+    l_acc += (pv[0] + pv[1]) + (pv[2] + pv[3]);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(co::THREADS, 2)
 chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_q,
@@ -71,7 +96,7 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
   __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
-  __shared__ float sm_ak[2][TW];
+  __shared__ __align__(16) float sm_ak[2][TW];
   __shared__ __align__(16) float sm_fk[2][TW];  // e^{r - a_j}, r = gate sum at the step's last key
   __shared__ float sm_r[2];
   __shared__ int sm_wide[2][2];                 // a loader warp saw r - a_j > 80 (overflow guard)
@@ -94,7 +119,6 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
   const int last_key = min(p.ck - 1, row0 + 127 + q_off);
   const int nJ = p.has_attn ? last_key / TW + 1 : 0;
   const bool has_state = chunk >= p.state_from_chunk;
-  const int n_items = has_state ? NBLK + 1 : 0;
 
   if (tid == 0) {
     abort_flag = 0;
@@ -250,9 +274,8 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
       const int kp0 = J * TW;
       const int sb = J & 1;
       if (tid < TW) {
-        const int kp = kp0 + tid;
         sm_ak[sb][tid] = av_n;
-        sm_fk[sb][tid] = kp < p.ck ? __expf(r_n - av_n) : 0.f;
+        sm_fk[sb][tid] = __expf(r_n - av_n);
         const bool wide = __any_sync(0xffffffffu, (r_n - av_n) > 80.f);
         if (lane == 0) sm_wide[sb][warp] = wide;
         if (tid == 0) sm_r[sb] = r_n;
@@ -263,62 +286,35 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
       if (!ok) break;
       tc_fence_after();
       const uint32_t col_s = COL_S + sb * TW;
-      // Steps that lie wholly below the diagonal for every row of this warp need no mask, and
-      // their gate factor separates: e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}; one exponential
-      // per row and per key instead of one per pair.  Steps on the diagonal, ragged steps and
-      // out-of-range exponents take the exact per-pair form.
-      const float r = sm_r[sb];
-      const bool fast = (kp0 + TW - 1 <= row0 + (warp << 5) + q_off) && (kp0 + TW - 1 < p.ck) &&
-                        !(sm_wide[sb][0] | sm_wide[sb][1]) &&
-                        !__any_sync(0xffffffffu, (a_i - r) > 80.f);
-      if (fast) {
-        const float c_i = s2 * __expf(a_i - r);
-        const float4* fk4 = reinterpret_cast<const float4*>(sm_fk[sb]);
+      // The gate factor separates, e^{a_i - a_j} = e^{a_i - r} * e^{r - a_j}: one exponential per
+      // row and per key instead of one per pair (both exponents <= 0 below the diagonal for gates
+      // <= 0; a warp falls back to the per-pair form if one exceeds 80).  Steps wholly below the
+      // diagonal need no mask; a warp whose rows all precede the step's keys writes zeros
+      // without reading the scores.
+      const int wq0 = row0 + (warp << 5) + q_off;  // key position of this warp's first query
+      if (kp0 > min(wq0 + 31, p.ck - 1)) {
+        uint32_t z[16];
 #pragma unroll
-        for (int q4 = 0; q4 < TW / 32; ++q4) {
-          uint32_t sv[32];
-          tmem_ld32(tmem + lane_addr + col_s + q4 * 32, sv);
-          tmem_wait_ld();
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const float4 f = fk4[q4 * 8 + (j >> 2)];
-            const float fv[4] = {f.x, f.y, f.z, f.w};
-            float pv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float s = __uint_as_float(sv[j + u]);
-              pv[u] = (s * s) * (c_i * fv[u]);
-            }
-            pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
-            pk[(j >> 1) + 1] = Pack2<T>::from_f32(pv[2], pv[3]);
-            l_acc += (pv[0] + pv[1]) + (pv[2] + pv[3]);
-          }
-          tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
-        }
+        for (int j = 0; j < 16; ++j) z[j] = 0u;
+        tmem_st16(tmem + lane_addr + col_s, z);
+        tmem_st16(tmem + lane_addr + col_s + 16, z);
       } else {
-        const float* ak = sm_ak[sb];
-#pragma unroll
+        const float r = sm_r[sb];
+        const bool mask = (kp0 + TW - 1 > wq0) || (kp0 + TW - 1 >= p.ck);
+        const bool sep = !(sm_wide[sb][0] | sm_wide[sb][1]) && !__any_sync(0xffffffffu, (a_i - r) > 80.f);
+        const float c_i = sep ? s2 * __expf(a_i - r) : s2;
+        const int lim = min(qpos, p.ck - 1) - kp0;  // last column this row keeps
+#pragma unroll 1
         for (int q4 = 0; q4 < TW / 32; ++q4) {
-          uint32_t sv[32];
+          uint32_t sv[32], pk[16];
           tmem_ld32(tmem + lane_addr + col_s + q4 * 32, sv);
           tmem_wait_ld();
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float pv[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int col = q4 * 32 + j + u;
-              const float s = __uint_as_float(sv[j + u]);
-              float w = s2 * s * s;
-              if (gated) w *= __expf(a_i - ak[col]);
-              const int kp = kp0 + col;
-              if (kp > qpos || kp >= p.ck) w = 0.f;
-              pv[u] = w;
-            }
-            pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
-            l_acc += pv[0] + pv[1];
+          const int lm = lim - q4 * 32;
+          if (sep) {
+            if (mask) out_half<T, true, true>(sv, sm_fk[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
+            else out_half<T, true, false>(sv, sm_fk[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
+          } else {
+            out_half<T, false, true>(sv, sm_ak[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
           }
           tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
         }

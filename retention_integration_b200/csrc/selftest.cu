@@ -322,6 +322,118 @@ extern "C" int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int d
 }
 
 namespace pr {
+// Micro-benchmark: round trip of tcgen05.ld (32 lanes x 32 columns, then wait) as seen by
+// `nwarps` reader warps, alone or while one more thread keeps the tensor core busy with
+// smem x smem products (M = 128, N = mma_n, K = 16) into other columns.  cycles[0] = SM clocks
+// the slowest reader took for `iters` loads, cycles[1] = clocks for the products.  With burst > 0 the
+// products come as mma_reps bursts of `burst` groups, each waited for, `gap` idle clocks apart:
+// cycles[1] = clocks inside bursts, [2] / [3] = first / last burst, [4] = clocks spent issuing (products and commit), [5] = products only.
+__global__ void tmem_ld_contention_kernel(int iters, int mma_reps, int mma_n, int burst, int gap, long long* cycles,
+                                          float* sink) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ unsigned long long worst;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int readers = (blockDim.x >> 5) - 1;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
+  for (int i = tid; i < 49152 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(sm)[i] = 0;
+  if (tid == 0) {
+    abort_flag = 0;
+    worst = 0;
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  if (warp < readers) {
+    const uint32_t base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    uint32_t acc = 0;
+    const long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+      uint32_t v[32];
+      tmem_ld32(base + ((it * 32) & 255), v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc ^= v[j];
+    }
+    const long long t1 = clock64();
+    atomicMax(&worst, (unsigned long long)(t1 - t0));
+    if (acc == 0x12345u) sink[0] = 1.f;
+  } else if (tid == readers * 32 && mma_reps > 0) {
+    const uint32_t a_addr = smem_u32(sm), b_addr = smem_u32(sm + 16384);
+    const uint32_t idesc = umma_idesc(128, mma_n, true, false, false);
+    if (burst <= 0) {
+      const long long t0 = clock64();
+      for (int r = 0; r < mma_reps; ++r) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + 256, umma_desc_sw128(a_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(b_addr + ks * 32, 16, 1024), idesc, 1u);
+      }
+      umma_commit(&bar);
+      mbar_wait(&bar, 0, &abort_flag);
+      cycles[1] = clock64() - t0;
+    } else {
+      // bursts of `burst` groups of four products, each burst waited for, `gap` idle clocks between bursts
+      long long in_burst = 0, issue = 0, mma_issue = 0;
+      for (int r = 0; r < mma_reps; ++r) {
+        const long long t0 = clock64();
+        for (int g = 0; g < burst; ++g) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ss(tmem + 256, umma_desc_sw128(a_addr + ks * 32, 16, 1024),
+                    umma_desc_sw128(b_addr + ks * 32, 16, 1024), idesc, 1u);
+        }
+        const long long tm = clock64();
+        umma_commit(&bar);
+        const long long t1 = clock64();
+        mbar_wait(&bar, r & 1, &abort_flag);
+        const long long t2 = clock64();
+        issue += t1 - t0;
+        mma_issue += tm - t0;
+        in_burst += t2 - t0;
+        if (r == 0) cycles[2] = t2 - t0;
+        if (r == mma_reps - 1) cycles[3] = t2 - t0;
+        while (clock64() - t2 < gap) {
+        }
+      }
+      cycles[1] = in_burst;
+      cycles[4] = issue;
+      cycles[5] = mma_issue;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) cycles[0] = (long long)worst;
+  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+}
+}  // namespace pr
+
+extern "C" int pr_selftest_tmem_ld_contention(int nwarps, int iters, int mma_reps, int mma_n, int burst, int gap,
+                                              long long* cycles, float* sink, int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE((nwarps == 4 || nwarps == 8 || nwarps == 16) && iters > 0 && mma_reps >= 0 &&
+                 (mma_n == 64 || mma_n == 128 || mma_n == 256) && cycles && sink,
+             PR_ERR_BAD_ARG, "bad arguments");
+  PR_CUDA(cudaSetDevice(device));
+  PR_CUDA(cudaFuncSetAttribute(tmem_ld_contention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 51200));
+  tmem_ld_contention_kernel<<<1, (nwarps + 1) * 32, 51200, static_cast<cudaStream_t>(stream)>>>(
+      iters, mma_reps, mma_n, burst, gap, cycles, sink);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+namespace pr {
 // Micro-benchmark: how fast the SMs can stream 16 KB tiles (128 rows x 128 B, swizzled) out of
 // L2 with TMA.  Every CTA walks `tiles` consecutive tiles of its region `reps` times through a
 // ring of `depth` stages; CTAs with the same blockIdx.x / share walk the same region.
@@ -366,7 +478,7 @@ tma_stream_kernel(int tiles, int reps, int depth, int share, long long* cycles,
 
 // buf_bytes must cover ceil(grid / share) * tiles * 16384 bytes.  cycles: one entry per CTA.
 extern "C" int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int grid, int tiles, int reps, int depth,
-                                      int share, long long* cycles, int device, void* stream) {
+                                      int share, int min_smem, long long* cycles, int device, void* stream) {
   using namespace pr;
   PR_REQUIRE(buf && cycles && grid > 0 && tiles > 0 && reps > 0 && depth >= 1 && depth <= 12 && share >= 1,
              PR_ERR_BAD_ARG, "bad arguments");
@@ -380,7 +492,7 @@ extern "C" int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int 
   uint32_t box[2] = {64, 128};
   int rc = make_tmap(&tm, buf, 2, 2, dims, strides, box, true);
   if (rc) return rc;
-  const int smem = 1024 + depth * 16384;
+  const int smem = max(1024 + depth * 16384, min(min_smem, 227 * 1024));  // min_smem limits the CTAs per SM
   PR_CUDA(cudaFuncSetAttribute(tma_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   tma_stream_kernel<<<grid, 64, smem, static_cast<cudaStream_t>(stream)>>>(tiles, reps, depth, share, cycles, tm);
   PR_CUDA(cudaGetLastError());
