@@ -27,12 +27,14 @@ namespace pr {
 
 namespace co {
 constexpr int HD = 64;
-constexpr int NS = 4;                 // stages of the expansion / Z ring
+constexpr int NS = 4;                 // stages of the expanded-operand ring in tensor memory
+constexpr int NR = 4;                 // shared-memory ring: stages of 16 KB (a key and a value tile, or two state blocks)
 constexpr int THREADS = 192;
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows x 64 16-bit features
 constexpr int TW = 64;                 // keys per attention step
 constexpr int KV_BYTES = TW * 128;     // one key or value tile
 constexpr int Z_BYTES = 64 * 128;      // 64 expanded rows x 64 features
+constexpr int R_BYTES = 2 * KV_BYTES;  // one ring stage
 constexpr int DR = ref_dim(HD);        // 2560 expanded rows
 constexpr int NBLK = DR / 64;          // 40 stages of 64 expanded rows (4 first factors x 16)
 constexpr uint32_t TMEM_COLS = 256;
@@ -92,8 +94,8 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
                  const __grid_constant__ CUtensorMap tm_glo) {
   using namespace co;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2], attn_done, g_full, acc_done;
-  __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
+  __shared__ uint64_t q_full, r_full[NR], r_empty[NR], s_full[2], p_full[2], attn_done, g_full, acc_done;
+  __shared__ uint64_t a_full[NS], a_empty[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ __align__(16) float sm_ak[2][TW];
@@ -105,10 +107,11 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smQ = sm;
-  uint8_t* smK = smQ + TILE_BYTES;        // 2 stages x KV_BYTES
-  uint8_t* smV = smK + 2 * KV_BYTES;      // 2 stages x KV_BYTES
-  uint8_t* smZ = smV + 2 * KV_BYTES;      // NS x Z_BYTES
-  uint8_t* smG = smZ + NS * Z_BYTES;      // hi, lo: 2 x Z_BYTES
+  // One ring serves both phases: attention step J takes stage J % NR (key tile, then value tile);
+  // the state read-out goes on with the same stage counter, two 64-row state blocks per stage,
+  // so state blocks stream in while the last attention steps are still being computed.
+  uint8_t* smR = smQ + TILE_BYTES;        // NR x R_BYTES
+  uint8_t* smG = smR + NR * R_BYTES;      // hi, lo: 2 x Z_BYTES
 
   const int tile_i = blockIdx.x % p.tiles_per_chunk;
   const int chunk = blockIdx.x / p.tiles_per_chunk;
@@ -124,17 +127,17 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
     abort_flag = 0;
     mbar_init(&q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&p_full[s], 4);
+    }
+    for (int s = 0; s < NR; ++s) {
+      mbar_init(&r_full[s], 1);
+      mbar_init(&r_empty[s], 1);
     }
     mbar_init(&attn_done, 1);
     mbar_init(&g_full, 1);
     mbar_init(&acc_done, 1);
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&z_full[s], 1);
-      mbar_init(&z_empty[s], 1);
       mbar_init(&a_full[s], 4);
       mbar_init(&a_empty[s], 1);
     }
@@ -155,24 +158,26 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
       bool ok = true;
       mbar_expect_tx(&q_full, TILE_BYTES);
       tma_load_4d(smQ, &tm_q, &q_full, 0, qhead, chunk * p.cq + row0, batch);
-      for (int J = 0; J < nJ && ok; ++J) {
-        const int s = J & 1, ph = (J >> 1) & 1;
-        ok = mbar_wait(&kv_empty[s], ph ^ 1, &abort_flag);
-        if (!ok) break;
-        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
-        tma_load_4d(smK + s * KV_BYTES, &tm_k, &kv_full[s], 0, kvhead, chunk * p.ck + J * TW, batch);
-        tma_load_4d(smV + s * KV_BYTES, &tm_v, &kv_full[s], 0, kvhead, chunk * p.ck + J * TW, batch);
-      }
-      if (ok && has_state) {
-        const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
+      const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
+      if (has_state) {
         mbar_expect_tx(&g_full, 2 * Z_BYTES);
         tma_load_2d(smG, &tm_ghi, &g_full, 0, ch * HD);
         tma_load_2d(smG + Z_BYTES, &tm_glo, &g_full, 0, ch * HD);
-        for (int blk = 0; blk < NBLK; ++blk) {
-          const int s = blk % NS, ph = (blk / NS) & 1;
-          if (!mbar_wait(&z_empty[s], ph ^ 1, &abort_flag)) break;
-          mbar_expect_tx(&z_full[s], Z_BYTES);
-          tma_load_2d(smZ + s * Z_BYTES, &tm_z, &z_full[s], 0, ch * DR + blk * 64);
+      }
+      const int n_ring = nJ + (has_state ? NBLK / 2 : 0);
+      for (int g = 0; g < n_ring && ok; ++g) {
+        const int s = g % NR, ph = (g / NR) & 1;
+        ok = mbar_wait(&r_empty[s], ph ^ 1, &abort_flag);
+        if (!ok) break;
+        mbar_expect_tx(&r_full[s], R_BYTES);
+        uint8_t* dst = smR + s * R_BYTES;
+        if (g < nJ) {
+          tma_load_4d(dst, &tm_k, &r_full[s], 0, kvhead, chunk * p.ck + g * TW, batch);
+          tma_load_4d(dst + KV_BYTES, &tm_v, &r_full[s], 0, kvhead, chunk * p.ck + g * TW, batch);
+        } else {
+          const int blk = 2 * (g - nJ);
+          tma_load_2d(dst, &tm_z, &r_full[s], 0, ch * DR + blk * 64);
+          tma_load_2d(dst + Z_BYTES, &tm_z, &r_full[s], 0, ch * DR + (blk + 1) * 64);
         }
       }
     }
@@ -188,9 +193,9 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
       // always have the next tile waiting (two score buffers, two key/value stages)
       auto issue_scores = [&](int J) -> bool {
         const int s = J & 1;
-        if (!mbar_wait(&kv_full[s], (J >> 1) & 1, &abort_flag)) return false;
+        if (!mbar_wait(&r_full[J % NR], (J / NR) & 1, &abort_flag)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(smK + s * KV_BYTES);
+        const uint32_t k_addr = smem_u32(smR + (J % NR) * R_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_ss(tmem + COL_S + s * TW, umma_desc_sw128(q_addr + ks * 32, 16, 1024),
@@ -206,12 +211,12 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
         ok = mbar_wait(&p_full[s], (J >> 1) & 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(smV + s * KV_BYTES);
+        const uint32_t v_addr = smem_u32(smR + (J % NR) * R_BYTES + KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < TW / 16; ++ks)
           umma_ts(tmem + COL_ACC, tmem + COL_S + s * TW + ks * 8, umma_desc_sw128(v_addr + ks * 2048, 8192, 1024),
                   idesc_v, (J > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&kv_empty[s]);
+        umma_commit(&r_empty[J % NR]);
         if (J == nJ - 1) umma_commit(&attn_done);
       }
       if (ok && has_state) {
@@ -231,17 +236,17 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
         }
         for (int it = 1; it <= NBLK && ok; ++it) {
           const int s = it % NS, ph = (it / NS) & 1;
-          const int zs = (it - 1) % NS, zph = ((it - 1) / NS) & 1;
-          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&z_full[zs], zph, &abort_flag);
+          const int blk = it - 1, g = nJ + (blk >> 1), rs = g % NR;
+          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&r_full[rs], (g / NR) & 1, &abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t z_addr = smem_u32(smZ + zs * Z_BYTES);
+          const uint32_t z_addr = smem_u32(smR + rs * R_BYTES + (blk & 1) * Z_BYTES);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             umma_ts(tmem + COL_ACC, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(z_addr + ks * 2048, 8192, 1024),
                     idesc_v, (nJ > 0 || it > 1 || ks > 0) ? 1u : 0u);
           umma_commit(&a_empty[s]);
-          umma_commit(&z_empty[zs]);
+          if (blk & 1) umma_commit(&r_empty[rs]);
         }
       }
       if (ok) umma_commit(&acc_done);
@@ -499,7 +504,7 @@ extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int 
     tm_ghi = tm_q;
     tm_glo = tm_q;
   }
-  const size_t smem = 1024 + TILE_BYTES + 4 * KV_BYTES + NS * Z_BYTES + 2 * Z_BYTES;
+  const size_t smem = 1024 + TILE_BYTES + NR * R_BYTES + 2 * Z_BYTES;
   dim3 grid(p.tiles_per_chunk * n_chunks, hq, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
