@@ -20,12 +20,14 @@ namespace pr {
 
 namespace dkv {
 constexpr int HD = 64;
-constexpr int NS = 4;
+constexpr int NS = 4;                    // stages of the expanded-operand ring in tensor memory
+constexpr int NR = 4;                    // shared-memory ring: stages of 16 KB (a query and a dO tile, or two state blocks)
 constexpr int THREADS = 192;
 constexpr int TILE_BYTES = 128 * 128;   // 128 key rows x 64 features
 constexpr int TW = 64;                  // queries per step
 constexpr int QD_BYTES = TW * 128;      // one query or dO tile
 constexpr int Z_BYTES = 64 * 128;
+constexpr int R_BYTES = 2 * QD_BYTES;   // one ring stage
 constexpr int DR = ref_dim(HD);
 constexpr int NBLK = DR / 64;           // 40 stages of 64 expanded rows
 constexpr uint32_t TMEM_COLS = 256;     // two CTAs per SM
@@ -92,8 +94,8 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
                  const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_ds) {
   using namespace dkv;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t kv_full, qd_full[2], qd_empty[2], sp_full, pd_full, attn_done, acc_done;
-  __shared__ uint64_t z_full[NS], z_empty[NS], a_full[NS], a_empty[NS];
+  __shared__ uint64_t kv_full, r_full[NR], r_empty[NR], sp_full, pd_full, attn_done, acc_done;
+  __shared__ uint64_t a_full[NS], a_empty[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ __align__(16) float sm_aq[2][TW], sm_dl[2][TW], sm_il[2][TW];
@@ -107,9 +109,10 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
   uint8_t* smK = sm;
   uint8_t* smV = smK + TILE_BYTES;
-  uint8_t* smQ = smV + TILE_BYTES;       // 2 stages x QD_BYTES
-  uint8_t* smDY = smQ + 2 * QD_BYTES;    // 2 stages x QD_BYTES
-  uint8_t* smZ = smDY + 2 * QD_BYTES;    // NS x Z_BYTES
+  // One ring serves both phases: attention step st takes stage st % NR (query tile, then dO tile);
+  // the state phase goes on with the same stage counter, two 64-row state blocks per stage, so
+  // state blocks stream in while the last attention steps are still being computed.
+  uint8_t* smR = smV + TILE_BYTES;       // NR x R_BYTES
 
   const int tile_j = blockIdx.x % p.tiles_per_chunk;
   const int chunk = blockIdx.x / p.tiles_per_chunk;
@@ -126,17 +129,15 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&qd_full[s], 1);
-      mbar_init(&qd_empty[s], 1);
+    for (int s = 0; s < NR; ++s) {
+      mbar_init(&r_full[s], 1);
+      mbar_init(&r_empty[s], 1);
     }
     mbar_init(&sp_full, 1);
     mbar_init(&pd_full, 4);
     mbar_init(&attn_done, 1);
     mbar_init(&acc_done, 1);
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&z_full[s], 1);
-      mbar_init(&z_empty[s], 1);
       mbar_init(&a_full[s], 4);
       mbar_init(&a_empty[s], 1);
     }
@@ -157,22 +158,22 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
       mbar_expect_tx(&kv_full, 2 * TILE_BYTES);
       tma_load_4d(smK, &tm_k, &kv_full, 0, kvhead, tok_chunk + row0, batch);
       tma_load_4d(smV, &tm_v, &kv_full, 0, kvhead, tok_chunk + row0, batch);
-      for (int st = 0; st < n_steps && ok; ++st) {
-        const int I = qt0 + st / ratio, qh = kvhead * ratio + st % ratio;
-        const int s = st & 1, ph = (st >> 1) & 1;
-        ok = mbar_wait(&qd_empty[s], ph ^ 1, &abort_flag);
+      const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
+      const int n_ring = n_steps + (has_state ? NBLK / 2 : 0);
+      for (int g = 0; g < n_ring && ok; ++g) {
+        const int s = g % NR, ph = (g / NR) & 1;
+        ok = mbar_wait(&r_empty[s], ph ^ 1, &abort_flag);
         if (!ok) break;
-        mbar_expect_tx(&qd_full[s], 2 * QD_BYTES);
-        tma_load_4d(smQ + s * QD_BYTES, &tm_q, &qd_full[s], 0, qh, tok_chunk + I * TW, batch);
-        tma_load_4d(smDY + s * QD_BYTES, &tm_dy, &qd_full[s], 0, qh, tok_chunk + I * TW, batch);
-      }
-      if (ok && has_state) {
-        const int ch = (batch * p.n_chunks + chunk) * p.h + kvhead;
-        for (int blk = 0; blk < NBLK; ++blk) {
-          const int s = blk % NS, ph = (blk / NS) & 1;
-          if (!mbar_wait(&z_empty[s], ph ^ 1, &abort_flag)) break;
-          mbar_expect_tx(&z_full[s], Z_BYTES);
-          tma_load_2d(smZ + s * Z_BYTES, &tm_ds, &z_full[s], 0, ch * DR + blk * 64);
+        mbar_expect_tx(&r_full[s], R_BYTES);
+        uint8_t* dst = smR + s * R_BYTES;
+        if (g < n_steps) {
+          const int I = qt0 + g / ratio, qh = kvhead * ratio + g % ratio;
+          tma_load_4d(dst, &tm_q, &r_full[s], 0, qh, tok_chunk + I * TW, batch);
+          tma_load_4d(dst + QD_BYTES, &tm_dy, &r_full[s], 0, qh, tok_chunk + I * TW, batch);
+        } else {
+          const int blk = 2 * (g - n_steps);
+          tma_load_2d(dst, &tm_ds, &r_full[s], 0, ch * DR + blk * 64);
+          tma_load_2d(dst + Z_BYTES, &tm_ds, &r_full[s], 0, ch * DR + (blk + 1) * 64);
         }
       }
     }
@@ -183,11 +184,11 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
       const uint32_t idesc_o = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
       const uint32_t k_addr = smem_u32(smK), v_addr = smem_u32(smV);
       for (int st = 0; st < n_steps && ok; ++st) {
-        const int sg = st & 1;
-        ok = mbar_wait(&qd_full[sg], (st >> 1) & 1, &abort_flag);
+        const int sg = st % NR;
+        ok = mbar_wait(&r_full[sg], (st / NR) & 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(smQ + sg * QD_BYTES), dy_addr = smem_u32(smDY + sg * QD_BYTES);
+        const uint32_t q_addr = smem_u32(smR + sg * R_BYTES), dy_addr = q_addr + QD_BYTES;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_ss(tmem + COL_S, umma_desc_sw128(k_addr + ks * 32, 16, 1024),
@@ -208,22 +209,23 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         for (int ks = 0; ks < TW / 16; ++ks)
           umma_ts(tmem + COL_DK, tmem + COL_DS + ks * 8, umma_desc_sw128(q_addr + ks * 2048, 8192, 1024), idesc_o,
                   (st > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&qd_empty[sg]);
+        umma_commit(&r_empty[sg]);
         if (st == n_steps - 1) umma_commit(&attn_done);
       }
       if (ok && has_state) {
         for (int it = 0; it < NBLK && ok; ++it) {
           const int s = it % NS, ph = (it / NS) & 1;
-          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&z_full[s], ph, &abort_flag);
+          const int g = n_steps + (it >> 1), rs = g % NR;
+          ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&r_full[rs], (g / NR) & 1, &abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t z_addr = smem_u32(smZ + s * Z_BYTES);
+          const uint32_t z_addr = smem_u32(smR + rs * R_BYTES + (it & 1) * Z_BYTES);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
             umma_ts(tmem + COL_DV, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(z_addr + ks * 2048, 8192, 1024),
                     idesc_o, 1u);
           umma_commit(&a_empty[s]);
-          umma_commit(&z_empty[s]);
+          if (it & 1) umma_commit(&r_empty[rs]);
         }
       }
       if (ok) umma_commit(&acc_done);
@@ -481,7 +483,7 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   } else {
     tm_ds = tm_q;
   }
-  const size_t smem = 1024 + 2 * TILE_BYTES + 4 * QD_BYTES + NS * Z_BYTES;
+  const size_t smem = 1024 + 2 * TILE_BYTES + NR * R_BYTES;
   dim3 grid(p.tiles_per_chunk * p.n_chunks, h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
