@@ -28,7 +28,7 @@ constexpr int NS = 4;           // shared-memory pipeline stages
 constexpr int NSA = 2;          // tensor-memory stages of each group's expansion ring
 constexpr int NG = 2;           // row tiles (groups of 4 warps) per CTA: each loaded stage feeds both
 constexpr int TOK = 64;         // tokens per stage
-constexpr int THREADS = 320;    // warps 0-3 / 4-7 expand + epilogue (one group per row tile), 8 TMA, 9 MMA
+constexpr int THREADS = 352;    // warps 0-3 / 4-7 expand + epilogue (one group per row tile), 8 TMA, 9 / 10 MMA of group 0 / 1
 constexpr int XT_BYTES = HD * TOK * 2;   // 8 KB
 constexpr int W_BYTES = TOK * HD * 2;    // 8 KB
 constexpr int GA_BYTES = 128 * TOK * 2;  // Gram A operand padded to 128 rows
@@ -81,14 +81,14 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
       mbar_init(&x_full[s], 1);
       mbar_init(&x_empty[s], 4 * NG);
       mbar_init(&w_full[s], 1);
-      mbar_init(&w_empty[s], 1);
+      mbar_init(&w_empty[s], gram_cta ? 1 : NG);  // one release per issuing thread
     }
     for (int g = 0; g < NG; ++g)
       for (int s = 0; s < NSA; ++s) {
         mbar_init(&a_full[g][s], 4);
         mbar_init(&a_empty[g][s], 1);
       }
-    mbar_init(&acc_done, 1);
+    mbar_init(&acc_done, gram_cta ? 1 : NG);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -125,9 +125,13 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         }
       }
     }
-  } else if (warp == 4 * NG + 1) {
-    // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+  } else if (warp >= 4 * NG + 1) {
+    // ------------------------------------------------------------- MMA issuers
+    // One issuing thread per group: a single thread needs some 60-80 clocks per tcgen05.mma it
+    // issues and as many per commit or barrier wait, which made one thread serving both groups
+    // the slowest stage of the pipeline.
+    const int g = warp - (4 * NG + 1);
+    if (lane == 0 && (!gram_cta || g == 0)) {
       bool ok = true;
       if (gram_cta) {
         const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
@@ -148,19 +152,15 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         for (int it = 0; it < total && ok; ++it) {
           const int s = it % NS, ph = (it / NS) & 1;
           const int sa = it % NSA, pha = (it / NSA) & 1;
-          ok = mbar_wait(&w_full[s], ph, &abort_flag);
-          const uint32_t b_addr = smem_u32(smW + s * W_BYTES);
-          for (int g = 0; g < NG && ok; ++g) {
-            ok = mbar_wait(&a_full[g][sa], pha, &abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < TOK / 16; ++ks)
-              umma_ts(tmem + COL_ACC + g * 64, tmem + COL_A + (g * NSA + sa) * 32 + ks * 8,
-                      umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc, (it > 0 || ks > 0) ? 1u : 0u);
-            umma_commit(&a_empty[g][sa]);
-          }
+          ok = mbar_wait(&w_full[s], ph, &abort_flag) && mbar_wait(&a_full[g][sa], pha, &abort_flag);
           if (!ok) break;
+          tc_fence_after();
+          const uint32_t b_addr = smem_u32(smW + s * W_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < TOK / 16; ++ks)
+            umma_ts(tmem + COL_ACC + g * 64, tmem + COL_A + (g * NSA + sa) * 32 + ks * 8,
+                    umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&a_empty[g][sa]);
           umma_commit(&w_empty[s]);
         }
       }
