@@ -204,7 +204,6 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
       f *= p.query_side ? __expf(0.5f * a_i) : __expf(0.5f * (p.A[ch] - a_i));
     }
     bool ok = mbar_wait(&w_full, 0, &abort_flag);
-    float x[HD], dx[HD];
     {
       uint32_t xp[32];
       uint8_t* xs = smX + rt * TILE_BYTES;
@@ -216,9 +215,6 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         for (int k = 0; k < 4; ++k) {
           const float2 raw = Pack2<T>::to_f32(w[k]);
           xp[4 * j + k] = Pack2<T>::from_f32(raw.x * f, raw.y * f);
-          const float2 rounded = Pack2<T>::to_f32(xp[4 * j + k]);
-          x[8 * j + 2 * k] = rounded.x;
-          x[8 * j + 2 * k + 1] = rounded.y;
         }
       }
       // the gated row replaces the raw one in this thread's slot of the tile (fetched by a
@@ -250,19 +246,36 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         __syncwarp();
         if (lane == 0) mbar_arrive(&d_empty[rt][1]);
       }
+      // dx~ lives in this thread's private column of shared memory (64 floats, stride 128): the
+      // first-factor terms are added at a run-time index, and the second-factor terms of a
+      // 16-block are kept in registers only while that block is being drained.  Keeping all 64
+      // accumulators and the row itself in registers left the compiler no room to overlap the
+      // FMAs of neighbouring entries.
+      float* sdx0 = smR + rt * 64 * 128 + r;
 #pragma unroll
-      for (int e = 0; e < HD; ++e) dx[e] = ok ? g * __uint_as_float(u[e]) : 0.f;
+      for (int e = 0; e < HD; ++e) sdx0[e * 128] = ok ? g * __uint_as_float(u[e]) : 0.f;
     }
-    // dx~[a] for the first factor a (a run-time index in the loop below) is accumulated in this
-    // thread's private column of shared memory; dx~[b] for the second factor stays in registers
     float* sdx = smR + rt * 64 * 128 + r;
-#pragma unroll
-    for (int e = 0; e < HD; ++e) sdx[e * 128] = 0.f;
     const uint8_t* xrow = smX + rt * TILE_BYTES;  // holds the gated row again (written above)
 
     int nt = 0;
     static_for<0, HD / 16>([&](auto yc) {
       constexpr int Y = decltype(yc)::value;
+      // second factors x~[16Y .. 16Y+15] of this block and their gradient accumulators
+      float x[16], dx[16];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint4 v4 = *reinterpret_cast<const uint4*>(xrow + swz128(r, 2 * Y + j));
+        const uint32_t w[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f2 = Pack2<T>::to_f32(w[k]);
+          x[8 * j + 2 * k] = f2.x;
+          x[8 * j + 2 * k + 1] = f2.y;
+          dx[8 * j + 2 * k] = 0.f;
+          dx[8 * j + 2 * k + 1] = 0.f;
+        }
+      }
 #pragma unroll 1
       for (int tt = 0; tt < 2 * (Y + 1); ++tt, ++nt) {
         const int b = nt & 1;
@@ -294,31 +307,40 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const float val = __uint_as_float(v[q & 1][16 * aa + i]);
-              dx[16 * Y + i] = fmaf(val, xa, dx[16 * Y + i]);
+              dx[i] = fmaf(val, xa, dx[i]);
               if (i & 1)
-                ra1 = fmaf(val, x[16 * Y + i], ra1);
+                ra1 = fmaf(val, x[i], ra1);
               else
-                ra0 = fmaf(val, x[16 * Y + i], ra0);
+                ra0 = fmaf(val, x[i], ra0);
             }
             sdx[(a + aa) * 128] += ra0 + ra1;
           }
         }
       }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) sdx[(16 * Y + i) * 128] += dx[i];
     });
-#pragma unroll
-    for (int e = 0; e < HD; ++e) dx[e] += sdx[e * 128];
 
-    if (ok) {
+    if (ok && row_valid) {
       float dot = 0.f;
+      float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
 #pragma unroll
-      for (int e = 0; e < HD; ++e) dot = fmaf(x[e], dx[e], dot);
-      if (row_valid) {
-        float4* dst = reinterpret_cast<float4*>(p.dX + ((tok0 + row) * p.hx + head) * HD);
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v4 = *reinterpret_cast<const uint4*>(xrow + swz128(r, j));
+        const uint32_t w[4] = {v4.x, v4.y, v4.z, v4.w};
+        float d8[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          dst[j] = make_float4(dx[4 * j] * f, dx[4 * j + 1] * f, dx[4 * j + 2] * f, dx[4 * j + 3] * f);
-        p.gdot[(tok0 + row) * p.hx + head] = 0.5f * dot;
+        for (int k = 0; k < 4; ++k) {
+          const float2 f2 = Pack2<T>::to_f32(w[k]);
+          d8[2 * k] = sdx[(8 * j + 2 * k) * 128];
+          d8[2 * k + 1] = sdx[(8 * j + 2 * k + 1) * 128];
+          dot = fmaf(f2.x, d8[2 * k], dot);
+          dot = fmaf(f2.y, d8[2 * k + 1], dot);
+        }
+        dst[2 * j] = make_float4(d8[0] * f, d8[1] * f, d8[2] * f, d8[3] * f);
+        dst[2 * j + 1] = make_float4(d8[4] * f, d8[5] * f, d8[6] * f, d8[7] * f);
       }
+      p.gdot[(tok0 + row) * p.hx + head] = 0.5f * dot;
     }
   }
   tc_fence_before();
