@@ -20,7 +20,7 @@ namespace pr {
 
 namespace dkv {
 constexpr int HD = 64;
-constexpr int NS = 4;                    // stages of the expanded-operand ring in tensor memory
+constexpr int NS = 2;                    // expanded-operand ring in tensor memory: 2 stages of 128 entries (64 columns)
 constexpr int NR = 4;                    // shared-memory ring: stages of 16 KB (a query and a dO tile, or two state blocks)
 constexpr int THREADS = 192;
 constexpr int TILE_BYTES = 128 * 128;   // 128 key rows x 64 features
@@ -213,19 +213,21 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         if (st == n_steps - 1) umma_commit(&attn_done);
       }
       if (ok && has_state) {
-        for (int it = 0; it < NBLK && ok; ++it) {
-          const int s = it % NS, ph = (it / NS) & 1;
-          const int g = n_steps + (it >> 1), rs = g % NR;
+        // 128 expanded entries against two state blocks (one ring stage) per item: eight products
+        // per pair of waits and commits keep this thread off the critical path
+        for (int k = 0; k < NBLK / 2 && ok; ++k) {
+          const int s = k % NS, ph = (k / NS) & 1;
+          const int g = n_steps + k, rs = g % NR;
           ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&r_full[rs], (g / NR) & 1, &abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t z_addr = smem_u32(smR + rs * R_BYTES + (it & 1) * Z_BYTES);
+          const uint32_t z_addr = smem_u32(smR + rs * R_BYTES);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ts(tmem + COL_DV, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(z_addr + ks * 2048, 8192, 1024),
-                    idesc_o, 1u);
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts(tmem + COL_DV, tmem + COL_A + s * 64 + ks * 8,
+                    umma_desc_sw128(z_addr + (ks >> 2) * Z_BYTES + (ks & 3) * 2048, 8192, 1024), idesc_o, 1u);
           umma_commit(&a_empty[s]);
-          if (it & 1) umma_commit(&r_empty[rs]);
+          umma_commit(&r_empty[rs]);
         }
       }
       if (ok) umma_commit(&acc_done);
@@ -256,7 +258,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
     };
     if (n_steps > 0) load_cols(0);
     for (int st = 0; st < n_steps; ++st) {
-      const int I = qt0 + st / ratio, qh = kvhead * ratio + st % ratio;
+      const int I = qt0 + st / ratio;
       const int qp0 = I * TW;
       const int sb = st & 1;
       if (tid < TW) {
@@ -351,18 +353,20 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<uint4*>(smK + swz128(tid, j)) = make_uint4(k2[4 * j], k2[4 * j + 1], k2[4 * j + 2], k2[4 * j + 3]);
       }
-      int it = 0;
+      int k = 0;
       static_for<0, HD / 16>([&](auto yc) {
         constexpr int Y = decltype(yc)::value;
 #pragma unroll 1
-        for (int a0 = 0; a0 < 16 * (Y + 1); a0 += 4, ++it) {
-          uint32_t r[32];
-          expand_stage<T, Y>(smK, tid, a0, k2, r);
-          const int s = it % NS, ph = (it / NS) & 1;
+        for (int a0 = 0; a0 < 16 * (Y + 1); a0 += 8, ++k) {
+          uint32_t r0[32], r1[32];
+          expand_stage<T, Y>(smK, tid, a0, k2, r0);
+          expand_stage<T, Y>(smK, tid, a0 + 4, k2, r1);
+          const int s = k % NS, ph = (k / NS) & 1;
           if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
           if (ok) {
             tc_fence_after();
-            tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+            tmem_st32(tmem + lane_addr + COL_A + s * 64, r0);
+            tmem_st32(tmem + lane_addr + COL_A + s * 64 + 32, r1);
             tmem_wait_st();
             tc_fence_before();
           }

@@ -27,7 +27,7 @@ namespace pr {
 
 namespace co {
 constexpr int HD = 64;
-constexpr int NS = 4;                 // stages of the expanded-operand ring in tensor memory
+constexpr int NS = 2;                 // expanded-operand ring in tensor memory: 2 stages of 128 entries (64 columns)
 constexpr int NR = 4;                 // shared-memory ring: stages of 16 KB (a key and a value tile, or two state blocks)
 constexpr int THREADS = 192;
 constexpr int TILE_BYTES = 128 * 128;  // 128 rows x 64 16-bit features
@@ -234,19 +234,22 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
                       (half > 0 || ks > 0) ? 1u : 0u);
           umma_commit(&a_empty[0]);
         }
-        for (int it = 1; it <= NBLK && ok; ++it) {
-          const int s = it % NS, ph = (it / NS) & 1;
-          const int blk = it - 1, g = nJ + (blk >> 1), rs = g % NR;
+        // ring items 1 .. NBLK/2: 128 expanded entries against two state blocks (one ring stage);
+        // eight products per pair of waits and commits keep this thread off the critical path
+        for (int k = 1; k <= NBLK / 2 && ok; ++k) {
+          const int s = k % NS, ph = (k / NS) & 1;
+          const int g = nJ + k - 1, rs = g % NR;
           ok = mbar_wait(&a_full[s], ph, &abort_flag) && mbar_wait(&r_full[rs], (g / NR) & 1, &abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t z_addr = smem_u32(smR + rs * R_BYTES + (blk & 1) * Z_BYTES);
+          const uint32_t z_addr = smem_u32(smR + rs * R_BYTES);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ts(tmem + COL_ACC, tmem + COL_A + s * 32 + ks * 8, umma_desc_sw128(z_addr + ks * 2048, 8192, 1024),
-                    idesc_v, (nJ > 0 || it > 1 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts(tmem + COL_ACC, tmem + COL_A + s * 64 + ks * 8,
+                    umma_desc_sw128(z_addr + (ks >> 2) * Z_BYTES + (ks & 3) * 2048, 8192, 1024), idesc_v,
+                    (nJ > 0 || k > 1 || ks > 0) ? 1u : 0u);
           umma_commit(&a_empty[s]);
-          if (blk & 1) umma_commit(&r_empty[rs]);
+          umma_commit(&r_empty[rs]);
         }
       }
       if (ok) umma_commit(&acc_done);
@@ -360,26 +363,28 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_full[0]);
       }
-      // items 1..NBLK: 64 expanded entries (32 packed products) each.  The gated row goes back
-      // to its own slot of the query tile so that the first factor can be fetched by a runtime
-      // index; the loop over first factors then has a body of 32 multiplies per stage.
+      // ring items 1..NBLK/2: 128 expanded entries (64 packed products) each.  The gated row goes
+      // back to its own slot of the query tile so that the first factor can be fetched by a runtime
+      // index; the loop over first factors then has a body of 64 multiplies per stage.
       if (ok) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<uint4*>(smQ + swz128(tid, j)) = make_uint4(q2[4 * j], q2[4 * j + 1], q2[4 * j + 2], q2[4 * j + 3]);
       }
-      int it = 1;
+      int k = 1;
       static_for<0, HD / 16>([&](auto yc) {
         constexpr int Y = decltype(yc)::value;
 #pragma unroll 1
-        for (int a0 = 0; a0 < 16 * (Y + 1); a0 += 4, ++it) {
-          uint32_t r[32];
-          expand_stage<T, Y>(smQ, tid, a0, q2, r);
-          const int s = it % NS, ph = (it / NS) & 1;
+        for (int a0 = 0; a0 < 16 * (Y + 1); a0 += 8, ++k) {
+          uint32_t r0[32], r1[32];
+          expand_stage<T, Y>(smQ, tid, a0, q2, r0);
+          expand_stage<T, Y>(smQ, tid, a0 + 4, q2, r1);
+          const int s = k % NS, ph = (k / NS) & 1;
           if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
           if (ok) {
             tc_fence_after();
-            tmem_st32(tmem + lane_addr + COL_A + s * 32, r);
+            tmem_st32(tmem + lane_addr + COL_A + s * 64, r0);
+            tmem_st32(tmem + lane_addr + COL_A + s * 64 + 32, r1);
             tmem_wait_st();
             tc_fence_before();
           }
