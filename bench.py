@@ -59,6 +59,11 @@ def make_inputs(b, t, h, d, device, seed0=0, heads=None):
     return (Q.bfloat16(), K.bfloat16(), V.bfloat16(), F.logsigmoid(G).float(), dO.bfloat16())
 
 
+# DRAM bytes (read + write) per launch of each tensor-core kernel, from the ncu capture of the t = 8192, h = 8 case
+# summarised in profiles/train_kernels_ncu_full_b1_t8192_h8_d64.md; traffic grows in proportion to tokens x heads
+NCU_DRAM_BYTES_T8192_H8 = {"pr_expand_grad": 34.6e6, "pr_chunk_dkv": 73.1e6, "pr_chunk_out": 50.5e6,
+                           "pr_chunk_state": 21.0e6, "pr_chunk_dq": 51.9e6}
+
 # the reference's only published figure for this exact metric and shape: 16.8 ms per fwd+bwd step on one H100
 PUBLISHED_TOKENS_PER_S = 65536 / 16.8e-3
 
@@ -164,7 +169,7 @@ def run_decode(args):
     from retention_integration_b200 import _lib, ops
 
     dev = torch.device("cuda", 0)
-    b, h, d, t0, steps = 16, 32, 64, 2048, 512
+    b, h, d, t0, steps = 16, 32, 64, 2048, args.decode_steps
     g = torch.Generator().manual_seed(0)
     mk = lambda *s: torch.randn(*s, generator=g).bfloat16().to(dev)
     Kp, Vp, qp = mk(b, t0, h, d), mk(b, t0, h, d), mk(b, 1, h, d)
@@ -220,11 +225,12 @@ def run_decode(args):
     print(json.dumps({
         "metric": "decode_tokens_per_sec", "value": b * steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
         "steps": steps, "ms_per_step": ms / steps, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "power_retention_inference decode b16 h32 d64 gated, state [16,32,2080,64], cache 1..512"},
+        "config": {"workload": f"power_retention_inference decode b16 h32 d64 gated, state [16,32,2080,64], cache 1..{steps}"},
         "prefill_to_state_ms": prefill_ms, "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": "pr_decode_state", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
-                     "traffic": None},
+                     "traffic": 140.67e6,  # ncu dram__bytes_read of one launch (profiles/decode_state_ncu_b16_h32_d64.md)
+                     "algorithmic_bytes": state_bytes},
         "kernels": {k: {"launches": n, "ms_total": t} for k, (n, t) in kern.items()},
         "device_status": _lib.device_status(0)}), flush=True)
 
@@ -238,6 +244,7 @@ def main():
     ap.add_argument("--t", type=int, default=CFG["t"], help="sequence length override (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="train", choices=["train", "decode"])
+    ap.add_argument("--decode-steps", type=int, default=512, help="single-token steps of the decode workload")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -385,7 +392,9 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-                         "frac": achieved / peak_tf, "peak_source": peak_src, "traffic": None,
+                         "frac": achieved / peak_tf, "peak_source": peak_src,
+                         "traffic": NCU_DRAM_BYTES_T8192_H8[top] * (t * hl) / (8192 * 8),
+                         "traffic_source": "ncu dram bytes read+write of the t=8192 h=8 capture, scaled by tokens x heads",
                          "whole_step_achieved": total_achieved, "whole_step_frac": total_achieved / peak_tf},
             "kernels": breakdown,
             "device_status": status,

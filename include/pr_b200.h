@@ -195,7 +195,9 @@ int pr_gate_grad(int b, int t, int h, int hq, int c, const float* da_q, const fl
  * pr_decode_state: one query token per sequence against the state (query_state of the
  * reference, retention/_query_state/reference.py:36-96, for tq = 1): Q [b,1,hq,d];
  * a_last [b,h] = cumulative log gate at the last cached key, or NULL.  Writes partial sums
- * part_y [b,hq,pr_decode_nsplit(),d] and part_l [b,hq,pr_decode_nsplit()].
+ * part_y and part_l: workspaces of b*hq*pr_decode_nsplit()*d and b*hq*pr_decode_nsplit() floats.  How many
+ * splits a call uses depends on b, h and hq only (one when there are enough (batch, head) pairs to fill the GPU);
+ * the contents are a hand-over to pr_decode_finish with the same sizes, not an interface.
  * pr_decode_finish: attention over the tk cached tokens (K,V [b,tk,h,d], a [b,tk,h]; may be
  * absent) + the partials (may be absent) -> O [b,1,hq,d].
  * pr_state_merge: the switch-over of :366-382: new_state = state*exp(a_last) + S, with

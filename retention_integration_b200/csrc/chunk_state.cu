@@ -194,6 +194,11 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
           r[4 * j + 2] = Pack2<T>::mul(va.z, vb.z);
           r[4 * j + 3] = Pack2<T>::mul(va.w, vb.w);
         }
+        // The stage is about to be handed back to TMA, which writes through the async proxy: order
+        // this thread's generic-proxy reads before that.  Without the fence a reload of the stage
+        // could overtake reads still in flight, and single rows of the state came out built from
+        // the wrong 64 tokens (only with two CTAs per SM and only at large grids).
+        fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&x_empty[s]);
         const int sa = it % NSA, pha = (it / NSA) & 1;

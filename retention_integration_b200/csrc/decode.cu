@@ -82,7 +82,10 @@ decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const 
   const T* sbase = state + (size_t)bh * DEX * HD;
   const float* kbase = sok + (size_t)bh * DEX;
   // four rows per thread in flight: the loads are issued before any of them is used
-  constexpr int UN = 4;
+#ifndef PR_DEC_UN
+#define PR_DEC_UN 4
+#endif
+  constexpr int UN = PR_DEC_UN;
   for (; D < d_end; D += UN * ROWS_PER_ITER) {
     uint4 v[UN];
     float sk[UN];
@@ -291,7 +294,24 @@ __global__ void state_merge_kernel(const T* __restrict__ state, const float* __r
 
 }  // namespace pr
 
-extern "C" int pr_decode_nsplit(void) { return 5; }
+#ifndef PR_DEC_NSPLIT
+#define PR_DEC_NSPLIT 5
+#endif
+extern "C" int pr_decode_nsplit(void) { return PR_DEC_NSPLIT; }
+
+namespace pr {
+// Splits of the expanded dimension actually used for a problem (<= pr_decode_nsplit(), which sizes
+// the partial-sum workspace).  A CTA that walks all 2080 rows of its (batch, head) state amortises
+// its prologue and reduction best - 71 % of the measured copy bandwidth at 512 CTAs against 57 %
+// with five splits - so the read is only split when there are too few (batch, head) pairs to fill
+// the GPU.  Both kernels of a step derive the count from the same sizes.
+static int decode_split(int b, int h, int hq) {
+  const int ratio = hq / h;
+  const int rg = ratio == 1 ? 1 : dec::RG_MAX;
+  const long long ctas = (long long)b * h * ((ratio + rg - 1) / rg);
+  return ctas >= 384 ? 1 : (ctas >= 160 ? 2 : PR_DEC_NSPLIT);
+}
+}  // namespace pr
 
 extern "C" int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
                                const float* sum_of_keys, const float* a_last, float scale, float* part_y,
@@ -309,7 +329,7 @@ extern "C" int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, c
   PR_REQUIRE(Q && state && sum_of_keys && part_y && part_l && aligned16(state) && aligned16(Q), PR_ERR_BAD_ARG,
              "null or misaligned pointer");
   PR_CUDA(cudaSetDevice(device));
-  const int nsplit = pr_decode_nsplit();
+  const int nsplit = decode_split(b, h, hq);
   const int ratio = hq / h;
   const int rg = ratio == 1 ? 1 : dec::RG_MAX;
   dim3 grid(b * h, nsplit, (ratio + rg - 1) / rg);
@@ -340,7 +360,7 @@ extern "C" int pr_decode_finish(int dtype, int b, int tk, int h, int hq, int d, 
   PR_REQUIRE((part_y == nullptr) == (part_l == nullptr), PR_ERR_BAD_ARG, "partials must come together");
   PR_REQUIRE(part_y != nullptr || (K != nullptr && tk > 0), PR_ERR_BAD_ARG, "neither a state nor cached tokens");
   PR_CUDA(cudaSetDevice(device));
-  const int nsplit = pr_decode_nsplit();
+  const int nsplit = decode_split(b, h, hq);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
     decode_finish_kernel<__nv_bfloat16><<<b * hq, 128, 0, s>>>(
@@ -439,7 +459,7 @@ namespace pr {
 namespace {
 constexpr int kStaticMaxRows = 1024;                                       // batch * query heads
 constexpr int kStaticMaxGates = 1 << 18;                                   // batch * cached tokens * kv heads
-constexpr int kStaticSplit = 5;                                            // == pr_decode_nsplit()
+constexpr int kStaticSplit = PR_DEC_NSPLIT;                                            // == pr_decode_nsplit()
 constexpr size_t kStaticPartY = (size_t)kStaticMaxRows * kStaticSplit * dec::HD;  // floats
 constexpr size_t kStaticPartL = (size_t)kStaticMaxRows * kStaticSplit;
 constexpr size_t kStaticFloats = kStaticPartY + kStaticPartL + kStaticMaxGates;

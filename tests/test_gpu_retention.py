@@ -174,6 +174,30 @@ def test_full_benchmark_size_properties(cuda_device):
     assert rel_l2(O1[:, pre, :2].float().cpu(), O_ref) < TOL
 
 
+def test_full_benchmark_size_is_bitwise_reproducible(cuda_device):
+    """Five forward+backward runs at b1 t65536 h8 d64 give bit-identical results for chunk 1024 and 512.  Races
+    between CTAs sharing an SM only show at grids of thousands of CTAs, far beyond the oracle-sized cases."""
+    import retention_integration_b200 as prb
+
+    g = torch.Generator().manual_seed(1)
+    b, t, h, d = 1, 65536, 8, 64
+    Q, K, V, dO = (torch.randn(b, t, h, d, generator=g).bfloat16().to(cuda_device) for _ in range(4))
+    lg = F.logsigmoid(torch.randn(b, t, h, generator=g)).to(cuda_device)
+
+    def run(c):
+        leaves = [x.detach().requires_grad_(True) for x in (Q, K, V, lg)]
+        O = prb.power_retention(*leaves, chunk_size=c)
+        O.backward(dO)
+        torch.cuda.synchronize()
+        return [O.detach()] + [x.grad for x in leaves]
+
+    for c in (1024, 512):
+        ref = run(c)
+        for _ in range(4):
+            for name, x, r in zip(("O", "dQ", "dK", "dV", "dlog_G"), run(c), ref):
+                assert torch.equal(x, r), (c, name)
+
+
 def test_rejects_what_the_reference_leaves_unfinished(cuda_device):
     import retention_integration_b200 as prb
 
