@@ -24,7 +24,9 @@
  *
  * Shapes use b batch, t tokens, h kv heads, hq query heads (multiple of h), d head
  * dim, c chunk length, n = t / c chunks, cp = c rounded up to 64, and
- * D2 = d*(d+2)/2 rows of the internal expansion layout (see layout.cuh).
+ * D2 = 128*(d/16)*(d/16+1) rows (2560 at d = 64) of the expansion layout the kernels and chunk states
+ * use: the reference's own block layout, retention/_update_state/reference.py:5-29 (see layout.cuh).
+ * Inference states cross this ABI in the exact layout, d*(d+1)/2 = 2080 rows.
  */
 #ifndef PR_B200_H_
 #define PR_B200_H_
