@@ -105,8 +105,9 @@ def test_sequence_parallel_over_nccl():
         assert max(ret[r]) < 5e-3, (r, ret[r])
 
 
-def test_host_pipeline_matches_direct_call(cuda_device):
-    """Pinned host tensors in, pinned host results out, head slices pipelined over three streams."""
+@pytest.mark.parametrize("slices", [None, [1, 1, 2], [2, 1, 1]])
+def test_host_pipeline_matches_direct_call(cuda_device, slices):
+    """Pinned host tensors in, pinned host results out, head slices (equal or uneven) pipelined over three streams."""
     import retention_integration_b200 as prb
     from retention_integration_b200.host import HostPipeline
 
@@ -116,7 +117,7 @@ def test_host_pipeline_matches_direct_call(cuda_device):
     Gh = F.logsigmoid(torch.randn(b, t, h, generator=g) + 2.0).pin_memory()
     out = {k: torch.empty(b, t, h, d, dtype=torch.bfloat16).pin_memory() for k in ("O", "dQ", "dK", "dV")}
     out["dlog_G"] = torch.empty(b, t, h).pin_memory()
-    pipe = HostPipeline(b, t, h, d, torch.bfloat16, cuda_device, c, n_slices=4)
+    pipe = HostPipeline(b, t, h, d, torch.bfloat16, cuda_device, c, n_slices=4, slices=slices)
     for _ in range(2):  # the second round reuses every buffer
         pipe.fwd_bwd(Qh, Kh, Vh, Gh, dOh, out)
         torch.cuda.synchronize()
