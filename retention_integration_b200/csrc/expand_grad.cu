@@ -261,19 +261,17 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     int nt = 0;
     static_for<0, HD / 16>([&](auto yc) {
       constexpr int Y = decltype(yc)::value;
-      // second factors x~[16Y .. 16Y+15] of this block and their gradient accumulators
-      float x[16], dx[16];
+      // second factors x~[16Y .. 16Y+15] of this block and their gradient accumulators, as pairs:
+      // the drain runs on packed fp32 FMAs (two entries per instruction)
+      float2 x[8], dx[8];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const uint4 v4 = *reinterpret_cast<const uint4*>(xrow + swz128(r, 2 * Y + j));
         const uint32_t w[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float2 f2 = Pack2<T>::to_f32(w[k]);
-          x[8 * j + 2 * k] = f2.x;
-          x[8 * j + 2 * k + 1] = f2.y;
-          dx[8 * j + 2 * k] = 0.f;
-          dx[8 * j + 2 * k + 1] = 0.f;
+          x[4 * j + k] = Pack2<T>::to_f32(w[k]);
+          dx[4 * j + k] = make_float2(0.f, 0.f);
         }
       }
 #pragma unroll 1
@@ -302,23 +300,28 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
               *reinterpret_cast<const uint32_t*>(xrow + swz128(r, a >> 3) + ((a & 7) << 1)));
 #pragma unroll
           for (int aa = 0; aa < 2; ++aa) {
-            const float xa = aa ? xa2.y : xa2.x;
-            float ra0 = 0.f, ra1 = 0.f;
+            const float xs = aa ? xa2.y : xa2.x;
+            const float2 xa = make_float2(xs, xs);
+            float2 ra0 = make_float2(0.f, 0.f), ra1 = ra0;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float val = __uint_as_float(v[q & 1][16 * aa + i]);
-              dx[i] = fmaf(val, xa, dx[i]);
+            for (int i = 0; i < 8; ++i) {
+              const float2 val = make_float2(__uint_as_float(v[q & 1][16 * aa + 2 * i]),
+                                             __uint_as_float(v[q & 1][16 * aa + 2 * i + 1]));
+              dx[i] = __ffma2_rn(val, xa, dx[i]);
               if (i & 1)
-                ra1 = fmaf(val, x[i], ra1);
+                ra1 = __ffma2_rn(val, x[i], ra1);
               else
-                ra0 = fmaf(val, x[i], ra0);
+                ra0 = __ffma2_rn(val, x[i], ra0);
             }
-            sdx[(a + aa) * 128] += ra0 + ra1;
+            sdx[(a + aa) * 128] += (ra0.x + ra0.y) + (ra1.x + ra1.y);
           }
         }
       }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) sdx[(16 * Y + i) * 128] += dx[i];
+      for (int i = 0; i < 8; ++i) {
+        sdx[(16 * Y + 2 * i) * 128] += dx[i].x;
+        sdx[(16 * Y + 2 * i + 1) * 128] += dx[i].y;
+      }
     });
 
     if (ok && row_valid) {
