@@ -58,33 +58,47 @@ __device__ __forceinline__ void dkv_half(const uint32_t (&sv)[32], const uint32_
                                          const float* __restrict__ il, const float* __restrict__ hl,
                                          const float* __restrict__ dl, float c_j, float a_j, int lo, int hi,
                                          uint32_t (&pk)[16], uint32_t (&dk)[16], float& da2) {
+  // two columns per instruction: packed fp32 multiplies and FMAs
   const float4* f4 = reinterpret_cast<const float4*>(fq);
   const float4* i4 = reinterpret_cast<const float4*>(il);
   const float4* h4 = reinterpret_cast<const float4*>(hl);
   const float4* d4 = reinterpret_cast<const float4*>(dl);
+  const float2 c2 = make_float2(c_j, c_j);
+  float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
     const float4 f = f4[j >> 2], iq = i4[j >> 2], hq = h4[j >> 2], dq = d4[j >> 2];
-    const float fv[4] = {f.x, f.y, f.z, f.w}, iv[4] = {iq.x, iq.y, iq.z, iq.w};
-    const float hv[4] = {hq.x, hq.y, hq.z, hq.w}, dv[4] = {dq.x, dq.y, dq.z, dq.w};
-    float pw[4], dsv[4];
+    const float2 fv[2] = {make_float2(f.x, f.y), make_float2(f.z, f.w)};
+    const float2 iv[2] = {make_float2(iq.x, iq.y), make_float2(iq.z, iq.w)};
+    const float2 hv[2] = {make_float2(hq.x, hq.y), make_float2(hq.z, hq.w)};
+    const float2 dv[2] = {make_float2(dq.x, dq.y), make_float2(dq.z, dq.w)};
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float s = __uint_as_float(sv[j + u]);
-      float g = SEP ? c_j * fv[u] : c_j * __expf(fv[u] - a_j);
-      if (MASK) g = (j + u >= lo) ? g : 0.f;
-      if (!SEP) g = (j + u <= hi) ? g : 0.f;
-      const float sg2 = s * g;  // 2 s^2 S e^{a_i-a_j}
-      const float dp = fmaf(__uint_as_float(pv[j + u]), iv[u], dv[u]);
-      dsv[u] = sg2 * dp;
-      da2 = fmaf(dsv[u], s, da2);
-      pw[u] = (sg2 * s) * hv[u];
+    for (int u = 0; u < 2; ++u) {
+      const int col = j + 2 * u;
+      const float2 s = make_float2(__uint_as_float(sv[col]), __uint_as_float(sv[col + 1]));
+      const float2 p = make_float2(__uint_as_float(pv[col]), __uint_as_float(pv[col + 1]));
+      float2 g;
+      if (SEP) {
+        g = __fmul2_rn(c2, fv[u]);
+      } else {
+        g = make_float2(c_j * __expf(fv[u].x - a_j), c_j * __expf(fv[u].y - a_j));
+        g.x = (col <= hi) ? g.x : 0.f;
+        g.y = (col + 1 <= hi) ? g.y : 0.f;
+      }
+      if (MASK) {
+        g.x = (col >= lo) ? g.x : 0.f;
+        g.y = (col + 1 >= lo) ? g.y : 0.f;
+      }
+      const float2 sg2 = __fmul2_rn(s, g);  // 2 s^2 S e^{a_i-a_j}
+      const float2 dp = __ffma2_rn(p, iv[u], dv[u]);
+      const float2 ds = __fmul2_rn(sg2, dp);
+      acc = __ffma2_rn(ds, s, acc);
+      const float2 pw = __fmul2_rn(__fmul2_rn(sg2, s), hv[u]);
+      pk[col >> 1] = Pack2<T>::from_f32(pw.x, pw.y);
+      dk[col >> 1] = Pack2<T>::from_f32(ds.x, ds.y);
     }
-    pk[j >> 1] = Pack2<T>::from_f32(pw[0], pw[1]);
-    pk[(j >> 1) + 1] = Pack2<T>::from_f32(pw[2], pw[3]);
-    dk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
-    dk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
   }
+  da2 += acc.x + acc.y;
 }
 
 template <typename T>

@@ -48,24 +48,36 @@ template <typename T, bool SEP, bool MASK>
 __device__ __forceinline__ void dq_half(const uint32_t (&sv)[32], const uint32_t (&pv)[32], const float* __restrict__ fk,
                                         float c_i, float a_i, float inv_l, float dl_i, int lim, uint32_t (&pk)[16],
                                         float& da2) {
+  // two columns per instruction: packed fp32 multiplies and FMAs
   const float4* f4 = reinterpret_cast<const float4*>(fk);
+  const float2 c2 = make_float2(c_i, c_i), il2 = make_float2(inv_l, inv_l), dl2 = make_float2(dl_i, dl_i);
+  float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
     const float4 f = f4[j >> 2];
-    const float fv[4] = {f.x, f.y, f.z, f.w};
-    float dsv[4];
+    const float2 fv[2] = {make_float2(f.x, f.y), make_float2(f.z, f.w)};
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float s = __uint_as_float(sv[j + u]);
-      const float dp = fmaf(__uint_as_float(pv[j + u]), inv_l, dl_i);
-      float g = SEP ? c_i * fv[u] : c_i * __expf(a_i - fv[u]);
-      if (MASK) g = (j + u <= lim) ? g : 0.f;
-      dsv[u] = (s * g) * dp;
-      da2 = fmaf(dsv[u], s, da2);
+    for (int u = 0; u < 2; ++u) {
+      const int col = j + 2 * u;
+      const float2 s = make_float2(__uint_as_float(sv[col]), __uint_as_float(sv[col + 1]));
+      const float2 p = make_float2(__uint_as_float(pv[col]), __uint_as_float(pv[col + 1]));
+      const float2 dp = __ffma2_rn(p, il2, dl2);
+      float2 g;
+      if (SEP) {
+        g = __fmul2_rn(c2, fv[u]);
+      } else {
+        g = make_float2(c_i * __expf(a_i - fv[u].x), c_i * __expf(a_i - fv[u].y));
+      }
+      if (MASK) {
+        g.x = (col <= lim) ? g.x : 0.f;
+        g.y = (col + 1 <= lim) ? g.y : 0.f;
+      }
+      const float2 ds = __fmul2_rn(__fmul2_rn(s, g), dp);  // 2 s^2 S e^{a_i-a_j} dp
+      acc = __ffma2_rn(ds, s, acc);
+      pk[col >> 1] = Pack2<T>::from_f32(ds.x, ds.y);
     }
-    pk[j >> 1] = Pack2<T>::from_f32(dsv[0], dsv[1]);
-    pk[(j >> 1) + 1] = Pack2<T>::from_f32(dsv[2], dsv[3]);
   }
+  da2 += acc.x + acc.y;
 }
 
 template <typename T>

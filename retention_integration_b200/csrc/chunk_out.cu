@@ -67,23 +67,34 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 template <typename T, bool SEP, bool MASK>
 __device__ __forceinline__ void out_half(const uint32_t (&sv)[32], const float* __restrict__ fk, float c_i, float a_i,
                                          int lim, uint32_t (&pk)[16], float& l_acc) {
+  // two columns per instruction: packed fp32 multiplies and adds
   const float4* f4 = reinterpret_cast<const float4*>(fk);
+  const float2 c2 = make_float2(c_i, c_i);
+  float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
     const float4 f = f4[j >> 2];
-    const float fv[4] = {f.x, f.y, f.z, f.w};
-    float pv[4];
+    const float2 fv[2] = {make_float2(f.x, f.y), make_float2(f.z, f.w)};
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float s = __uint_as_float(sv[j + u]);
-      float g = SEP ? c_i * fv[u] : c_i * __expf(a_i - fv[u]);
-      if (MASK) g = (j + u <= lim) ? g : 0.f;
-      pv[u] = (s * s) * g;
+    for (int u = 0; u < 2; ++u) {
+      const int col = j + 2 * u;
+      const float2 s = make_float2(__uint_as_float(sv[col]), __uint_as_float(sv[col + 1]));
+      float2 g;
+      if (SEP) {
+        g = __fmul2_rn(c2, fv[u]);
+      } else {
+        g = make_float2(c_i * __expf(a_i - fv[u].x), c_i * __expf(a_i - fv[u].y));
+      }
+      if (MASK) {
+        g.x = (col <= lim) ? g.x : 0.f;
+        g.y = (col + 1 <= lim) ? g.y : 0.f;
+      }
+      const float2 pv = __fmul2_rn(__fmul2_rn(s, s), g);
+      acc = __fadd2_rn(acc, pv);
+      pk[col >> 1] = Pack2<T>::from_f32(pv.x, pv.y);
     }
-    pk[j >> 1] = Pack2<T>::from_f32(pv[0], pv[1]);
-    pk[(j >> 1) + 1] = Pack2<T>::from_f32(pv[2], pv[3]);
-    l_acc += (pv[0] + pv[1]) + (pv[2] + pv[3]);
   }
+  l_acc += acc.x + acc.y;
 }
 
 template <typename T>
