@@ -408,26 +408,26 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
     if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
     tc_fence_after();
     if (ok) {
-      uint32_t acc[64];
-      tmem_ld32(tmem + lane_addr + COL_ACC, acc);
-      tmem_ld32(tmem + lane_addr + COL_ACC + 32, acc + 32);
       float l = l_acc;
       if (has_state) {
+        // the state part of the row sum first, so that u and the accumulators are not live together
         uint32_t u[64];
         tmem_ld32(tmem + lane_addr + COL_U, u);
         tmem_ld32(tmem + lane_addr + COL_U + 32, u + 32);
         tmem_wait_ld();
-        float ls = 0.f;
+        float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const float2 qv = Pack2<T>::to_f32(q2[j]);
-          ls = fmaf(__uint_as_float(u[2 * j]), qv.x, ls);
-          ls = fmaf(__uint_as_float(u[2 * j + 1]), qv.y, ls);
+          ls0 = fmaf(__uint_as_float(u[2 * j]), qv.x, ls0);
+          ls1 = fmaf(__uint_as_float(u[2 * j + 1]), qv.y, ls1);
         }
-        l += ls;
-      } else {
-        tmem_wait_ld();
+        l += ls0 + ls1;
       }
+      uint32_t acc[64];
+      tmem_ld32(tmem + lane_addr + COL_ACC, acc);
+      tmem_ld32(tmem + lane_addr + COL_ACC + 32, acc + 32);
+      tmem_wait_ld();
       if (row_valid) {
         const size_t tok = (size_t)batch * p.n_chunks * p.cq + (size_t)chunk * p.cq + row;
         const float inv = p.normalize ? safe_recip(l) : 1.f;
