@@ -178,6 +178,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     int a = 0, b = 0;
     if (valid) ref_decode(drow, &a, &b);
     bool ok = true;
+    const uint32_t a_base = a * 128 + ((a & 7) << 4), b_base = b * 128 + ((b & 7) << 4);
     if (!gram_cta) {
       for (int it = 0; it < total; ++it) {
         const int s = it % NS, ph = (it / NS) & 1;
@@ -187,8 +188,9 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         uint32_t r[32];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint4 va = *reinterpret_cast<const uint4*>(xs + swz128(a, j));
-          const uint4 vb = *reinterpret_cast<const uint4*>(xs + swz128(b, j));
+          // swz128(row, j) = (row * 128 + ((row & 7) << 4)) ^ (j << 4): one XOR per address
+          const uint4 va = *reinterpret_cast<const uint4*>(xs + (a_base ^ (j << 4)));
+          const uint4 vb = *reinterpret_cast<const uint4*>(xs + (b_base ^ (j << 4)));
           r[4 * j + 0] = Pack2<T>::mul(va.x, vb.x);
           r[4 * j + 1] = Pack2<T>::mul(va.y, vb.y);
           r[4 * j + 2] = Pack2<T>::mul(va.z, vb.z);
