@@ -138,9 +138,11 @@ def inference_cases(ref):
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference>")
+    ref = load_reference(sys.argv[1])
     torch.set_num_threads(os.cpu_count() or 1)
-    # BASELINE config 1 (b1 t1024 h4 d64 fp32 c128 gated); outputs kept for every 8th token
+    # the reference's CPU-runnable case (b1 t1024 h4 d64 fp32 c128 gated); outputs kept for every 8th token
     training_case(ref, "train_cfg1_fp32", 1, 1, 1024, 4, 64, 1, torch.float32, True, 128, stride=8)
     training_case(ref, "train_gated_fp32", 2, 1, 256, 2, 64, 1, torch.float32, True, 64)
     training_case(ref, "train_ungated_gqa_pad_fp32", 3, 2, 200, 2, 32, 2, torch.float32, False, 64)
