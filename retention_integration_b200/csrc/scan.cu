@@ -222,22 +222,46 @@ scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg
   float run = (active && carry_in) ? carry_in[cbase + e] : 0.f;
   float run_t = (active && carry_in) ? carry_in[cbase + et] : 0.f;
   float* part = dA_part + (((size_t)batch * h + head) * gridDim.x * 8 + blockIdx.x * 8 + warp) * n;
-  for (int m = n - 1; m >= 0; --m) {
-    const size_t base = (((size_t)batch * n + m) * h + head) * E;
-    const float g = __expf(A[((size_t)batch * n + m) * h + head]);
-    float dot = 0.f;
-    if (active) {
-      const float sym = run + run_t;
-      const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(sym)) : T(__float2half_rn(sym));
-      hi[base + e] = hv;
-      lo[base + e] = T(sym - float(hv));
-      dot = Zg[base + e] * run * g;
-      run = fmaf(run, g, dZg[base + e]);
-      run_t = fmaf(run_t, g, dZg[base + et]);
+  // The loads of a chunk do not depend on the running gradient: four chunks' worth are issued
+  // before the dependent chain of FMAs walks through them.
+  constexpr int UN = 4;
+  for (int m0 = n - 1; m0 >= 0; m0 -= UN) {
+    float dz[UN], dzt[UN], zg[UN], gg[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int m = m0 - u;
+      dz[u] = dzt[u] = zg[u] = 0.f;
+      gg[u] = 1.f;
+      if (m >= 0) {
+        const size_t base = (((size_t)batch * n + m) * h + head) * E;
+        gg[u] = A[((size_t)batch * n + m) * h + head];
+        if (active) {
+          dz[u] = dZg[base + e];
+          dzt[u] = dZg[base + et];
+          zg[u] = Zg[base + e];
+        }
+      }
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    if (lane == 0) part[m] = dot;
+    for (int u = 0; u < UN; ++u) {
+      const int m = m0 - u;
+      if (m < 0) break;
+      const size_t base = (((size_t)batch * n + m) * h + head) * E;
+      const float g = __expf(gg[u]);
+      float dot = 0.f;
+      if (active) {
+        const float sym = run + run_t;
+        const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(sym)) : T(__float2half_rn(sym));
+        hi[base + e] = hv;
+        lo[base + e] = T(sym - float(hv));
+        dot = zg[u] * run * g;
+        run = fmaf(run, g, dz[u]);
+        run_t = fmaf(run_t, g, dzt[u]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      if (lane == 0) part[m] = dot;
+    }
   }
   if (active && carry_out) carry_out[cbase + e] = run;
 }
