@@ -196,18 +196,20 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
           r[4 * j + 2] = Pack2<T>::mul(va.z, vb.z);
           r[4 * j + 3] = Pack2<T>::mul(va.w, vb.w);
         }
-        // The stage is about to be handed back to TMA, which writes through the async proxy: order
-        // this thread's generic-proxy reads before that.  Without the fence a reload of the stage
-        // could overtake reads still in flight, and single rows of the state came out built from
-        // the wrong 64 tokens (only with two CTAs per SM and only at large grids).
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&x_empty[s]);
         const int sa = it % NSA, pha = (it / NSA) & 1;
         ok = mbar_wait(&a_empty[grp][sa], pha ^ 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
         tmem_st32(tmem + lane_addr + COL_A + (grp * NSA + sa) * 32, r);
+        // The shared-memory stage goes back to TMA only here: the store above has consumed every
+        // product, so every load of the stage has delivered its data.  Released right after the
+        // loads were issued (a plain arrive), a refill could overtake loads still queued in this
+        // LDS-heavy kernel, and single rows of the state came out built from the wrong 64 tokens
+        // (seen only with two CTAs per SM at grids of thousands of CTAs).  The proxy fence orders
+        // this thread's generic-proxy reads before the async-proxy write that follows the release.
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&x_empty[s]);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
