@@ -29,7 +29,7 @@ namespace eg {
 constexpr int HD = 64;
 constexpr int D2 = ref_dim(HD);          // 2560 expanded rows (block layout, see layout.cuh)
 constexpr int NT = D2 / 128;             // 20 tiles of 128 rows = 8 first factors x 16
-constexpr int THREADS = 320;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9 MMA
+constexpr int THREADS = 352;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9 / 10 MMA of row tile 0 / 1
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int G_BYTES = 64 * 128;
 constexpr int NSS = 4;                   // state tiles in flight (TMA latency x L2 bandwidth needs ~100 KB per SM)
@@ -114,7 +114,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     }
     for (int s = 0; s < NSS; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 1);
+      mbar_init(&s_empty[s], 2);  // both issuing threads release a state tile
     }
     fence_mbar_init();
   }
@@ -145,48 +145,45 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         tma_load_2d(smS + s * TILE_BYTES, &tm_s, &s_full[s], 0, ch * D2 + nt * 128);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp >= 9) {
+    // One issuing thread per row tile: a thread pays some 60-80 clocks per tcgen05.mma it issues
+    // and as much again per commit or barrier wait, so two short instruction streams run side by
+    // side instead of one long one.
     if (lane == 0) {
+      const int rt = warp - 9;
       bool ok = mbar_wait(&w_full, 0, &abort_flag);
-      const uint32_t w_addr = smem_u32(smW);
+      const uint32_t w_addr = smem_u32(smW) + rt * TILE_BYTES;
+      const uint32_t idesc = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
       for (int nt = 0; nt < NT && ok; ++nt) {
         const int s = nt % NSS, ph = (nt / NSS) & 1;
-        ok = mbar_wait(&s_full[s], ph, &abort_flag);
-        if (!ok) break;
-        const uint32_t idesc = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
-        const uint32_t s_addr = smem_u32(smS + s * TILE_BYTES);
         const int b = nt & 1;
-        for (int rt = 0; rt < 2 && ok; ++rt) {
-          // buffer 0 has been drained nt/2 times before tile nt; buffer 1 once more (the Gram part)
-          ok = mbar_wait(&d_empty[rt][b], ((nt >> 1) & 1) ^ (b ^ 1), &abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tmem + col_d(rt, b), umma_desc_sw128(w_addr + rt * TILE_BYTES + ks * 32, 16, 1024),
-                    umma_desc_sw128(s_addr + ks * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
-          umma_commit(&d_full[rt][b]);
-        }
+        // buffer 0 has been drained nt/2 times before tile nt; buffer 1 once more (the Gram part)
+        ok = mbar_wait(&d_empty[rt][b], ((nt >> 1) & 1) ^ (b ^ 1), &abort_flag) &&
+             mbar_wait(&s_full[s], ph, &abort_flag);
         if (!ok) break;
+        tc_fence_after();
+        const uint32_t s_addr = smem_u32(smS + s * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + col_d(rt, b), umma_desc_sw128(w_addr + ks * 32, 16, 1024),
+                  umma_desc_sw128(s_addr + ks * 32, 16, 1024), idesc, ks > 0 ? 1u : 0u);
+        umma_commit(&d_full[rt][b]);
         umma_commit(&s_empty[s]);
         if (nt == 0) {
           // Gram part: u = x~ (Gs_hi + Gs_lo), once per row tile
-          ok = mbar_wait(&g_full, 0, &abort_flag);
+          ok = mbar_wait(&g_full, 0, &abort_flag) && mbar_wait(&xa_full[rt], 0, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
           const uint32_t idesc_g = umma_idesc(128, HD, Pack2<T>::is_bf16, false, false);
           const uint32_t g_addr = smem_u32(smG);
-          for (int rt = 0; rt < 2 && ok; ++rt) {
-            ok = mbar_wait(&xa_full[rt], 0, &abort_flag);
-            if (!ok) break;
-            tc_fence_after();
 #pragma unroll
-            for (int half = 0; half < 2; ++half)
+          for (int half = 0; half < 2; ++half)
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                umma_ts(tmem + col_d(rt, 1) + OFF_U, tmem + col_d(rt, 1) + OFF_XA + ks * 8,
-                        umma_desc_sw128(g_addr + half * G_BYTES + ks * 32, 16, 1024), idesc_g,
-                        (half > 0 || ks > 0) ? 1u : 0u);
-            umma_commit(&u_full[rt]);
-          }
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ts(tmem + col_d(rt, 1) + OFF_U, tmem + col_d(rt, 1) + OFF_XA + ks * 8,
+                      umma_desc_sw128(g_addr + half * G_BYTES + ks * 32, 16, 1024), idesc_g,
+                      (half > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&u_full[rt]);
         }
       }
     }
