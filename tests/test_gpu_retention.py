@@ -67,6 +67,9 @@ CASES = [
     (1, 600, 1, 8, False, 0.0, 128),   # GQA ratio 8 + padding
     (1, 2048, 1, 1, True, 0.0, 1024),  # the benchmark's chunk size
     (1, 300, 2, 1, True, 2.0, None),   # quadratic branch, ragged length
+    (1, 768, 2, 1, True, 1.0, 192),    # chunk not a multiple of the 128-row tile (second tile half empty)
+    (1, 480, 1, 2, True, 0.0, 96),     # chunk shorter than a tile, ragged 64-key steps, GQA
+    (1, 1280, 2, 1, False, 0.0, 320),  # two and a half tiles per chunk, ungated
 ]
 
 
