@@ -219,6 +219,15 @@ int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, const void* 
 int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
                    const float* log_g, const void* state, const float* sum_of_keys, float scale, float* a_scratch,
                    float* part_y, float* part_l, void* O, int device, void* stream);
+/* pr_decode_step for a query and a cache that are slices of longer preallocated tensors (a serving loop's KV and gate
+ * cache [b, max_len, h, d] read as [:, :tk]): consecutive batch entries of Q are q_bstride elements apart, of K and V
+ * kv_bstride elements (a multiple of 8), of log_g g_bstride floats; inside a batch entry the tensors are dense.  The
+ * reference takes such slices as they are (torch indexing); here they need no copy either.  No counterpart of its
+ * own in the reference: it is retention/power_retention_maker.py:287-390 for tq = 1 on strided inputs. */
+int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, int d, const void* Q, long long q_bstride,
+                           const void* K, const void* V, long long kv_bstride, const float* log_g, long long g_bstride,
+                           const void* state, const float* sum_of_keys, float scale, float* a_scratch, float* part_y,
+                           float* part_l, void* O, int device, void* stream);
 /* No counterpart in the reference.  pr_decode_step for hosts that cannot hand over scratch
  * memory (a frozen memory pool, a stream callback, an allocator owned by another component): the gate and
  * partial-sum scratch sits in a fixed device array of about 2.4 MB that the library carries on

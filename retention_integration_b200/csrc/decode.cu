@@ -42,8 +42,8 @@ __device__ __forceinline__ void exact_decode(int D, int* a, int* b) {
 template <typename T, int RG>
 __global__ void __launch_bounds__(dec::THREADS)
 decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const float* __restrict__ sok,
-                    const float* __restrict__ a_last, long long a_batch_stride, float scale, int h, int hq,
-                    int nsplit, float* __restrict__ part_y, float* __restrict__ part_l) {
+                    const float* __restrict__ a_last, long long a_batch_stride, long long q_bs, float scale, int h,
+                    int hq, int nsplit, float* __restrict__ part_y, float* __restrict__ part_l) {
   using namespace dec;
   __shared__ float sq[RG][HD];
   __shared__ float red_y[THREADS / 32][RG][HD];
@@ -59,7 +59,7 @@ decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const 
   if (a_last != nullptr) f *= __expf(0.5f * a_last[(size_t)batch * a_batch_stride + head]);
   for (int i = tid; i < nr * HD; i += THREADS) {
     const int r = i / HD, e = i % HD;
-    const float q = float(Q[((size_t)batch * hq + head * ratio + r0 + r) * HD + e]);
+    const float q = float(Q[(size_t)batch * q_bs + (size_t)(head * ratio + r0 + r) * HD + e]);
     sq[r][e] = float(T(q * f));
   }
   __syncthreads();
@@ -174,15 +174,16 @@ decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const 
 template <typename T>
 __global__ void __launch_bounds__(128)
 decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
-                     const float* __restrict__ a, float scale, int tk, int h, int hq, int nsplit,
-                     const float* __restrict__ part_y, const float* __restrict__ part_l, T* __restrict__ O) {
+                     const float* __restrict__ a, long long q_bs, long long kv_bs, float scale, int tk, int h, int hq,
+                     int nsplit, const float* __restrict__ part_y, const float* __restrict__ part_l,
+                     T* __restrict__ O) {
   constexpr int HD = dec::HD;
   __shared__ float sq[HD];
   __shared__ float red[4][HD + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int batch = blockIdx.x / hq, qh = blockIdx.x % hq;
   const int kvh = qh / (hq / h);
-  if (tid < HD) sq[tid] = float(Q[((size_t)batch * hq + qh) * HD + tid]);
+  if (tid < HD) sq[tid] = float(Q[(size_t)batch * q_bs + (size_t)qh * HD + tid]);
   __syncthreads();
   float y[HD];
 #pragma unroll
@@ -192,7 +193,7 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
     const float a_q = a ? a[((size_t)batch * tk + tk - 1) * h + kvh] : 0.f;
     const float s2 = scale * scale;
     for (int j = tid; j < tk; j += 128) {
-      const uint4* kr = reinterpret_cast<const uint4*>(K + (((size_t)batch * tk + j) * h + kvh) * HD);
+      const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)batch * kv_bs + ((size_t)j * h + kvh) * HD);
       float s = 0.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -208,7 +209,7 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
       float wgt = s2 * s * s;
       if (a) wgt *= __expf(a_q - a[((size_t)batch * tk + j) * h + kvh]);
       l += wgt;
-      const uint4* vr = reinterpret_cast<const uint4*>(V + (((size_t)batch * tk + j) * h + kvh) * HD);
+      const uint4* vr = reinterpret_cast<const uint4*>(V + (size_t)batch * kv_bs + ((size_t)j * h + kvh) * HD);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const uint4 v = vr[c];
@@ -244,6 +245,37 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
       }
     }
     O[((size_t)batch * hq + qh) * HD + tid] = T(yt * safe_recip(lt));
+  }
+}
+
+// Cumulative log gates of the cached tokens, a[b, tk, h] (dense) from log_g whose batch entries are
+// g_bs floats apart (a cache kept as a slice of a longer preallocated tensor).  One CTA per
+// (batch, head); tk is small (below the switch-over length), so one block-wide scan per 256 tokens.
+__global__ void __launch_bounds__(256)
+decode_gate_cumsum_kernel(const float* __restrict__ log_g, long long g_bs, float* __restrict__ a, int tk, int h) {
+  __shared__ float warp_tot[8];
+  __shared__ float carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int batch = blockIdx.x / h, head = blockIdx.x % h;
+  if (tid == 0) carry_s = 0.f;
+  __syncthreads();
+  for (int base = 0; base < tk; base += 256) {
+    const int i = base + tid;
+    float v = (i < tk) ? log_g[(size_t)batch * g_bs + (size_t)i * h + head] : 0.f;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float o = __shfl_up_sync(0xffffffffu, v, off);
+      if (lane >= off) v += o;
+    }
+    if (lane == 31) warp_tot[warp] = v;
+    __syncthreads();
+    float pre = carry_s;
+    for (int w = 0; w < warp; ++w) pre += warp_tot[w];
+    v += pre;
+    if (i < tk) a[((size_t)batch * tk + i) * h + head] = v;
+    __syncthreads();
+    if (tid == 255) carry_s = v;
+    __syncthreads();
   }
 }
 
@@ -320,9 +352,26 @@ extern "C" int pr_decode_state(int dtype, int b, int h, int hq, int d, const voi
                                  stream);
 }
 
+namespace pr {
+static int launch_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, long long q_bs, const void* state,
+                               const float* sum_of_keys, const float* a_last, long long a_batch_stride, float scale,
+                               float* part_y, float* part_l, int device, void* stream);
+static int launch_decode_finish(int dtype, int b, int tk, int h, int hq, int d, const void* Q, long long q_bs,
+                                const void* K, const void* V, long long kv_bs, const float* a, float scale,
+                                const float* part_y, const float* part_l, void* O, int device, void* stream);
+}  // namespace pr
+
 extern "C" int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
                                        const float* sum_of_keys, const float* a_last, long long a_batch_stride,
                                        float scale, float* part_y, float* part_l, int device, void* stream) {
+  return pr::launch_decode_state(dtype, b, h, hq, d, Q, (long long)hq * d, state, sum_of_keys, a_last, a_batch_stride,
+                                 scale, part_y, part_l, device, stream);
+}
+
+static int pr::launch_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, long long q_bs,
+                                   const void* state, const float* sum_of_keys, const float* a_last,
+                                   long long a_batch_stride, float scale, float* part_y, float* part_l, int device,
+                                   void* stream) {
   using namespace pr;
   PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0, PR_ERR_BAD_ARG, "bad sizes b=%d h=%d hq=%d", b, h, hq);
@@ -336,8 +385,8 @@ extern "C" int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, c
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define PR_LAUNCH_DECODE(TT, RGV)                                                                              \
   decode_state_kernel<TT, RGV><<<grid, dec::THREADS, 0, s>>>(static_cast<const TT*>(Q), static_cast<const TT*>(state), \
-                                                             sum_of_keys, a_last, a_batch_stride, scale, h, hq,      \
-                                                             nsplit, part_y, part_l)
+                                                             sum_of_keys, a_last, a_batch_stride, q_bs, scale, h,    \
+                                                             hq, nsplit, part_y, part_l)
   if (dtype == PR_BF16) {
     if (rg == 1) PR_LAUNCH_DECODE(__nv_bfloat16, 1); else PR_LAUNCH_DECODE(__nv_bfloat16, 4);
   } else if (dtype == PR_FP16) {
@@ -353,7 +402,15 @@ extern "C" int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, c
 extern "C" int pr_decode_finish(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K,
                                 const void* V, const float* a, float scale, const float* part_y, const float* part_l,
                                 void* O, int device, void* stream) {
+  return pr::launch_decode_finish(dtype, b, tk, h, hq, d, Q, (long long)hq * d, K, V, (long long)tk * h * d, a, scale,
+                                  part_y, part_l, O, device, stream);
+}
+
+static int pr::launch_decode_finish(int dtype, int b, int tk, int h, int hq, int d, const void* Q, long long q_bs,
+                                    const void* K, const void* V, long long kv_bs, const float* a, float scale,
+                                    const float* part_y, const float* part_l, void* O, int device, void* stream) {
   using namespace pr;
+  PR_REQUIRE(kv_bs % 8 == 0, PR_ERR_BAD_ARG, "batch stride of K / V must be a multiple of 8 elements");
   PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0 && tk >= 0, PR_ERR_BAD_ARG, "bad sizes");
   PR_REQUIRE(Q && O && aligned16(K) && aligned16(V), PR_ERR_BAD_ARG, "null or misaligned pointer");
@@ -365,11 +422,12 @@ extern "C" int pr_decode_finish(int dtype, int b, int tk, int h, int hq, int d, 
   if (dtype == PR_BF16)
     decode_finish_kernel<__nv_bfloat16><<<b * hq, 128, 0, s>>>(
         static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
-        static_cast<const __nv_bfloat16*>(V), a, scale, tk, h, hq, nsplit, part_y, part_l,
+        static_cast<const __nv_bfloat16*>(V), a, q_bs, kv_bs, scale, tk, h, hq, nsplit, part_y, part_l,
         static_cast<__nv_bfloat16*>(O));
   else if (dtype == PR_FP16)
     decode_finish_kernel<__half><<<b * hq, 128, 0, s>>>(static_cast<const __half*>(Q), static_cast<const __half*>(K),
-                                                        static_cast<const __half*>(V), a, scale, tk, h, hq, nsplit,
+                                                        static_cast<const __half*>(V), a, q_bs, kv_bs, scale, tk, h, hq,
+                                                        nsplit,
                                                         part_y, part_l, static_cast<__half*>(O));
   else
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
@@ -411,29 +469,45 @@ extern "C" int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, co
                               const void* V, const float* log_g, const void* state, const float* sum_of_keys,
                               float scale, float* a_scratch, float* part_y, float* part_l, void* O, int device,
                               void* stream) {
+  return pr_decode_step_strided(dtype, b, tk, h, hq, d, Q, (long long)hq * d, K, V, (long long)tk * h * d, log_g,
+                                (long long)tk * h, state, sum_of_keys, scale, a_scratch, part_y, part_l, O, device,
+                                stream);
+}
+
+// The same step for a query and a cache that are slices of longer preallocated tensors: batch
+// entry i of Q starts q_bstride elements after entry i-1, of K and V kv_bstride elements, of
+// log_g g_bstride floats; inside a batch entry the tensors are dense ([1,hq,d], [tk,h,d], [tk,h]).
+extern "C" int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, int d, const void* Q,
+                                      long long q_bstride, const void* K, const void* V, long long kv_bstride,
+                                      const float* log_g, long long g_bstride, const void* state,
+                                      const float* sum_of_keys, float scale, float* a_scratch, float* part_y,
+                                      float* part_l, void* O, int device, void* stream) {
   using namespace pr;
   const bool has_cache = (K != nullptr && V != nullptr && tk > 0);
   const bool gated = has_cache && log_g != nullptr;
+  PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0 && tk >= 0, PR_ERR_BAD_ARG, "bad sizes");
   PR_REQUIRE(!gated || a_scratch != nullptr, PR_ERR_BAD_ARG, "gated decode needs a_scratch");
   PR_REQUIRE(state == nullptr || (part_y != nullptr && part_l != nullptr && sum_of_keys != nullptr), PR_ERR_BAD_ARG,
              "a state needs sum_of_keys and the partial-sum workspace");
+  PR_REQUIRE(q_bstride >= (long long)hq * d && (!has_cache || kv_bstride >= (long long)tk * h * d) &&
+                 (!gated || g_bstride >= (long long)tk * h),
+             PR_ERR_BAD_ARG, "a batch stride is smaller than one batch entry");
   int rc = PR_OK;
   if (gated) {
-    rc = pr_gate_prep(dtype, b, tk, h, h, d, tk, log_g, nullptr, a_scratch, nullptr, nullptr, nullptr, nullptr, 0, 1.f,
-                      1, device, stream);
-    if (rc) return rc;
+    PR_CUDA(cudaSetDevice(device));
+    decode_gate_cumsum_kernel<<<b * h, 256, 0, static_cast<cudaStream_t>(stream)>>>(log_g, g_bstride, a_scratch, tk, h);
+    PR_CUDA(cudaGetLastError());
   }
   if (state != nullptr) {
-    // a_last[b,h] is the last row of a_scratch: element (batch, tk-1, head); the kernel indexes
-    // it as a_last[batch*h + head], so hand it a pointer with the batch stride folded in when b == 1,
-    // else use the strided variant below
-    rc = pr_decode_state_strided(dtype, b, h, hq, d, Q, state, sum_of_keys, gated ? a_scratch + (size_t)(tk - 1) * h : nullptr,
-                                 gated ? (long long)tk * h : 0, scale, part_y, part_l, device, stream);
+    // a_last[b,h] is the last row of a_scratch: element (batch, tk-1, head), batch entries tk*h apart
+    rc = launch_decode_state(dtype, b, h, hq, d, Q, q_bstride, state, sum_of_keys,
+                             gated ? a_scratch + (size_t)(tk - 1) * h : nullptr, gated ? (long long)tk * h : 0, scale,
+                             part_y, part_l, device, stream);
     if (rc) return rc;
   }
-  return pr_decode_finish(dtype, b, has_cache ? tk : 0, h, hq, d, Q, has_cache ? K : nullptr, has_cache ? V : nullptr,
-                          gated ? a_scratch : nullptr, scale, state ? part_y : nullptr, state ? part_l : nullptr, O,
-                          device, stream);
+  return launch_decode_finish(dtype, b, has_cache ? tk : 0, h, hq, d, Q, q_bstride, has_cache ? K : nullptr,
+                              has_cache ? V : nullptr, kv_bstride, gated ? a_scratch : nullptr, scale,
+                              state ? part_y : nullptr, state ? part_l : nullptr, O, device, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -304,11 +304,38 @@ def state_merge(state, sum_of_keys, S, gram, a_last):
 _decode_ws = {}
 
 
+def _batch_strided(t: torch.Tensor):
+    """(tensor, batch stride in elements) with everything inside a batch entry dense.  A slice [:, :tk] of a
+    longer preallocated cache qualifies as it is; anything else is copied."""
+    if t is None:
+        return None, 0
+    if t.dim() >= 2:
+        inner = 1
+        dense = True
+        for size, stride in zip(reversed(t.shape[1:]), reversed(t.stride()[1:])):
+            if size != 1 and stride != inner:
+                dense = False
+                break
+            inner *= size
+        if dense and (t.shape[0] == 1 or t.stride(0) >= inner):
+            return t, (t.stride(0) if t.shape[0] > 1 else inner)
+    t = t.contiguous()
+    return t, (t.stride(0) if t.dim() >= 1 else 0)
+
+
 def decode_step(Q, K, V, log_g, state, sum_of_keys, scale: float, h: int):
-    """One decode step (tq = 1) in a single library call.  Returns O [b,1,hq,d]."""
+    """One decode step (tq = 1) in a single library call.  Returns O [b,1,hq,d].  Q, K, V and log_g may be
+    slices along the token axis of longer tensors (a preallocated cache): they are read in place."""
     b, _, hq, d = Q.shape
     tk = K.shape[1] if K is not None else 0
-    O = torch.empty_like(Q)
+    Q, q_bs = _batch_strided(Q)
+    K, k_bs = _batch_strided(K)
+    V, v_bs = _batch_strided(V)
+    if K is not None and (k_bs != v_bs or k_bs % 8 != 0 or K.data_ptr() % 16 or V.data_ptr() % 16):
+        K, V = K.contiguous(), V.contiguous()
+        k_bs = v_bs = tk * h * d
+    log_g, g_bs = _batch_strided(log_g)
+    O = torch.empty(b, 1, hq, d, device=Q.device, dtype=Q.dtype)
     a = torch.empty(b, tk, h, device=Q.device, dtype=torch.float32) if (log_g is not None and tk > 0) else None
     part_y = part_l = None
     if state is not None:
@@ -318,7 +345,8 @@ def decode_step(Q, K, V, log_g, state, sum_of_keys, scale: float, h: int):
             _decode_ws[key] = (torch.empty(b, hq, ns, d, device=Q.device, dtype=torch.float32),
                                torch.empty(b, hq, ns, device=Q.device, dtype=torch.float32))
         part_y, part_l = _decode_ws[key]
-    _call("pr_decode_step", c_int(dtype_code(Q.dtype)), c_int(b), c_int(tk), c_int(h), c_int(hq), c_int(d), ptr(Q),
-          ptr(K), ptr(V), ptr(log_g), ptr(state), ptr(sum_of_keys), c_float(scale), ptr(a), ptr(part_y), ptr(part_l),
-          ptr(O), c_int(_dev(Q)), stream_ptr(Q.device))
+    _call("pr_decode_step_strided", c_int(dtype_code(Q.dtype)), c_int(b), c_int(tk), c_int(h), c_int(hq), c_int(d),
+          ptr(Q), c_longlong(q_bs), ptr(K), ptr(V), c_longlong(k_bs), ptr(log_g), c_longlong(g_bs), ptr(state),
+          ptr(sum_of_keys), c_float(scale), ptr(a), ptr(part_y), ptr(part_l), ptr(O), c_int(_dev(Q)),
+          stream_ptr(Q.device))
     return O

@@ -176,7 +176,6 @@ def power_retention_inference(Q, K, V, log_G=None, initial_state=None, sum_of_ke
         assert Q.dtype == K.dtype == V.dtype, "dtypes of inputs must match"
         assert K.shape[1] == V.shape[1], "key and value must have the same seq_len"
         tk, h = K.shape[1], K.shape[2]
-        K, V = K.contiguous(), V.contiguous()
     else:
         tk, h = 0, initial_state.shape[1]
     assert hq % h == 0
@@ -184,17 +183,25 @@ def power_retention_inference(Q, K, V, log_G=None, initial_state=None, sum_of_ke
         D = layout.exact_dim(d)
         assert initial_state.shape == (b, h, D, d), f"state must be [b,h,{D},{d}] (exact layout)"
         assert sum_of_keys.shape == (b, h, D) and sum_of_keys.dtype == torch.float32
-    Q = Q.contiguous()
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     gated = has_cache and log_G is not None
     if gated:
         assert log_G.shape == K.shape[:3]
-        log_G = log_G.to(torch.float32).contiguous()
+        log_G = log_G.to(torch.float32)
     switch = switch_over_seq_len is not None and tk >= switch_over_seq_len
+    decode = tq == 1 and initial_state is not None
+    if not decode or switch:
+        # every path but the plain decode step wants dense tensors; the decode step reads a query and a cache
+        # that are slices of longer preallocated tensors in place
+        Q = Q.contiguous()
+        if has_cache:
+            K, V = K.contiguous(), V.contiguous()
+        if gated:
+            log_G = log_G.contiguous()
 
     # ---- read-out
     a = None
-    if tq == 1 and initial_state is not None:
+    if decode:
         # the decode step proper: one library call (gate cumsum, state read, cache attention)
         Y = ops.decode_step(Q, K if tk > 0 else None, V if tk > 0 else None, log_G if gated else None,
                             initial_state.contiguous(), sum_of_keys.contiguous(), scale, h)

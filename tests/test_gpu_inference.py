@@ -86,3 +86,29 @@ def test_prefill_then_decode_matches_full_sequence(cuda_device):
                                                   sk, switch_over_seq_len=1024)
         assert s2 is state and k2 is sk
         assert rel_l2(Y.float().cpu(), ref[:, hi - 1:hi].float()) < 1e-2, i
+
+
+@pytest.mark.parametrize("ratio", [1, 4])
+def test_decode_reads_cache_slices_in_place(cuda_device, ratio):
+    """A query and a cache that are slices [:, :tk] of longer preallocated tensors (a serving loop's KV and gate
+    cache) give bit-identical results to dense copies, with and without GQA, while the cache grows."""
+    import retention_integration_b200 as prb
+
+    g = torch.Generator().manual_seed(41)
+    b, h, d, cap = 3, 2, 64, 40
+    hq = h * ratio
+    mk = lambda *s: torch.randn(*s, generator=g).bfloat16().to(cuda_device)
+    Kc, Vc, Qs = mk(b, cap, h, d), mk(b, cap, h, d), mk(b, cap, hq, d)
+    lgc = F.logsigmoid(torch.randn(b, cap, h, generator=g) + 1.0).to(cuda_device)
+    K0, V0 = mk(b, 256, h, d), mk(b, 256, h, d)
+    lg0 = F.logsigmoid(torch.randn(b, 256, h, generator=g) + 1.0).to(cuda_device)
+    _, state, sk = prb.power_retention_inference(mk(b, 1, hq, d), K0, V0, lg0, switch_over_seq_len=256)
+    for tk in (1, 7, 33, cap):
+        q, k, v, lg = Qs[:, tk - 1:tk], Kc[:, :tk], Vc[:, :tk], lgc[:, :tk]
+        assert not k.is_contiguous() or tk == cap
+        y_view, _, _ = prb.power_retention_inference(q, k, v, lg, state, sk, switch_over_seq_len=1024)
+        y_copy, _, _ = prb.power_retention_inference(q.contiguous(), k.contiguous(), v.contiguous(),
+                                                     lg.contiguous(), state, sk, switch_over_seq_len=1024)
+        torch.cuda.synchronize()
+        assert torch.equal(y_view, y_copy), tk
+        assert torch.isfinite(y_view).all()
