@@ -50,6 +50,8 @@ class HostPipeline:
         self.res = [None, None]  # results of the slice in flight per parity (kept alive until copied out)
         self.ev_in = [torch.cuda.Event() for _ in range(self.n_slices)]
         self.ev_cmp = [torch.cuda.Event() for _ in range(self.n_slices)]
+        self.ev_qkv = [torch.cuda.Event() for _ in range(self.n_slices)]
+        self.ev_fwd = [torch.cuda.Event() for _ in range(self.n_slices)]
         self.ev_out = [torch.cuda.Event() for _ in range(self.n_slices)]
 
     @staticmethod
@@ -81,12 +83,16 @@ class HostPipeline:
             Kd, Vd = view(self.K[p], hs), view(self.V[p], hs)
             if i >= 2:  # the buffers of this parity are free once slice i-2 has been computed
                 self.s_in.wait_event(self.ev_cmp[i - 2])
+            # Q, K, V first: the forward starts as soon as they are in, the upstream gradient follows
             for host, devbuf, heads, hoff, full in ((Qh, Qd, hs * r, off * r, h * r), (Kh, Kd, hs, off, h),
-                                                    (Vh, Vd, hs, off, h), (dOh, dOd, hs * r, off * r, h * r)):
+                                                    (Vh, Vd, hs, off, h)):
                 _copy2d(devbuf, 0, heads * d * es, host, hoff * d * es, full * d * es, heads * d * es, rows, 1,
                         self.idx, self.s_in)
+            self.ev_qkv[i].record(self.s_in)
+            _copy2d(dOd, 0, hs * r * d * es, dOh, off * r * d * es, h * r * d * es, hs * r * d * es, rows, 1, self.idx,
+                    self.s_in)
             self.ev_in[i].record(self.s_in)
-            self.s_cmp.wait_event(self.ev_in[i])
+            self.s_cmp.wait_event(self.ev_qkv[i])
             if i >= 2:  # results of slice i-2 must have left before their tensors are dropped
                 self.s_cmp.wait_event(self.ev_out[i - 2])
             with torch.cuda.stream(self.s_cmp):
@@ -95,14 +101,21 @@ class HostPipeline:
                 if self.gated:
                     g = self.G[:, :, off:off + hs].contiguous().requires_grad_(True)
                 O = power_retention(q, k, v, g, deg=2, chunk_size=self.chunk)
+            # the output leaves while the backward runs
+            self.ev_fwd[i].record(self.s_cmp)
+            self.s_out.wait_event(self.ev_fwd[i])
+            Od = O.detach()
+            _copy2d(out["O"], off * r * d * es, h * r * d * es, Od, 0, hs * r * d * es, hs * r * d * es, rows, 0,
+                    self.idx, self.s_out)
+            self.s_cmp.wait_event(self.ev_in[i])
+            with torch.cuda.stream(self.s_cmp):
                 O.backward(dOd)
                 if self.gated:
                     self.dG[:, :, off:off + hs].copy_(g.grad)
-                self.res[p] = (O.detach(), q.grad, k.grad, v.grad)
+                self.res[p] = (Od, q.grad, k.grad, v.grad)
             self.ev_cmp[i].record(self.s_cmp)
             self.s_out.wait_event(self.ev_cmp[i])
-            for name, src, heads, hoff, full in (("O", self.res[p][0], hs * r, off * r, h * r),
-                                                 ("dQ", self.res[p][1], hs * r, off * r, h * r),
+            for name, src, heads, hoff, full in (("dQ", self.res[p][1], hs * r, off * r, h * r),
                                                  ("dK", self.res[p][2], hs, off, h), ("dV", self.res[p][3], hs, off, h)):
                 _copy2d(out[name], hoff * d * es, full * d * es, src, 0, heads * d * es, heads * d * es, rows, 0,
                         self.idx, self.s_out)
