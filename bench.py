@@ -330,8 +330,8 @@ def main():
     # call: head slices pipelined over copy-in / compute / copy-out streams)
     from retention_integration_b200.host import HostPipeline
 
-    # equal slices: a shorter first slice (HostPipeline.default_slices) fills the pipeline sooner but its 128-byte
-    # rows copy at 46 instead of 55 GB/s and its launches are less efficient; measured 8.0 against 7.7 ms per step
+    # equal two-head slices: slices of one head copy their 128-byte rows at 46 instead of 55 GB/s and launch less
+    # efficiently; measured per step: 2,2,2,2 heads 7.1 ms, 1,1,2,2,2 8.0 ms, eight one-head slices 10.8 ms
     n_slices = 4 if hl % 4 == 0 else (2 if hl % 2 == 0 else 1)
     pipe = HostPipeline(b, t, hl, d, torch.bfloat16, dev, c, n_slices=n_slices)
     outs_h = {k: torch.empty(b, t, hl, d, dtype=torch.bfloat16).pin_memory() for k in ("O", "dQ", "dK", "dV")}
