@@ -336,7 +336,16 @@ def decode_step(Q, K, V, log_g, state, sum_of_keys, scale: float, h: int):
         k_bs = v_bs = tk * h * d
     log_g, g_bs = _batch_strided(log_g)
     O = torch.empty(b, 1, hq, d, device=Q.device, dtype=Q.dtype)
-    a = torch.empty(b, tk, h, device=Q.device, dtype=torch.float32) if (log_g is not None and tk > 0) else None
+    a = None
+    if log_g is not None and tk > 0:
+        # scratch for the cumulative gates, kept between steps and grown geometrically with the cache
+        gkey = (Q.device, "gates")
+        need = b * tk * h
+        buf = _decode_ws.get(gkey)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(max(need * 2, 1 << 16), device=Q.device, dtype=torch.float32)
+            _decode_ws[gkey] = buf
+        a = buf
     part_y = part_l = None
     if state is not None:
         key = (Q.device, b, hq, d)
