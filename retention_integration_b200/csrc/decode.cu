@@ -171,6 +171,8 @@ decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const 
 }
 
 // One CTA per (batch, query head): attention over the tk cached tokens + merge + normalise.
+// Eight lanes share a token (16 bytes of its key and value row each), so a warp streams four
+// tokens per iteration with fully used 128-byte rows; two iterations are in flight per lane.
 template <typename T>
 __global__ void __launch_bounds__(128)
 decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
@@ -178,60 +180,89 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
                      int nsplit, const float* __restrict__ part_y, const float* __restrict__ part_l,
                      T* __restrict__ O) {
   constexpr int HD = dec::HD;
-  __shared__ float sq[HD];
   __shared__ float red[4][HD + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = lane & 7, slot = lane >> 3;
   const int batch = blockIdx.x / hq, qh = blockIdx.x % hq;
   const int kvh = qh / (hq / h);
-  if (tid < HD) sq[tid] = float(Q[(size_t)batch * q_bs + (size_t)qh * HD + tid]);
-  __syncthreads();
-  float y[HD];
+  // this lane's eight query features
+  float q[8];
+  {
+    const uint4 qv = *reinterpret_cast<const uint4*>(Q + (size_t)batch * q_bs + (size_t)qh * HD + sub * 8);
+    const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-  for (int e = 0; e < HD; ++e) y[e] = 0.f;
+    for (int k = 0; k < 4; ++k) {
+      const float2 p2 = Pack2<T>::to_f32(w[k]);
+      q[2 * k] = p2.x;
+      q[2 * k + 1] = p2.y;
+    }
+  }
+  float y[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) y[e] = 0.f;
   float l = 0.f;
   if (K != nullptr && tk > 0) {
     const float a_q = a ? a[((size_t)batch * tk + tk - 1) * h + kvh] : 0.f;
     const float s2 = scale * scale;
-    for (int j = tid; j < tk; j += 128) {
-      const uint4* kr = reinterpret_cast<const uint4*>(K + (size_t)batch * kv_bs + ((size_t)j * h + kvh) * HD);
-      float s = 0.f;
+    const T* kb = K + (size_t)batch * kv_bs + (size_t)kvh * HD + sub * 8;
+    const T* vb = V + (size_t)batch * kv_bs + (size_t)kvh * HD + sub * 8;
+    constexpr int UN = 2;
+    // the trip count depends on the warp only: every lane takes part in the shuffles below, lanes
+    // whose token lies past the cache contribute zero weight
+    for (int base = warp * 4; base < tk; base += 16 * UN) {
+      const int j0 = base + slot;
+      uint4 kv[UN], vv[UN];
+      float aj[UN];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 v = kr[c];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 p2 = Pack2<T>::to_f32(w[k]);
-          s = fmaf(p2.x, sq[c * 8 + 2 * k], s);
-          s = fmaf(p2.y, sq[c * 8 + 2 * k + 1], s);
+      for (int u = 0; u < UN; ++u) {
+        const int j = j0 + 16 * u;
+        kv[u] = vv[u] = make_uint4(0, 0, 0, 0);
+        aj[u] = 0.f;
+        if (j < tk) {
+          kv[u] = *reinterpret_cast<const uint4*>(kb + (size_t)j * h * HD);
+          vv[u] = *reinterpret_cast<const uint4*>(vb + (size_t)j * h * HD);
+          if (a) aj[u] = a[((size_t)batch * tk + j) * h + kvh];
         }
       }
-      float wgt = s2 * s * s;
-      if (a) wgt *= __expf(a_q - a[((size_t)batch * tk + j) * h + kvh]);
-      l += wgt;
-      const uint4* vr = reinterpret_cast<const uint4*>(V + (size_t)batch * kv_bs + ((size_t)j * h + kvh) * HD);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 v = vr[c];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      for (int u = 0; u < UN; ++u) {
+        const int j = j0 + 16 * u;
+        const uint32_t kw[4] = {kv[u].x, kv[u].y, kv[u].z, kv[u].w};
+        float sdot = 0.f;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float2 p2 = Pack2<T>::to_f32(w[k]);
-          y[c * 8 + 2 * k] = fmaf(wgt, p2.x, y[c * 8 + 2 * k]);
-          y[c * 8 + 2 * k + 1] = fmaf(wgt, p2.y, y[c * 8 + 2 * k + 1]);
+          const float2 p2 = Pack2<T>::to_f32(kw[k]);
+          sdot = fmaf(p2.x, q[2 * k], sdot);
+          sdot = fmaf(p2.y, q[2 * k + 1], sdot);
+        }
+        sdot += __shfl_xor_sync(0xffffffffu, sdot, 1);
+        sdot += __shfl_xor_sync(0xffffffffu, sdot, 2);
+        sdot += __shfl_xor_sync(0xffffffffu, sdot, 4);
+        float wgt = (j < tk) ? s2 * sdot * sdot : 0.f;
+        if (a && j < tk) wgt *= __expf(a_q - aj[u]);
+        if (sub == 0) l += wgt;
+        const uint32_t vw[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 p2 = Pack2<T>::to_f32(vw[k]);
+          y[2 * k] = fmaf(wgt, p2.x, y[2 * k]);
+          y[2 * k + 1] = fmaf(wgt, p2.y, y[2 * k + 1]);
         }
       }
     }
   }
+  // sum over the four token slots of the warp, then over the warps
 #pragma unroll
-  for (int e = 0; e < HD; ++e) {
-    float t = y[e];
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-    if (lane == 0) red[warp][e] = t;
+  for (int e = 0; e < 8; ++e) {
+    y[e] += __shfl_xor_sync(0xffffffffu, y[e], 8);
+    y[e] += __shfl_xor_sync(0xffffffffu, y[e], 16);
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+  if (lane < 8) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) red[warp][lane * 8 + e] = y[e];
+  }
   if (lane == 0) red[warp][HD] = l;
   __syncthreads();
   if (tid < HD) {
@@ -410,7 +441,8 @@ static int pr::launch_decode_finish(int dtype, int b, int tk, int h, int hq, int
                                     const void* K, const void* V, long long kv_bs, const float* a, float scale,
                                     const float* part_y, const float* part_l, void* O, int device, void* stream) {
   using namespace pr;
-  PR_REQUIRE(kv_bs % 8 == 0, PR_ERR_BAD_ARG, "batch stride of K / V must be a multiple of 8 elements");
+  PR_REQUIRE(kv_bs % 8 == 0 && q_bs % 8 == 0 && aligned16(Q), PR_ERR_BAD_ARG,
+             "Q must be 16-byte aligned and the batch strides of Q, K, V multiples of 8 elements");
   PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0 && tk >= 0, PR_ERR_BAD_ARG, "bad sizes");
   PR_REQUIRE(Q && O && aligned16(K) && aligned16(V), PR_ERR_BAD_ARG, "null or misaligned pointer");

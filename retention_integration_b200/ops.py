@@ -329,6 +329,9 @@ def decode_step(Q, K, V, log_g, state, sum_of_keys, scale: float, h: int):
     b, _, hq, d = Q.shape
     tk = K.shape[1] if K is not None else 0
     Q, q_bs = _batch_strided(Q)
+    if q_bs % 8 != 0 or Q.data_ptr() % 16:
+        Q = Q.contiguous()
+        q_bs = hq * d
     K, k_bs = _batch_strided(K)
     V, v_bs = _batch_strided(V)
     if K is not None and (k_bs != v_bs or k_bs % 8 != 0 or K.data_ptr() % 16 or V.data_ptr() % 16):
