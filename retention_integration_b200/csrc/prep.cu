@@ -20,8 +20,11 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
                  int write_a) {
   extern __shared__ float sm_f[];
   float* sm_a = sm_f;                                    // [c] cumulative gates
-  T* tile = reinterpret_cast<T*>(sm_f + ((c + 3) & ~3)); // [64][d + 2]
-  T* tile2 = tile + 64 * (d + 2);                        // same, times row_scale
+  // transposed tiles [d features][64 tokens], 128-byte rows; the 16-byte chunk holding tokens 8j..8j+7 of
+  // feature f sits at chunk j ^ ((f >> 3) & 7), which keeps both the scattered 16-bit writes and the 128-bit
+  // row reads free of bank conflicts
+  T* tile = reinterpret_cast<T*>(sm_f + ((c + 3) & ~3));
+  T* tile2 = tile + 64 * d;                               // same, times row_scale
   __shared__ float warp_tot[kPrepThreads / 32];
   __shared__ float carry_s;
 
@@ -68,7 +71,6 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
   if (xt == nullptr) return;
 
   // ---- gated transpose, 64 tokens at a time
-  const int ld = d + 2;
   const int vec_per_row = d / 8;
   T* out_base = xt + ((size_t)(batch * n + chunk) * hx + head) * (size_t)d * cp;
   T* out2_base = xts ? xts + ((size_t)(batch * n + chunk) * hx + head) * (size_t)d * cp : nullptr;
@@ -97,26 +99,33 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
         float2 pr_ = Pack2<T>::to_f32(w[k]);
         w2[k] = Pack2<T>::from_f32(pr_.x * rs, pr_.y * rs);
       }
-      uint32_t* dst = reinterpret_cast<uint32_t*>(tile + r * ld + v * 8);
-      dst[0] = w[0]; dst[1] = w[1]; dst[2] = w[2]; dst[3] = w[3];
+      // features v*8 .. v*8+7 of token r: one 16-bit store each, into the row of its feature
+      const int pos = ((((r >> 3) ^ v) & 7) << 3) + (r & 7);
+      uint16_t* dst = reinterpret_cast<uint16_t*>(tile) + (v * 8) * 64 + pos;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        dst[(2 * k) * 64] = (uint16_t)(w[k] & 0xffffu);
+        dst[(2 * k + 1) * 64] = (uint16_t)(w[k] >> 16);
+      }
       if (xts != nullptr) {
-        uint32_t* dst2 = reinterpret_cast<uint32_t*>(tile2 + r * ld + v * 8);
-        dst2[0] = w2[0]; dst2[1] = w2[1]; dst2[2] = w2[2]; dst2[3] = w2[3];
+        uint16_t* dst2 = reinterpret_cast<uint16_t*>(tile2) + (v * 8) * 64 + pos;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          dst2[(2 * k) * 64] = (uint16_t)(w2[k] & 0xffffu);
+          dst2[(2 * k + 1) * 64] = (uint16_t)(w2[k] >> 16);
+        }
       }
     }
     __syncthreads();
     // each thread writes 8 consecutive tokens of one feature row
     for (int idx = tid; idx < d * 8; idx += kPrepThreads) {
       const int row = idx >> 3, tv = idx & 7;
-      T vals[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) vals[k] = tile[(tv * 8 + k) * ld + row];
-      *reinterpret_cast<uint4*>(out_base + (size_t)row * cp + tb + tv * 8) = *reinterpret_cast<uint4*>(vals);
-      if (xts != nullptr) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) vals[k] = tile2[(tv * 8 + k) * ld + row];
-        *reinterpret_cast<uint4*>(out2_base + (size_t)row * cp + tb + tv * 8) = *reinterpret_cast<uint4*>(vals);
-      }
+      const int chunk8 = ((tv ^ (row >> 3)) & 7) << 3;
+      *reinterpret_cast<uint4*>(out_base + (size_t)row * cp + tb + tv * 8) =
+          *reinterpret_cast<const uint4*>(tile + row * 64 + chunk8);
+      if (xts != nullptr)
+        *reinterpret_cast<uint4*>(out2_base + (size_t)row * cp + tb + tv * 8) =
+            *reinterpret_cast<const uint4*>(tile2 + row * 64 + chunk8);
     }
   }
 }
@@ -275,7 +284,7 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
              "scaled copy requested without xt or row_scale");
   PR_CUDA(cudaSetDevice(device));
   const int cp = (c + 63) / 64 * 64;
-  const size_t smem = (size_t)((c + 3) & ~3) * 4 + (size_t)2 * 64 * (d + 2) * 2;
+  const size_t smem = (size_t)((c + 3) & ~3) * 4 + (size_t)2 * 64 * d * 2;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int tiles = cp / 64;
   const dim3 grid(b * (t / c) * hx, xt ? (tiles >= 8 ? 4 : (tiles >= 2 ? 2 : 1)) : 1);
