@@ -40,9 +40,17 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
   if (log_g != nullptr) {
     if (tid == 0) carry_s = 0.f;
     __syncthreads();
-    for (int base = 0; base < c; base += kPrepThreads) {
-      const int i = base + tid;
-      float v = (i < c) ? log_g[(tok0 + i) * h + gh] : 0.f;
+    // four consecutive gates per thread and round (their loads are independent), then one
+    // block-wide scan of the per-thread totals: a 1024-token chunk is one round
+    for (int base = 0; base < c; base += 4 * kPrepThreads) {
+      const int i0 = base + 4 * tid;
+      float p[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) p[k] = (i0 + k < c) ? log_g[(tok0 + i0 + k) * h + gh] : 0.f;
+      p[1] += p[0];
+      p[2] += p[1];
+      p[3] += p[2];
+      float v = p[3];
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
         const float o = __shfl_up_sync(0xffffffffu, v, off);
@@ -50,12 +58,13 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
       }
       if (lane == 31) warp_tot[warp] = v;
       __syncthreads();
-      float pre = carry_s;
+      float pre = carry_s + (v - p[3]);  // everything before this thread's four gates
       for (int w = 0; w < warp; ++w) pre += warp_tot[w];
-      v += pre;
-      if (i < c) sm_a[i] = v;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (i0 + k < c) sm_a[i0 + k] = p[k] + pre;
       __syncthreads();
-      if (tid == kPrepThreads - 1) carry_s = v;
+      if (tid == kPrepThreads - 1) carry_s = p[3] + pre;
       __syncthreads();
     }
   } else {
