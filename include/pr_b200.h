@@ -58,6 +58,10 @@ const char* pr_last_error(void);
  * *status is 0 when nothing failed. */
 int pr_device_status(int device, int* status);
 
+/* The same read as an error code: PR_OK, or PR_ERR_TIMEOUT when a kernel gave up on a bounded
+ * wait since the last read (the outputs of that launch are then undefined).  Clears the word. */
+int pr_device_check(int device);
+
 /* Strided copy of `rows` rows of `width_bytes` between pinned host memory and device memory
  * (to_device = 1: host -> device), e.g. one slice of heads of a [b,t,h,d] tensor; the host-buffer
  * variant of the public call pipelines such slices.  No counterpart in the reference, whose
@@ -77,25 +81,12 @@ int pr_copy_2d(void* dst, long long dst_pitch, const void* src, long long src_pi
 int pr_selftest_umma(int variant, int dtype, int n, int k, const void* a, const void* b, float* out,
                      int device, void* stream);
 
-/* Micro-benchmark of tensor-memory reads: nwarps (4, 8, 16) warps of one CTA each issue `iters`
- * loads of 32 lanes x 32 columns; cycles[0] receives the SM clock cycles taken. */
-/* Micro-benchmark of the tcgen05.mma issue rate for the operand shapes used here (mode 0: smem x smem
- * N=128; 1: smem x smem N=64; 2: tmem x smem N=64; 3: tmem x smem N=128); 4*reps MMAs of K=16. */
-int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int device, void* stream);
-int pr_selftest_tmem_bw(int nwarps, int iters, long long* cycles, float* sink, int device, void* stream);
-/* Round trip of a 32-lane x 32-column tensor-memory load seen by nwarps (4, 8, 16) reader warps while one more thread
- * issues mma_reps groups of four M=128, N=mma_n, K=16 products (0 = idle tensor core).  cycles[0] = clocks of the slowest
- * reader for `iters` loads, cycles[1] = clocks of the products.  burst > 0: mma_reps bursts of `burst` groups, each
- * waited for, `gap` idle clocks apart; cycles[1] = clocks inside bursts, [2]/[3] = first/last burst, [4] = issuing (products and commit), [5] = products only;
- * cycles holds 8 entries. */
-int pr_selftest_tmem_ld_contention(int nwarps, int iters, int mma_reps, int mma_n, int burst, int gap,
-                                   long long* cycles, float* sink, int device, void* stream);
-/* L2 -> shared memory streaming rate of TMA: `grid` CTAs each walk `tiles` 16 KB tiles `reps` times through a ring
- * of `depth` stages (<= 12); CTAs with equal blockIdx.x / share read the same region; the regions must fit in
- * buf_bytes; min_smem (bytes of dynamic shared memory asked for at least) limits the CTAs per SM.
- * cycles[grid] = SM clocks. */
-int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int grid, int tiles, int reps, int depth, int share,
-                           int min_smem, long long* cycles, int device, void* stream);
+/* Self-test of the bounded device-side waits: one CTA waits on a barrier that nothing arrives at,
+ * with a budget of budget_us microseconds (the kernels of the library use two seconds), gives up,
+ * releases its tensor memory and returns.  *gave_up (device int, zeroed by the caller) counts the
+ * threads whose wait ran out; afterwards pr_device_status reports 1 and pr_device_check returns
+ * PR_ERR_TIMEOUT.  Nothing traps and the context stays usable.  No counterpart in the reference. */
+int pr_selftest_timeout(int budget_us, int* gave_up, int device, void* stream);
 
 /* Gate glue of retention/power_retention_maker.py:143-155,183-186 in one pass.
  * log_g [b,t,h] or NULL; x [b,t,hx,d].  Writes (when write_a) a [b,t,h] = inclusive
@@ -105,6 +96,13 @@ int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int grid, int t
 int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c, const float* log_g, const void* x,
                  float* a_out, float* A_out, void* xt, const float* row_scale, void* xts, int query_side,
                  float mult, int write_a, int device, void* stream);
+
+/* log_G.cumsum(1) of retention/power_retention_maker.py:129,347 for sequences of any length:
+ * a_out [b,t,h] (dense) from log_g whose batch entries are g_bstride floats apart.  Used where one
+ * "chunk" is the whole sequence (state-free quadratic branch, long inference caches) and the chunk
+ * would not fit pr_gate_prep's shared memory (c > 16384). */
+int pr_gate_cumsum(int b, int t, int h, const float* log_g, long long g_bstride, float* a_out, int device,
+                   void* stream);
 
 /* update_state (retention/_update_state/reference.py:31-53; the old binding
  * compute_update_states, retention/_update_state/cuda.py:30).
@@ -206,6 +204,9 @@ int pr_gate_grad(int b, int t, int h, int hq, int c, const float* da_q, const fl
  * S [b,1,h,D2,d] and gram [b,1,h,d,d] from pr_chunk_state over the cached tokens; state and
  * sum_of_keys may be NULL (first compression). */
 int pr_decode_nsplit(void);
+/* Parts the decode step of a given shape is split into, in [1, pr_decode_nsplit()]; 1 means that
+ * pr_decode_step / pr_decode_recurrent need no part_y / part_l.  Negative on bad sizes. */
+int pr_decode_split(int b, int h, int hq);
 int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
                     const float* sum_of_keys, const float* a_last, float scale, float* part_y, float* part_l,
                     int device, void* stream);
@@ -213,9 +214,12 @@ int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const
 int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
                             const float* sum_of_keys, const float* a_last, long long a_batch_stride, float scale,
                             float* part_y, float* part_l, int device, void* stream);
-/* One decode step in one call: cumulative gates of the tk cached tokens (into a_scratch
- * [b,tk,h], needed when log_g is given), state read-out and attention over the cache, merged
- * and normalised into O [b,1,hq,d].  K/V/log_g and state/sum_of_keys may each be absent. */
+/* One decode step (retention/power_retention_maker.py:287-363 for tq = 1) in one call and one kernel:
+ * gate sums of the tk cached tokens, state read-out and attention over the cache, merged and
+ * normalised into O [b,1,hq,d].  K/V/log_g and state/sum_of_keys may each be absent.  part_y
+ * [b,hq,pr_decode_nsplit(),d] and part_l [b,hq,pr_decode_nsplit()] are needed (and a second, tiny
+ * kernel runs) only when b*h*ceil(hq/h/4) < 384, where each (batch, head) pair is split over several
+ * CTAs; a_scratch is unused (kept for callers of the earlier three-kernel step) and may be NULL. */
 int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
                    const float* log_g, const void* state, const float* sum_of_keys, float scale, float* a_scratch,
                    float* part_y, float* part_l, void* O, int device, void* stream);
@@ -228,11 +232,28 @@ int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, int d, const
                            const void* K, const void* V, long long kv_bstride, const float* log_g, long long g_bstride,
                            const void* state, const float* sum_of_keys, float scale, float* a_scratch, float* part_y,
                            float* part_l, void* O, int device, void* stream);
+/* A state in the exact layout (state [b,h,d(d+1)/2,d], sum_of_keys [b,h,d(d+1)/2]) converted to the
+ * chunk-state layout of the training kernels: out16 [b,h,D2,d] 16-bit, out32 the same in fp32 (a carry_in
+ * for pr_discumsum_fwd), gram [b,h,d,d] fp32 (carry_in for pr_gram_scan_fwd), gram_hi / gram_lo 16-bit
+ * halves (for pr_chunk_out); any output may be NULL.  Serves initial_state of
+ * retention/power_retention_maker.py:72-73,158-160 and several-token queries against a state (:354-363). */
+int pr_state_to_chunk_layout(int dtype, int b, int h, int d, const void* state, const float* sum_of_keys, void* out16,
+                             float* out32, float* gram, void* gram_hi, void* gram_lo, int device, void* stream);
+/* Pure-recurrent decode step: the state is advanced by one token (k, v [b,1,h,d], log_g [b,1,h] or NULL)
+ * and read by q [b,1,hq,d] in one pass over it: the reference's inference step with
+ * switch_over_seq_len = 1 (retention/power_retention_maker.py:354-382: one cached token, then
+ * compression) and what deploy/models/powercoder/kvgs_dynamic_cache.py:131-172 would hold as a cache
+ * of length one.  Batch entries of q / k, v / log_g are q_bstride / kv_bstride / g_bstride elements
+ * apart.  new_state, new_sum_of_keys may alias the inputs when hq / h <= 4.  part_y / part_l as for
+ * pr_decode_step (needed only for small b*h). */
+int pr_decode_recurrent(int dtype, int b, int h, int hq, int d, const void* Q, long long q_bstride, const void* K,
+                        const void* V, long long kv_bstride, const float* log_g, long long g_bstride,
+                        const void* state, const float* sum_of_keys, void* new_state, float* new_sum_of_keys,
+                        float scale, float* part_y, float* part_l, void* O, int device, void* stream);
 /* No counterpart in the reference.  pr_decode_step for hosts that cannot hand over scratch
- * memory (a frozen memory pool, a stream callback, an allocator owned by another component): the gate and
- * partial-sum scratch sits in a fixed device array of about 2.4 MB that the library carries on
- * every GPU.  Limits: b*hq <= 1024 and b*tk*h <= 262144, beyond which PR_ERR_BAD_ARG is
- * returned.  The array is shared by all calls on a device, so calls that overlap on the GPU
+ * memory (a memory pool frozen after start-up, an allocator owned by another component): the
+ * partial-sum scratch of a split step sits in a fixed device array of about 1.3 MB that the library
+ * carries on every GPU.  Limit: b*hq <= 1024, beyond which PR_ERR_BAD_ARG is returned.  The array is shared by all calls on a device, so calls that overlap on the GPU
  * race; nothing in it needs zeroing between calls.  The first call on a device looks up the
  * array's device address and should be made outside any stream capture. */
 int pr_decode_step_static(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K,

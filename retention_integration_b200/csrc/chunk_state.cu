@@ -66,9 +66,13 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
   uint8_t* smW = sm + NS * XT_BYTES;          // NS x W_BYTES  (rows = tokens, 64 features)
   uint8_t* smG = smW;                         // Gram CTA only: 2 x GA_BYTES over the (unused) value ring
 
+  // grid.x = slots * (batch, chunk, head) triples, slot fastest: the CTAs of one triple run together and
+  // share their operand tiles through L2, and the triple count is not bound by the 65535 limit of grid.y
   const int n_tile_ctas = (p.n_tiles + NG - 1) / NG;
-  const bool gram_cta = ((int)blockIdx.x == n_tile_ctas);
-  const int ch = blockIdx.y;  // (batch * n + chunk) * nh + head
+  const int slots = n_tile_ctas + (p.gram ? 1 : 0);
+  const int slot = (int)(blockIdx.x % (unsigned)slots);
+  const bool gram_cta = (slot == n_tile_ctas);
+  const int ch = (int)(blockIdx.x / (unsigned)slots);  // (batch * n + chunk) * nh + head
   const int head = ch % p.nh;
   const int chunk = (ch / p.nh) % p.n_chunks;
   const int batch = ch / (p.nh * p.n_chunks);
@@ -172,7 +176,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int D2 = ref_dim(HD);
-    const int tile = (int)blockIdx.x * NG + grp;
+    const int tile = slot * NG + grp;
     int drow = tile * 128 + row_in_tile;
     const bool valid = !gram_cta && drow < D2;  // rows past the end still take part in the pipeline
     int a = 0, b = 0;
@@ -261,7 +265,9 @@ static int launch_chunk_state(const ChunkStateParams& p, int b, const CUtensorMa
   static_assert(2 * GA_BYTES <= NS * W_BYTES, "Gram stages must fit in the value ring");
   PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-  dim3 grid((p.n_tiles + NG - 1) / NG + (p.gram ? 1 : 0), b * p.n_chunks * p.nh);
+  const long long ctas = (long long)((p.n_tiles + NG - 1) / NG + (p.gram ? 1 : 0)) * b * p.n_chunks * p.nh;
+  PR_REQUIRE(ctas < (1ll << 31), PR_ERR_BAD_ARG, "%lld CTAs exceed the grid limit", ctas);
+  dim3 grid((unsigned)ctas);
   chunk_state_kernel<T><<<grid, THREADS, smem, stream>>>(p, tm_xt, tm_xs, tm_w);
   PR_CUDA(cudaGetLastError());
   return PR_OK;

@@ -2,6 +2,7 @@
 #include <mutex>
 
 #include "host.cuh"
+#include "sm100.cuh"
 
 namespace pr {
 
@@ -91,6 +92,18 @@ extern "C" int pr_device_status(int device, int* status) {
   if (rc != PR_OK) return rc;
   *status = *h;
   *h = 0;
+  return PR_OK;
+}
+
+// The status word turned into an error code: PR_ERR_TIMEOUT when a kernel gave up on a bounded
+// wait since the last read, PR_ERR_BAD_ARG when a kernel refused its arguments.  Clears the word.
+extern "C" int pr_device_check(int device) {
+  int st = 0;
+  int rc = pr_device_status(device, &st);
+  if (rc != PR_OK) return rc;
+  if (st == pr::ST_TIMEOUT)
+    return pr::fail(PR_ERR_TIMEOUT, "a kernel on device %d gave up on a bounded device-side wait", device);
+  if (st != pr::ST_OK) return pr::fail(PR_ERR_BAD_ARG, "a kernel on device %d reported status %d", device, st);
   return PR_OK;
 }
 

@@ -279,6 +279,458 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
   }
 }
 
+// The whole decode step for one (batch, kv head, group of up to RG query heads) in one CTA: the
+// state rows [d_begin, d_end) and the cached tokens [t_begin, t_end) of split `blockIdx.y` are
+// streamed once, both into the same per-lane accumulators (lane sub = tid & 7 owns eight output
+// features in both phases).  The gate sums the step needs are formed here from log_g itself:
+// the total a_last (the state's decay, folded into the query as exp(a_last / 2)) and, per cached
+// token j, the suffix sum of the gates after j, so no cumulative-gate scratch is written or read.
+// With one split the CTA normalises and writes the output itself; otherwise it writes partial
+// sums and decode_merge_kernel finishes.
+template <typename T, int RG>
+__global__ void __launch_bounds__(dec::THREADS, RG == 1 ? 4 : 2)
+decode_fused_kernel(const T* __restrict__ Q, long long q_bs, const T* __restrict__ K, const T* __restrict__ V,
+                    long long kv_bs, const float* __restrict__ log_g, long long g_bs, const T* __restrict__ state,
+                    const float* __restrict__ sok, float scale, int tk, int h, int hq, int nsplit,
+                    float* __restrict__ part_y, float* __restrict__ part_l, T* __restrict__ O) {
+  using namespace dec;
+  constexpr int BLK = 4 * THREADS;  // cached tokens per gate block
+  __shared__ float sq[RG][HD];      // gated, scaled, rounded queries (state phase)
+  __shared__ __align__(16) float sqr[RG][HD];  // raw queries (attention phase)
+  __shared__ float red_y[THREADS / 32][RG][HD];
+  __shared__ float red_l[THREADS / 32][RG];
+  __shared__ float sfx[BLK];
+  __shared__ float wsum[THREADS / 32][2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int bh = blockIdx.x, split = blockIdx.y, grp = blockIdx.z;
+  const int batch = bh / h, head = bh % h;
+  const int ratio = hq / h;
+  const int r0 = grp * RG, nr = min(RG, ratio - r0);
+  const bool gated = (log_g != nullptr) && tk > 0;
+  const int t_per = (tk + nsplit - 1) / nsplit;
+  const int t_begin = min(tk, split * t_per), t_end = min(tk, t_begin + t_per);
+
+  // ---- gate sums: the total, and the part after this split's last token
+  float a_last = 0.f, tail = 0.f;
+  if (gated) {
+    const float* gp = log_g + (size_t)batch * g_bs + head;
+    float tot = 0.f, tl = 0.f;
+    for (int u = tid; u < tk; u += THREADS) {
+      const float g = gp[(size_t)u * h];
+      tot += g;
+      if (u >= t_end) tl += g;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      tot += __shfl_xor_sync(0xffffffffu, tot, off);
+      tl += __shfl_xor_sync(0xffffffffu, tl, off);
+    }
+    if (lane == 0) {
+      wsum[warp][0] = tot;
+      wsum[warp][1] = tl;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) {
+      a_last += wsum[w][0];
+      tail += wsum[w][1];
+    }
+    __syncthreads();
+  }
+  const float f = scale * (gated ? __expf(0.5f * a_last) : 1.f);
+  for (int i = tid; i < RG * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    float q = 0.f;
+    if (r < nr) q = float(Q[(size_t)batch * q_bs + (size_t)(head * ratio + r0 + r) * HD + e]);
+    sqr[r][e] = q;
+    sq[r][e] = float(T(q * f));  // rounded like the reference rounds Q * exp(.) to Q's dtype
+  }
+  __syncthreads();
+
+  const int sub = tid & 7;
+  float acc[RG][8];
+  float accl[RG];
+#pragma unroll
+  for (int r = 0; r < RG; ++r) {
+    accl[r] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[r][k] = 0.f;
+  }
+
+  // ---- state rows
+  if (state != nullptr) {
+    const int rows_per_split = (DEX + nsplit - 1) / nsplit;
+    const int d_begin = split * rows_per_split, d_end = min(DEX, d_begin + rows_per_split);
+    int D = d_begin + (tid >> 3);
+    int a = 0, b = 0;
+    if (D < DEX) exact_decode(D, &a, &b);
+    const T* sbase = state + (size_t)bh * DEX * HD;
+    const float* kbase = sok + (size_t)bh * DEX;
+    constexpr int UN = PR_DEC_UN;
+    for (; D < d_end; D += UN * ROWS_PER_ITER) {
+      uint4 v[UN];
+      float sk[UN];
+      int ra[UN], rb[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        const int Du = D + u * ROWS_PER_ITER;
+        ra[u] = a;
+        rb[u] = b;
+        if (Du < d_end) {
+          v[u] = __ldg(reinterpret_cast<const uint4*>(sbase + (size_t)Du * HD + sub * 8));
+          sk[u] = __ldg(kbase + Du);
+        }
+        b += ROWS_PER_ITER;
+        while (b >= HD && a < HD) {
+          b = b - HD + a + 1;
+          ++a;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        if (D + u * ROWS_PER_ITER >= d_end) break;
+        float x[8];
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 p2 = Pack2<T>::to_f32(w[k]);
+          x[2 * k] = p2.x;
+          x[2 * k + 1] = p2.y;
+        }
+#pragma unroll
+        for (int r = 0; r < RG; ++r) {
+          if (r < nr) {
+            const float phi = float(T(sq[r][min(ra[u], HD - 1)] * sq[r][min(rb[u], HD - 1)]));
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(phi, x[k], acc[r][k]);
+            accl[r] = fmaf(phi, sk[u], accl[r]);
+          }
+        }
+      }
+    }
+    // the eight lanes of a row hold the same normaliser term: keep one copy
+#pragma unroll
+    for (int r = 0; r < RG; ++r) accl[r] = (sub == 0) ? accl[r] : 0.f;
+  }
+
+  // ---- cached tokens, in blocks of BLK from the newest to the oldest
+  if (K != nullptr && t_end > t_begin) {
+    const float s2 = scale * scale;
+    const int slot = lane >> 3;
+    const T* kb = K + (size_t)batch * kv_bs + (size_t)head * HD + sub * 8;
+    const T* vb = V + (size_t)batch * kv_bs + (size_t)head * HD + sub * 8;
+    float q[RG][8];
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+      const float4 q0 = *reinterpret_cast<const float4*>(&sqr[r][sub * 8]);
+      const float4 q1 = *reinterpret_cast<const float4*>(&sqr[r][sub * 8 + 4]);
+      q[r][0] = q0.x; q[r][1] = q0.y; q[r][2] = q0.z; q[r][3] = q0.w;
+      q[r][4] = q1.x; q[r][5] = q1.y; q[r][6] = q1.z; q[r][7] = q1.w;
+    }
+    for (int blk_end = t_end; blk_end > t_begin; blk_end -= BLK) {
+      const int blk_lo = max(t_begin, blk_end - BLK);
+      const int n_blk = blk_end - blk_lo;
+      if (gated) {
+        // sfx[i] = sum of the gates after token blk_lo + i (up to the newest token of the cache)
+        const float* gp = log_g + (size_t)batch * g_bs + head;
+        float g4[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int i = 4 * tid + k;
+          g4[k] = i < n_blk ? gp[(size_t)(blk_lo + i) * h] : 0.f;
+        }
+        const float mine = g4[0] + g4[1] + g4[2] + g4[3];
+        // inclusive reverse scan of the per-thread totals over the block
+        float inc = mine;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const float o = __shfl_down_sync(0xffffffffu, inc, off);
+          if (lane + off < 32) inc += o;
+        }
+        if (lane == 0) wsum[warp][0] = inc;
+        __syncthreads();
+        float after = tail;  // everything after this thread's four tokens
+#pragma unroll
+        for (int w = 0; w < THREADS / 32; ++w) {
+          if (w > warp) after += wsum[w][0];
+        }
+        after += inc - mine;
+        float blk_total = 0.f;
+#pragma unroll
+        for (int w = 0; w < THREADS / 32; ++w) blk_total += wsum[w][0];
+        sfx[4 * tid + 3] = after;
+        sfx[4 * tid + 2] = after + g4[3];
+        sfx[4 * tid + 1] = after + g4[3] + g4[2];
+        sfx[4 * tid + 0] = after + g4[3] + g4[2] + g4[1];
+        tail += blk_total;
+        __syncthreads();
+      }
+      constexpr int UNT = 2;
+      // the trip count depends on the warp only: every lane takes part in the shuffles, lanes whose
+      // token lies outside the block contribute zero weight
+      for (int base = warp * 4; base < n_blk; base += (THREADS / 32) * 4 * UNT) {
+        uint4 kv[UNT], vv[UNT];
+        float sf[UNT];
+#pragma unroll
+        for (int u = 0; u < UNT; ++u) {
+          const int i = base + slot + (THREADS / 32) * 4 * u;
+          kv[u] = vv[u] = make_uint4(0, 0, 0, 0);
+          sf[u] = 0.f;
+          if (i < n_blk) {
+            const size_t j = (size_t)(blk_lo + i);
+            kv[u] = *reinterpret_cast<const uint4*>(kb + j * h * HD);
+            vv[u] = *reinterpret_cast<const uint4*>(vb + j * h * HD);
+            if (gated) sf[u] = sfx[i];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UNT; ++u) {
+          const int i = base + slot + (THREADS / 32) * 4 * u;
+          const uint32_t kw[4] = {kv[u].x, kv[u].y, kv[u].z, kv[u].w};
+          const uint32_t vw[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+          float kf[8], vf[8];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 p2 = Pack2<T>::to_f32(kw[k]);
+            kf[2 * k] = p2.x;
+            kf[2 * k + 1] = p2.y;
+            const float2 v2 = Pack2<T>::to_f32(vw[k]);
+            vf[2 * k] = v2.x;
+            vf[2 * k + 1] = v2.y;
+          }
+          const float gf = (i < n_blk) ? (gated ? s2 * __expf(sf[u]) : s2) : 0.f;
+#pragma unroll
+          for (int r = 0; r < RG; ++r) {
+            float sdot = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sdot = fmaf(kf[k], q[r][k], sdot);
+            sdot += __shfl_xor_sync(0xffffffffu, sdot, 1);
+            sdot += __shfl_xor_sync(0xffffffffu, sdot, 2);
+            sdot += __shfl_xor_sync(0xffffffffu, sdot, 4);
+            const float wgt = gf * sdot * sdot;
+            if (sub == 0) accl[r] += wgt;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(wgt, vf[k], acc[r][k]);
+          }
+        }
+      }
+      if (gated) __syncthreads();  // sfx is rewritten by the next block
+    }
+  }
+
+  // ---- reduce: the four rows / tokens a warp covers per pass (lanes with equal sub), then the warps
+#pragma unroll
+  for (int r = 0; r < RG; ++r) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float t = acc[r][k];
+      t += __shfl_xor_sync(0xffffffffu, t, 8);
+      t += __shfl_xor_sync(0xffffffffu, t, 16);
+      acc[r][k] = t;
+    }
+    float t = accl[r];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+    accl[r] = t;
+  }
+  if (lane < 8) {
+#pragma unroll
+    for (int r = 0; r < RG; ++r)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) red_y[warp][r][lane * 8 + k] = acc[r][k];
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < RG; ++r) red_l[warp][r] = accl[r];
+  }
+  __syncthreads();
+  for (int i = tid; i < nr * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    float yt = 0.f, lt = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) {
+      yt += red_y[w][r][e];
+      lt += red_l[w][r];
+    }
+    const size_t row = (size_t)batch * hq + head * ratio + r0 + r;
+    if (nsplit == 1) {
+      O[row * HD + e] = T(yt * safe_recip(lt));
+    } else {
+      part_y[(row * nsplit + split) * HD + e] = yt;
+      if (e == 0) part_l[row * nsplit + split] = lt;
+    }
+  }
+}
+
+// Pure-recurrent decode step: the state is advanced by one token and read in the same pass,
+//     S' = e^g S + phi_K(k) v^T,   z' = e^g z + phi_K(k),   y = phi(s q)^T S' / phi(s q) . z'
+// which is the reference's inference step with switch_over_seq_len = 1 (one cached token, then
+// compression, retention/power_retention_maker.py:354-382) without the cache round trip.  Every
+// state row is read once and written once; rows are owned by threads exactly as in the read-only
+// step, so with one group of query heads per kv head the update may be done in place.
+template <typename T, int RG>
+__global__ void __launch_bounds__(dec::THREADS, RG == 1 ? 4 : 2)
+decode_recurrent_kernel(const T* __restrict__ Q, long long q_bs, const T* __restrict__ Kt, const T* __restrict__ Vt,
+                        long long kv_bs, const float* __restrict__ log_g, long long g_bs, const T* state,
+                        const float* sok, T* new_state, float* new_sok, float scale, int h, int hq, int nsplit,
+                        float* __restrict__ part_y, float* __restrict__ part_l, T* __restrict__ O) {
+  using namespace dec;
+  __shared__ float sq[RG][HD];
+  __shared__ float skv[2][HD];  // the token's key and value
+  __shared__ float red_y[THREADS / 32][RG][HD];
+  __shared__ float red_l[THREADS / 32][RG];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int bh = blockIdx.x, split = blockIdx.y, grp = blockIdx.z;
+  const int batch = bh / h, head = bh % h;
+  const int ratio = hq / h;
+  const int r0 = grp * RG, nr = min(RG, ratio - r0);
+  const bool writer = (grp == 0);  // one group of query heads writes the new state
+  const float decay = log_g ? __expf(log_g[(size_t)batch * g_bs + head]) : 1.f;
+  for (int i = tid; i < RG * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    float q = 0.f;
+    if (r < nr) q = float(Q[(size_t)batch * q_bs + (size_t)(head * ratio + r0 + r) * HD + e]);
+    sq[r][e] = float(T(q * scale));
+  }
+  if (tid < 2 * HD) {
+    const T* src = (tid < HD ? Kt : Vt) + (size_t)batch * kv_bs + (size_t)head * HD + (tid & (HD - 1));
+    skv[tid / HD][tid & (HD - 1)] = float(*src);
+  }
+  __syncthreads();
+
+  const int rows_per_split = (DEX + nsplit - 1) / nsplit;
+  const int d_begin = split * rows_per_split, d_end = min(DEX, d_begin + rows_per_split);
+  const int sub = tid & 7;
+  int D = d_begin + (tid >> 3);
+  int a = 0, b = 0;
+  if (D < DEX) exact_decode(D, &a, &b);
+  float vt[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) vt[k] = skv[1][sub * 8 + k];
+  float acc[RG][8];
+  float accl[RG];
+#pragma unroll
+  for (int r = 0; r < RG; ++r) {
+    accl[r] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[r][k] = 0.f;
+  }
+  const T* sbase = state + (size_t)bh * DEX * HD;
+  const float* kbase = sok + (size_t)bh * DEX;
+  T* obase = new_state + (size_t)bh * DEX * HD;
+  float* okbase = new_sok + (size_t)bh * DEX;
+  constexpr int UN = PR_DEC_UN;
+  for (; D < d_end; D += UN * ROWS_PER_ITER) {
+    uint4 v[UN];
+    float sk[UN];
+    int ra[UN], rb[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int Du = D + u * ROWS_PER_ITER;
+      ra[u] = a;
+      rb[u] = b;
+      if (Du < d_end) {
+        v[u] = *reinterpret_cast<const uint4*>(sbase + (size_t)Du * HD + sub * 8);
+        sk[u] = kbase[Du];
+      }
+      b += ROWS_PER_ITER;
+      while (b >= HD && a < HD) {
+        b = b - HD + a + 1;
+        ++a;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int Du = D + u * ROWS_PER_ITER;
+      if (Du >= d_end) break;
+      const int ia = min(ra[u], HD - 1), ib = min(rb[u], HD - 1);
+      // key-side expansion entry of the new token, rounded like the inputs, with the pair weight
+      const float phik = float(T(skv[0][ia] * skv[0][ib])) * (ia == ib ? 1.f : 2.f);
+      float x[8];
+      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 p2 = Pack2<T>::to_f32(w[k]);
+        // the reference rounds state * decay to the state's dtype before adding the update (:374-382)
+        const float2 od = Pack2<T>::to_f32(Pack2<T>::from_f32(p2.x * decay, p2.y * decay));
+        x[2 * k] = fmaf(phik, vt[2 * k], od.x);
+        x[2 * k + 1] = fmaf(phik, vt[2 * k + 1], od.y);
+        ow[k] = Pack2<T>::from_f32(x[2 * k], x[2 * k + 1]);
+      }
+      const float skn = fmaf(sk[u], decay, phik);
+      if (writer) {
+        *reinterpret_cast<uint4*>(obase + (size_t)Du * HD + sub * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        if (sub == 0) okbase[Du] = skn;
+      }
+#pragma unroll
+      for (int r = 0; r < RG; ++r) {
+        if (r < nr) {
+          const float phi = float(T(sq[r][ia] * sq[r][ib]));
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(phi, x[k], acc[r][k]);
+          accl[r] = fmaf(phi, skn, accl[r]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RG; ++r) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float t = acc[r][k];
+      t += __shfl_xor_sync(0xffffffffu, t, 8);
+      t += __shfl_xor_sync(0xffffffffu, t, 16);
+      acc[r][k] = t;
+    }
+    float t = (sub == 0) ? accl[r] : 0.f;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+    accl[r] = t;
+  }
+  if (lane < 8) {
+#pragma unroll
+    for (int r = 0; r < RG; ++r)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) red_y[warp][r][lane * 8 + k] = acc[r][k];
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < RG; ++r) red_l[warp][r] = accl[r];
+  }
+  __syncthreads();
+  for (int i = tid; i < nr * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    float yt = 0.f, lt = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) {
+      yt += red_y[w][r][e];
+      lt += red_l[w][r];
+    }
+    const size_t row = (size_t)batch * hq + head * ratio + r0 + r;
+    if (nsplit == 1) {
+      O[row * HD + e] = T(yt * safe_recip(lt));
+    } else {
+      part_y[(row * nsplit + split) * HD + e] = yt;
+      if (e == 0) part_l[row * nsplit + split] = lt;
+    }
+  }
+}
+
+// Sums the partial results of a split decode step, normalises and writes the output.
+template <typename T>
+__global__ void __launch_bounds__(dec::HD)
+decode_merge_kernel(const float* __restrict__ part_y, const float* __restrict__ part_l, int nsplit, T* __restrict__ O) {
+  const size_t row = blockIdx.x;
+  const int e = threadIdx.x;
+  float yt = 0.f, lt = 0.f;
+  for (int sp = 0; sp < nsplit; ++sp) {
+    yt += part_y[(row * nsplit + sp) * dec::HD + e];
+    lt += part_l[row * nsplit + sp];
+  }
+  O[row * dec::HD + e] = T(yt * safe_recip(lt));
+}
+
 // Cumulative log gates of the cached tokens, a[b, tk, h] (dense) from log_g whose batch entries are
 // g_bs floats apart (a cache kept as a slice of a longer preallocated tensor).  One CTA per
 // (batch, head); tk is small (below the switch-over length), so one block-wide scan per 256 tokens.
@@ -355,6 +807,57 @@ __global__ void state_merge_kernel(const T* __restrict__ state, const float* __r
   }
 }
 
+// Inverse of the switch-over conversion: a state in the exact layout (as inference keeps it) into
+// the chunk-state layout the training kernels read, as 16-bit rows (a state for pr_chunk_out) and /
+// or as an fp32 carry for the scans; sum_of_keys into the Gram matrix (fp32 and / or hi + lo
+// 16-bit halves).  Pairs stored twice in the chunk layout (both indices in one 16-block) get half
+// of the exact entry each.
+template <typename T>
+__global__ void state_to_chunk_kernel(const T* __restrict__ state, const float* __restrict__ sok,
+                                      T* __restrict__ out16, float* __restrict__ out32, float* __restrict__ gram,
+                                      T* __restrict__ ghi, T* __restrict__ glo, int bh_total) {
+  constexpr int HD = dec::HD, DEX = dec::DEX, DR = ref_dim(HD);
+  const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 elements
+  if (gid < (size_t)bh_total * HD * HD && (gram || ghi)) {
+    const int bh = (int)(gid / (HD * HD)), a = (int)(gid / HD) % HD, b = (int)(gid % HD);
+    const int lo = min(a, b), hi = max(a, b);
+    const float v = sok[(size_t)bh * DEX + lo * HD - lo * (lo - 1) / 2 + (hi - lo)] * (a == b ? 1.f : 0.5f);
+    if (gram) gram[gid] = v;
+    if (ghi) {
+      const T hv = T(v);
+      ghi[gid] = hv;
+      glo[gid] = T(v - float(hv));
+    }
+  }
+  if (gid >= (size_t)bh_total * DR * 8) return;
+  const int sub = (int)(gid & 7);
+  const size_t rowg = gid >> 3;
+  const int r = (int)(rowg % DR);
+  const int bh = (int)(rowg / DR);
+  int a, b;
+  ref_decode(r, &a, &b);
+  const int lo = min(a, b), hi = max(a, b);
+  const float coef = (a != b && (a >> 4) == (b >> 4)) ? 0.5f : 1.f;
+  const uint4 sv =
+      *reinterpret_cast<const uint4*>(state + ((size_t)bh * DEX + lo * HD - lo * (lo - 1) / 2 + (hi - lo)) * HD + sub * 8);
+  const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+  float x[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 p2 = Pack2<T>::to_f32(sw[k]);
+    x[2 * k] = p2.x * coef;
+    x[2 * k + 1] = p2.y * coef;
+  }
+  const size_t o = ((size_t)bh * DR + r) * HD + sub * 8;
+  if (out16)
+    *reinterpret_cast<uint4*>(out16 + o) = make_uint4(Pack2<T>::from_f32(x[0], x[1]), Pack2<T>::from_f32(x[2], x[3]),
+                                                      Pack2<T>::from_f32(x[4], x[5]), Pack2<T>::from_f32(x[6], x[7]));
+  if (out32) {
+    *reinterpret_cast<float4*>(out32 + o) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(out32 + o + 4) = make_float4(x[4], x[5], x[6], x[7]);
+  }
+}
+
 }  // namespace pr
 
 #ifndef PR_DEC_NSPLIT
@@ -375,6 +878,12 @@ static int decode_split(int b, int h, int hq) {
   return ctas >= 384 ? 1 : (ctas >= 160 ? 2 : PR_DEC_NSPLIT);
 }
 }  // namespace pr
+
+// Parts a decode step of this shape is split into (1: no partial-sum workspace is needed).
+extern "C" int pr_decode_split(int b, int h, int hq) {
+  if (b <= 0 || h <= 0 || hq <= 0 || hq % h != 0) return pr::fail(PR_ERR_BAD_ARG, "bad sizes b=%d h=%d hq=%d", b, h, hq);
+  return pr::decode_split(b, h, hq);
+}
 
 extern "C" int pr_decode_state(int dtype, int b, int h, int hq, int d, const void* Q, const void* state,
                                const float* sum_of_keys, const float* a_last, float scale, float* part_y,
@@ -494,9 +1003,58 @@ extern "C" int pr_state_merge(int dtype, int b, int h, int d, const void* state,
   return PR_OK;
 }
 
-// One decode step in a single call: cumulative gates of the cached tokens, state read-out,
-// attention over the cache, merge.  a_scratch [b,tk,h] fp32 (only when log_g is given),
-// part_y / part_l as for pr_decode_state (only when a state is given).
+// Exact-layout state [b,h,2080,d] and sum_of_keys [b,h,2080] -> chunk-state layout: out16 [b,h,D2,d]
+// (16-bit, a state pr_chunk_out can read), out32 (the same in fp32: a carry for pr_discumsum_fwd), gram
+// [b,h,d,d] fp32 (carry for pr_gram_scan_fwd), gram_hi / gram_lo (16-bit halves for pr_chunk_out).  Any output
+// may be NULL.  The layout change of layout.exact_to_reference as one kernel.
+extern "C" int pr_state_to_chunk_layout(int dtype, int b, int h, int d, const void* state, const float* sum_of_keys,
+                                        void* out16, float* out32, float* gram, void* gram_hi, void* gram_lo,
+                                        int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && h > 0 && state && sum_of_keys, PR_ERR_BAD_ARG, "bad sizes or null inputs");
+  PR_REQUIRE(aligned16(state) && aligned16(out16) && aligned16(out32), PR_ERR_BAD_ARG, "misaligned pointer");
+  PR_REQUIRE((gram_hi == nullptr) == (gram_lo == nullptr), PR_ERR_BAD_ARG, "gram_hi and gram_lo come together");
+  PR_CUDA(cudaSetDevice(device));
+  const size_t threads = (size_t)b * h * ref_dim(d) * 8;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PR_BF16)
+    state_to_chunk_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(state), sum_of_keys, static_cast<__nv_bfloat16*>(out16), out32, gram,
+        static_cast<__nv_bfloat16*>(gram_hi), static_cast<__nv_bfloat16*>(gram_lo), b * h);
+  else if (dtype == PR_FP16)
+    state_to_chunk_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(state), sum_of_keys,
+                                                      static_cast<__half*>(out16), out32, gram,
+                                                      static_cast<__half*>(gram_hi), static_cast<__half*>(gram_lo), b * h);
+  else
+    return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+// Cumulative log gates of whole sequences, a[b, t, h] = cumsum_t log_g (the reference's
+// log_G.cumsum(1), retention/power_retention_maker.py:129,347), for any t: one CTA per (batch, head)
+// walks the sequence in blocks of 256 tokens.  Serves the state-free quadratic branch and long caches,
+// where the chunk-local gate pass (pr_gate_prep) would not fit a chunk in shared memory.
+extern "C" int pr_gate_cumsum(int b, int t, int h, const float* log_g, long long g_bstride, float* a_out, int device,
+                              void* stream) {
+  using namespace pr;
+  PR_REQUIRE(b > 0 && t > 0 && h > 0 && g_bstride >= (long long)t * h, PR_ERR_BAD_ARG, "bad sizes b=%d t=%d h=%d", b,
+             t, h);
+  PR_REQUIRE(log_g && a_out, PR_ERR_BAD_ARG, "null pointer");
+  PR_CUDA(cudaSetDevice(device));
+  decode_gate_cumsum_kernel<<<b * h, 256, 0, static_cast<cudaStream_t>(stream)>>>(log_g, g_bstride, a_out, t, h);
+  PR_CUDA(cudaGetLastError());
+  return PR_OK;
+}
+
+// One decode step in a single call (one kernel; a second, tiny one when the work of a (batch, head)
+// pair is split over several CTAs because there are too few pairs to fill the GPU): gate sums of the
+// cached tokens, state read-out, attention over the cache, merge, normalisation.
+// part_y / part_l as for pr_decode_state; they are touched only when the step is split
+// (b * h * ceil(ratio / 4) < 384 CTAs).  a_scratch is not used any more (the gate sums are formed
+// inside the kernel) and may be NULL; the argument stays so that existing callers keep working.
 extern "C" int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K,
                               const void* V, const float* log_g, const void* state, const float* sum_of_keys,
                               float scale, float* a_scratch, float* part_y, float* part_l, void* O, int device,
@@ -515,60 +1073,129 @@ extern "C" int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, i
                                       const float* sum_of_keys, float scale, float* a_scratch, float* part_y,
                                       float* part_l, void* O, int device, void* stream) {
   using namespace pr;
+  (void)a_scratch;
   const bool has_cache = (K != nullptr && V != nullptr && tk > 0);
   const bool gated = has_cache && log_g != nullptr;
+  PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0 && tk >= 0, PR_ERR_BAD_ARG, "bad sizes");
-  PR_REQUIRE(!gated || a_scratch != nullptr, PR_ERR_BAD_ARG, "gated decode needs a_scratch");
-  PR_REQUIRE(state == nullptr || (part_y != nullptr && part_l != nullptr && sum_of_keys != nullptr), PR_ERR_BAD_ARG,
-             "a state needs sum_of_keys and the partial-sum workspace");
+  PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_REQUIRE(state != nullptr || has_cache, PR_ERR_BAD_ARG, "neither a state nor cached tokens");
+  PR_REQUIRE(state == nullptr || sum_of_keys != nullptr, PR_ERR_BAD_ARG, "a state needs its sum_of_keys");
+  PR_REQUIRE(Q && O && aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(state), PR_ERR_BAD_ARG,
+             "null or misaligned pointer");
   PR_REQUIRE(q_bstride >= (long long)hq * d && (!has_cache || kv_bstride >= (long long)tk * h * d) &&
                  (!gated || g_bstride >= (long long)tk * h),
              PR_ERR_BAD_ARG, "a batch stride is smaller than one batch entry");
-  int rc = PR_OK;
-  if (gated) {
-    PR_CUDA(cudaSetDevice(device));
-    decode_gate_cumsum_kernel<<<b * h, 256, 0, static_cast<cudaStream_t>(stream)>>>(log_g, g_bstride, a_scratch, tk, h);
+  PR_REQUIRE(q_bstride % 8 == 0 && (!has_cache || kv_bstride % 8 == 0), PR_ERR_BAD_ARG,
+             "the batch strides of Q, K, V must be multiples of 8 elements");
+  const int nsplit = decode_split(b, h, hq);
+  PR_REQUIRE(nsplit == 1 || (part_y != nullptr && part_l != nullptr), PR_ERR_BAD_ARG,
+             "this problem is split %d ways and needs the partial-sum workspace", nsplit);
+  PR_CUDA(cudaSetDevice(device));
+  const int ratio = hq / h;
+  const int rg = ratio == 1 ? 1 : dec::RG_MAX;
+  dim3 grid(b * h, nsplit, (ratio + rg - 1) / rg);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PR_LAUNCH_FUSED(TT, RGV)                                                                                      \
+  decode_fused_kernel<TT, RGV><<<grid, dec::THREADS, 0, s>>>(                                                          \
+      static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(has_cache ? K : nullptr),                          \
+      static_cast<const TT*>(has_cache ? V : nullptr), kv_bstride, gated ? log_g : nullptr, g_bstride,                \
+      static_cast<const TT*>(state), sum_of_keys, scale, has_cache ? tk : 0, h, hq, nsplit, part_y, part_l,            \
+      static_cast<TT*>(O))
+  if (dtype == PR_BF16) {
+    if (rg == 1) PR_LAUNCH_FUSED(__nv_bfloat16, 1); else PR_LAUNCH_FUSED(__nv_bfloat16, 4);
+  } else {
+    if (rg == 1) PR_LAUNCH_FUSED(__half, 1); else PR_LAUNCH_FUSED(__half, 4);
+  }
+#undef PR_LAUNCH_FUSED
+  PR_CUDA(cudaGetLastError());
+  if (nsplit > 1) {
+    if (dtype == PR_BF16)
+      decode_merge_kernel<__nv_bfloat16><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__nv_bfloat16*>(O));
+    else
+      decode_merge_kernel<__half><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__half*>(O));
     PR_CUDA(cudaGetLastError());
   }
-  if (state != nullptr) {
-    // a_last[b,h] is the last row of a_scratch: element (batch, tk-1, head), batch entries tk*h apart
-    rc = launch_decode_state(dtype, b, h, hq, d, Q, q_bstride, state, sum_of_keys,
-                             gated ? a_scratch + (size_t)(tk - 1) * h : nullptr, gated ? (long long)tk * h : 0, scale,
-                             part_y, part_l, device, stream);
-    if (rc) return rc;
+  return PR_OK;
+}
+
+// Pure-recurrent decode step (see decode_recurrent_kernel): q [b,1,hq,d], k, v [b,1,h,d] (batch
+// entries q_bstride / kv_bstride elements apart), log_g [b,1,h] (g_bstride floats apart) or NULL.
+// new_state / new_sum_of_keys may alias state / sum_of_keys when hq / h <= 4 (each state row is then
+// read and written by one thread only); with more query heads per kv head they must be other buffers.
+extern "C" int pr_decode_recurrent(int dtype, int b, int h, int hq, int d, const void* Q, long long q_bstride,
+                                   const void* K, const void* V, long long kv_bstride, const float* log_g,
+                                   long long g_bstride, const void* state, const float* sum_of_keys, void* new_state,
+                                   float* new_sum_of_keys, float scale, float* part_y, float* part_l, void* O,
+                                   int device, void* stream) {
+  using namespace pr;
+  PR_REQUIRE(d == dec::HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
+  PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0, PR_ERR_BAD_ARG, "bad sizes b=%d h=%d hq=%d", b, h, hq);
+  PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_REQUIRE(Q && K && V && state && sum_of_keys && new_state && new_sum_of_keys && O, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(Q) && aligned16(state) && aligned16(new_state), PR_ERR_BAD_ARG, "misaligned pointer");
+  PR_REQUIRE(q_bstride >= (long long)hq * d && kv_bstride >= (long long)h * d && (!log_g || g_bstride >= h),
+             PR_ERR_BAD_ARG, "a batch stride is smaller than one batch entry");
+  const int ratio = hq / h;
+  const int rg = ratio == 1 ? 1 : dec::RG_MAX;
+  const int groups = (ratio + rg - 1) / rg;
+  PR_REQUIRE(groups == 1 || (new_state != state && new_sum_of_keys != sum_of_keys), PR_ERR_BAD_ARG,
+             "in-place update needs hq / h <= %d", dec::RG_MAX);
+  const int nsplit = decode_split(b, h, hq);
+  PR_REQUIRE(nsplit == 1 || (part_y != nullptr && part_l != nullptr), PR_ERR_BAD_ARG,
+             "this problem is split %d ways and needs the partial-sum workspace", nsplit);
+  PR_CUDA(cudaSetDevice(device));
+  dim3 grid(b * h, nsplit, groups);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PR_LAUNCH_REC(TT, RGV)                                                                                        \
+  decode_recurrent_kernel<TT, RGV><<<grid, dec::THREADS, 0, s>>>(                                                      \
+      static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(K), static_cast<const TT*>(V), kv_bstride, log_g,  \
+      g_bstride, static_cast<const TT*>(state), sum_of_keys, static_cast<TT*>(new_state), new_sum_of_keys, scale, h,  \
+      hq, nsplit, part_y, part_l, static_cast<TT*>(O))
+  if (dtype == PR_BF16) {
+    if (rg == 1) PR_LAUNCH_REC(__nv_bfloat16, 1); else PR_LAUNCH_REC(__nv_bfloat16, 4);
+  } else {
+    if (rg == 1) PR_LAUNCH_REC(__half, 1); else PR_LAUNCH_REC(__half, 4);
   }
-  return launch_decode_finish(dtype, b, has_cache ? tk : 0, h, hq, d, Q, q_bstride, has_cache ? K : nullptr,
-                              has_cache ? V : nullptr, kv_bstride, gated ? a_scratch : nullptr, scale,
-                              state ? part_y : nullptr, state ? part_l : nullptr, O, device, stream);
+#undef PR_LAUNCH_REC
+  PR_CUDA(cudaGetLastError());
+  if (nsplit > 1) {
+    if (dtype == PR_BF16)
+      decode_merge_kernel<__nv_bfloat16><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__nv_bfloat16*>(O));
+    else
+      decode_merge_kernel<__half><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__half*>(O));
+    PR_CUDA(cudaGetLastError());
+  }
+  return PR_OK;
 }
 
 // ---------------------------------------------------------------------------------------
 // Decode step for callers that must not allocate.
 //
-// pr_decode_step needs two pieces of scratch memory from its caller: the cumulative gates
-// of the cached tokens and the partial sums of the split state read.  Some hosts of this
-// library cannot provide them: a serving loop that froze its memory pool after start-up, a
-// plugin running inside another runtime's stream callback (no CUDA API calls allowed there
-// beyond launches), or a process whose device allocator belongs to a different component and
-// hands out nothing at request time.  For them the same
-// step is offered with its scratch in the fixed device array below, which every GPU that
-// loads this library carries until the process exits (kStaticScratchBytes, about 2.4 MB).
+// pr_decode_step needs scratch memory from its caller whenever the step is split over several
+// CTAs per (batch, head) pair: the partial sums of the parts.  Some hosts of this library
+// cannot provide it: a serving loop that froze its memory pool after start-up, or a process
+// whose device allocator belongs to a different component and hands out nothing at request
+// time.  (The entry point still makes CUDA runtime calls - set device, launches, a one-time
+// symbol lookup - so it is not for host callbacks enqueued on a stream, which may make none.)
+// For them the same step is offered with its scratch in the fixed device array below, which
+// every GPU that loads this library carries until the process exits (kStaticScratchBytes,
+// about 1.3 MB).
 //
-// Limits: batch * query_heads <= kStaticMaxRows and batch * cached_tokens * kv_heads <=
-// kStaticMaxGates; larger problems are refused with PR_ERR_BAD_ARG.  All calls on a device
-// share the one array: two calls whose kernels overlap on the GPU (different streams, or
-// different threads) race on it, so keep such calls on one stream.  Nothing in the array has
-// to start at zero - each call overwrites every word it later reads - so stale contents of the
-// previous call are harmless.  The device address of the array is looked up the first time
-// the entry point runs on a device; make that first call outside any stream capture.
+// Limit: batch * query_heads <= kStaticMaxRows; larger problems are refused with
+// PR_ERR_BAD_ARG.  All calls on a device share the one array: two calls whose kernels overlap
+// on the GPU (different streams, or different threads) race on it, so keep such calls on one
+// stream.  Nothing in the array has to start at zero - each call overwrites every word it later
+// reads - so stale contents of the previous call are harmless.  The device address of the array
+// is looked up the first time the entry point runs on a device; make that first call outside
+// any stream capture.
 namespace pr {
 namespace {
-constexpr int kStaticMaxRows = 1024;                                       // batch * query heads
-constexpr int kStaticMaxGates = 1 << 18;                                   // batch * cached tokens * kv heads
-constexpr int kStaticSplit = PR_DEC_NSPLIT;                                            // == pr_decode_nsplit()
+constexpr int kStaticMaxRows = 1024;                                              // batch * query heads
+constexpr int kStaticSplit = PR_DEC_NSPLIT;                                       // == pr_decode_nsplit()
 constexpr size_t kStaticPartY = (size_t)kStaticMaxRows * kStaticSplit * dec::HD;  // floats
 constexpr size_t kStaticPartL = (size_t)kStaticMaxRows * kStaticSplit;
-constexpr size_t kStaticFloats = kStaticPartY + kStaticPartL + kStaticMaxGates;
+constexpr size_t kStaticFloats = kStaticPartY + kStaticPartL;
 constexpr size_t kStaticScratchBytes = kStaticFloats * sizeof(float);
 
 static __device__ __align__(256) float g_decode_scratch[kStaticFloats];
@@ -603,16 +1230,13 @@ extern "C" int pr_decode_step_static(int dtype, int b, int tk, int h, int hq, in
   PR_REQUIRE((long long)b * hq <= kStaticMaxRows, PR_ERR_BAD_ARG,
              "batch * query heads = %lld exceeds the static scratch limit of %d rows", (long long)b * hq,
              kStaticMaxRows);
-  PR_REQUIRE((long long)b * tk * h <= kStaticMaxGates, PR_ERR_BAD_ARG,
-             "batch * cached tokens * kv heads = %lld exceeds the static scratch limit of %d gates",
-             (long long)b * tk * h, kStaticMaxGates);
+  PR_REQUIRE(device >= 0 && device < kStaticMaxDevices, PR_ERR_BAD_ARG, "device ordinal %d out of range", device);
   PR_CUDA(cudaSetDevice(device));
   float* scratch = nullptr;
   int rc = static_scratch(device, &scratch);
   if (rc) return rc;
   float* part_y = scratch;
   float* part_l = scratch + kStaticPartY;
-  float* gates = scratch + kStaticPartY + kStaticPartL;
-  return pr_decode_step(dtype, b, tk, h, hq, d, Q, K, V, log_g, state, sum_of_keys, scale, gates, part_y, part_l, O,
+  return pr_decode_step(dtype, b, tk, h, hq, d, Q, K, V, log_g, state, sum_of_keys, scale, nullptr, part_y, part_l, O,
                         device, stream);
 }

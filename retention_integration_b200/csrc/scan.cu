@@ -42,7 +42,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // X, Y: [b, n(_out), h, E]; A: [b, n, h]; carries: [b, h, E] fp32
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
-scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restrict__ A,
+scan_fwd_kernel(const T* X, T* Y, const float* __restrict__ A,  // X and Y may be the same buffer: no __restrict__
                 const float* __restrict__ carry_in, float* __restrict__ carry_out, int n, int n_out, int h,
                 size_t E) {
   const size_t e0 = ((size_t)blockIdx.x * kScanThreads + threadIdx.x) * 8;
@@ -96,7 +96,7 @@ scan_fwd_kernel(const T* __restrict__ X, T* __restrict__ Y, const float* __restr
 // row_weights: apply the key-side weight (1 or 2) of expanded row (e / row_len) to dX.
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
-scan_bwd_kernel(const T* __restrict__ dY, const T* __restrict__ Y, T* __restrict__ dX, const float* __restrict__ A,
+scan_bwd_kernel(const T* dY, const T* __restrict__ Y, T* dX, const float* __restrict__ A,  // dY may alias dX
                 const float* __restrict__ carry_in, float* __restrict__ carry_out, float* __restrict__ dA_part, int n,
                 int h, size_t E, int row_len, int row_weights) {
   const size_t e0 = ((size_t)blockIdx.x * kScanThreads + threadIdx.x) * 8;

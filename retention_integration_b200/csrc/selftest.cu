@@ -194,317 +194,48 @@ extern "C" int pr_selftest_umma(int variant, int dtype, int n, int k, const void
                           : launch_selftest<__half>(variant, n, k, a, b, out, status, s);
 }
 
-// Micro-benchmark: tensor-memory read bandwidth.  `nwarps` warps (4, 8 or 16) each issue
-// `iters` loads of 32 lanes x 32 columns from an allocated region; returns SM clock cycles.
+// Self-test of the give-up path of the bounded waits.  One CTA allocates tensor memory and
+// waits on an mbarrier that nothing ever arrives at; the wait budget is `budget_us`
+// microseconds instead of the library's two seconds.  Every warp gives up on its own, the
+// CTA meets at its teardown barrier, writes ST_TIMEOUT to the status word, releases its
+// tensor memory and returns: no trap, no unbounded spin, and the context stays usable.
 namespace pr {
-// mode 0: x32 load then wait; 1: two x32 loads then one wait; 2: x16 loads; 3: x8 loads
-__global__ void tmem_bw_kernel(int iters, int mode, long long* cycles, float* sink) {
-  __shared__ uint32_t tmem_base_s;
-  const int warp = threadIdx.x >> 5;
-  if (warp == 0) {
-    tmem_alloc(&tmem_base_s, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_base_s + ((uint32_t)((warp & 3) * 32) << 16);
-  uint32_t v[64];
-  float acc = 0.f;
-  __syncthreads();
-  const long long t0 = clock64();
-  if (mode == 0) {
-    for (int it = 0; it < iters; ++it) {
-      tmem_ld32(tmem + ((it * 32) & 511), v);
-      tmem_wait_ld();
-      acc += __uint_as_float(v[it & 31]);
-    }
-  } else if (mode == 1) {
-    for (int it = 0; it < iters; it += 2) {
-      tmem_ld32(tmem + ((it * 32) & 511), v);
-      tmem_ld32(tmem + ((it * 32 + 32) & 511), v + 32);
-      tmem_wait_ld();
-      acc += __uint_as_float(v[it & 63]);
-    }
-  } else if (mode == 2) {
-    for (int it = 0; it < iters; ++it) {
-      tmem_ld16(tmem + ((it * 32) & 511), v);
-      tmem_ld16(tmem + ((it * 32 + 16) & 511), v + 16);
-      tmem_wait_ld();
-      acc += __uint_as_float(v[it & 31]);
-    }
-  } else {
-    for (int it = 0; it < iters; ++it) {
-      uint32_t w[8];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        tmem_ld8(tmem + ((it * 32 + 8 * k) & 511), w);
-        v[8 * k] = w[0] ^ w[7];
-      }
-      tmem_wait_ld();
-      acc += __uint_as_float(v[(it & 3) * 8]);
-    }
-  }
-  __syncthreads();
-  const long long t1 = clock64();
-  if (threadIdx.x == 0) cycles[blockIdx.x] = t1 - t0;
-  if (acc == 123.456f) sink[0] = acc;
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
-}
-}  // namespace pr
-
-namespace pr {
-// Micro-benchmark: issue rate of tcgen05.mma for the operand shapes the kernels use.
-// mode 0: A,B in smem, N=128 (K-major); 1: A,B in smem, N=64; 2: A in TMEM, B MN-major smem, N=64;
-// 3: A in TMEM, B MN-major, N=128 (two 64-wide blocks).  `reps` groups of four K=16 steps.
-__global__ void mma_rate_kernel(int reps, int mode, long long* cycles) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar;
+__global__ void __launch_bounds__(128) selftest_timeout_kernel(unsigned long long budget_ns, int* status, int* gave_up) {
+  __shared__ uint64_t never;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
-  for (int i = tid; i < 49152 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(sm)[i] = 0;
   if (tid == 0) {
     abort_flag = 0;
-    mbar_init(&bar, 1);
+    mbar_init(&never, 1);
     fence_mbar_init();
   }
   if (warp == 0) {
-    tmem_alloc(&tmem_base_s, 512);
+    tmem_alloc(&tmem_base_s, 32);
     tmem_relinquish();
   }
-  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (tid == 0) {
-    const uint32_t a_addr = smem_u32(sm), b_addr = smem_u32(sm + 16384), tmem = tmem_base_s;
-    // modes 4-7 repeat 0-3 with two accumulators used alternately; mode 8: smem x smem, N=256
-    const int alt = (mode >= 4 && mode <= 7) ? 1 : 0;
-    const int m4 = mode & 3;
-    const int n = mode == 8 ? 256 : ((m4 == 0 || m4 == 3) ? 128 : 64);
-    const bool ts = mode != 8 && m4 >= 2;
-    const uint32_t idesc = umma_idesc(128, n, true, false, ts);
-    const long long t0 = clock64();
-    for (int r = 0; r < reps; ++r) {
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint32_t dcol = tmem + (alt ? (ks & 1) * 128 : 0);
-        if (ts)
-          umma_ts(dcol, tmem + 256 + ks * 8, umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc, 1u);
-        else
-          umma_ss(dcol, umma_desc_sw128(a_addr + ks * 32, 16, 1024), umma_desc_sw128(b_addr + ks * 32, 16, 1024),
-                  idesc, 1u);
-      }
-    }
-    umma_commit(&bar);
-    mbar_wait(&bar, 0, &abort_flag);
-    cycles[0] = clock64() - t0;
-  }
+  const bool ok = mbar_wait_for(&never, 0, &abort_flag, budget_ns);
+  if (!ok) atomicAdd(gave_up, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
+  if (tid == 0 && abort_flag) *status = ST_TIMEOUT;
+  if (warp == 0) tmem_dealloc(tmem_base_s, 32);
 }
 }  // namespace pr
 
-extern "C" int pr_selftest_mma_rate(int reps, int mode, long long* cycles, int device, void* stream) {
+extern "C" int pr_selftest_timeout(int budget_us, int* gave_up, int device, void* stream) {
   using namespace pr;
-  PR_REQUIRE(reps > 0 && mode >= 0 && mode <= 8 && cycles, PR_ERR_BAD_ARG, "bad arguments");
+  PR_REQUIRE(budget_us > 0 && budget_us <= 100000, PR_ERR_BAD_ARG, "budget of %d us not in (0, 100000]", budget_us);
+  PR_REQUIRE(gave_up != nullptr, PR_ERR_BAD_ARG, "gave_up is null");
   PR_CUDA(cudaSetDevice(device));
-  PR_CUDA(cudaFuncSetAttribute(mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 51200));
-  mma_rate_kernel<<<1, 128, 51200, static_cast<cudaStream_t>(stream)>>>(reps, mode, cycles);
-  PR_CUDA(cudaGetLastError());
-  return PR_OK;
-}
-
-namespace pr {
-// Micro-benchmark: round trip of tcgen05.ld (32 lanes x 32 columns, then wait) as seen by
-// `nwarps` reader warps, alone or while one more thread keeps the tensor core busy with
-// smem x smem products (M = 128, N = mma_n, K = 16) into other columns.  cycles[0] = SM clocks
-// the slowest reader took for `iters` loads, cycles[1] = clocks for the products.  With burst > 0 the
-// products come as mma_reps bursts of `burst` groups, each waited for, `gap` idle clocks apart:
-// cycles[1] = clocks inside bursts, [2] / [3] = first / last burst, [4] = clocks spent issuing (products and commit), [5] = products only.
-__global__ void tmem_ld_contention_kernel(int iters, int mma_reps, int mma_n, int burst, int gap, long long* cycles,
-                                          float* sink) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar;
-  __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_flag;
-  __shared__ unsigned long long worst;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int readers = (blockDim.x >> 5) - 1;
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
-  for (int i = tid; i < 49152 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(sm)[i] = 0;
-  if (tid == 0) {
-    abort_flag = 0;
-    worst = 0;
-    mbar_init(&bar, 1);
-    fence_mbar_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(&tmem_base_s, 512);
-    tmem_relinquish();
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_base_s;
-  if (warp < readers) {
-    const uint32_t base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    uint32_t acc = 0;
-    const long long t0 = clock64();
-    for (int it = 0; it < iters; ++it) {
-      uint32_t v[32];
-      tmem_ld32(base + ((it * 32) & 255), v);
-      tmem_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) acc ^= v[j];
-    }
-    const long long t1 = clock64();
-    atomicMax(&worst, (unsigned long long)(t1 - t0));
-    if (acc == 0x12345u) sink[0] = 1.f;
-  } else if (tid == readers * 32 && mma_reps > 0) {
-    const uint32_t a_addr = smem_u32(sm), b_addr = smem_u32(sm + 16384);
-    const uint32_t idesc = umma_idesc(128, mma_n, true, false, false);
-    if (burst <= 0) {
-      const long long t0 = clock64();
-      for (int r = 0; r < mma_reps; ++r) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_ss(tmem + 256, umma_desc_sw128(a_addr + ks * 32, 16, 1024),
-                  umma_desc_sw128(b_addr + ks * 32, 16, 1024), idesc, 1u);
-      }
-      umma_commit(&bar);
-      mbar_wait(&bar, 0, &abort_flag);
-      cycles[1] = clock64() - t0;
-    } else {
-      // bursts of `burst` groups of four products, each burst waited for, `gap` idle clocks between bursts
-      long long in_burst = 0, issue = 0, mma_issue = 0;
-      for (int r = 0; r < mma_reps; ++r) {
-        const long long t0 = clock64();
-        for (int g = 0; g < burst; ++g) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ss(tmem + 256, umma_desc_sw128(a_addr + ks * 32, 16, 1024),
-                    umma_desc_sw128(b_addr + ks * 32, 16, 1024), idesc, 1u);
-        }
-        const long long tm = clock64();
-        umma_commit(&bar);
-        const long long t1 = clock64();
-        mbar_wait(&bar, r & 1, &abort_flag);
-        const long long t2 = clock64();
-        issue += t1 - t0;
-        mma_issue += tm - t0;
-        in_burst += t2 - t0;
-        if (r == 0) cycles[2] = t2 - t0;
-        if (r == mma_reps - 1) cycles[3] = t2 - t0;
-        while (clock64() - t2 < gap) {
-        }
-      }
-      cycles[1] = in_burst;
-      cycles[4] = issue;
-      cycles[5] = mma_issue;
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (tid == 0) cycles[0] = (long long)worst;
-  if (warp == 0) tmem_dealloc(tmem_base_s, 512);
-}
-}  // namespace pr
-
-extern "C" int pr_selftest_tmem_ld_contention(int nwarps, int iters, int mma_reps, int mma_n, int burst, int gap,
-                                              long long* cycles, float* sink, int device, void* stream) {
-  using namespace pr;
-  PR_REQUIRE((nwarps == 4 || nwarps == 8 || nwarps == 16) && iters > 0 && mma_reps >= 0 &&
-                 (mma_n == 64 || mma_n == 128 || mma_n == 256) && cycles && sink,
-             PR_ERR_BAD_ARG, "bad arguments");
-  PR_CUDA(cudaSetDevice(device));
-  PR_CUDA(cudaFuncSetAttribute(tmem_ld_contention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 51200));
-  tmem_ld_contention_kernel<<<1, (nwarps + 1) * 32, 51200, static_cast<cudaStream_t>(stream)>>>(
-      iters, mma_reps, mma_n, burst, gap, cycles, sink);
-  PR_CUDA(cudaGetLastError());
-  return PR_OK;
-}
-
-namespace pr {
-// Micro-benchmark: how fast the SMs can stream 16 KB tiles (128 rows x 128 B, swizzled) out of
-// L2 with TMA.  Every CTA walks `tiles` consecutive tiles of its region `reps` times through a
-// ring of `depth` stages; CTAs with the same blockIdx.x / share walk the same region.
-__global__ void __launch_bounds__(64)
-tma_stream_kernel(int tiles, int reps, int depth, int share, long long* cycles,
-                  const __grid_constant__ CUtensorMap tm) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t full[12], empty[12];
-  __shared__ int abort_flag;
-  const int tid = threadIdx.x;
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
-  if (tid == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < depth; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    fence_mbar_init();
-  }
-  __syncthreads();
-  const int region = blockIdx.x / share;
-  const int total = tiles * reps;
-  const long long t0 = clock64();
-  if (tid == 0) {
-    for (int i = 0; i < total; ++i) {
-      const int s = i % depth, ph = (i / depth) & 1;
-      if (!mbar_wait(&empty[s], ph ^ 1, &abort_flag)) break;
-      mbar_expect_tx(&full[s], 16384);
-      tma_load_2d(sm + s * 16384, &tm, &full[s], 0, (region * tiles + i % tiles) * 128);
-    }
-  } else if (tid == 32) {
-    for (int i = 0; i < total; ++i) {
-      const int s = i % depth, ph = (i / depth) & 1;
-      if (!mbar_wait(&full[s], ph, &abort_flag)) break;
-      mbar_arrive(&empty[s]);
-    }
-    cycles[blockIdx.x] = clock64() - t0;
-  }
-}
-}  // namespace pr
-
-// buf_bytes must cover ceil(grid / share) * tiles * 16384 bytes.  cycles: one entry per CTA.
-extern "C" int pr_selftest_tma_stream(const void* buf, long long buf_bytes, int grid, int tiles, int reps, int depth,
-                                      int share, int min_smem, long long* cycles, int device, void* stream) {
-  using namespace pr;
-  PR_REQUIRE(buf && cycles && grid > 0 && tiles > 0 && reps > 0 && depth >= 1 && depth <= 12 && share >= 1,
-             PR_ERR_BAD_ARG, "bad arguments");
-  PR_REQUIRE((long long)((grid + share - 1) / share) * tiles * 16384 <= buf_bytes, PR_ERR_BAD_ARG,
-             "buffer of %lld bytes is smaller than the %d regions of %d tiles", buf_bytes, (grid + share - 1) / share,
-             tiles);
-  PR_CUDA(cudaSetDevice(device));
-  CUtensorMap tm;
-  uint64_t dims[2] = {64, (uint64_t)((grid + share - 1) / share) * tiles * 128};
-  uint64_t strides[2] = {0, 128};
-  uint32_t box[2] = {64, 128};
-  int rc = make_tmap(&tm, buf, 2, 2, dims, strides, box, true);
+  int* status = nullptr;
+  int rc = status_word(device, &status, nullptr);
   if (rc) return rc;
-  const int smem = max(1024 + depth * 16384, min(min_smem, 227 * 1024));  // min_smem limits the CTAs per SM
-  PR_CUDA(cudaFuncSetAttribute(tma_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  tma_stream_kernel<<<grid, 64, smem, static_cast<cudaStream_t>(stream)>>>(tiles, reps, depth, share, cycles, tm);
-  PR_CUDA(cudaGetLastError());
-  return PR_OK;
-}
-
-extern "C" int pr_selftest_tmem_bw(int nwarps, int iters, long long* cycles, float* sink, int device, void* stream) {
-  using namespace pr;
-  PR_REQUIRE(nwarps == 4 || nwarps == 8 || nwarps == 16, PR_ERR_BAD_ARG, "nwarps must be 4, 8 or 16");
-  PR_REQUIRE(cycles && sink && iters > 0, PR_ERR_BAD_ARG, "bad arguments");
-  PR_CUDA(cudaSetDevice(device));
-  tmem_bw_kernel<<<1, nwarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(iters & 0xffffff, iters >> 24, cycles, sink);
+  selftest_timeout_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>((unsigned long long)budget_us * 1000ull,
+                                                                            status, gave_up);
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }

@@ -78,14 +78,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA.  The slow
 // path is kept out of line so that heavily unrolled callers stay small.
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                   uint64_t budget_ns = PR_WAIT_BUDGET_NS) {
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > PR_WAIT_BUDGET_NS) {
+    if (globaltimer_ns() - t0 > budget_ns) {
       *abort_flag = 1;
       return false;
     }
@@ -94,6 +95,12 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag);
+}
+// The same wait with a caller-chosen budget (the self-test of the give-up path uses a few ms).
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              uint64_t budget_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, budget_ns);
 }
 
 // --------------------------------------------------------------------- TMA

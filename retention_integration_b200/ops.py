@@ -86,6 +86,15 @@ def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.
     n = t // c
     cp = (c + 63) // 64 * 64
     write = want_gates and not query_side
+    if not want_xt and c > 16384:
+        # one chunk longer than the chunk-local pass holds in shared memory: plain cumulative sum over the sequence
+        if log_g is None:
+            return None, None, None
+        assert n == 1, "long chunks are only supported where the chunk is the whole sequence"
+        a = torch.empty(b, t, h, device=x.device, dtype=torch.float32)
+        _call("pr_gate_cumsum", c_int(b), c_int(t), c_int(h), ptr(log_g), c_longlong(t * h), ptr(a), c_int(_dev(x)),
+              stream_ptr(x.device))
+        return a, a[:, -1:, :].contiguous(), None
     a = torch.empty(b, t, h, device=x.device, dtype=torch.float32) if (write and log_g is not None) else None
     A = torch.empty(b, n, h, device=x.device, dtype=torch.float32) if write else None
     xt = torch.empty(b, n, hx, d, cp, device=x.device, dtype=x.dtype) if want_xt else None
@@ -301,7 +310,42 @@ def state_merge(state, sum_of_keys, S, gram, a_last):
     return new_state, new_sok
 
 
+def state_to_chunk_layout(state, sum_of_keys, want16: bool = False, want32: bool = False, want_gram: bool = False,
+                          want_gram_halves: bool = False):
+    """Exact-layout (state [b,h,D,d], sum_of_keys [b,h,D]) -> dict with the requested forms in the kernels'
+    chunk-state layout: "z16" [b,h,DR,d], "z32" fp32, "gram" [b,h,d,d] fp32, "ghi"/"glo" 16-bit."""
+    b, h, _, d = state.shape
+    dev, DR = state.device, state_rows(d)
+    out = {
+        "z16": torch.empty(b, h, DR, d, device=dev, dtype=state.dtype) if want16 else None,
+        "z32": torch.empty(b, h, DR, d, device=dev, dtype=torch.float32) if want32 else None,
+        "gram": torch.empty(b, h, d, d, device=dev, dtype=torch.float32) if want_gram else None,
+        "ghi": torch.empty(b, h, d, d, device=dev, dtype=state.dtype) if want_gram_halves else None,
+        "glo": torch.empty(b, h, d, d, device=dev, dtype=state.dtype) if want_gram_halves else None,
+    }
+    _call("pr_state_to_chunk_layout", c_int(dtype_code(state.dtype)), c_int(b), c_int(h), c_int(d), ptr(state),
+          ptr(sum_of_keys), ptr(out["z16"]), ptr(out["z32"]), ptr(out["gram"]), ptr(out["ghi"]), ptr(out["glo"]),
+          c_int(_dev(state)), stream_ptr(dev))
+    return out
+
+
 _decode_ws = {}
+
+
+def _decode_partials(dev, b: int, h: int, hq: int, d: int):
+    """Partial-sum workspace of a split decode step, or (None, None) when the step runs unsplit.  One
+    workspace per (device, stream, shape): calls that may overlap on the GPU (other streams) get their own;
+    calls on one stream are ordered and share it."""
+    if lib().pr_decode_split(c_int(b), c_int(h), c_int(hq)) <= 1:
+        return None, None
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream, b, hq, d)
+    ws = _decode_ws.get(key)
+    if ws is None:
+        ns = lib().pr_decode_nsplit()
+        ws = (torch.empty(b, hq, ns, d, device=dev, dtype=torch.float32),
+              torch.empty(b, hq, ns, device=dev, dtype=torch.float32))
+        _decode_ws[key] = ws
+    return ws
 
 
 def _batch_strided(t: torch.Tensor):
@@ -324,8 +368,9 @@ def _batch_strided(t: torch.Tensor):
 
 
 def decode_step(Q, K, V, log_g, state, sum_of_keys, scale: float, h: int):
-    """One decode step (tq = 1) in a single library call.  Returns O [b,1,hq,d].  Q, K, V and log_g may be
-    slices along the token axis of longer tensors (a preallocated cache): they are read in place."""
+    """One decode step (tq = 1) in a single library call and a single kernel.  Returns O [b,1,hq,d].  Q, K, V
+    and log_g may be slices along the token axis of longer tensors (a preallocated cache): they are read in place.
+    The partial-sum workspace a small problem needs is kept per (device, stream, shape), see _decode_partials."""
     b, _, hq, d = Q.shape
     tk = K.shape[1] if K is not None else 0
     Q, q_bs = _batch_strided(Q)
@@ -339,26 +384,32 @@ def decode_step(Q, K, V, log_g, state, sum_of_keys, scale: float, h: int):
         k_bs = v_bs = tk * h * d
     log_g, g_bs = _batch_strided(log_g)
     O = torch.empty(b, 1, hq, d, device=Q.device, dtype=Q.dtype)
-    a = None
-    if log_g is not None and tk > 0:
-        # scratch for the cumulative gates, kept between steps and grown geometrically with the cache
-        gkey = (Q.device, "gates")
-        need = b * tk * h
-        buf = _decode_ws.get(gkey)
-        if buf is None or buf.numel() < need:
-            buf = torch.empty(max(need * 2, 1 << 16), device=Q.device, dtype=torch.float32)
-            _decode_ws[gkey] = buf
-        a = buf
-    part_y = part_l = None
-    if state is not None:
-        key = (Q.device, b, hq, d)
-        if key not in _decode_ws:
-            ns = lib().pr_decode_nsplit()
-            _decode_ws[key] = (torch.empty(b, hq, ns, d, device=Q.device, dtype=torch.float32),
-                               torch.empty(b, hq, ns, device=Q.device, dtype=torch.float32))
-        part_y, part_l = _decode_ws[key]
+    part_y, part_l = _decode_partials(Q.device, b, h, hq, d)
     _call("pr_decode_step_strided", c_int(dtype_code(Q.dtype)), c_int(b), c_int(tk), c_int(h), c_int(hq), c_int(d),
           ptr(Q), c_longlong(q_bs), ptr(K), ptr(V), c_longlong(k_bs), ptr(log_g), c_longlong(g_bs), ptr(state),
-          ptr(sum_of_keys), c_float(scale), ptr(a), ptr(part_y), ptr(part_l), ptr(O), c_int(_dev(Q)),
+          ptr(sum_of_keys), c_float(scale), ptr(None), ptr(part_y), ptr(part_l), ptr(O), c_int(_dev(Q)),
           stream_ptr(Q.device))
+    return O
+
+
+def decode_recurrent(q, k, v, log_g, state, sum_of_keys, new_state, new_sum_of_keys, scale: float):
+    """Pure-recurrent step: advances (state, sum_of_keys) by the token (k, v, log_g) into (new_state,
+    new_sum_of_keys) - which may be the same tensors when hq / h <= 4 - and reads it with q.  Returns O [b,1,hq,d]."""
+    b, _, hq, d = q.shape
+    h = k.shape[2]
+    q, q_bs = _batch_strided(q)
+    k, k_bs = _batch_strided(k)
+    v, v_bs = _batch_strided(v)
+    if k_bs != v_bs:
+        k, v = k.contiguous(), v.contiguous()
+        k_bs = v_bs = h * d
+    if q_bs % 8 != 0 or q.data_ptr() % 16:
+        q, q_bs = q.contiguous(), hq * d
+    log_g, g_bs = _batch_strided(log_g)
+    O = torch.empty(b, 1, hq, d, device=q.device, dtype=q.dtype)
+    part_y, part_l = _decode_partials(q.device, b, h, hq, d)
+    _call("pr_decode_recurrent", c_int(dtype_code(q.dtype)), c_int(b), c_int(h), c_int(hq), c_int(d), ptr(q),
+          c_longlong(q_bs), ptr(k), ptr(v), c_longlong(k_bs), ptr(log_g), c_longlong(g_bs), ptr(state),
+          ptr(sum_of_keys), ptr(new_state), ptr(new_sum_of_keys), c_float(scale), ptr(part_y), ptr(part_l), ptr(O),
+          c_int(_dev(q)), stream_ptr(q.device))
     return O

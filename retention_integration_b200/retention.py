@@ -35,25 +35,38 @@ def _check_inputs(Q, K, V, log_G, deg):
 
 
 class _ChunkedRetention(torch.autograd.Function):
-    """Chunked forward/backward.  Sequence length is a multiple of the chunk size here."""
+    """Chunked forward/backward.  Sequence length is a multiple of the chunk size here.
+
+    `carry` is None or (Cs [b,h,DR*d], Cg [b,h,d*d]) fp32: the state and Gram matrix entering the first
+    chunk, in the kernels' chunk-state layout (initial_state).  With `want_final` the state and Gram matrix
+    leaving the last chunk come back in the same form (not differentiable)."""
 
     @staticmethod
-    def forward(ctx, Q, K, V, log_G, c, scale):
+    def forward(ctx, Q, K, V, log_G, c, scale, carry, want_final):
         b, t, hq, d = Q.shape
         h = K.shape[2]
         n = t // c
+        Cs, Cg = carry if carry is not None else (None, None)
+        first = carry is None
         a, A, KT = ops.gate_prep(K, log_G, c, query_side=False)
         S, gram = ops.chunk_state(KT, None, V, c, h, key_weights=True, want_gram=True)
         del KT
-        Z = ops.discumsum_fwd(S, A, inplace=True)
-        zhi, zlo, zfull = ops.gram_scan_fwd(gram, A, Q.dtype, want_full=True)
-        O, l = ops.chunk_out(Q, K, V, a, Z, zhi, zlo, n, c, c, 1, scale)
+        Fs = Fg = None
+        if want_final:
+            Z, Fs = ops.discumsum_fwd(S, A, inplace=True, carry_in=Cs, want_carry=True)
+            zhi, zlo, zfull, Fg = ops.gram_scan_fwd(gram, A, Q.dtype, want_full=True, carry_in=Cg, want_carry=True)
+        else:
+            Z = ops.discumsum_fwd(S, A, inplace=True, carry_in=Cs)
+            zhi, zlo, zfull = ops.gram_scan_fwd(gram, A, Q.dtype, want_full=True, carry_in=Cg)
+        O, l = ops.chunk_out(Q, K, V, a, Z, zhi, zlo, n, c, c, 1 if first else 0, scale)
         ctx.save_for_backward(Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull)
-        ctx.c, ctx.scale = c, scale
-        return O
+        ctx.c, ctx.scale, ctx.first = c, scale, first
+        if want_final:
+            ctx.mark_non_differentiable(Fs, Fg)
+        return O, Fs, Fg
 
     @staticmethod
-    def backward(ctx, dO):
+    def backward(ctx, dO, _dFs=None, _dFg=None):
         Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull = ctx.saved_tensors
         c, scale = ctx.c, ctx.scale
         b, t, hq, d = Q.shape
@@ -68,19 +81,18 @@ class _ChunkedRetention(torch.autograd.Function):
         # reverse scans: dS_m (with key weights folded in) and the chunk-gate gradient
         wdS, dA_state = ops.discumsum_bwd(dZ, Z, A, row_len=d, row_weights=True, inplace=True)
         ghi, glo, dA_gram = ops.gram_scan_bwd(dZg, zfull, A, Q.dtype)
-        # gradients through the expansions
-        dq_state, gq = ops.expand_grad(dy, Q, Z, zhi, zlo, a, A if a is not None else None, dl, c, h, True, scale, 2.0,
-                                       1, n - 1)
-        dk_state, wk = ops.expand_grad(V, K, wdS, ghi, glo, a, A if a is not None else None, None, c, h, False, 1.0,
-                                       1.0, 0, n - 2)
+        # gradients through the expansions (chunk 0 reads a state only when one was carried in)
+        gate_A = A if a is not None else None
+        dq_state, gq = ops.expand_grad(dy, Q, Z, zhi, zlo, a, gate_A, dl, c, h, True, scale, 2.0,
+                                       1 if ctx.first else 0, n - 1)
+        dk_state, wk = ops.expand_grad(V, K, wdS, ghi, glo, a, gate_A, None, c, h, False, 1.0, 1.0, 0, n - 2)
         # intra-chunk attention backward, merged with the state-path terms
         dQ, da_q = ops.chunk_dq(Q, dO, K, V, a, dl, l, dq_state, c, scale)
-        dK, dV, da_k = ops.chunk_dkv(Q, dO, K, V, wdS, a, A if a is not None else None, dl, l, dk_state, c, n - 2,
-                                     scale)
+        dK, dV, da_k = ops.chunk_dkv(Q, dO, K, V, wdS, a, gate_A, dl, l, dk_state, c, n - 2, scale)
         dlog_G = None
         if log_G is not None:
             dlog_G = ops.gate_grad(da_q, gq, da_k, wk, dA_state, dA_gram, c)
-        return dQ, dK, dV, dlog_G, None, None
+        return dQ, dK, dV, dlog_G, None, None, None, None
 
 
 class _QuadraticRetention(torch.autograd.Function):
@@ -111,20 +123,40 @@ class _QuadraticRetention(torch.autograd.Function):
         return dQ, dK, dV, dlog_G, None
 
 
+def _pad_head_dim(x, d_to):
+    return torch.nn.functional.pad(x, (0, d_to - x.shape[-1]))
+
+
 def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=False, deg=2, scale=None,
                     chunk_size=None, switch_over_seq_len=None):
     """Symmetric power retention, training forward (differentiable).
 
     Same arguments as the reference (retention/power_retention_maker.py:72-73):
     Q [b,t,hq,d]; K, V [b,t,h,d]; log_G [b,t,h] float32 or None; returns [b,t,hq,d].
-    `initial_state` / `return_final_state` are unfinished in the reference
-    (retention/power_retention_maker.py:43,158-160) and are rejected here.
+
+    `initial_state` / `return_final_state` (retention/power_retention_maker.py:131-140,158-172, left
+    unfinished there: the state is passed without its normaliser and the returned one is the state
+    *entering* the last chunk) are finished here: the state is the pair (state [b,h,D,d], sum_of_keys [b,h,D]
+    fp32) in the exact layout, exactly what power_retention_inference takes and returns; the sequence
+    continues from it, and with return_final_state the call returns (out, (state, sum_of_keys)) after the
+    last token.  Gradients flow to Q, K, V and log_G; the states are treated as constants.
+
+    Head dims 16, 32 and 48 run on the d = 64 kernels with zero-padded features (exact: the padded
+    features contribute nothing to any dot product); they take no states.
     """
     assert deg % 2 == 0, f"deg must be even: {deg=}"
-    if initial_state is not None or return_final_state:
-        raise PRError("initial_state / return_final_state are not implemented (unfinished in the reference too)")
+    d_orig = Q.shape[-1]
+    if d_orig in (16, 32, 48):
+        if initial_state is not None or return_final_state:
+            raise PRError(f"states are kept for head dim 64 only (got {d_orig})")
+        if not scale:
+            scale = 1.0 / math.sqrt(d_orig)
+        out = power_retention(_pad_head_dim(Q, 64), _pad_head_dim(K, 64), _pad_head_dim(V, 64), log_G, None, False,
+                              deg, scale, chunk_size, switch_over_seq_len)
+        return out[..., :d_orig]
     _check_inputs(Q, K, V, log_G, deg)
     b, t, hq, d = Q.shape
+    h = K.shape[2]
     if log_G is not None:
         log_G = log_G.to(torch.float32).contiguous()
     if not scale:
@@ -142,11 +174,28 @@ def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=
             log_G = torch.nn.functional.pad(log_G, (0, 0, 0, t_pad))
     Q, K, V = Q.contiguous(), K.contiguous(), V.contiguous()
     tt = t + t_pad
-    if switch_over_seq_len is None or tt <= switch_over_seq_len or chunk_size is None:
+    quadratic = switch_over_seq_len is None or tt <= switch_over_seq_len or chunk_size is None
+    with_state = initial_state is not None or return_final_state
+    if quadratic and not with_state:
         out = _QuadraticRetention.apply(Q, K, V, log_G, float(scale))
-    else:
-        out = _ChunkedRetention.apply(Q, K, V, log_G, int(chunk_size), float(scale))
-    return out[:, :t] if t_pad else out
+        return out[:, :t] if t_pad else out
+    carry = None
+    if initial_state is not None:
+        state, sok = initial_state
+        D = layout.exact_dim(d)
+        assert state.shape == (b, h, D, d), f"state must be [b,h,{D},{d}] (exact layout)"
+        assert sok.shape == (b, h, D) and sok.dtype == torch.float32
+        conv = ops.state_to_chunk_layout(state.to(Q.dtype).contiguous(), sok.contiguous(), want32=True, want_gram=True)
+        carry = (conv["z32"].view(b, h, -1), conv["gram"].view(b, h, -1))
+    # a short sequence that carries a state is one chunk of the chunked form (same arithmetic as the quadratic branch)
+    c = tt if quadratic else int(chunk_size)
+    out, Fs, Fg = _ChunkedRetention.apply(Q, K, V, log_G, c, float(scale), carry, bool(return_final_state))
+    out = out[:, :t] if t_pad else out
+    if not return_final_state:
+        return out
+    DR = ops.state_rows(d)
+    final = ops.state_merge(None, None, Fs.to(Q.dtype).view(b, 1, h, DR, d), Fg.view(b, 1, h, d, d), None)
+    return out, final
 
 
 def power_retention_inference(Q, K, V, log_G=None, initial_state=None, sum_of_keys=None, deg=2, scale=None,
@@ -212,16 +261,13 @@ def power_retention_inference(Q, K, V, log_G=None, initial_state=None, sum_of_ke
             Y, _ = ops.chunk_out(Q, K, V, a, None, None, None, 1, tq, tk, 1, scale, want_l=False)
         else:
             # several query tokens against a state: the tensor-core path, state converted to its layout
-            Z = layout.exact_to_reference(initial_state, d, dim=-2).unsqueeze(1).contiguous()
-            zg = layout.exact_sum_of_keys_to_gram(sum_of_keys, d)
-            zhi = zg.to(Q.dtype)
-            zlo = (zg - zhi.float()).to(Q.dtype)
+            conv = ops.state_to_chunk_layout(initial_state.contiguous(), sum_of_keys.contiguous(), want16=True,
+                                             want_gram_halves=True)
+            Z, zhi, zlo = conv["z16"].unsqueeze(1), conv["ghi"].unsqueeze(1), conv["glo"].unsqueeze(1)
             if tk > 0:
-                Y, _ = ops.chunk_out(Q, K, V, a, Z, zhi.unsqueeze(1).contiguous(), zlo.unsqueeze(1).contiguous(), 1,
-                                     tq, tk, 0, scale, q_gate_last=True, want_l=False)
+                Y, _ = ops.chunk_out(Q, K, V, a, Z, zhi, zlo, 1, tq, tk, 0, scale, q_gate_last=True, want_l=False)
             else:
-                Y, _ = ops.chunk_out(Q, None, None, None, Z, zhi.unsqueeze(1).contiguous(),
-                                     zlo.unsqueeze(1).contiguous(), 1, tq, tq, 0, scale, want_l=False)
+                Y, _ = ops.chunk_out(Q, None, None, None, Z, zhi, zlo, 1, tq, tq, 0, scale, want_l=False)
 
     # ---- optionally compress the cache into the state
     if switch:

@@ -1,0 +1,83 @@
+"""The caller-side cache (preallocated K/V/gate storage, switch-over policy, pure-recurrent mode) against
+the quadratic form over the whole token stream."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import power_retention_oracle as oracle
+from tests._golden import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _stream(b, t, h, r, seed, shift=3.0):
+    g = torch.Generator().manual_seed(seed)
+    Q = torch.randn(b, t, h * r, 64, generator=g).bfloat16()
+    K = torch.randn(b, t, h, 64, generator=g).bfloat16()
+    V = torch.randn(b, t, h, 64, generator=g).bfloat16()
+    lg = F.logsigmoid(torch.randn(b, t, h, generator=g) + shift)
+    return Q, K, V, lg
+
+
+@pytest.mark.parametrize("r", [1, 2])
+def test_token_cache_with_switch_over(cuda_device, r):
+    """Prompt through prefill(), then 40 generated tokens with a switch-over every 16: the cache fills, is
+    compressed into the state and cleared, twice; its storage never moves."""
+    from retention_integration_b200.cache import RetentionCache
+
+    b, h, t0, steps = 2, 2, 256, 40
+    Q, K, V, lg = _stream(b, t0 + steps, h, r, seed=31 + r)
+    ref = oracle.power_retention_quadratic(Q, K, V, lg)
+    dev = cuda_device
+    Qd, Kd, Vd, ld = (x.to(dev) for x in (Q, K, V, lg))
+    cache = RetentionCache(b, h, 64, torch.bfloat16, dev, capacity=16, switch_over_seq_len=16)
+    Y0 = cache.prefill(Qd[:, :t0], Kd[:, :t0], Vd[:, :t0], ld[:, :t0], chunk_size=128)
+    assert rel_l2(Y0.float().cpu(), ref[:, :t0].float()) < 2e-2
+    assert cache.get_seq_length() == 0 and cache.state is not None
+    storage = cache.keys.data_ptr()
+    for i in range(steps):
+        j = t0 + i
+        y = cache.decode(Qd[:, j:j + 1], Kd[:, j:j + 1], Vd[:, j:j + 1], ld[:, j:j + 1])
+        assert rel_l2(y.float().cpu(), ref[:, j:j + 1].float()) < 1.5e-2, i
+        assert cache.get_seq_length() == (i + 1) % 16
+    assert cache.keys.data_ptr() == storage  # written in place, never reallocated
+
+
+@pytest.mark.parametrize("r,b,h", [(1, 2, 2), (4, 1, 2), (8, 1, 1), (1, 16, 32)])
+def test_recurrent_mode(cuda_device, r, b, h):
+    """State advanced and read once per token; (16, 32) is the benchmark's shape (unsplit state pass)."""
+    from retention_integration_b200.cache import RetentionCache
+
+    steps = 24 if b * h < 64 else 6
+    Q, K, V, lg = _stream(b, steps, h, r, seed=5 * r + b)
+    dev = cuda_device
+    Qd, Kd, Vd, ld = (x.to(dev) for x in (Q, K, V, lg))
+    cache = RetentionCache(b, h, 64, torch.bfloat16, dev, recurrent=True)
+    check = [(0, 0), (b - 1, h - 1)]
+    outs = []
+    for j in range(steps):
+        outs.append(cache.decode(Qd[:, j:j + 1], Kd[:, j:j + 1], Vd[:, j:j + 1], ld[:, j:j + 1]))
+    Y = torch.cat(outs, dim=1).float().cpu()
+    for bi, hi in check:
+        sl = slice(hi * r, (hi + 1) * r)
+        ref = oracle.power_retention_quadratic(Q[bi:bi + 1, :, sl], K[bi:bi + 1, :, hi:hi + 1], V[bi:bi + 1, :, hi:hi + 1],
+                                               lg[bi:bi + 1, :, hi:hi + 1])
+        assert rel_l2(Y[bi:bi + 1, :, sl], ref.float()) < 1.5e-2, (bi, hi)
+    assert cache.get_seq_length() == 0
+
+
+def test_recurrent_state_equals_switch_over_state(cuda_device):
+    """After n recurrent steps the state pair is what one switch-over over the same n tokens produces."""
+    import retention_integration_b200 as prb
+    from retention_integration_b200.cache import RetentionCache
+
+    b, h, n = 2, 2, 32
+    Q, K, V, lg = _stream(b, n, h, 1, seed=77)
+    dev = cuda_device
+    Qd, Kd, Vd, ld = (x.to(dev) for x in (Q, K, V, lg))
+    cache = RetentionCache(b, h, 64, torch.bfloat16, dev, recurrent=True)
+    for j in range(n):
+        cache.decode(Qd[:, j:j + 1], Kd[:, j:j + 1], Vd[:, j:j + 1], ld[:, j:j + 1])
+    _, state, sok = prb.power_retention_inference(Qd[:, -1:], Kd, Vd, ld, switch_over_seq_len=n)
+    assert rel_l2(cache.state.float(), state.float()) < 1e-2
+    assert rel_l2(cache.sum_of_keys, sok) < 5e-3

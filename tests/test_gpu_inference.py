@@ -112,3 +112,51 @@ def test_decode_reads_cache_slices_in_place(cuda_device, ratio):
         torch.cuda.synchronize()
         assert torch.equal(y_view, y_copy), tk
         assert torch.isfinite(y_view).all()
+
+
+def _decode_vs_oracle(dev, b, h, r, tk, seed, check_rows):
+    """One decode step (tq = 1, state given) against oracle.power_retention_inference, compared on the
+    (batch, kv head) pairs in `check_rows` (the oracle expands every query, so a few pairs keep it quick)."""
+    import retention_integration_b200 as prb
+    from retention_integration_b200 import layout
+
+    g = torch.Generator().manual_seed(seed)
+    d, D = 64, 2080
+    hq = h * r
+    Q = torch.randn(b, 1, hq, d, generator=g).bfloat16()
+    state = (torch.randn(b, h, D, d, generator=g) * 0.05).bfloat16()
+    sok = torch.rand(b, h, D, generator=g) * 0.5 + 0.25
+    K = V = lg = None
+    if tk > 0:
+        K = torch.randn(b, tk, h, d, generator=g).bfloat16()
+        V = torch.randn(b, tk, h, d, generator=g).bfloat16()
+        lg = F.logsigmoid(torch.randn(b, tk, h, generator=g))
+    to = lambda x: None if x is None else x.to(dev)
+    Y, s2, k2 = prb.power_retention_inference(to(Q), to(K), to(V), to(lg), to(state), to(sok),
+                                              switch_over_seq_len=1024)
+    torch.cuda.synchronize()
+    assert torch.isfinite(Y.float()).all()
+    for bi, hi in check_rows:
+        sl_q = slice(hi * r, (hi + 1) * r)
+        cut = lambda x: None if x is None else x[bi:bi + 1, :, hi:hi + 1]
+        st_ref = layout.to_reference_layout(state[bi:bi + 1, hi:hi + 1].float(), d)
+        sk_ref = layout.to_reference_layout(sok[bi:bi + 1, hi:hi + 1], d, dim=-1)
+        Kc, Vc = cut(K), cut(V)
+        Y_ref, _, _ = oracle.power_retention_inference(
+            Q[bi:bi + 1, :, sl_q].float(), None if Kc is None else Kc.float(), None if Vc is None else Vc.float(),
+            cut(lg), st_ref, sk_ref, deg=2, switch_over_seq_len=1024)
+        assert rel_l2(Y[bi:bi + 1, :, sl_q].float().cpu(), Y_ref) < 1e-2, (bi, hi, tk)
+
+
+@pytest.mark.parametrize("tk", [0, 1, 300])
+def test_decode_at_benchmark_shape_unsplit_state_read(cuda_device, tk):
+    """b16 h32: 512 (batch, head) pairs, so every CTA of the state read walks all 2080 rows of its state
+    (no split of the expanded dimension) - the path the decode benchmark runs."""
+    _decode_vs_oracle(cuda_device, 16, 32, 1, tk, seed=100 + tk,
+                      check_rows=[(0, 0), (7, 13), (15, 31), (3, 30)])
+
+
+@pytest.mark.parametrize("b,h,r,tk", [(8, 24, 1, 65), (6, 32, 1, 0), (10, 20, 4, 17), (2, 3, 1, 9)])
+def test_decode_state_read_split_in_two_and_five(cuda_device, b, h, r, tk):
+    """192-200 (batch, head) pairs: the expanded dimension is read in two halves; 6 pairs: in five parts."""
+    _decode_vs_oracle(cuda_device, b, h, r, tk, seed=b * h + tk, check_rows=[(0, 0), (b - 1, h - 1), (b // 2, h // 2)])

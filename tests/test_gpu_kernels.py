@@ -154,3 +154,30 @@ def test_fused_output_kernel_matches_attention_then_query_state(cuda_device):
     assert _status(cuda_device) == 0
     assert rel_l2(O.float().cpu(), O_ref) < 5e-3
     assert g["O"].shape[-1] == 32  # fixture sanity (kept for the d = 32 build)
+
+
+def test_bounded_wait_gives_up_and_reports(cuda_device):
+    """A wait that nothing will ever satisfy, with a budget of 3 ms: every thread gives up on its own,
+    the CTA releases its tensor memory and returns, the status word turns into PR_ERR_TIMEOUT through
+    pr_device_check, and the next launch on the same context works."""
+    import ctypes
+
+    from retention_integration_b200 import _lib, ops
+
+    L = _lib.lib()
+    torch.cuda.synchronize()
+    _lib.device_status(0)  # clear whatever earlier tests left
+    gave_up = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    _lib.check(L.pr_selftest_timeout(3000, _lib.ptr(gave_up), 0, _lib.stream_ptr(cuda_device)), "pr_selftest_timeout")
+    torch.cuda.synchronize()
+    assert int(gave_up.item()) == 128
+    assert L.pr_device_check(0) == -3 and b"bounded" in L.pr_last_error()
+    assert L.pr_device_check(0) == 0  # reading cleared it
+    # the context is intact: a normal tensor-core launch still gives the right product
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(128, 64, generator=g).bfloat16().to(cuda_device)
+    b = torch.randn(64, 64, generator=g).bfloat16().to(cuda_device)
+    out = ops.selftest_umma(0, a, b, 64, 64)
+    torch.cuda.synchronize()
+    assert torch.allclose(out, a.float() @ b.float().t(), atol=1e-3, rtol=1e-3)
+    assert _lib.device_status(0) == 0

@@ -66,6 +66,8 @@ CASES = [
     (2, 512, 2, 2, True, 4.0, 256),    # GQA + slow decay
     (1, 600, 1, 8, False, 0.0, 128),   # GQA ratio 8 + padding
     (1, 2048, 1, 1, True, 0.0, 1024),  # the benchmark's chunk size
+    (1, 4096, 1, 1, True, 0.0, 1024),  # four chunks of it: middle chunks carry state terms on both sides
+    (1, 5120, 1, 2, False, 0.0, 1024), # five chunks, ungated, GQA
     (1, 300, 2, 1, True, 2.0, None),   # quadratic branch, ragged length
     (1, 768, 2, 1, True, 1.0, 192),    # chunk not a multiple of the 128-row tile (second tile half empty)
     (1, 480, 1, 2, True, 0.0, 96),     # chunk shorter than a tile, ragged 64-key steps, GQA
@@ -201,11 +203,13 @@ def test_full_benchmark_size_is_bitwise_reproducible(cuda_device):
                 assert torch.equal(x, r), (c, name)
 
 
-def test_rejects_what_the_reference_leaves_unfinished(cuda_device):
+def test_rejects_unsupported_arguments(cuda_device):
     import retention_integration_b200 as prb
 
     q = torch.zeros(1, 128, 1, 64, dtype=torch.bfloat16, device=cuda_device)
-    with pytest.raises(prb.PRError):
-        prb.power_retention(q, q, q, None, return_final_state=True, chunk_size=64)
     with pytest.raises(AssertionError):
-        prb.power_retention(q, q, q, None, deg=3)
+        prb.power_retention(q, q, q, None, deg=3)            # odd degree: refused by the reference too
+    with pytest.raises(prb.PRError):
+        prb.power_retention(q, q, q, None, deg=4, chunk_size=64)  # states exist for deg 2 only, here and there
+    with pytest.raises(prb.PRError):
+        prb.power_retention(q.float(), q.float(), q.float(), None)  # 16-bit inputs only
