@@ -38,8 +38,17 @@ def head_slice(n_kv_heads: int, ratio: int, rank: int, world: int):
     return slice(rank * per, (rank + 1) * per), slice(rank * per * ratio, (rank + 1) * per * ratio)
 
 
+class ExchangeTimeout(PRError):
+    """A boundary-state exchange did not complete within the process group's timeout: a peer never
+    joined, left, or its message was lost.  The host-side counterpart of PR_ERR_TIMEOUT."""
+
+
 class DistComm:
-    """Neighbour exchange over torch.distributed (NCCL for CUDA tensors, gloo for CPU ones)."""
+    """Boundary-state exchange over torch.distributed (NCCL for CUDA tensors, gloo for CPU ones).
+
+    Failure handling is the process group's: create the group with a short `timeout=` and a peer that
+    never shows up ends the exchange with `ExchangeTimeout` on the ranks that waited, instead of blocking
+    them for ever.  Nothing is retried here; the caller decides whether to rebuild the group."""
 
     def __init__(self, group=None):
         import torch.distributed as dist
@@ -50,13 +59,40 @@ class DistComm:
     def _peer(self, r):
         return self.dist.get_global_rank(self.group, r) if self.group is not None else r
 
+    def _guard(self, what, fn):
+        try:
+            return fn()
+        except RuntimeError as exc:  # DistBackendError, gloo timeouts and lost connections all derive from it
+            raise ExchangeTimeout(f"{what} on rank {self.rank} of {self.world} failed or timed out: {exc}") from exc
+
     def send(self, t, to_rank):
-        self.dist.send(t.contiguous(), self._peer(to_rank), group=self.group)
+        self._guard("send", lambda: self.dist.send(t.contiguous(), self._peer(to_rank), group=self.group))
 
     def recv(self, like, from_rank):
         buf = torch.empty_like(like)
-        self.dist.recv(buf, self._peer(from_rank), group=self.group)
+        self._guard("recv", lambda: self.dist.recv(buf, self._peer(from_rank), group=self.group))
         return buf
+
+    def all_gather(self, t):
+        """[world, *t.shape]: every rank's tensor, in rank order (one collective)."""
+        flat = t.contiguous().view(-1)
+        out = torch.empty(self.world * flat.numel(), device=t.device, dtype=t.dtype)
+        self._guard("all_gather", lambda: self.dist.all_gather_into_tensor(out, flat, group=self.group))
+        return out.view((self.world,) + tuple(t.shape))
+
+
+class ChainComm:
+    """A DistComm restricted to neighbour send / recv: forces the rank-to-rank chain (used by tests and
+    by callers whose backend has no gather)."""
+
+    def __init__(self, inner: DistComm):
+        self.inner, self.rank, self.world = inner, inner.rank, inner.world
+
+    def send(self, t, to_rank):
+        self.inner.send(t, to_rank)
+
+    def recv(self, like, from_rank):
+        return self.inner.recv(like, from_rank)
 
 
 class MailboxComm:
@@ -75,7 +111,20 @@ class MailboxComm:
 
 def forward_chain(comm, F: torch.Tensor, L: torch.Tensor):
     """F [b,h,E] fp32: what this rank's block alone leaves behind; L [b,h]: its total log gate.
-    Returns the state entering this rank's block (None on rank 0)."""
+    Returns the state entering this rank's block (None on rank 0).
+
+    With a communicator that can gather (torch.distributed) the summaries of all ranks are exchanged
+    in ONE collective and every rank runs the short recurrence C_{q+1} = C_q exp(L_q) + F_q over the
+    ranks before it on its own copy: the latency of one exchange instead of world-1 dependent hops.
+    Otherwise (the in-process mailbox) the summaries travel rank to rank."""
+    if hasattr(comm, "all_gather"):
+        if comm.world == 1:
+            return None
+        Fs, Ls = comm.all_gather(F), comm.all_gather(L)
+        C = None
+        for q in range(comm.rank):
+            C = Fs[q].clone() if C is None else torch.addcmul(Fs[q], C, torch.exp(Ls[q]).unsqueeze(-1))
+        return C
     C = None
     if comm.rank > 0:
         C = comm.recv(F, comm.rank - 1)
@@ -88,7 +137,16 @@ def forward_chain(comm, F: torch.Tensor, L: torch.Tensor):
 def backward_chain(comm, G: torch.Tensor, L: torch.Tensor):
     """G [b,h,E] fp32: gradient carry this rank's block produces with nothing coming in from
     the right.  Returns the carry entering from rank+1 (None on the last rank) after sending
-    the completed carry G + exp(L) * incoming to rank-1."""
+    the completed carry G + exp(L) * incoming to rank-1.  One gather instead of the chain where the
+    communicator offers it (see forward_chain)."""
+    if hasattr(comm, "all_gather"):
+        if comm.world == 1:
+            return None
+        Gs, Ls = comm.all_gather(G), comm.all_gather(L)
+        inc = None
+        for q in range(comm.world - 1, comm.rank, -1):
+            inc = Gs[q].clone() if inc is None else torch.addcmul(Gs[q], inc, torch.exp(Ls[q]).unsqueeze(-1))
+        return inc
     inc = None
     if comm.rank < comm.world - 1:
         inc = comm.recv(G, comm.rank + 1)

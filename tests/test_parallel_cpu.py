@@ -47,7 +47,13 @@ def _worker(rank, world, port, ret):
         comm = parallel.DistComm()
         C = parallel.forward_chain(comm, F, L)
         inc = parallel.backward_chain(comm, Gl, L)
+        # the rank-to-rank chain gives the same carries as the single gather
+        chain = parallel.ChainComm(comm)
+        C2 = parallel.forward_chain(chain, F, L)
+        inc2 = parallel.backward_chain(chain, Gl, L)
         ok = True
+        ok &= (C is None) == (C2 is None) and (C is None or torch.allclose(C, C2, atol=1e-5))
+        ok &= (inc is None) == (inc2 is None) and (inc is None or torch.allclose(inc, inc2, atol=1e-5))
         if rank == 0:
             ok &= C is None
         else:
@@ -73,6 +79,52 @@ def test_carry_chains_over_gloo(world):
         p.join(120)
         assert p.exitcode == 0
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def _absent_peer_worker(rank, world, port, ret, mode):
+    import datetime
+    import time
+
+    import torch.distributed as dist
+
+    from retention_integration_b200 import parallel
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    F, L = torch.ones(1, 1, 8), torch.zeros(1, 1)
+    comm = parallel.DistComm()
+    if mode == "chain":
+        comm = parallel.ChainComm(comm)
+    if rank == 0:
+        # this rank joins the group and then never takes part in the exchange (a hung or lost peer)
+        time.sleep(10)
+        ret[rank] = "absent"
+        return
+    t0 = time.time()
+    try:
+        parallel.forward_chain(comm, F, L)
+        ret[rank] = "returned"
+    except parallel.ExchangeTimeout:
+        ret[rank] = f"timeout after {time.time() - t0:.1f}s"
+
+
+@pytest.mark.parametrize("mode", ["gather", "chain"])
+def test_exchange_with_an_absent_peer_times_out(mode):
+    """A peer that never sends: the waiting rank gets ExchangeTimeout after the group's deadline (4 s here)
+    instead of blocking.  Host-side fault injection only - no GPU is involved."""
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_absent_peer_worker, args=(r, 2, port, ret, mode)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert str(ret.get(1, "")).startswith("timeout"), dict(ret)
+    assert float(ret[1].split()[2][:-1]) < 9.0, dict(ret)
 
 
 def test_mailbox_chain_matches_dist_semantics():
