@@ -456,10 +456,14 @@ def main():
 
     # ---- per-kernel breakdown: a separate pass with CUDA events around every launch (the event
     # records cost host time, so this pass is not the one the headline is taken from)
+    from retention_integration_b200 import retention as _ret
+
     ops.launch_log.reset(timing=True)
+    _ret.NATIVE_SEQUENCER = False  # kernel by kernel from Python for this pass: one event pair per launch
     for _ in range(min(args.steps, 3)):
         step(Q, K, V, G, dO)
     barrier()
+    _ret.NATIVE_SEQUENCER = True
     kernels = ops.launch_log.summary()
     breakdown_steps = min(args.steps, 3)
     launches_per_step = ops.launch_log.count // breakdown_steps

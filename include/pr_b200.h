@@ -146,10 +146,11 @@ int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const float* dZg, co
  * Q [b,n*cq,hq,d]; K,V [b,n*ck,h,d] or NULL (state only); a [b,n*ck,h] or NULL;
  * Z [b,n,h,D2,d], zg_hi/zg_lo [b,n,h,d,d] or NULL.  Query i of a chunk sits at key
  * position i + ck - cq.  Chunks >= state_from_chunk read the state.  O [b,n*cq,hq,d] =
- * y / l (normalize=1) or y; l_out [b,n*cq,hq] or NULL. */
+ * y / l (normalize=1) or y; l_out [b,n*cq,hq] or NULL.  deg = 2, or 4 without a state (the
+ * reference's attention takes any even degree, its state operators degree 2 only). */
 int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int hq, int h, int d, const void* Q,
                  const void* K, const void* V, const float* a, const void* Z, const void* zg_hi, const void* zg_lo,
-                 int state_from_chunk, int q_gate_last, int normalize, float scale, void* O, float* l_out,
+                 int state_from_chunk, int q_gate_last, int normalize, float scale, int deg, void* O, float* l_out,
                  int device, void* stream);
 
 /* Backward prologue: dy = dO / l, dl = -<O, dO> / l over `rows` rows of d elements. */
@@ -172,13 +173,14 @@ int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int c, const v
  * from the forward and from pr_dout_prep.
  * pr_chunk_dq : dQ [b,t,hq,d] (+ dq_state fp32 if given), da_q [b,t,hq].
  * pr_chunk_dkv: dK, dV [b,t,h,d] (+ dk_state; + the state path of dV from wdS
- *               [b,n,h,D2,d] for chunks <= state_chunk_hi), da_k [b,t,h]. */
+ *               [b,n,h,D2,d] for chunks <= state_chunk_hi), da_k [b,t,h].
+ * deg = 2, or 4 without state-path terms. */
 int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO, const void* K,
                 const void* V, const float* a, const float* dl, const float* l, const float* dq_state, float scale,
-                void* dQ, float* da_q, int device, void* stream);
+                int deg, void* dQ, float* da_q, int device, void* stream);
 int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO, const void* K,
                  const void* V, const void* wdS, const float* a, const float* A, const float* dl, const float* l,
-                 const float* dk_state, int state_chunk_hi, float scale, void* dK, void* dV, float* da_k,
+                 const float* dk_state, int state_chunk_hi, float scale, int deg, void* dK, void* dV, float* da_k,
                  int device, void* stream);
 
 /* Assembles dlog_G [b,t,h] (the autograd of the cumsum / exp glue of
@@ -232,6 +234,42 @@ int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, int d, const
                            const void* K, const void* V, long long kv_bstride, const float* log_g, long long g_bstride,
                            const void* state, const float* sum_of_keys, float scale, float* a_scratch, float* part_y,
                            float* part_l, void* O, int device, void* stream);
+/* ---- The whole operator in one call per pass -------------------------------------------------
+ * power_retention's chunked branch (retention/power_retention_maker.py:143-193) and its backward
+ * (what autograd runs: retention/_query_state/triton.py:544-621, _attention/triton.py:742-810,
+ * _discumsum/triton.py:334-355, _update_state/triton.py:329-355 and the gradients of the glue),
+ * sequenced in native code over the entry points above.  t must be a multiple of c (the caller
+ * pads, as the reference's wrapper does, :71-90); deg = 2. */
+typedef struct pr_problem {
+  int dtype;   /* PR_BF16 / PR_FP16 */
+  int b, t;    /* batch, tokens */
+  int h, hq;   /* kv heads, query heads (multiple of h) */
+  int d;       /* head dim (64) */
+  int c;       /* chunk length */
+  float scale; /* score scale (the reference's default is 1/sqrt(d)) */
+} pr_problem;
+
+enum { PR_WS_SAVED = 0, PR_WS_FWD_SCRATCH = 1, PR_WS_BWD_SCRATCH = 2 };
+
+/* Bytes of the three caller-allocated workspaces of a problem: PR_WS_SAVED (written by the forward,
+ * read by the backward: gate sums, row sums, scanned states), PR_WS_FWD_SCRATCH and
+ * PR_WS_BWD_SCRATCH (dead once the call's work has run; reusable by later calls on the same stream). */
+int pr_workspace_bytes(const pr_problem* problem, int what, size_t* out);
+
+/* Forward.  Q [b,t,hq,d]; K, V [b,t,h,d]; log_G [b,t,h] fp32 or NULL; O [b,t,hq,d].
+ * carry_state [b,h,D2*d] / carry_gram [b,h,d*d] fp32 or NULL: the state entering the first chunk
+ * (initial_state, :158-160; from pr_state_to_chunk_layout).  final_state / final_gram (same
+ * shapes) or NULL receive the state after the last chunk (return_final_state, :171-172). */
+int pr_retention_fwd(const pr_problem* problem, const void* Q, const void* K, const void* V, const float* log_G,
+                     const float* carry_state, const float* carry_gram, void* O, void* saved, void* scratch,
+                     float* final_state, float* final_gram, int device, void* stream);
+
+/* Backward.  dO [b,t,hq,d] -> dQ, dK, dV (shapes of Q, K, V) and dlog_G [b,t,h] fp32 (NULL when
+ * ungated).  `saved` as the forward left it; had_carry = 1 when the forward was given carries. */
+int pr_retention_bwd(const pr_problem* problem, const void* Q, const void* K, const void* V, const float* log_G,
+                     const void* O, const void* dO, int had_carry, void* saved, void* scratch, void* dQ, void* dK,
+                     void* dV, float* dlog_G, int device, void* stream);
+
 /* A state in the exact layout (state [b,h,d(d+1)/2,d], sum_of_keys [b,h,d(d+1)/2]) converted to the
  * chunk-state layout of the training kernels: out16 [b,h,D2,d] 16-bit, out32 the same in fp32 (a carry_in
  * for pr_discumsum_fwd), gram [b,h,d,d] fp32 (carry_in for pr_gram_scan_fwd), gram_hi / gram_lo 16-bit

@@ -53,7 +53,7 @@ struct ChunkDkvParams {
 // p * dp into da2.  SEP: the gate factor is c_j * fq[col] (c_j carries 2 s^2); otherwise
 // 2 s^2 e^{aq[col] - a_j} per pair, with columns beyond `hi` (past the chunk) dropped as well.
 // MASK: columns before `lo` (queries that precede this key) are dropped.
-template <typename T, bool SEP, bool MASK>
+template <typename T, int DEG, bool SEP, bool MASK>
 __device__ __forceinline__ void dkv_half(const uint32_t (&sv)[32], const uint32_t (&pv)[32], const float* __restrict__ fq,
                                          const float* __restrict__ il, const float* __restrict__ hl,
                                          const float* __restrict__ dl, float c_j, float a_j, int lo, int hi,
@@ -89,7 +89,8 @@ __device__ __forceinline__ void dkv_half(const uint32_t (&sv)[32], const uint32_
         g.x = (col >= lo) ? g.x : 0.f;
         g.y = (col + 1 >= lo) ? g.y : 0.f;
       }
-      const float2 sg2 = __fmul2_rn(s, g);  // 2 s^2 S e^{a_i-a_j}
+      const float2 sp = DEG == 4 ? __fmul2_rn(s, __fmul2_rn(s, s)) : s;  // S^(deg-1)
+      const float2 sg2 = __fmul2_rn(sp, g);  // deg s^deg S^(deg-1) e^{a_i-a_j}
       const float2 dp = __ffma2_rn(p, iv[u], dv[u]);
       const float2 ds = __fmul2_rn(sg2, dp);
       acc = __ffma2_rn(ds, s, acc);
@@ -101,7 +102,7 @@ __device__ __forceinline__ void dkv_half(const uint32_t (&sv)[32], const uint32_
   da2 += acc.x + acc.y;
 }
 
-template <typename T>
+template <typename T, int DEG>
 __global__ void __launch_bounds__(dkv::THREADS, 2)
 chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_q,
@@ -254,7 +255,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
     const size_t tok_base = (size_t)batch * p.n_chunks * p.c + tok_chunk;
     const float* a_chunk = gated ? p.a + tok_base * p.h + kvhead : nullptr;
     const float a_j = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
-    const float s2 = p.scale * p.scale;
+    const float s2 = DEG == 4 ? (p.scale * p.scale) * (p.scale * p.scale) : p.scale * p.scale;  // s^deg
     float da2 = 0.f;  // twice the row sum of p * dp
     bool ok = true;
     // per-query values of the next step, loaded one step ahead by the first TW threads
@@ -281,7 +282,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         sm_aq[sb][tid] = av_n;
         sm_dl[sb][tid] = dl_n;
         sm_il[sb][tid] = il;
-        sm_hl[sb][tid] = 0.5f * il;
+        sm_hl[sb][tid] = (1.f / DEG) * il;
         sm_fq[sb][tid] = v ? __expf(av_n - r_n) : 0.f;
         const bool wide = __any_sync(0xffffffffu, (av_n - r_n) > 80.f);
         if (lane == 0) sm_wide[sb][warp] = wide;
@@ -311,7 +312,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
         const bool mask = (wrow0 + 31 > qp0) || (wrow0 + 31 >= p.c);
         const bool sep = (qp0 + TW - 1 < p.c) && !(sm_wide[sb][0] | sm_wide[sb][1]) &&
                          !__any_sync(0xffffffffu, (r - a_j) > 80.f);
-        const float c_j = sep ? 2.f * s2 * __expf(r - a_j) : 2.f * s2;
+        const float c_j = sep ? (float)DEG * s2 * __expf(r - a_j) : (float)DEG * s2;
         const int lo = row_valid ? row - qp0 : TW;  // first query column this key keeps
         const int hi = p.c - 1 - qp0;               // last column inside the chunk
 #pragma unroll 1
@@ -325,10 +326,10 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
           const float* dl = sm_dl[sb] + q4 * 32;
           const int lo4 = lo - q4 * 32, hi4 = hi - q4 * 32;
           if (sep) {
-            if (mask) dkv_half<T, true, true>(sv, pv, sm_fq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
-            else dkv_half<T, true, false>(sv, pv, sm_fq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
+            if (mask) dkv_half<T, DEG, true, true>(sv, pv, sm_fq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
+            else dkv_half<T, DEG, true, false>(sv, pv, sm_fq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
           } else {
-            dkv_half<T, false, true>(sv, pv, sm_aq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
+            dkv_half<T, DEG, false, true>(sv, pv, sm_aq[sb] + q4 * 32, il, hl, dl, c_j, a_j, lo4, hi4, pk, dk, da2);
           }
           tmem_st16(tmem + lane_addr + COL_P + q4 * 16, pk);
           tmem_st16(tmem + lane_addr + COL_DS + q4 * 16, dk);
@@ -433,7 +434,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
           v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
           dst[j] = v;
         }
-        p.da_k[tok * p.h + kvhead] = -0.5f * da2;
+        p.da_k[tok * p.h + kvhead] = (-1.f / DEG) * da2;
       }
     }
   }
@@ -448,10 +449,11 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
 extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO,
                             const void* K, const void* V, const void* wdS, const float* a, const float* A,
                             const float* dl, const float* l, const float* dk_state, int state_chunk_hi, float scale,
-                            void* dK,
-                            void* dV, float* da_k, int device, void* stream) {
+                            int deg, void* dK, void* dV, float* da_k, int device, void* stream) {
   using namespace pr;
   using namespace pr::dkv;
+  PR_REQUIRE(deg == 2 || (deg == 4 && wdS == nullptr && dk_state == nullptr), PR_ERR_BAD_ARG,
+             "deg=%d: states exist for deg 2; deg 4 runs state-free (attention only)", deg);
   PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && t > 0 && hq > 0 && h > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
              "bad sizes b=%d t=%d hq=%d h=%d c=%d", b, t, hq, h, c);
@@ -504,16 +506,18 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   const size_t smem = 1024 + 2 * TILE_BYTES + NR * R_BYTES;
   dim3 grid(p.tiles_per_chunk * p.n_chunks, h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PR_LAUNCH_DKV(TT, DG)                                                                                      \
+  do {                                                                                                             \
+    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<TT, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<TT, DG>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));    \
+    chunk_dkv_kernel<TT, DG><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);                         \
+  } while (0)
   if (dtype == PR_BF16) {
-    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_dkv_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);
+    if (deg == 4) PR_LAUNCH_DKV(__nv_bfloat16, 4); else PR_LAUNCH_DKV(__nv_bfloat16, 2);
   } else {
-    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_dkv_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);
+    if (deg == 4) PR_LAUNCH_DKV(__half, 4); else PR_LAUNCH_DKV(__half, 2);
   }
+#undef PR_LAUNCH_DKV
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }

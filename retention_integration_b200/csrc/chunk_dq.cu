@@ -44,7 +44,7 @@ struct ChunkDqParams {
 // One 32-column half of a step for one row: dS = 2 s^2 S g dp into `pk`, row sum of dS * S into da2.
 // SEP: the gate factor is c_i * fk[col] (c_i carries 2 s^2); otherwise 2 s^2 e^{a_i - ak[col]} per pair.
 // MASK: columns beyond `lim` (the row's own position, relative to the step) are dropped.
-template <typename T, bool SEP, bool MASK>
+template <typename T, int DEG, bool SEP, bool MASK>
 __device__ __forceinline__ void dq_half(const uint32_t (&sv)[32], const uint32_t (&pv)[32], const float* __restrict__ fk,
                                         float c_i, float a_i, float inv_l, float dl_i, int lim, uint32_t (&pk)[16],
                                         float& da2) {
@@ -72,7 +72,8 @@ __device__ __forceinline__ void dq_half(const uint32_t (&sv)[32], const uint32_t
         g.x = (col <= lim) ? g.x : 0.f;
         g.y = (col + 1 <= lim) ? g.y : 0.f;
       }
-      const float2 ds = __fmul2_rn(__fmul2_rn(s, g), dp);  // 2 s^2 S e^{a_i-a_j} dp
+      const float2 sp = DEG == 4 ? __fmul2_rn(s, __fmul2_rn(s, s)) : s;  // S^(deg-1)
+      const float2 ds = __fmul2_rn(__fmul2_rn(sp, g), dp);  // deg s^deg S^(deg-1) e^{a_i-a_j} dp
       acc = __ffma2_rn(ds, s, acc);
       pk[col >> 1] = Pack2<T>::from_f32(ds.x, ds.y);
     }
@@ -80,7 +81,7 @@ __device__ __forceinline__ void dq_half(const uint32_t (&sv)[32], const uint32_t
   da2 += acc.x + acc.y;
 }
 
-template <typename T>
+template <typename T, int DEG>
 __global__ void __launch_bounds__(dq::THREADS, 2)
 chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_k,
@@ -216,7 +217,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
     const float a_i = (gated && row_valid) ? a_chunk[(size_t)row * p.h] : 0.f;
     const float dl_i = row_valid ? p.dl[tok * p.hq + qhead] : 0.f;
     const float inv_l = row_valid ? safe_recip(p.l[tok * p.hq + qhead]) : 0.f;
-    const float s2x2 = 2.f * p.scale * p.scale;
+    const float s2x2 = DEG == 4 ? 4.f * (p.scale * p.scale) * (p.scale * p.scale) : 2.f * p.scale * p.scale;  // deg s^deg
     const int wrow0 = row0 + (warp << 5);  // first row of this warp
     float da2 = 0.f;                       // twice the row sum of p * dp
     bool ok = true;
@@ -271,10 +272,10 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
           tmem_wait_ld();
           const int lm = lim - q4 * 32;
           if (sep) {
-            if (mask) dq_half<T, true, true>(sv, pv, sm_fk[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
-            else dq_half<T, true, false>(sv, pv, sm_fk[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
+            if (mask) dq_half<T, DEG, true, true>(sv, pv, sm_fk[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
+            else dq_half<T, DEG, true, false>(sv, pv, sm_fk[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
           } else {
-            dq_half<T, false, true>(sv, pv, sm_ak[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
+            dq_half<T, DEG, false, true>(sv, pv, sm_ak[sb] + q4 * 32, c_i, a_i, inv_l, dl_i, lm, pk, da2);
           }
           tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
         }
@@ -310,7 +311,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
           v.w = Pack2<T>::from_f32(__uint_as_float(acc[8 * j + 6]) + s1.z, __uint_as_float(acc[8 * j + 7]) + s1.w);
           dst[j] = v;
         }
-        p.da_q[tok * p.hq + qhead] = 0.5f * da2;
+        p.da_q[tok * p.hq + qhead] = (1.f / DEG) * da2;
       }
     }
   }
@@ -324,9 +325,12 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
 
 extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c, const void* Q, const void* dO,
                            const void* K, const void* V, const float* a, const float* dl, const float* l,
-                           const float* dq_state, float scale, void* dQ, float* da_q, int device, void* stream) {
+                           const float* dq_state, float scale, int deg, void* dQ, float* da_q, int device,
+                           void* stream) {
   using namespace pr;
   using namespace pr::dq;
+  PR_REQUIRE(deg == 2 || (deg == 4 && dq_state == nullptr), PR_ERR_BAD_ARG,
+             "deg=%d: states exist for deg 2; deg 4 runs state-free (attention only)", deg);
   PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && t > 0 && hq > 0 && h > 0 && hq % h == 0 && c > 0 && t % c == 0, PR_ERR_BAD_ARG,
              "bad sizes b=%d t=%d hq=%d h=%d c=%d", b, t, hq, h, c);
@@ -371,16 +375,18 @@ extern "C" int pr_chunk_dq(int dtype, int b, int t, int hq, int h, int d, int c,
   const size_t smem = 1024 + 2 * TILE_BYTES + 2 * NKV * KV_BYTES;
   dim3 grid(p.tiles_per_chunk * p.n_chunks, hq, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PR_LAUNCH_DQ(TT, DG)                                                                                      \
+  do {                                                                                                           \
+    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<TT, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<TT, DG>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));    \
+    chunk_dq_kernel<TT, DG><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v, tm_st);                         \
+  } while (0)
   if (dtype == PR_BF16) {
-    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_dq_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v, tm_st);
+    if (deg == 4) PR_LAUNCH_DQ(__nv_bfloat16, 4); else PR_LAUNCH_DQ(__nv_bfloat16, 2);
   } else {
-    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(chunk_dq_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_dq_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_dy, tm_k, tm_v, tm_st);
+    if (deg == 4) PR_LAUNCH_DQ(__half, 4); else PR_LAUNCH_DQ(__half, 2);
   }
+#undef PR_LAUNCH_DQ
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }

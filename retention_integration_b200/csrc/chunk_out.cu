@@ -64,7 +64,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 // One 32-column half of an attention step for one query row: p = s^2 S^2 g into `pk`, row sum into
 // l_acc.  SEP: the gate factor is c_i * fk[col] (c_i carries s^2); otherwise s^2 e^{a_i - ak[col]} per
 // pair.  MASK: columns beyond `lim` (the row's own key position, relative to the step) are dropped.
-template <typename T, bool SEP, bool MASK>
+template <typename T, int DEG, bool SEP, bool MASK>
 __device__ __forceinline__ void out_half(const uint32_t (&sv)[32], const float* __restrict__ fk, float c_i, float a_i,
                                          int lim, uint32_t (&pk)[16], float& l_acc) {
   // two columns per instruction: packed fp32 multiplies and adds
@@ -89,7 +89,9 @@ __device__ __forceinline__ void out_half(const uint32_t (&sv)[32], const float* 
         g.x = (col <= lim) ? g.x : 0.f;
         g.y = (col + 1 <= lim) ? g.y : 0.f;
       }
-      const float2 pv = __fmul2_rn(__fmul2_rn(s, s), g);
+      float2 sq = __fmul2_rn(s, s);
+      if (DEG == 4) sq = __fmul2_rn(sq, sq);
+      const float2 pv = __fmul2_rn(sq, g);
       acc = __fadd2_rn(acc, pv);
       pk[col >> 1] = Pack2<T>::from_f32(pv.x, pv.y);
     }
@@ -97,7 +99,7 @@ __device__ __forceinline__ void out_half(const uint32_t (&sv)[32], const float* 
   l_acc += acc.x + acc.y;
 }
 
-template <typename T>
+template <typename T, int DEG>
 __global__ void __launch_bounds__(co::THREADS, 2)
 chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -275,7 +277,7 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
     const float* a_chunk = gated ? p.a + ((size_t)batch * p.n_chunks * p.ck + (size_t)chunk * p.ck) * p.h + kvhead
                                  : nullptr;
     const float a_i = (gated && row_valid) ? a_chunk[(size_t)qpos * p.h] : 0.f;
-    const float s2 = p.scale * p.scale;
+    const float s2 = DEG == 4 ? (p.scale * p.scale) * (p.scale * p.scale) : p.scale * p.scale;  // s^deg
     float l_acc = 0.f;
     bool ok = true;
     // gate sums of the next step's keys, loaded one step ahead by the first TW threads
@@ -330,10 +332,10 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
           tmem_wait_ld();
           const int lm = lim - q4 * 32;
           if (sep) {
-            if (mask) out_half<T, true, true>(sv, sm_fk[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
-            else out_half<T, true, false>(sv, sm_fk[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
+            if (mask) out_half<T, DEG, true, true>(sv, sm_fk[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
+            else out_half<T, DEG, true, false>(sv, sm_fk[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
           } else {
-            out_half<T, false, true>(sv, sm_ak[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
+            out_half<T, DEG, false, true>(sv, sm_ak[sb] + q4 * 32, c_i, a_i, lm, pk, l_acc);
           }
           tmem_st16(tmem + lane_addr + col_s + q4 * 16, pk);
         }
@@ -456,13 +458,15 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
 extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int hq, int h, int d, const void* Q,
                             const void* K, const void* V, const float* a, const void* Z, const void* zg_hi,
                             const void* zg_lo, int state_from_chunk, int q_gate_last, int normalize, float scale,
-                            void* O, float* l_out, int device, void* stream) {
+                            int deg, void* O, float* l_out, int device, void* stream) {
   using namespace pr;
   using namespace pr::co;
   PR_REQUIRE(d == HD, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", d);
   PR_REQUIRE(b > 0 && n_chunks > 0 && cq > 0 && ck >= cq && hq > 0 && h > 0 && hq % h == 0, PR_ERR_BAD_ARG,
              "bad sizes b=%d n=%d cq=%d ck=%d hq=%d h=%d", b, n_chunks, cq, ck, hq, h);
   PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
+  PR_REQUIRE(deg == 2 || (deg == 4 && Z == nullptr), PR_ERR_BAD_ARG,
+             "deg=%d: states exist for deg 2; deg 4 runs state-free (attention only)", deg);
   const bool has_attn = (K != nullptr && V != nullptr);
   PR_REQUIRE(Q && O && aligned16(Q) && aligned16(O) && aligned16(K) && aligned16(V), PR_ERR_BAD_ARG,
              "null or misaligned pointer");
@@ -523,16 +527,18 @@ extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int 
   const size_t smem = 1024 + TILE_BYTES + NR * R_BYTES + 2 * Z_BYTES;
   dim3 grid(p.tiles_per_chunk * n_chunks, hq, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PR_LAUNCH_OUT(TT, DG)                                                                                      \
+  do {                                                                                                             \
+    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<TT, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<TT, DG>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));    \
+    chunk_out_kernel<TT, DG><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);                 \
+  } while (0)
   if (dtype == PR_BF16) {
-    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_out_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);
+    if (deg == 4) PR_LAUNCH_OUT(__nv_bfloat16, 4); else PR_LAUNCH_OUT(__nv_bfloat16, 2);
   } else {
-    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<__half>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
-    chunk_out_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);
+    if (deg == 4) PR_LAUNCH_OUT(__half, 4); else PR_LAUNCH_OUT(__half, 2);
   }
+#undef PR_LAUNCH_OUT
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }

@@ -1,0 +1,222 @@
+// Whole-operator entry points: the chunked forward and backward of power retention
+// (retention/power_retention_maker.py:96-197 and what autograd executes for it) as ONE call
+// each.  The launch sequence that the Python wrapper otherwise drives kernel by kernel lives
+// here in native code, so a host in any language runs the operator through three symbols
+// (pr_workspace_bytes, pr_retention_fwd, pr_retention_bwd) and a Python host pays one ctypes
+// call per pass instead of six / eleven.
+//
+// Memory: the caller allocates everything.  `saved` is what the backward needs from the
+// forward (gate sums, row sums, scanned states and Gram matrices); `scratch` is dead when the
+// call returns its work to the stream and may be reused by the next call on the same stream.
+#include "host.cuh"
+#include "layout.cuh"
+
+namespace pr {
+namespace {
+
+constexpr size_t kAlign = 256;
+inline size_t up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+
+struct Sizes {
+  int n, cp, DR, esz;
+  size_t a, A, l, Z, zh, zfull;             // saved
+  size_t KT, gram;                          // forward scratch
+  size_t dy, dl, QT, dZ, dZg, partS, partG, gh, dqs, gq, dks, wk, daq, dak;  // backward scratch
+  int blocksS, blocksG;
+};
+
+int sizes_of(const pr_problem* p, Sizes* s) {
+  PR_REQUIRE(p != nullptr, PR_ERR_BAD_ARG, "problem is null");
+  PR_REQUIRE(p->d == 64, PR_ERR_BAD_ARG, "head dim %d: this build handles d = 64", p->d);
+  PR_REQUIRE(p->dtype == PR_BF16 || p->dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", p->dtype);
+  PR_REQUIRE(p->b > 0 && p->t > 0 && p->h > 0 && p->hq > 0 && p->hq % p->h == 0 && p->c > 0 && p->t % p->c == 0,
+             PR_ERR_BAD_ARG, "bad sizes b=%d t=%d h=%d hq=%d c=%d", p->b, p->t, p->h, p->hq, p->c);
+  const size_t b = p->b, t = p->t, h = p->h, hq = p->hq, d = p->d;
+  s->n = p->t / p->c;
+  s->cp = (p->c + 63) / 64 * 64;
+  s->DR = ref_dim(p->d);
+  s->esz = 2;
+  const size_t n = s->n, DR = s->DR, cp = s->cp;
+  s->a = up(b * t * h * 4);
+  s->A = up(b * n * h * 4);
+  s->l = up(b * t * hq * 4);
+  s->Z = up(b * n * h * DR * d * 2);
+  s->zh = up(b * n * h * d * d * 2);
+  s->zfull = up(b * n * h * d * d * 4);
+  s->KT = up(b * n * h * d * cp * 2);
+  s->gram = up(b * n * h * d * d * 4);
+  s->dy = up(b * t * hq * d * 2);
+  s->dl = up(b * t * hq * 4);
+  s->QT = up(b * n * hq * d * cp * 2);
+  s->dZ = s->Z;
+  s->dZg = s->gram;
+  s->blocksS = pr_discumsum_bwd_blocks((long long)DR * d);
+  s->blocksG = pr_gram_scan_bwd_blocks(p->d);
+  s->partS = up(b * h * s->blocksS * n * 4);
+  s->partG = up(b * h * s->blocksG * n * 4);
+  s->gh = s->zh;
+  s->dqs = up(b * t * hq * d * 4);
+  s->gq = up(b * t * hq * 4);
+  s->dks = up(b * t * h * d * 4);
+  s->wk = up(b * t * h * 4);
+  s->daq = up(b * t * hq * 4);
+  s->dak = up(b * t * h * 4);
+  return PR_OK;
+}
+
+struct Carver {
+  uint8_t* p;
+  template <typename T>
+  T* take(size_t bytes) {
+    T* r = reinterpret_cast<T*>(p);
+    p += bytes;
+    return r;
+  }
+};
+
+struct Saved {
+  float *a, *A, *l, *zfull;
+  void *Z, *zhi, *zlo;
+};
+Saved carve_saved(void* base, const Sizes& s) {
+  Carver c{static_cast<uint8_t*>(base)};
+  Saved v;
+  v.a = c.take<float>(s.a);
+  v.A = c.take<float>(s.A);
+  v.l = c.take<float>(s.l);
+  v.Z = c.take<void>(s.Z);
+  v.zhi = c.take<void>(s.zh);
+  v.zlo = c.take<void>(s.zh);
+  v.zfull = c.take<float>(s.zfull);
+  return v;
+}
+
+}  // namespace
+}  // namespace pr
+
+extern "C" int pr_workspace_bytes(const pr_problem* prob, int what, size_t* out) {
+  using namespace pr;
+  PR_REQUIRE(out != nullptr, PR_ERR_BAD_ARG, "out is null");
+  Sizes s;
+  int rc = sizes_of(prob, &s);
+  if (rc) return rc;
+  switch (what) {
+    case PR_WS_SAVED:
+      *out = s.a + s.A + s.l + s.Z + 2 * s.zh + s.zfull;
+      break;
+    case PR_WS_FWD_SCRATCH:
+      *out = s.KT + s.gram;
+      break;
+    case PR_WS_BWD_SCRATCH:
+      *out = s.dy + s.dl + 2 * s.QT + s.dZ + s.dZg + s.partS + s.partG + 2 * s.gh + s.dqs + s.gq + s.dks + s.wk +
+             s.daq + s.dak;
+      break;
+    default:
+      return fail(PR_ERR_BAD_ARG, "workspace kind %d", what);
+  }
+  return PR_OK;
+}
+
+extern "C" int pr_retention_fwd(const pr_problem* prob, const void* Q, const void* K, const void* V,
+                                const float* log_G, const float* carry_state, const float* carry_gram, void* O,
+                                void* saved, void* scratch, float* final_state, float* final_gram, int device,
+                                void* stream) {
+  using namespace pr;
+  Sizes s;
+  int rc = sizes_of(prob, &s);
+  if (rc) return rc;
+  PR_REQUIRE(Q && K && V && O && saved && scratch, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(saved) && aligned16(scratch), PR_ERR_BAD_ARG, "workspaces must be 16-byte aligned");
+  PR_REQUIRE((carry_state == nullptr) == (carry_gram == nullptr), PR_ERR_BAD_ARG, "the two carries come together");
+  PR_REQUIRE((final_state == nullptr) == (final_gram == nullptr), PR_ERR_BAD_ARG, "the two final carries come together");
+  const pr_problem& p = *prob;
+  const bool gated = log_G != nullptr;
+  Saved sv = carve_saved(saved, s);
+  Carver c{static_cast<uint8_t*>(scratch)};
+  void* KT = c.take<void>(s.KT);
+  float* gram = c.take<float>(s.gram);
+  const long long E = (long long)s.DR * p.d;
+  // gate sums, discounted transposed keys
+  if ((rc = pr_gate_prep(p.dtype, p.b, p.t, p.h, p.h, p.d, p.c, log_G, K, gated ? sv.a : nullptr, sv.A, KT, nullptr,
+                         nullptr, 0, 1.f, 1, device, stream)))
+    return rc;
+  // chunk states and Gram matrices, then their scans (in place: Z[m] = state entering chunk m)
+  if ((rc = pr_chunk_state(p.dtype, p.b, p.t, p.h, 1, p.d, p.c, KT, KT, V, sv.Z, gram, 1, device, stream))) return rc;
+  if ((rc = pr_discumsum_fwd(p.dtype, p.b, s.n, s.n, p.h, E, sv.Z, sv.Z, sv.A, carry_state, final_state, device,
+                             stream)))
+    return rc;
+  if ((rc = pr_gram_scan_fwd(p.dtype, p.b, s.n, p.h, p.d, gram, sv.zhi, sv.zlo, sv.zfull, sv.A, carry_gram, final_gram,
+                             device, stream)))
+    return rc;
+  // attention + state read-out + normalisation
+  return pr_chunk_out(p.dtype, p.b, s.n, p.c, p.c, p.hq, p.h, p.d, Q, K, V, gated ? sv.a : nullptr, sv.Z, sv.zhi,
+                      sv.zlo, carry_state ? 0 : 1, 0, 1, p.scale, 2, O, sv.l, device, stream);
+}
+
+extern "C" int pr_retention_bwd(const pr_problem* prob, const void* Q, const void* K, const void* V,
+                                const float* log_G, const void* O, const void* dO, int had_carry, void* saved,
+                                void* scratch, void* dQ, void* dK, void* dV, float* dlog_G, int device, void* stream) {
+  using namespace pr;
+  Sizes s;
+  int rc = sizes_of(prob, &s);
+  if (rc) return rc;
+  PR_REQUIRE(Q && K && V && O && dO && saved && scratch && dQ && dK && dV, PR_ERR_BAD_ARG, "null pointer");
+  PR_REQUIRE(aligned16(saved) && aligned16(scratch), PR_ERR_BAD_ARG, "workspaces must be 16-byte aligned");
+  const pr_problem& p = *prob;
+  const bool gated = log_G != nullptr;
+  PR_REQUIRE(!gated || dlog_G != nullptr, PR_ERR_BAD_ARG, "gated problem without a dlog_G output");
+  Saved sv = carve_saved(saved, s);
+  Carver c{static_cast<uint8_t*>(scratch)};
+  void* dy = c.take<void>(s.dy);
+  float* dl = c.take<float>(s.dl);
+  void* QT = c.take<void>(s.QT);
+  void* QTs = c.take<void>(s.QT);
+  void* dZ = c.take<void>(s.dZ);
+  float* dZg = c.take<float>(s.dZg);
+  float* partS = c.take<float>(s.partS);
+  float* partG = c.take<float>(s.partG);
+  void* ghi = c.take<void>(s.gh);
+  void* glo = c.take<void>(s.gh);
+  float* dqs = c.take<float>(s.dqs);
+  float* gq = c.take<float>(s.gq);
+  float* dks = c.take<float>(s.dks);
+  float* wk = c.take<float>(s.wk);
+  float* daq = c.take<float>(s.daq);
+  float* dak = c.take<float>(s.dak);
+  const long long E = (long long)s.DR * p.d;
+  const float* a = gated ? sv.a : nullptr;
+  const float* A = gated ? sv.A : nullptr;
+  const int group = p.hq / p.h;
+  // dy = dO / l, dl = -<O, dO> / l
+  if ((rc = pr_dout_prep(p.dtype, (long long)p.b * p.t * p.hq, p.d, O, dO, sv.l, dy, dl, device, stream))) return rc;
+  // gradient of the state read-out: dZ_m, dZg_m from the gated queries
+  if ((rc = pr_gate_prep(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, log_G, Q, nullptr, nullptr, QT, dl, QTs, 1, p.scale, 0,
+                         device, stream)))
+    return rc;
+  if ((rc = pr_chunk_state(p.dtype, p.b, p.t, p.h, group, p.d, p.c, QT, QTs, dy, dZ, dZg, 0, device, stream))) return rc;
+  // reverse scans (in place: dZ becomes w (.) dS_m)
+  if ((rc = pr_discumsum_bwd(p.dtype, p.b, s.n, p.h, E, dZ, sv.Z, dZ, sv.A, nullptr, nullptr, partS, p.d, 1, device,
+                             stream)))
+    return rc;
+  if ((rc = pr_gram_scan_bwd(p.dtype, p.b, s.n, p.h, p.d, dZg, sv.zfull, ghi, glo, sv.A, nullptr, nullptr, partG, device,
+                             stream)))
+    return rc;
+  // gradients through the expansions
+  if ((rc = pr_expand_grad(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, dy, Q, sv.Z, sv.zhi, sv.zlo, a, A, dl, 1, p.scale,
+                           2.f, had_carry ? 0 : 1, s.n - 1, dqs, gq, device, stream)))
+    return rc;
+  if ((rc = pr_expand_grad(p.dtype, p.b, p.t, p.h, p.h, p.d, p.c, V, K, dZ, ghi, glo, a, A, nullptr, 0, 1.f, 1.f, 0,
+                           s.n - 2, dks, wk, device, stream)))
+    return rc;
+  // attention backward merged with the state-path terms
+  if ((rc = pr_chunk_dq(p.dtype, p.b, p.t, p.hq, p.h, p.d, p.c, Q, dO, K, V, a, dl, sv.l, dqs, p.scale, 2, dQ, daq,
+                        device, stream)))
+    return rc;
+  if ((rc = pr_chunk_dkv(p.dtype, p.b, p.t, p.hq, p.h, p.d, p.c, Q, dO, K, V, dZ, a, A, dl, sv.l, dks, s.n - 2, p.scale,
+                         2, dK, dV, dak, device, stream)))
+    return rc;
+  if (gated)
+    return pr_gate_grad(p.b, p.t, p.h, p.hq, p.c, daq, gq, dak, wk, partS, s.blocksS, partG, s.blocksG, dlog_G, device,
+                        stream);
+  return PR_OK;
+}

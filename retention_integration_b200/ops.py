@@ -208,7 +208,7 @@ def gram_scan_bwd(dZg: torch.Tensor, Zg: torch.Tensor, A: torch.Tensor, dtype, c
 
 
 def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, state_from_chunk: int, scale: float,
-              normalize: bool = True, q_gate_last: bool = False, want_l: bool = True):
+              normalize: bool = True, q_gate_last: bool = False, want_l: bool = True, deg: int = 2):
     """Fused attention + state read-out.  Q [b,n*cq,hq,d]; K,V [b,n*ck,h,d] or None; a [b,n*ck,h] or None;
     Z [b,n,h,DR,d] or None.  Returns (O [b,n*cq,hq,d], l [b,n*cq,hq] fp32 or None)."""
     b, tq, hq, d = Q.shape
@@ -218,7 +218,7 @@ def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, stat
     _call("pr_chunk_out", c_int(dtype_code(Q.dtype)), c_int(b), c_int(n_chunks), c_int(cq), c_int(ck), c_int(hq),
                              c_int(h), c_int(d), ptr(Q), ptr(K), ptr(V), ptr(a), ptr(Z), ptr(zg_hi), ptr(zg_lo),
                              c_int(state_from_chunk), c_int(1 if q_gate_last else 0), c_int(1 if normalize else 0),
-                             c_float(scale), ptr(O), ptr(l), c_int(_dev(Q)), stream_ptr(Q.device))
+                             c_float(scale), c_int(deg), ptr(O), ptr(l), c_int(_dev(Q)), stream_ptr(Q.device))
     return O, l
 
 
@@ -236,19 +236,19 @@ def expand_grad(W, X, State, g_hi, g_lo, a, A, row_g, c: int, h: int, query_side
     return dX, gdot
 
 
-def chunk_dq(Q, dO, K, V, a, dl, l, dq_state, c: int, scale: float):
+def chunk_dq(Q, dO, K, V, a, dl, l, dq_state, c: int, scale: float, deg: int = 2):
     """Returns (dQ [b,t,hq,d], da_q [b,t,hq] fp32)."""
     b, t, hq, d = Q.shape
     h = K.shape[2]
     dQ = torch.empty_like(Q)
     da_q = torch.empty(b, t, hq, device=Q.device, dtype=torch.float32)
     _call("pr_chunk_dq", c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
-                            ptr(Q), ptr(dO), ptr(K), ptr(V), ptr(a), ptr(dl), ptr(l), ptr(dq_state), c_float(scale), ptr(dQ),
-                            ptr(da_q), c_int(_dev(Q)), stream_ptr(Q.device))
+                            ptr(Q), ptr(dO), ptr(K), ptr(V), ptr(a), ptr(dl), ptr(l), ptr(dq_state), c_float(scale),
+                            c_int(deg), ptr(dQ), ptr(da_q), c_int(_dev(Q)), stream_ptr(Q.device))
     return dQ, da_q
 
 
-def chunk_dkv(Q, dO, K, V, wdS, a, A, dl, l, dk_state, c: int, state_chunk_hi: int, scale: float):
+def chunk_dkv(Q, dO, K, V, wdS, a, A, dl, l, dk_state, c: int, state_chunk_hi: int, scale: float, deg: int = 2):
     """Returns (dK, dV [b,t,h,d], da_k [b,t,h] fp32)."""
     b, t, hq, d = Q.shape
     h = K.shape[2]
@@ -256,8 +256,8 @@ def chunk_dkv(Q, dO, K, V, wdS, a, A, dl, l, dk_state, c: int, state_chunk_hi: i
     da_k = torch.empty(b, t, h, device=Q.device, dtype=torch.float32)
     _call("pr_chunk_dkv", c_int(dtype_code(Q.dtype)), c_int(b), c_int(t), c_int(hq), c_int(h), c_int(d), c_int(c),
                              ptr(Q), ptr(dO), ptr(K), ptr(V), ptr(wdS), ptr(a), ptr(A), ptr(dl), ptr(l), ptr(dk_state),
-                             c_int(state_chunk_hi), c_float(scale), ptr(dK), ptr(dV), ptr(da_k), c_int(_dev(Q)),
-                             stream_ptr(Q.device))
+                             c_int(state_chunk_hi), c_float(scale), c_int(deg), ptr(dK), ptr(dV), ptr(da_k),
+                             c_int(_dev(Q)), stream_ptr(Q.device))
     return dK, dV, da_k
 
 
@@ -308,6 +308,56 @@ def state_merge(state, sum_of_keys, S, gram, a_last):
     _call("pr_state_merge", c_int(dtype_code(S.dtype)), c_int(b), c_int(h), c_int(d), ptr(state), ptr(sum_of_keys),
           ptr(S), ptr(gram), ptr(a_last), ptr(new_state), ptr(new_sok), c_int(_dev(S)), stream_ptr(S.device))
     return new_state, new_sok
+
+
+class _Problem(ctypes.Structure):
+    _fields_ = [("dtype", c_int), ("b", c_int), ("t", c_int), ("h", c_int), ("hq", c_int), ("d", c_int), ("c", c_int),
+                ("scale", c_float)]
+
+
+def _problem(Q, h: int, c: int, scale: float) -> _Problem:
+    b, t, hq, d = Q.shape
+    return _Problem(dtype_code(Q.dtype), b, t, h, hq, d, c, scale)
+
+
+def _workspace(prob: _Problem, what: int, dev) -> torch.Tensor:
+    n = ctypes.c_size_t(0)
+    check(lib().pr_workspace_bytes(ctypes.byref(prob), c_int(what), ctypes.byref(n)), "pr_workspace_bytes")
+    return torch.empty(max(n.value, 16), device=dev, dtype=torch.uint8)
+
+
+def retention_fwd(Q, K, V, log_G, c: int, scale: float, carry=None, want_final: bool = False):
+    """The chunked forward in one library call.  Returns (O, saved workspace, final (state, gram) fp32 carries or
+    (None, None))."""
+    b, t, hq, d = Q.shape
+    h = K.shape[2]
+    prob = _problem(Q, h, c, scale)
+    saved = _workspace(prob, 0, Q.device)
+    scratch = _workspace(prob, 1, Q.device)
+    O = torch.empty_like(Q)
+    Cs, Cg = carry if carry is not None else (None, None)
+    Fs = Fg = None
+    if want_final:
+        Fs = torch.empty(b, h, state_rows(d) * d, device=Q.device, dtype=torch.float32)
+        Fg = torch.empty(b, h, d * d, device=Q.device, dtype=torch.float32)
+    _call("pr_retention_fwd", ctypes.byref(prob), ptr(Q), ptr(K), ptr(V), ptr(log_G), ptr(Cs), ptr(Cg), ptr(O),
+          ptr(saved), ptr(scratch), ptr(Fs), ptr(Fg), c_int(_dev(Q)), stream_ptr(Q.device))
+    launch_log.count += 4  # five kernels behind one call
+    return O, saved, Fs, Fg
+
+
+def retention_bwd(Q, K, V, log_G, O, dO, saved, c: int, scale: float, had_carry: bool):
+    """The chunked backward in one library call.  Returns (dQ, dK, dV, dlog_G or None)."""
+    h = K.shape[2]
+    prob = _problem(Q, h, c, scale)
+    scratch = _workspace(prob, 2, Q.device)
+    dQ, dK, dV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+    dG = torch.empty_like(log_G) if log_G is not None else None
+    _call("pr_retention_bwd", ctypes.byref(prob), ptr(Q), ptr(K), ptr(V), ptr(log_G), ptr(O), ptr(dO),
+          c_int(1 if had_carry else 0), ptr(saved), ptr(scratch), ptr(dQ), ptr(dK), ptr(dV), ptr(dG), c_int(_dev(Q)),
+          stream_ptr(Q.device))
+    launch_log.count += 10 if log_G is not None else 9  # eleven (ten ungated) kernels behind one call
+    return dQ, dK, dV, dG
 
 
 def state_to_chunk_layout(state, sum_of_keys, want16: bool = False, want32: bool = False, want_gram: bool = False,

@@ -16,10 +16,16 @@ from ._lib import PRError
 
 _SUPPORTED_D = (64,)
 
+# True: forward and backward of the chunked branch are one library call each (the launch sequence runs in native
+# code); False: the same kernels are launched one by one from Python (per-kernel timing, the sequence-parallel
+# variant, debugging).  Both orders of launches are identical.
+NATIVE_SEQUENCER = True
 
-def _check_inputs(Q, K, V, log_G, deg):
-    if deg != 2:
-        raise PRError(f"deg={deg}: the state kernels implement deg=2 (as the reference's state operators do)")
+
+def _check_inputs(Q, K, V, log_G, deg, state_free=False):
+    if deg != 2 and not (deg == 4 and state_free):
+        raise PRError(f"deg={deg}: the state kernels implement deg=2 (as the reference's state operators do); "
+                      "deg=4 runs on the state-free branch only (chunk_size=None or t <= switch_over_seq_len)")
     if not (Q.is_cuda and K.is_cuda and V.is_cuda):
         raise PRError("Q, K, V must be CUDA tensors: this package has no CPU path")
     assert Q.dtype == K.dtype == V.dtype, f"dtypes of inputs must match: {Q.dtype=}, {K.dtype=}, {V.dtype=}"
@@ -48,6 +54,14 @@ class _ChunkedRetention(torch.autograd.Function):
         n = t // c
         Cs, Cg = carry if carry is not None else (None, None)
         first = carry is None
+        ctx.c, ctx.scale, ctx.first = c, scale, first
+        ctx.native = NATIVE_SEQUENCER
+        if ctx.native:
+            O, saved, Fs, Fg = ops.retention_fwd(Q, K, V, log_G, c, scale, carry, want_final)
+            ctx.save_for_backward(Q, K, V, log_G, O, saved)
+            if want_final:
+                ctx.mark_non_differentiable(Fs, Fg)
+            return O, Fs, Fg
         a, A, KT = ops.gate_prep(K, log_G, c, query_side=False)
         S, gram = ops.chunk_state(KT, None, V, c, h, key_weights=True, want_gram=True)
         del KT
@@ -60,15 +74,18 @@ class _ChunkedRetention(torch.autograd.Function):
             zhi, zlo, zfull = ops.gram_scan_fwd(gram, A, Q.dtype, want_full=True, carry_in=Cg)
         O, l = ops.chunk_out(Q, K, V, a, Z, zhi, zlo, n, c, c, 1 if first else 0, scale)
         ctx.save_for_backward(Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull)
-        ctx.c, ctx.scale, ctx.first = c, scale, first
         if want_final:
             ctx.mark_non_differentiable(Fs, Fg)
         return O, Fs, Fg
 
     @staticmethod
     def backward(ctx, dO, _dFs=None, _dFg=None):
-        Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull = ctx.saved_tensors
         c, scale = ctx.c, ctx.scale
+        if ctx.native:
+            Q, K, V, log_G, O, saved = ctx.saved_tensors
+            dQ, dK, dV, dlog_G = ops.retention_bwd(Q, K, V, log_G, O, dO.contiguous(), saved, c, scale, not ctx.first)
+            return dQ, dK, dV, dlog_G, None, None, None, None
+        Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull = ctx.saved_tensors
         b, t, hq, d = Q.shape
         h = K.shape[2]
         n = t // c
@@ -100,14 +117,14 @@ class _QuadraticRetention(torch.autograd.Function):
     t <= switch_over_seq_len (retention/power_retention_maker.py:128-132)."""
 
     @staticmethod
-    def forward(ctx, Q, K, V, log_G, scale):
+    def forward(ctx, Q, K, V, log_G, scale, deg):
         t = Q.shape[1]
         a = None
         if log_G is not None:
             a, _, _ = ops.gate_prep(K, log_G, t, query_side=False, want_xt=False)
-        O, l = ops.chunk_out(Q, K, V, a, None, None, None, 1, t, t, 1, scale)
+        O, l = ops.chunk_out(Q, K, V, a, None, None, None, 1, t, t, 1, scale, deg=deg)
         ctx.save_for_backward(Q, K, V, a, O, l)
-        ctx.scale = scale
+        ctx.scale, ctx.deg = scale, deg
         ctx.gated = log_G is not None
         return O
 
@@ -117,10 +134,10 @@ class _QuadraticRetention(torch.autograd.Function):
         t = Q.shape[1]
         dO = dO.contiguous()
         _, dl = ops.dout_prep(O, dO, l)
-        dQ, da_q = ops.chunk_dq(Q, dO, K, V, a, dl, l, None, t, ctx.scale)
-        dK, dV, da_k = ops.chunk_dkv(Q, dO, K, V, None, a, None, dl, l, None, t, -1, ctx.scale)
+        dQ, da_q = ops.chunk_dq(Q, dO, K, V, a, dl, l, None, t, ctx.scale, deg=ctx.deg)
+        dK, dV, da_k = ops.chunk_dkv(Q, dO, K, V, None, a, None, dl, l, None, t, -1, ctx.scale, deg=ctx.deg)
         dlog_G = ops.gate_grad(da_q, None, da_k, None, None, None, t) if ctx.gated else None
-        return dQ, dK, dV, dlog_G, None
+        return dQ, dK, dV, dlog_G, None, None
 
 
 def _pad_head_dim(x, d_to):
@@ -154,15 +171,18 @@ def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=
         out = power_retention(_pad_head_dim(Q, 64), _pad_head_dim(K, 64), _pad_head_dim(V, 64), log_G, None, False,
                               deg, scale, chunk_size, switch_over_seq_len)
         return out[..., :d_orig]
-    _check_inputs(Q, K, V, log_G, deg)
     b, t, hq, d = Q.shape
     h = K.shape[2]
+    if chunk_size is not None and switch_over_seq_len is None:
+        switch_over_seq_len = chunk_size
+    t_padded = t if chunk_size is None else -(-t // chunk_size) * chunk_size
+    state_free = (switch_over_seq_len is None or t_padded <= switch_over_seq_len or chunk_size is None) and \
+        initial_state is None and not return_final_state
+    _check_inputs(Q, K, V, log_G, deg, state_free)
     if log_G is not None:
         log_G = log_G.to(torch.float32).contiguous()
     if not scale:
         scale = 1.0 / math.sqrt(d)
-    if chunk_size is not None and switch_over_seq_len is None:
-        switch_over_seq_len = chunk_size
     t_pad = 0
     if chunk_size is not None and t % chunk_size != 0:
         # pad with zero tokens whose gate is 1, as the reference does (:75-83)
@@ -177,7 +197,7 @@ def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=
     quadratic = switch_over_seq_len is None or tt <= switch_over_seq_len or chunk_size is None
     with_state = initial_state is not None or return_final_state
     if quadratic and not with_state:
-        out = _QuadraticRetention.apply(Q, K, V, log_G, float(scale))
+        out = _QuadraticRetention.apply(Q, K, V, log_G, float(scale), int(deg))
         return out[:, :t] if t_pad else out
     carry = None
     if initial_state is not None:

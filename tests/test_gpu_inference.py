@@ -5,7 +5,7 @@ import torch
 import torch.nn.functional as F
 
 from oracle import power_retention_oracle as oracle
-from tests._golden import load, rel_l2
+from tests._golden import load, make_state, rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -124,8 +124,7 @@ def _decode_vs_oracle(dev, b, h, r, tk, seed, check_rows):
     d, D = 64, 2080
     hq = h * r
     Q = torch.randn(b, 1, hq, d, generator=g).bfloat16()
-    state = (torch.randn(b, h, D, d, generator=g) * 0.05).bfloat16()
-    sok = torch.rand(b, h, D, generator=g) * 0.5 + 0.25
+    state, sok = make_state(b, h, d, 24, g)
     K = V = lg = None
     if tk > 0:
         K = torch.randn(b, tk, h, d, generator=g).bfloat16()
