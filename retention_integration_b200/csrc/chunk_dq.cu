@@ -20,7 +20,7 @@ namespace pr {
 
 namespace dq {
 constexpr int HD = 64;
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;             // warps 0-3 rows, 4 TMA, 5 and 6 issue tcgen05.mma
 constexpr int TILE_BYTES = 128 * 128;   // 128 query rows x 64 features
 constexpr int TW = 64;                  // keys per step
 constexpr int KV_BYTES = TW * 128;      // one key or value tile
@@ -88,7 +88,7 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_st) {
   using namespace dq;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, kv_full[NKV], kv_empty[NKV], sp_full, ds_full, acc_done, qdy_free, st_full;
+  __shared__ uint64_t q_full, kv_full[NKV], kv_empty[NKV], sp_full, ds_full, acc_done, qdy_free, st_full, dq_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ __align__(16) float sm_ak[2][TW];  // gate sums a_j of the step's keys
@@ -125,6 +125,8 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
     mbar_init(&acc_done, 1);
     mbar_init(&qdy_free, 1);
     mbar_init(&st_full, 1);
+    mbar_init(&dq_done[0], 1);
+    mbar_init(&dq_done[1], 1);
     fence_mbar_init();
   }
   if (warp == 0) {
@@ -158,13 +160,13 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
       }
     }
   } else if (warp == 5) {
+    // Issuing thread A: S and dP.  One thread issues a product only every ~108 clocks whatever its
+    // shape (measured), so the three products of a step are shared between two threads: this one runs
+    // ahead with S(J+1) and dP(J+1), thread B follows with dQ(J).
     if (lane == 0) {
       bool ok = mbar_wait(&q_full, 0, &abort_flag);
       const uint32_t idesc_s = umma_idesc(128, TW, Pack2<T>::is_bf16, false, false);
-      const uint32_t idesc_q = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
       const uint32_t q_addr = smem_u32(smQ), dy_addr = smem_u32(smDY);
-      // Issue order per step J: S(J+1) while the rows still work on step J, then, once dS(J) is
-      // in tensor memory, dP(J+1) (so the rows can go on) and only then dQ += dS(J) K_J.
       auto issue_s = [&](int J) {
         const uint32_t k_addr = smem_u32(smK + (J % NKV) * KV_BYTES);
 #pragma unroll
@@ -187,23 +189,36 @@ chunk_dq_kernel(const ChunkDqParams p, const __grid_constant__ CUtensorMap tm_q,
         issue_s(0);
         issue_dp(0);
       }
-      for (int J = 0; J < nJ && ok; ++J) {
-        if (J + 1 < nJ) {
-          ok = mbar_wait(&kv_full[(J + 1) % NKV], ((J + 1) / NKV) & 1, &abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(J + 1);
-        }
+      for (int J = 0; J + 1 < nJ && ok; ++J) {
+        ok = mbar_wait(&kv_full[(J + 1) % NKV], ((J + 1) / NKV) & 1, &abort_flag);
+        // S(J+1) overwrites the buffer whose dS fed dQ(J-1): that product must have completed
+        if (ok && J >= 1) ok = mbar_wait(&dq_done[(J + 1) & 1], ((J - 1) >> 1) & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_s(J + 1);
+        // dP(J+1) overwrites dP(J), which the rows have read once dS(J) is in tensor memory
         ok = mbar_wait(&ds_full, J & 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
-        if (J + 1 < nJ) issue_dp(J + 1);
+        issue_dp(J + 1);
+      }
+    }
+  } else if (warp == 6) {
+    // Issuing thread B: dQ += dS(J) K_J, releases the key/value stage
+    if (lane == 0) {
+      bool ok = true;
+      const uint32_t idesc_q = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
+      for (int J = 0; J < nJ && ok; ++J) {
+        ok = mbar_wait(&ds_full, J & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
         const uint32_t k_addr = smem_u32(smK + (J % NKV) * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < TW / 16; ++ks)
           umma_ts(tmem + COL_ACC, tmem + COL_S + (J & 1) * TW + ks * 8,
                   umma_desc_sw128(k_addr + ks * 2048, 8192, 1024), idesc_q, (J > 0 || ks > 0) ? 1u : 0u);
         umma_commit(&kv_empty[J % NKV]);
+        umma_commit(&dq_done[J & 1]);
       }
       if (ok) umma_commit(&acc_done);
     }

@@ -8,12 +8,14 @@
 // Backward use (gradient of the state read-out, retention/_query_state/triton.py:337-448):
 //   x = gated queries, v = dO / l, weights off -> dZ_m; xs = x * dl -> gram = d(gram of Z).
 //
-// One CTA owns two tiles of 128 expanded rows (one group of four warps each), so every
-// operand stage fetched from L2 feeds two products.  The expansion is never written to shared
-// or global memory: each thread owns one expanded row (a, b), multiplies rows a
-// and b of the transposed operand (TMA-loaded, 128-byte swizzled) with packed 16-bit
-// multiplies and stores the products straight into tensor memory as the A operand of
-// tcgen05.mma; the values come in by TMA as the MN-major B operand; fp32 accumulation in
+// One CTA owns two tiles of 128 expanded rows, so every operand stage fetched from L2 feeds two
+// products.  The expansion is never written to shared or global memory: each thread owns the
+// expanded rows (a, b) and (a + 8, b) - the same row of both tiles, which share their second
+// factor - for half of the tokens of a stage, multiplies rows a, a + 8 and b of the transposed
+// operand (TMA-loaded, 128-byte swizzled) with packed 16-bit multiplies and stores the products
+// straight into tensor memory as the A operands of tcgen05.mma.  The kernel is bound by the
+// shared-memory reads that feed those multiplies (traced: ~1000 clocks per stage and SM against ~430
+// for the tensor core), which is why the second factor is read once for two products; the values come in by TMA as the MN-major B operand; fp32 accumulation in
 // tensor memory.  The last grid slot in x computes the Gram matrix with both operands
 // in shared memory.
 #include "host.cuh"
@@ -83,13 +85,13 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     abort_flag = 0;
     for (int s = 0; s < NS; ++s) {
       mbar_init(&x_full[s], 1);
-      mbar_init(&x_empty[s], 4 * NG);
+      mbar_init(&x_empty[s], 4 * NG);  // every expansion warp
       mbar_init(&w_full[s], 1);
       mbar_init(&w_empty[s], gram_cta ? 1 : NG);  // one release per issuing thread
     }
     for (int g = 0; g < NG; ++g)
       for (int s = 0; s < NSA; ++s) {
-        mbar_init(&a_full[g][s], 4);
+        mbar_init(&a_full[g][s], 4 * NG);  // every expansion warp fills its half of each tile's stage
         mbar_init(&a_empty[g][s], 1);
       }
     mbar_init(&acc_done, gram_cta ? 1 : NG);
@@ -176,36 +178,49 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int D2 = ref_dim(HD);
+    // expansion: this thread's row of both tiles (first factors a0 and a0 + 8, common second factor b),
+    // tokens [32 grp, 32 grp + 32) of every stage; epilogue: its row of tile `grp`
+    const int drow0 = slot * NG * 128 + row_in_tile;
+    int a0 = 0, b = 0;
+    if (!gram_cta && drow0 < D2) ref_decode(drow0, &a0, &b);
+    const int a1 = min(a0 + 8, HD - 1);  // the second tile of a pair lies in the same block of second factors
     const int tile = slot * NG + grp;
-    int drow = tile * 128 + row_in_tile;
+    const int drow = tile * 128 + row_in_tile;
     const bool valid = !gram_cta && drow < D2;  // rows past the end still take part in the pipeline
-    int a = 0, b = 0;
-    if (valid) ref_decode(drow, &a, &b);
+    const int a = grp ? a1 : a0;
     bool ok = true;
-    const uint32_t a_base = a * 128 + ((a & 7) << 4), b_base = b * 128 + ((b & 7) << 4);
+    // swz128(row, j) = (row * 128 + ((row & 7) << 4)) ^ (j << 4): one XOR per address
+    const uint32_t a0_base = a0 * 128 + ((a0 & 7) << 4), a1_base = a1 * 128 + ((a1 & 7) << 4),
+                   b_base = b * 128 + ((b & 7) << 4);
     if (!gram_cta) {
       for (int it = 0; it < total; ++it) {
         const int s = it % NS, ph = (it / NS) & 1;
         ok = mbar_wait(&x_full[s], ph, &abort_flag);
         if (!ok) break;
         const uint8_t* xs = smX + s * XT_BYTES;
-        uint32_t r[32];
+        uint32_t r0[16], r1[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          // swz128(row, j) = (row * 128 + ((row & 7) << 4)) ^ (j << 4): one XOR per address
-          const uint4 va = *reinterpret_cast<const uint4*>(xs + (a_base ^ (j << 4)));
-          const uint4 vb = *reinterpret_cast<const uint4*>(xs + (b_base ^ (j << 4)));
-          r[4 * j + 0] = Pack2<T>::mul(va.x, vb.x);
-          r[4 * j + 1] = Pack2<T>::mul(va.y, vb.y);
-          r[4 * j + 2] = Pack2<T>::mul(va.z, vb.z);
-          r[4 * j + 3] = Pack2<T>::mul(va.w, vb.w);
+        for (int jj = 0; jj < 4; ++jj) {
+          const uint32_t off = (uint32_t)((4 * grp + jj) << 4);
+          const uint4 vb = *reinterpret_cast<const uint4*>(xs + (b_base ^ off));
+          const uint4 va = *reinterpret_cast<const uint4*>(xs + (a0_base ^ off));
+          const uint4 vc = *reinterpret_cast<const uint4*>(xs + (a1_base ^ off));
+          r0[4 * jj + 0] = Pack2<T>::mul(va.x, vb.x);
+          r0[4 * jj + 1] = Pack2<T>::mul(va.y, vb.y);
+          r0[4 * jj + 2] = Pack2<T>::mul(va.z, vb.z);
+          r0[4 * jj + 3] = Pack2<T>::mul(va.w, vb.w);
+          r1[4 * jj + 0] = Pack2<T>::mul(vc.x, vb.x);
+          r1[4 * jj + 1] = Pack2<T>::mul(vc.y, vb.y);
+          r1[4 * jj + 2] = Pack2<T>::mul(vc.z, vb.z);
+          r1[4 * jj + 3] = Pack2<T>::mul(vc.w, vb.w);
         }
         const int sa = it % NSA, pha = (it / NSA) & 1;
-        ok = mbar_wait(&a_empty[grp][sa], pha ^ 1, &abort_flag);
+        ok = mbar_wait(&a_empty[0][sa], pha ^ 1, &abort_flag) && mbar_wait(&a_empty[1][sa], pha ^ 1, &abort_flag);
         if (!ok) break;
         tc_fence_after();
-        tmem_st32(tmem + lane_addr + COL_A + (grp * NSA + sa) * 32, r);
-        // The shared-memory stage goes back to TMA only here: the store above has consumed every
+        tmem_st16(tmem + lane_addr + COL_A + (0 * NSA + sa) * 32 + 16 * grp, r0);
+        tmem_st16(tmem + lane_addr + COL_A + (1 * NSA + sa) * 32 + 16 * grp, r1);
+        // The shared-memory stage goes back to TMA only here: the stores above have consumed every
         // product, so every load of the stage has delivered its data.  Released right after the
         // loads were issued (a plain arrive), a refill could overtake loads still queued in this
         // LDS-heavy kernel, and single rows of the state came out built from the wrong 64 tokens
@@ -217,7 +232,10 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[grp][sa]);
+        if (lane == 0) {
+          mbar_arrive(&a_full[0][sa]);
+          mbar_arrive(&a_full[1][sa]);
+        }
       }
     }
     if (ok) ok = mbar_wait(&acc_done, 0, &abort_flag);
@@ -237,15 +255,17 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         }
       } else if (valid) {
         const float wgt = p.key_weights ? ref_key_weight(a, b) : 1.f;
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(p.out) + ((size_t)ch * D2 + drow) * HD);
+        T* dst = static_cast<T*>(p.out) + ((size_t)ch * D2 + drow) * HD;
+        // four 32-byte stores: a full sector per thread and instruction
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint4 v;
-          v.x = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 0]), wgt * __uint_as_float(acc[8 * j + 1]));
-          v.y = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 2]), wgt * __uint_as_float(acc[8 * j + 3]));
-          v.z = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 4]), wgt * __uint_as_float(acc[8 * j + 5]));
-          v.w = Pack2<T>::from_f32(wgt * __uint_as_float(acc[8 * j + 6]), wgt * __uint_as_float(acc[8 * j + 7]));
-          dst[j] = v;
+        for (int j = 0; j < 4; ++j) {
+          uint32_t v[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            v[k] = Pack2<T>::from_f32(wgt * __uint_as_float(acc[16 * j + 2 * k]), wgt * __uint_as_float(acc[16 * j + 2 * k + 1]));
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 16 * j), "r"(v[0]), "r"(v[1]),
+                       "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                       : "memory");
         }
       }
     }

@@ -29,7 +29,7 @@ namespace eg {
 constexpr int HD = 64;
 constexpr int D2 = ref_dim(HD);          // 2560 expanded rows (block layout, see layout.cuh)
 constexpr int NT = D2 / 128;             // 20 tiles of 128 rows = 8 first factors x 16
-constexpr int THREADS = 352;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9 / 10 MMA of row tile 0 / 1
+constexpr int THREADS = 416;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9-12 MMA (two per row tile)
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int G_BYTES = 64 * 128;
 constexpr int NSS = 4;                   // state tiles in flight (TMA latency x L2 bandwidth needs ~100 KB per SM)
@@ -146,17 +146,18 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
       }
     }
   } else if (warp >= 9) {
-    // One issuing thread per row tile: a thread pays some 60-80 clocks per tcgen05.mma it issues
-    // and as much again per commit or barrier wait, so two short instruction streams run side by
-    // side instead of one long one.
+    // Two issuing threads per row tile, one per tensor-memory buffer (even / odd state tiles): a thread
+    // needs ~108 clocks per tcgen05.mma it issues and more per commit, whatever the shape (measured), and
+    // traced timelines showed one thread per row tile setting the kernel's pace at ~1300 clocks per tile
+    // against ~900 for the drain.
     if (lane == 0) {
-      const int rt = warp - 9;
+      const int rt = (warp - 9) >> 1, par = (warp - 9) & 1;
       bool ok = mbar_wait(&w_full, 0, &abort_flag);
       const uint32_t w_addr = smem_u32(smW) + rt * TILE_BYTES;
       const uint32_t idesc = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
-      for (int nt = 0; nt < NT && ok; ++nt) {
+      for (int nt = par; nt < NT && ok; nt += 2) {
         const int s = nt % NSS, ph = (nt / NSS) & 1;
-        const int b = nt & 1;
+        const int b = par;
         // buffer 0 has been drained nt/2 times before tile nt; buffer 1 once more (the Gram part)
         ok = mbar_wait(&d_empty[rt][b], ((nt >> 1) & 1) ^ (b ^ 1), &abort_flag) &&
              mbar_wait(&s_full[s], ph, &abort_flag);
@@ -170,7 +171,8 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         umma_commit(&d_full[rt][b]);
         umma_commit(&s_empty[s]);
         if (nt == 0) {
-          // Gram part: u = x~ (Gs_hi + Gs_lo), once per row tile
+          // Gram part: u = x~ (Gs_hi + Gs_lo), once per row tile, in the columns of buffer 1 (whose own
+          // issuing thread waits until the rows have taken u out)
           ok = mbar_wait(&g_full, 0, &abort_flag) && mbar_wait(&xa_full[rt], 0, &abort_flag);
           if (!ok) break;
           tc_fence_after();
@@ -278,6 +280,20 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
         tc_fence_after();
         if (!ok) continue;
         const uint32_t cd = tmem + lane_addr + col_d(rt, b);
+        // the tile's eight first factors x~[8 tt .. 8 tt + 7] in one 16-byte load, and their gradient
+        // terms collected in registers: the shared-memory column is touched once per tile, after the
+        // loop, so no load of the loop has to wait behind a store to the same memory space
+        float xa8[8], rsum[8];
+        {
+          const uint4 w4 = *reinterpret_cast<const uint4*>(xrow + swz128(r, tt));
+          const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f2 = Pack2<T>::to_f32(w[k]);
+            xa8[2 * k] = f2.x;
+            xa8[2 * k + 1] = f2.y;
+          }
+        }
         // two register buffers: the load of the next 32 columns is in flight while these are used
         uint32_t v[2][32];
         tmem_ld32(cd, v[0]);
@@ -292,12 +308,9 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
             __syncwarp();
             if (lane == 0) mbar_arrive(&d_empty[rt][b]);
           }
-          const int a = 8 * tt + 2 * q;  // first factors a, a+1 (a even)
-          const float2 xa2 = Pack2<T>::to_f32(
-              *reinterpret_cast<const uint32_t*>(xrow + swz128(r, a >> 3) + ((a & 7) << 1)));
 #pragma unroll
           for (int aa = 0; aa < 2; ++aa) {
-            const float xs = aa ? xa2.y : xa2.x;
+            const float xs = xa8[2 * q + aa];  // first factor a = 8 tt + 2 q + aa
             const float2 xa = make_float2(xs, xs);
             float2 ra0 = make_float2(0.f, 0.f), ra1 = ra0;
 #pragma unroll
@@ -310,9 +323,11 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
               else
                 ra0 = __ffma2_rn(val, x[i], ra0);
             }
-            sdx[(a + aa) * 128] += (ra0.x + ra0.y) + (ra1.x + ra1.y);
+            rsum[2 * q + aa] = (ra0.x + ra0.y) + (ra1.x + ra1.y);
           }
         }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sdx[(8 * tt + j) * 128] += rsum[j];
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -337,8 +352,11 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
           dot = fmaf(f2.x, d8[2 * k], dot);
           dot = fmaf(f2.y, d8[2 * k + 1], dot);
         }
-        dst[2 * j] = make_float4(d8[0] * f, d8[1] * f, d8[2] * f, d8[3] * f);
-        dst[2 * j + 1] = make_float4(d8[4] * f, d8[5] * f, d8[6] * f, d8[7] * f);
+        // one 32-byte store: a full sector per thread and instruction
+        asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 2 * j), "f"(d8[0] * f),
+                     "f"(d8[1] * f), "f"(d8[2] * f), "f"(d8[3] * f), "f"(d8[4] * f), "f"(d8[5] * f), "f"(d8[6] * f),
+                     "f"(d8[7] * f)
+                     : "memory");
       }
       p.gdot[(tok0 + row) * p.hx + head] = 0.5f * dot;
     }

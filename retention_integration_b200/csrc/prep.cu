@@ -13,7 +13,7 @@ namespace pr {
 constexpr int kPrepThreads = 256;
 
 template <typename T>
-__global__ void __launch_bounds__(kPrepThreads)
+__global__ void __launch_bounds__(kPrepThreads, 4)
 gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float* __restrict__ a_out,
                  float* __restrict__ A_out, T* __restrict__ xt, const float* __restrict__ row_scale,
                  T* __restrict__ xts, int t, int h, int hx, int d, int c, int cp, int query_side, float mult,
@@ -86,19 +86,40 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
   // the chunk's 64-token tiles are split over gridDim.y blocks (each recomputes the cheap scan)
   const int tiles = cp / 64, tiles_per = (tiles + gridDim.y - 1) / gridDim.y;
   const int tb_end = min(cp, (int)(blockIdx.y + 1) * tiles_per * 64);
-  for (int tb = blockIdx.y * tiles_per * 64; tb < tb_end; tb += 64) {
-    __syncthreads();
-    for (int idx = tid; idx < 64 * vec_per_row; idx += kPrepThreads) {
-      const int r = idx / vec_per_row, v = idx % vec_per_row;
-      const int i = tb + r;
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      float f = 0.f, rs = 0.f;
-      if (i < c) {
-        raw = *reinterpret_cast<const uint4*>(x + ((tok0 + i) * hx + head) * (size_t)d + v * 8);
-        f = query_side ? mult * __expf(0.5f * sm_a[i]) : mult * __expf(0.5f * (A - sm_a[i]));
-        if (xts != nullptr) rs = row_scale[(tok0 + i) * hx + head];
+  // The loads of tile k+1 are issued before tile k is transposed and written out, so a CTA always has
+  // a tile's worth of reads in flight (64 tokens x d features: up to four 16-byte vectors per thread).
+  constexpr int kMaxVec = 4;
+  const int nvec = (64 * vec_per_row + kPrepThreads - 1) / kPrepThreads;  // <= kMaxVec for d <= 128
+  uint4 raw[kMaxVec];
+  float fac[kMaxVec], rsc[kMaxVec];
+  auto load_tile = [&](int tb) {
+#pragma unroll
+    for (int q = 0; q < kMaxVec; ++q) {
+      const int idx = tid + q * kPrepThreads;
+      raw[q] = make_uint4(0, 0, 0, 0);
+      fac[q] = rsc[q] = 0.f;
+      if (q < nvec && idx < 64 * vec_per_row) {
+        const int r = idx / vec_per_row, v = idx % vec_per_row;
+        const int i = tb + r;
+        if (i < c) {
+          raw[q] = *reinterpret_cast<const uint4*>(x + ((tok0 + i) * hx + head) * (size_t)d + v * 8);
+          fac[q] = query_side ? mult * __expf(0.5f * sm_a[i]) : mult * __expf(0.5f * (A - sm_a[i]));
+          if (xts != nullptr) rsc[q] = row_scale[(tok0 + i) * hx + head];
+        }
       }
-      uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    }
+  };
+  const int tb_begin = blockIdx.y * tiles_per * 64;
+  if (tb_begin < tb_end) load_tile(tb_begin);
+  for (int tb = tb_begin; tb < tb_end; tb += 64) {
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kMaxVec; ++q) {
+      const int idx = tid + q * kPrepThreads;
+      if (q >= nvec || idx >= 64 * vec_per_row) continue;
+      const int r = idx / vec_per_row, v = idx % vec_per_row;
+      const float f = fac[q], rs = rsc[q];
+      uint32_t w[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
       uint32_t w2[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -125,6 +146,7 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
         }
       }
     }
+    if (tb + 64 < tb_end) load_tile(tb + 64);  // in flight while this tile is written out
     __syncthreads();
     // each thread writes 8 consecutive tokens of one feature row
     for (int idx = tid; idx < d * 8; idx += kPrepThreads) {

@@ -103,6 +103,22 @@ __device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, vo
   return mbar_wait_slow(bar, parity, abort_flag, budget_ns);
 }
 
+// A wait for something that is far away (a whole phase of the kernel): polls with pauses in between,
+// so that the waiting warp leaves its issue slots to the warps that work.  Bounded like the others.
+static __device__ __noinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                      unsigned pause_ns = 500) {
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(pause_ns);
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > PR_WAIT_BUDGET_NS) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
