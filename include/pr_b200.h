@@ -92,7 +92,8 @@ int pr_selftest_timeout(int budget_us, int* gave_up, int device, void* stream);
  * log_g [b,t,h] or NULL; x [b,t,hx,d].  Writes (when write_a) a [b,t,h] = inclusive
  * cumulative log gate inside each chunk and A [b,n,h] = chunk totals; xt [b,n,hx,d,cp] =
  * gated, transposed copy of x (keys: x*exp((A-a)/2); queries: x*mult*exp(a/2)), zero
- * padded to cp; xts = xt scaled per token by row_scale [b,t,hx] (or NULL). */
+ * padded to cp; xts = xt scaled per token by row_scale [b,t,hx] (or NULL).  With write_a = 0 and a_out given,
+ * a_out is an INPUT: the cumulative gates an earlier call wrote, read instead of scanned again. */
 int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c, const float* log_g, const void* x,
                  float* a_out, float* A_out, void* xt, const float* row_scale, void* xts, int query_side,
                  float mult, int write_a, int device, void* stream);
@@ -139,6 +140,18 @@ int pr_gram_scan_bwd_blocks(int d);
 int pr_gram_scan_bwd(int dtype, int b, int n, int h, int d, const float* dZg, const float* Zg, void* hi, void* lo,
                      const float* A, const float* carry_in, float* carry_out, float* dA_part, int device,
                      void* stream);
+
+/* The two forward scans of a pass (states in place, then Gram matrices) in ONE launch, and the two reverse scans
+ * likewise: same arguments and results as pr_discumsum_fwd (n_out = n, Y = X = Z) + pr_gram_scan_fwd, and as
+ * pr_discumsum_bwd (dX = dY = dZ, row_len = d, key weights on) + pr_gram_scan_bwd.  The reference scans the
+ * states and the sum of keys with two discumsum calls (retention/power_retention_maker.py:167-170). */
+int pr_state_scan_fwd(int dtype, int b, int n, int h, int d, long long E, void* Z, const float* A,
+                      const float* carry_in, float* carry_out, const float* G, void* g_hi, void* g_lo, float* g_full,
+                      const float* g_carry_in, float* g_carry_out, int device, void* stream);
+int pr_state_scan_bwd(int dtype, int b, int n, int h, int d, long long E, void* dZ, const void* Z, const float* A,
+                      const float* carry_in, float* carry_out, float* dA_part, const float* dZg, const float* Zg,
+                      void* g_hi, void* g_lo, const float* g_carry_in, float* g_carry_out, float* g_dA_part, int device,
+                      void* stream);
 
 /* attention + query_state fused (retention/_attention/reference.py:10-69 and
  * retention/_query_state/reference.py:36-96; old bindings attention_fwd,

@@ -14,12 +14,12 @@ constexpr int kPrepThreads = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(kPrepThreads, 4)
-gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float* __restrict__ a_out,
-                 float* __restrict__ A_out, T* __restrict__ xt, const float* __restrict__ row_scale,
-                 T* __restrict__ xts, int t, int h, int hx, int d, int c, int cp, int query_side, float mult,
-                 int write_a) {
+gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in, const T* __restrict__ x,
+                 float* __restrict__ a_out, float* __restrict__ A_out, T* __restrict__ xt,
+                 const float* __restrict__ row_scale, T* __restrict__ xts, int t, int h, int hx, int d, int c, int cp,
+                 int query_side, float mult, int write_a) {
   extern __shared__ float sm_f[];
-  float* sm_a = sm_f;                                    // [c] cumulative gates
+  float* sm_a = sm_f;                                    // [c] cumulative gates (given, or scanned here)
   // transposed tiles [d features][64 tokens], 128-byte rows; the 16-byte chunk holding tokens 8j..8j+7 of
   // feature f sits at chunk j ^ ((f >> 3) & 7), which keeps both the scattered 16-bit writes and the 128-bit
   // row reads free of bank conflicts
@@ -36,8 +36,12 @@ gate_prep_kernel(const float* __restrict__ log_g, const T* __restrict__ x, float
   const int gh = head / (hx / h);  // gate / kv head of this head
   const size_t tok0 = (size_t)batch * t + (size_t)chunk * c;
 
-  // ---- block-wide inclusive scan of the chunk's log gates
-  if (log_g != nullptr) {
+  // ---- the chunk's cumulative log gates: read if a pass before this one has made them, else a
+  // block-wide inclusive scan of the log gates
+  if (a_in != nullptr) {
+    for (int i = tid; i < c; i += kPrepThreads) sm_a[i] = a_in[(tok0 + i) * h + gh];
+    __syncthreads();
+  } else if (log_g != nullptr) {
     if (tid == 0) carry_s = 0.f;
     __syncthreads();
     // four consecutive gates per thread and round (their loads are independent), then one
@@ -319,20 +323,35 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int tiles = cp / 64;
   const dim3 grid(b * (t / c) * hx, xt ? (tiles >= 8 ? 4 : (tiles >= 2 ? 2 : 1)) : 1);
+  // The cumulative gates are scanned once per (batch, chunk, gate head), not once per CTA of the transposing
+  // pass: either they are handed in (write_a = 0 with a_out given: the backward reuses the forward's), or a
+  // first small launch makes them and the transposing launch reads them.
+  const float* a_in = (write_a == 0 && a_out != nullptr && log_g != nullptr) ? a_out : nullptr;
+  const bool two_pass = write_a && xt != nullptr && log_g != nullptr && a_out != nullptr && !query_side && hx == h;
+#define PR_LAUNCH_PREP(TT, GRID, LG, AIN, XT, XTS, WRITE)                                                       \
+  do {                                                                                                         \
+    PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    gate_prep_kernel<TT><<<GRID, kPrepThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,       \
+                                                         static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), t, \
+                                                         h, hx, d, c, cp, query_side, mult, WRITE);               \
+    PR_CUDA(cudaGetLastError());                                                                               \
+  } while (0)
   if (dtype == PR_BF16) {
-    PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    gate_prep_kernel<__nv_bfloat16><<<grid, kPrepThreads, smem, s>>>(
-        log_g, static_cast<const __nv_bfloat16*>(x), a_out, A_out, static_cast<__nv_bfloat16*>(xt), row_scale,
-        static_cast<__nv_bfloat16*>(xts), t, h, hx, d, c, cp, query_side, mult, write_a);
+    if (two_pass) {
+      PR_LAUNCH_PREP(__nv_bfloat16, dim3(b * (t / c) * h, 1), log_g, nullptr, nullptr, nullptr, 1);
+      PR_LAUNCH_PREP(__nv_bfloat16, grid, log_g, a_out, xt, xts, 0);
+    } else {
+      PR_LAUNCH_PREP(__nv_bfloat16, grid, log_g, a_in, xt, xts, write_a);
+    }
   } else {
-    PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    gate_prep_kernel<__half><<<grid, kPrepThreads, smem, s>>>(log_g, static_cast<const __half*>(x), a_out, A_out,
-                                                              static_cast<__half*>(xt), row_scale,
-                                                              static_cast<__half*>(xts), t, h, hx, d, c, cp,
-                                                              query_side, mult, write_a);
+    if (two_pass) {
+      PR_LAUNCH_PREP(__half, dim3(b * (t / c) * h, 1), log_g, nullptr, nullptr, nullptr, 1);
+      PR_LAUNCH_PREP(__half, grid, log_g, a_out, xt, xts, 0);
+    } else {
+      PR_LAUNCH_PREP(__half, grid, log_g, a_in, xt, xts, write_a);
+    }
   }
-  PR_CUDA(cudaGetLastError());
+#undef PR_LAUNCH_PREP
   return PR_OK;
 }
 

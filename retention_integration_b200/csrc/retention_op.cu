@@ -142,11 +142,8 @@ extern "C" int pr_retention_fwd(const pr_problem* prob, const void* Q, const voi
     return rc;
   // chunk states and Gram matrices, then their scans (in place: Z[m] = state entering chunk m)
   if ((rc = pr_chunk_state(p.dtype, p.b, p.t, p.h, 1, p.d, p.c, KT, KT, V, sv.Z, gram, 1, device, stream))) return rc;
-  if ((rc = pr_discumsum_fwd(p.dtype, p.b, s.n, s.n, p.h, E, sv.Z, sv.Z, sv.A, carry_state, final_state, device,
-                             stream)))
-    return rc;
-  if ((rc = pr_gram_scan_fwd(p.dtype, p.b, s.n, p.h, p.d, gram, sv.zhi, sv.zlo, sv.zfull, sv.A, carry_gram, final_gram,
-                             device, stream)))
+  if ((rc = pr_state_scan_fwd(p.dtype, p.b, s.n, p.h, p.d, E, sv.Z, sv.A, carry_state, final_state, gram, sv.zhi,
+                              sv.zlo, sv.zfull, carry_gram, final_gram, device, stream)))
     return rc;
   // attention + state read-out + normalisation
   return pr_chunk_out(p.dtype, p.b, s.n, p.c, p.c, p.hq, p.h, p.d, Q, K, V, gated ? sv.a : nullptr, sv.Z, sv.zhi,
@@ -190,16 +187,13 @@ extern "C" int pr_retention_bwd(const pr_problem* prob, const void* Q, const voi
   // dy = dO / l, dl = -<O, dO> / l
   if ((rc = pr_dout_prep(p.dtype, (long long)p.b * p.t * p.hq, p.d, O, dO, sv.l, dy, dl, device, stream))) return rc;
   // gradient of the state read-out: dZ_m, dZg_m from the gated queries
-  if ((rc = pr_gate_prep(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, log_G, Q, nullptr, nullptr, QT, dl, QTs, 1, p.scale, 0,
-                         device, stream)))
+  if ((rc = pr_gate_prep(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, log_G, Q, gated ? sv.a : nullptr, nullptr, QT, dl,
+                         QTs, 1, p.scale, 0, device, stream)))  // the forward's cumulative gates are read, not rescanned
     return rc;
   if ((rc = pr_chunk_state(p.dtype, p.b, p.t, p.h, group, p.d, p.c, QT, QTs, dy, dZ, dZg, 0, device, stream))) return rc;
   // reverse scans (in place: dZ becomes w (.) dS_m)
-  if ((rc = pr_discumsum_bwd(p.dtype, p.b, s.n, p.h, E, dZ, sv.Z, dZ, sv.A, nullptr, nullptr, partS, p.d, 1, device,
-                             stream)))
-    return rc;
-  if ((rc = pr_gram_scan_bwd(p.dtype, p.b, s.n, p.h, p.d, dZg, sv.zfull, ghi, glo, sv.A, nullptr, nullptr, partG, device,
-                             stream)))
+  if ((rc = pr_state_scan_bwd(p.dtype, p.b, s.n, p.h, p.d, E, dZ, sv.Z, sv.A, nullptr, nullptr, partS, dZg, sv.zfull,
+                              ghi, glo, nullptr, nullptr, partG, device, stream)))
     return rc;
   // gradients through the expansions
   if ((rc = pr_expand_grad(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, dy, Q, sv.Z, sv.zhi, sv.zlo, a, A, dl, 1, p.scale,

@@ -17,7 +17,16 @@
 namespace pr {
 
 constexpr int kScanThreads = 256;
-constexpr int kScanUnroll = 4;
+// Chunks in flight per thread and CTAs per SM the kernels are compiled for: measured on the benchmark's shape,
+// 4 chunks at three CTAs per SM (register cap 85) beat deeper unrolling at lower occupancy (forward 0.073 ms
+// against 0.080, backward 0.101 against 0.119).
+#ifndef PR_SCAN_UNROLL
+#define PR_SCAN_UNROLL 4
+#endif
+constexpr int kScanUnroll = PR_SCAN_UNROLL;
+#ifndef PR_SCAN_MINB
+#define PR_SCAN_MINB 3
+#endif
 
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -39,15 +48,136 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return v;
 }
 
-// X, Y: [b, n(_out), h, E]; A: [b, n, h]; carries: [b, h, E] fp32
+// ---- Gram matrices (d x d fp32 per chunk): tiny, one thread per element.
+// forward: Zg[m] (entering chunk m) as hi + lo 16-bit halves for the tensor cores,
+// and optionally in fp32 for the backward dot product.
+// Arguments of a Gram scan riding along with a state scan (extra CTAs of the same launch).
+struct GramScanArgs {
+  const float* in;      // G (forward) or dZg (backward); null: no Gram scan in this launch
+  const float* zg;      // backward: Zg
+  void* hi;
+  void* lo;
+  float* full;          // forward: optional fp32 copy
+  const float* carry_in;
+  float* carry_out;
+  float* dA_part;       // backward
+  int d;
+};
+
+template <typename T>
+__device__ __forceinline__ void scan_gram_fwd_body(const float* __restrict__ G, T* __restrict__ hi, T* __restrict__ lo,
+                                                   float* __restrict__ full, const float* __restrict__ A,
+                                                   const float* __restrict__ carry_in, float* __restrict__ carry_out,
+                                                   int n, int h, int E, int blk, int head, int batch) {
+  const int e = blk * kScanThreads + threadIdx.x;
+  if (e >= E) return;
+  float run = carry_in ? carry_in[((size_t)batch * h + head) * E + e] : 0.f;
+  for (int m = 0; m < n; ++m) {
+    const size_t idx = (((size_t)batch * n + m) * h + head) * E + e;
+    const float x = G[idx];
+    const float g = __expf(A[((size_t)batch * n + m) * h + head]);
+    const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(run)) : T(__float2half_rn(run));
+    hi[idx] = hv;
+    lo[idx] = T(run - float(hv));
+    if (full) full[idx] = run;
+    run = fmaf(run, g, x);
+  }
+  if (carry_out) carry_out[((size_t)batch * h + head) * E + e] = run;
+}
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads)
+scan_gram_fwd_kernel(const float* __restrict__ G, T* __restrict__ hi, T* __restrict__ lo, float* __restrict__ full,
+                     const float* __restrict__ A, const float* __restrict__ carry_in, float* __restrict__ carry_out,
+                     int n, int h, int E) {
+  scan_gram_fwd_body<T>(G, hi, lo, full, A, carry_in, carry_out, n, h, E, blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+// backward: dG[m] = Gamma[m+1] (+ its transpose: the consumer needs the symmetrised
+// matrix) as hi + lo halves, and the gate-gradient partial sums.  One thread per matrix
+// element; it carries the running gradient of its own element and of the mirrored one.
+template <typename T>
+__device__ __forceinline__ void scan_gram_bwd_body(const float* __restrict__ dZg, const float* __restrict__ Zg,
+                                                   T* __restrict__ hi, T* __restrict__ lo, const float* __restrict__ A,
+                                                   const float* __restrict__ carry_in, float* __restrict__ carry_out,
+                                                   float* __restrict__ dA_part, int n, int h, int d, int blk, int nblk,
+                                                   int head, int batch) {
+  const int E = d * d;
+  const int e = blk * 256 + threadIdx.x;
+  const bool active = e < E;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int et = active ? (e % d) * d + e / d : 0;  // mirrored element
+  const size_t cbase = ((size_t)batch * h + head) * E;
+  float run = (active && carry_in) ? carry_in[cbase + e] : 0.f;
+  float run_t = (active && carry_in) ? carry_in[cbase + et] : 0.f;
+  float* part = dA_part + (((size_t)batch * h + head) * nblk * 8 + blk * 8 + warp) * n;
+  // The loads of a chunk do not depend on the running gradient: four chunks' worth are issued
+  // before the dependent chain of FMAs walks through them.
+  constexpr int UN = 4;
+  for (int m0 = n - 1; m0 >= 0; m0 -= UN) {
+    float dz[UN], dzt[UN], zg[UN], gg[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int m = m0 - u;
+      dz[u] = dzt[u] = zg[u] = 0.f;
+      gg[u] = 1.f;
+      if (m >= 0) {
+        const size_t base = (((size_t)batch * n + m) * h + head) * E;
+        gg[u] = A[((size_t)batch * n + m) * h + head];
+        if (active) {
+          dz[u] = dZg[base + e];
+          dzt[u] = dZg[base + et];
+          zg[u] = Zg[base + e];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int m = m0 - u;
+      if (m < 0) break;
+      const size_t base = (((size_t)batch * n + m) * h + head) * E;
+      const float g = __expf(gg[u]);
+      float dot = 0.f;
+      if (active) {
+        const float sym = run + run_t;
+        const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(sym)) : T(__float2half_rn(sym));
+        hi[base + e] = hv;
+        lo[base + e] = T(sym - float(hv));
+        dot = zg[u] * run * g;
+        run = fmaf(run, g, dz[u]);
+        run_t = fmaf(run_t, g, dzt[u]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      if (lane == 0) part[m] = dot;
+    }
+  }
+  if (active && carry_out) carry_out[cbase + e] = run;
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg, T* __restrict__ hi,
+                     T* __restrict__ lo, const float* __restrict__ A, const float* __restrict__ carry_in,
+                     float* __restrict__ carry_out, float* __restrict__ dA_part, int n, int h, int d) {
+  scan_gram_bwd_body<T>(dZg, Zg, hi, lo, A, carry_in, carry_out, dA_part, n, h, d, blockIdx.x, gridDim.x, blockIdx.y,
+                        blockIdx.z);
+}
+
+// X, Y: [b, n(_out), h, E]; A: [b, n, h]; carries: [b, h, E] fp32
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads, PR_SCAN_MINB)
 scan_fwd_kernel(const T* X, T* Y, const float* __restrict__ A,  // X and Y may be the same buffer: no __restrict__
                 const float* __restrict__ carry_in, float* __restrict__ carry_out, int n, int n_out, int h,
-                size_t E) {
+                size_t E, int state_blocks, GramScanArgs gram) {
+  const int head = blockIdx.y, batch = blockIdx.z;
+  if ((int)blockIdx.x >= state_blocks) {
+    // the Gram matrices' scan rides along in the last CTAs of the grid: its 4096 serial chains per head would
+    // otherwise be a launch of their own that does nothing but wait for memory
+    scan_gram_fwd_body<T>(gram.in, static_cast<T*>(gram.hi), static_cast<T*>(gram.lo), gram.full, A, gram.carry_in,
+                          gram.carry_out, n, h, gram.d * gram.d, (int)blockIdx.x - state_blocks, head, batch);
+    return;
+  }
   const size_t e0 = ((size_t)blockIdx.x * kScanThreads + threadIdx.x) * 8;
   if (e0 >= E) return;
-  const int head = blockIdx.y, batch = blockIdx.z;
   float run[8];
   if (carry_in != nullptr) {
     const float4* ci = reinterpret_cast<const float4*>(carry_in + ((size_t)batch * h + head) * E + e0);
@@ -95,13 +225,19 @@ scan_fwd_kernel(const T* X, T* Y, const float* __restrict__ A,  // X and Y may b
 // dA_part: [b, h, 8 * gridDim.x, n] per-warp partial sums of exp(A[m]) * <Y[m], G[m+1]>.
 // row_weights: apply the key-side weight (1 or 2) of expanded row (e / row_len) to dX.
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanThreads, PR_SCAN_MINB)
 scan_bwd_kernel(const T* dY, const T* __restrict__ Y, T* dX, const float* __restrict__ A,  // dY may alias dX
                 const float* __restrict__ carry_in, float* __restrict__ carry_out, float* __restrict__ dA_part, int n,
-                int h, size_t E, int row_len, int row_weights) {
+                int h, size_t E, int row_len, int row_weights, int state_blocks, GramScanArgs gram) {
+  const int head = blockIdx.y, batch = blockIdx.z;
+  if ((int)blockIdx.x >= state_blocks) {
+    scan_gram_bwd_body<T>(gram.in, gram.zg, static_cast<T*>(gram.hi), static_cast<T*>(gram.lo), A, gram.carry_in,
+                          gram.carry_out, gram.dA_part, n, h, gram.d, (int)blockIdx.x - state_blocks,
+                          (int)gridDim.x - state_blocks, head, batch);
+    return;
+  }
   const size_t e0 = ((size_t)blockIdx.x * kScanThreads + threadIdx.x) * 8;
   const bool active = e0 < E;
-  const int head = blockIdx.y, batch = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float run[8];
 #pragma unroll
@@ -124,7 +260,7 @@ scan_bwd_kernel(const T* dY, const T* __restrict__ Y, T* dX, const float* __rest
   const bool reduce_only = (dX == nullptr);
   // one partial per warp and chunk: no block-wide barrier inside the chunk loop
   float* part = reduce_only ? nullptr
-                            : dA_part + (((size_t)batch * h + head) * gridDim.x * (kScanThreads / 32) +
+                            : dA_part + (((size_t)batch * h + head) * state_blocks * (kScanThreads / 32) +
                                          blockIdx.x * (kScanThreads / 32) + warp) * n;
   for (int m0 = n - 1; m0 >= 0; m0 -= kScanUnroll) {
     uint4 gv[kScanUnroll], yv[kScanUnroll];
@@ -179,98 +315,12 @@ scan_bwd_kernel(const T* dY, const T* __restrict__ Y, T* dX, const float* __rest
   }
 }
 
-// ---- Gram matrices (d x d fp32 per chunk): tiny, one thread per element.
-// forward: Zg[m] (entering chunk m) as hi + lo 16-bit halves for the tensor cores,
-// and optionally in fp32 for the backward dot product.
-template <typename T>
-__global__ void scan_gram_fwd_kernel(const float* __restrict__ G, T* __restrict__ hi, T* __restrict__ lo,
-                                     float* __restrict__ full, const float* __restrict__ A,
-                                     const float* __restrict__ carry_in, float* __restrict__ carry_out, int n, int h,
-                                     int E) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= E) return;
-  const int head = blockIdx.y, batch = blockIdx.z;
-  float run = carry_in ? carry_in[((size_t)batch * h + head) * E + e] : 0.f;
-  for (int m = 0; m < n; ++m) {
-    const size_t idx = (((size_t)batch * n + m) * h + head) * E + e;
-    const float x = G[idx];
-    const float g = __expf(A[((size_t)batch * n + m) * h + head]);
-    const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(run)) : T(__float2half_rn(run));
-    hi[idx] = hv;
-    lo[idx] = T(run - float(hv));
-    if (full) full[idx] = run;
-    run = fmaf(run, g, x);
-  }
-  if (carry_out) carry_out[((size_t)batch * h + head) * E + e] = run;
-}
-
-// backward: dG[m] = Gamma[m+1] (+ its transpose: the consumer needs the symmetrised
-// matrix) as hi + lo halves, and the gate-gradient partial sums.  One thread per matrix
-// element; it carries the running gradient of its own element and of the mirrored one.
-template <typename T>
-__global__ void __launch_bounds__(256)
-scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg, T* __restrict__ hi,
-                     T* __restrict__ lo, const float* __restrict__ A, const float* __restrict__ carry_in,
-                     float* __restrict__ carry_out, float* __restrict__ dA_part, int n, int h, int d) {
-  const int E = d * d;
-  const int e = blockIdx.x * 256 + threadIdx.x;
-  const bool active = e < E;
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int et = active ? (e % d) * d + e / d : 0;  // mirrored element
-  const size_t cbase = ((size_t)batch * h + head) * E;
-  float run = (active && carry_in) ? carry_in[cbase + e] : 0.f;
-  float run_t = (active && carry_in) ? carry_in[cbase + et] : 0.f;
-  float* part = dA_part + (((size_t)batch * h + head) * gridDim.x * 8 + blockIdx.x * 8 + warp) * n;
-  // The loads of a chunk do not depend on the running gradient: four chunks' worth are issued
-  // before the dependent chain of FMAs walks through them.
-  constexpr int UN = 4;
-  for (int m0 = n - 1; m0 >= 0; m0 -= UN) {
-    float dz[UN], dzt[UN], zg[UN], gg[UN];
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int m = m0 - u;
-      dz[u] = dzt[u] = zg[u] = 0.f;
-      gg[u] = 1.f;
-      if (m >= 0) {
-        const size_t base = (((size_t)batch * n + m) * h + head) * E;
-        gg[u] = A[((size_t)batch * n + m) * h + head];
-        if (active) {
-          dz[u] = dZg[base + e];
-          dzt[u] = dZg[base + et];
-          zg[u] = Zg[base + e];
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int m = m0 - u;
-      if (m < 0) break;
-      const size_t base = (((size_t)batch * n + m) * h + head) * E;
-      const float g = __expf(gg[u]);
-      float dot = 0.f;
-      if (active) {
-        const float sym = run + run_t;
-        const T hv = Pack2<T>::is_bf16 ? T(__float2bfloat16_rn(sym)) : T(__float2half_rn(sym));
-        hi[base + e] = hv;
-        lo[base + e] = T(sym - float(hv));
-        dot = zg[u] * run * g;
-        run = fmaf(run, g, dz[u]);
-        run_t = fmaf(run_t, g, dzt[u]);
-      }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-      if (lane == 0) part[m] = dot;
-    }
-  }
-  if (active && carry_out) carry_out[cbase + e] = run;
-}
-
 }  // namespace pr
 
-extern "C" int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long long E, const void* X, void* Y,
-                                const float* A, const float* carry_in, float* carry_out, int device, void* stream) {
-  using namespace pr;
+namespace pr {
+static int launch_scan_fwd(int dtype, int b, int n, int n_out, int h, long long E, const void* X, void* Y, const float* A,
+                           const float* carry_in, float* carry_out, const GramScanArgs& gram, int device,
+                           void* stream) {
   PR_REQUIRE(b > 0 && n > 0 && h > 0 && E > 0 && E % 8 == 0, PR_ERR_BAD_ARG, "bad sizes b=%d n=%d h=%d E=%lld", b, n,
              h, E);
   PR_REQUIRE(n_out == n || n_out == n + 1, PR_ERR_BAD_ARG, "n_out=%d must be n or n+1", n_out);
@@ -278,30 +328,57 @@ extern "C" int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long 
   PR_REQUIRE(X && A && aligned16(X) && aligned16(Y), PR_ERR_BAD_ARG, "null or misaligned pointer");
   PR_REQUIRE(Y != nullptr || carry_out != nullptr, PR_ERR_BAD_ARG, "neither an output nor a carry was requested");
   PR_REQUIRE(h <= 65535 && b <= 65535, PR_ERR_BAD_ARG, "h and b must be <= 65535");
+  PR_REQUIRE(gram.in == nullptr || (gram.hi && gram.lo && gram.d > 0), PR_ERR_BAD_ARG, "Gram scan without outputs");
   PR_CUDA(cudaSetDevice(device));
-  dim3 grid((unsigned)((E / 8 + kScanThreads - 1) / kScanThreads), h, b);
+  const int state_blocks = (int)((E / 8 + kScanThreads - 1) / kScanThreads);
+  const int gram_blocks = gram.in ? (gram.d * gram.d + kScanThreads - 1) / kScanThreads : 0;
+  dim3 grid((unsigned)(state_blocks + gram_blocks), h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
     scan_fwd_kernel<__nv_bfloat16><<<grid, kScanThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(X),
                                                                 static_cast<__nv_bfloat16*>(Y), A, carry_in, carry_out,
-                                                                n, n_out, h, (size_t)E);
+                                                                n, n_out, h, (size_t)E, state_blocks, gram);
   else if (dtype == PR_FP16)
     scan_fwd_kernel<__half><<<grid, kScanThreads, 0, s>>>(static_cast<const __half*>(X), static_cast<__half*>(Y), A,
-                                                         carry_in, carry_out, n, n_out, h, (size_t)E);
+                                                         carry_in, carry_out, n, n_out, h, (size_t)E, state_blocks,
+                                                         gram);
   else
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_CUDA(cudaGetLastError());
   return PR_OK;
+}
+}  // namespace pr
+
+extern "C" int pr_discumsum_fwd(int dtype, int b, int n, int n_out, int h, long long E, const void* X, void* Y,
+                                const float* A, const float* carry_in, float* carry_out, int device, void* stream) {
+  pr::GramScanArgs none = {};
+  return pr::launch_scan_fwd(dtype, b, n, n_out, h, E, X, Y, A, carry_in, carry_out, none, device, stream);
+}
+
+// pr_discumsum_fwd (in place: n_out = n) and pr_gram_scan_fwd in ONE launch: the Gram scan takes the last CTAs.
+extern "C" int pr_state_scan_fwd(int dtype, int b, int n, int h, int d, long long E, void* Z, const float* A,
+                                 const float* carry_in, float* carry_out, const float* G, void* g_hi, void* g_lo,
+                                 float* g_full, const float* g_carry_in, float* g_carry_out, int device, void* stream) {
+  PR_REQUIRE(G && g_hi && g_lo && d > 0, PR_ERR_BAD_ARG, "null Gram pointers");
+  pr::GramScanArgs g = {};
+  g.in = G;
+  g.hi = g_hi;
+  g.lo = g_lo;
+  g.full = g_full;
+  g.carry_in = g_carry_in;
+  g.carry_out = g_carry_out;
+  g.d = d;
+  return pr::launch_scan_fwd(dtype, b, n, n, h, E, Z, Z, A, carry_in, carry_out, g, device, stream);
 }
 
 extern "C" int pr_discumsum_bwd_blocks(long long E) {
   return (int)((E / 8 + pr::kScanThreads - 1) / pr::kScanThreads) * (pr::kScanThreads / 32);
 }
 
-extern "C" int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, const void* dY, const void* Y, void* dX,
-                                const float* A, const float* carry_in, float* carry_out, float* dA_part, int row_len,
-                                int row_weights, int device, void* stream) {
-  using namespace pr;
+namespace pr {
+static int launch_scan_bwd(int dtype, int b, int n, int h, long long E, const void* dY, const void* Y, void* dX,
+                           const float* A, const float* carry_in, float* carry_out, float* dA_part, int row_len,
+                           int row_weights, const GramScanArgs& gram, int device, void* stream) {
   PR_REQUIRE(b > 0 && n > 0 && h > 0 && E > 0 && E % 8 == 0, PR_ERR_BAD_ARG, "bad sizes b=%d n=%d h=%d E=%lld", b, n,
              h, E);
   PR_REQUIRE(dY && A && aligned16(dY) && aligned16(Y) && aligned16(dX), PR_ERR_BAD_ARG,
@@ -309,22 +386,53 @@ extern "C" int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, con
   PR_REQUIRE((dX == nullptr && carry_out != nullptr) || (dX != nullptr && Y != nullptr && dA_part != nullptr),
              PR_ERR_BAD_ARG, "give dX, Y and dA_part together, or none of them and a carry_out");
   PR_REQUIRE(!row_weights || (row_len > 0 && row_len % 8 == 0), PR_ERR_BAD_ARG, "row_len %d", row_len);
+  PR_REQUIRE(gram.in == nullptr || (gram.zg && gram.hi && gram.lo && gram.dA_part && gram.d > 0 && gram.d <= 128),
+             PR_ERR_BAD_ARG, "Gram scan without its tensors");
   PR_CUDA(cudaSetDevice(device));
-  dim3 grid((unsigned)((E / 8 + kScanThreads - 1) / kScanThreads), h, b);
+  const int state_blocks = (int)((E / 8 + kScanThreads - 1) / kScanThreads);
+  const int gram_blocks = gram.in ? (gram.d * gram.d + 255) / 256 : 0;
+  dim3 grid((unsigned)(state_blocks + gram_blocks), h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
     scan_bwd_kernel<__nv_bfloat16><<<grid, kScanThreads, 0, s>>>(
         static_cast<const __nv_bfloat16*>(dY), static_cast<const __nv_bfloat16*>(Y), static_cast<__nv_bfloat16*>(dX),
-        A, carry_in, carry_out, dA_part, n, h, (size_t)E, row_len, row_weights);
+        A, carry_in, carry_out, dA_part, n, h, (size_t)E, row_len, row_weights, state_blocks, gram);
   else if (dtype == PR_FP16)
     scan_bwd_kernel<__half><<<grid, kScanThreads, 0, s>>>(static_cast<const __half*>(dY),
                                                          static_cast<const __half*>(Y), static_cast<__half*>(dX), A,
                                                          carry_in, carry_out, dA_part, n, h, (size_t)E, row_len,
-                                                         row_weights);
+                                                         row_weights, state_blocks, gram);
   else
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_CUDA(cudaGetLastError());
   return PR_OK;
+}
+}  // namespace pr
+
+extern "C" int pr_discumsum_bwd(int dtype, int b, int n, int h, long long E, const void* dY, const void* Y, void* dX,
+                                const float* A, const float* carry_in, float* carry_out, float* dA_part, int row_len,
+                                int row_weights, int device, void* stream) {
+  pr::GramScanArgs none = {};
+  return pr::launch_scan_bwd(dtype, b, n, h, E, dY, Y, dX, A, carry_in, carry_out, dA_part, row_len, row_weights, none,
+                             device, stream);
+}
+
+// pr_discumsum_bwd (in place, with key weights) and pr_gram_scan_bwd in ONE launch.
+extern "C" int pr_state_scan_bwd(int dtype, int b, int n, int h, int d, long long E, void* dZ, const void* Z,
+                                 const float* A, const float* carry_in, float* carry_out, float* dA_part,
+                                 const float* dZg, const float* Zg, void* g_hi, void* g_lo, const float* g_carry_in,
+                                 float* g_carry_out, float* g_dA_part, int device, void* stream) {
+  PR_REQUIRE(dZg && Zg && g_hi && g_lo && g_dA_part && d > 0, PR_ERR_BAD_ARG, "null Gram pointers");
+  pr::GramScanArgs g = {};
+  g.in = dZg;
+  g.zg = Zg;
+  g.hi = g_hi;
+  g.lo = g_lo;
+  g.carry_in = g_carry_in;
+  g.carry_out = g_carry_out;
+  g.dA_part = g_dA_part;
+  g.d = d;
+  return pr::launch_scan_bwd(dtype, b, n, h, E, dZ, Z, dZ, A, carry_in, carry_out, dA_part, d, 1, g, device, stream);
 }
 
 extern "C" int pr_gram_scan_fwd(int dtype, int b, int n, int h, int d, const float* G, void* hi, void* lo,

@@ -77,7 +77,7 @@ def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, n: int, k: int
 
 
 def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.0, want_gates: bool = True,
-              row_scale=None, want_xt: bool = True):
+              row_scale=None, want_xt: bool = True, a_in=None):
     """x [b,t,hx,d], log_g [b,t,h] fp32 or None ->
     (a [b,t,h] fp32 or None, A [b,n,h] fp32, xT [b,n,hx,d,cp]) with cp = c rounded up to 64.
     With row_scale [b,t,hx] fp32 a fourth result is the copy of xT scaled per token."""
@@ -99,10 +99,11 @@ def gate_prep(x: torch.Tensor, log_g, c: int, query_side: bool, mult: float = 1.
     A = torch.empty(b, n, h, device=x.device, dtype=torch.float32) if write else None
     xt = torch.empty(b, n, hx, d, cp, device=x.device, dtype=x.dtype) if want_xt else None
     xts = torch.empty_like(xt) if (row_scale is not None and want_xt) else None
+    # a_in: cumulative gates an earlier call has made (the backward reuses the forward's): read, not recomputed
     _call("pr_gate_prep", c_int(dtype_code(x.dtype)), c_int(b), c_int(t), c_int(h), c_int(hx), c_int(d), c_int(c),
-                             ptr(log_g), ptr(x), ptr(a), ptr(A), ptr(xt), ptr(row_scale), ptr(xts),
-                             c_int(1 if query_side else 0), c_float(mult), c_int(1 if write else 0), c_int(_dev(x)),
-                             stream_ptr(x.device))
+                             ptr(log_g), ptr(x), ptr(a if a_in is None else a_in), ptr(A), ptr(xt), ptr(row_scale),
+                             ptr(xts), c_int(1 if query_side else 0), c_float(mult),
+                             c_int(1 if (write and a_in is None) else 0), c_int(_dev(x)), stream_ptr(x.device))
     if row_scale is not None:
         return a, A, xt, xts
     return a, A, xt
@@ -205,6 +206,41 @@ def gram_scan_bwd(dZg: torch.Tensor, Zg: torch.Tensor, A: torch.Tensor, dtype, c
                                  ptr(hi), ptr(lo), ptr(A), ptr(carry_in), ptr(carry_out), ptr(part), c_int(_dev(dZg)),
                                  stream_ptr(dZg.device))
     return (hi, lo, part, carry_out) if want_carry else (hi, lo, part)
+
+
+def state_scan_fwd(S, gram, A, dtype, carry_in=None, gcarry_in=None, want_carry: bool = False):
+    """discumsum_fwd (in place) + gram_scan_fwd (with the fp32 copy) in one launch.
+    Returns (Z, zhi, zlo, zfull, carry_out or None, gram carry_out or None)."""
+    b, n, h = S.shape[:3]
+    d = gram.shape[-1]
+    E = S[0, 0, 0].numel()
+    hi = torch.empty(b, n, h, d, d, device=S.device, dtype=dtype)
+    lo = torch.empty_like(hi)
+    full = torch.empty_like(gram)
+    co = torch.empty(b, h, E, device=S.device, dtype=torch.float32) if want_carry else None
+    gco = torch.empty(b, h, d * d, device=S.device, dtype=torch.float32) if want_carry else None
+    _call("pr_state_scan_fwd", c_int(dtype_code(S.dtype)), c_int(b), c_int(n), c_int(h), c_int(d), c_longlong(E),
+          ptr(S), ptr(A), ptr(carry_in), ptr(co), ptr(gram), ptr(hi), ptr(lo), ptr(full), ptr(gcarry_in), ptr(gco),
+          c_int(_dev(S)), stream_ptr(S.device))
+    return S, hi, lo, full, co, gco
+
+
+def state_scan_bwd(dZ, Z, dZg, zfull, A, dtype, carry_in=None, gcarry_in=None):
+    """discumsum_bwd (in place, key weights on) + gram_scan_bwd in one launch.
+    Returns (wdS, dA_state partial sums, ghi, glo, dA_gram partial sums)."""
+    b, n, h = dZ.shape[:3]
+    d = dZg.shape[-1]
+    E = dZ[0, 0, 0].numel()
+    blocks = lib().pr_discumsum_bwd_blocks(c_longlong(E))
+    gblocks = lib().pr_gram_scan_bwd_blocks(c_int(d))
+    part = torch.empty(b, h, blocks, n, device=dZ.device, dtype=torch.float32)
+    gpart = torch.empty(b, h, gblocks, n, device=dZ.device, dtype=torch.float32)
+    hi = torch.empty(b, n, h, d, d, device=dZ.device, dtype=dtype)
+    lo = torch.empty_like(hi)
+    _call("pr_state_scan_bwd", c_int(dtype_code(dZ.dtype)), c_int(b), c_int(n), c_int(h), c_int(d), c_longlong(E),
+          ptr(dZ), ptr(Z), ptr(A), ptr(carry_in), ptr(None), ptr(part), ptr(dZg), ptr(zfull), ptr(hi), ptr(lo),
+          ptr(gcarry_in), ptr(None), ptr(gpart), c_int(_dev(dZ)), stream_ptr(dZ.device))
+    return dZ, part, hi, lo, gpart
 
 
 def chunk_out(Q, K, V, a, Z, zg_hi, zg_lo, n_chunks: int, cq: int, ck: int, state_from_chunk: int, scale: float,

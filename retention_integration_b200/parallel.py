@@ -190,7 +190,7 @@ class _SeqParallelRetention(torch.autograd.Function):
         n = t // c
         dO = dO.contiguous()
         dy, dl = ops.dout_prep(O, dO, l)
-        _, _, QT, QTs = ops.gate_prep(Q, log_G, c, query_side=True, mult=scale, row_scale=dl)
+        _, _, QT, QTs = ops.gate_prep(Q, log_G, c, query_side=True, mult=scale, row_scale=dl, a_in=a)
         dZ, dZg = ops.chunk_state(QT, QTs, dy, c, h, key_weights=False, want_gram=True)
         del QT, QTs
         # gradient carries: what this block sends left if nothing came from the right

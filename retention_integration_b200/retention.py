@@ -65,13 +65,7 @@ class _ChunkedRetention(torch.autograd.Function):
         a, A, KT = ops.gate_prep(K, log_G, c, query_side=False)
         S, gram = ops.chunk_state(KT, None, V, c, h, key_weights=True, want_gram=True)
         del KT
-        Fs = Fg = None
-        if want_final:
-            Z, Fs = ops.discumsum_fwd(S, A, inplace=True, carry_in=Cs, want_carry=True)
-            zhi, zlo, zfull, Fg = ops.gram_scan_fwd(gram, A, Q.dtype, want_full=True, carry_in=Cg, want_carry=True)
-        else:
-            Z = ops.discumsum_fwd(S, A, inplace=True, carry_in=Cs)
-            zhi, zlo, zfull = ops.gram_scan_fwd(gram, A, Q.dtype, want_full=True, carry_in=Cg)
+        Z, zhi, zlo, zfull, Fs, Fg = ops.state_scan_fwd(S, gram, A, Q.dtype, Cs, Cg, want_carry=want_final)
         O, l = ops.chunk_out(Q, K, V, a, Z, zhi, zlo, n, c, c, 1 if first else 0, scale)
         ctx.save_for_backward(Q, K, V, log_G, a, A, O, l, Z, zhi, zlo, zfull)
         if want_final:
@@ -92,12 +86,11 @@ class _ChunkedRetention(torch.autograd.Function):
         dO = dO.contiguous()
         dy, dl = ops.dout_prep(O, dO, l)
         # state read-out: dZ_m = sum_i phi(q~_i) dy_i^T, dZg_m = sum_i dl_i q~_i q~_i^T
-        _, _, QT, QTs = ops.gate_prep(Q, log_G, c, query_side=True, mult=scale, row_scale=dl)
+        _, _, QT, QTs = ops.gate_prep(Q, log_G, c, query_side=True, mult=scale, row_scale=dl, a_in=a)
         dZ, dZg = ops.chunk_state(QT, QTs, dy, c, h, key_weights=False, want_gram=True)
         del QT, QTs
         # reverse scans: dS_m (with key weights folded in) and the chunk-gate gradient
-        wdS, dA_state = ops.discumsum_bwd(dZ, Z, A, row_len=d, row_weights=True, inplace=True)
-        ghi, glo, dA_gram = ops.gram_scan_bwd(dZg, zfull, A, Q.dtype)
+        wdS, dA_state, ghi, glo, dA_gram = ops.state_scan_bwd(dZ, Z, dZg, zfull, A, Q.dtype)
         # gradients through the expansions (chunk 0 reads a state only when one was carried in)
         gate_A = A if a is not None else None
         dq_state, gq = ops.expand_grad(dy, Q, Z, zhi, zlo, a, gate_A, dl, c, h, True, scale, 2.0,
