@@ -10,10 +10,11 @@
 
 namespace pr {
 
-constexpr int kPrepThreads = 256;
+constexpr int kPrepThreads = 256;   // gate_grad
+constexpr int kGpThreads = 128;     // gate_prep: small CTAs, eight per SM, four 16-byte loads in flight per thread
 
-template <typename T>
-__global__ void __launch_bounds__(kPrepThreads, 4)
+template <typename T, int NV>
+__global__ void __launch_bounds__(kGpThreads, NV == 4 ? 8 : 4)
 gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in, const T* __restrict__ x,
                  float* __restrict__ a_out, float* __restrict__ A_out, T* __restrict__ xt,
                  const float* __restrict__ row_scale, T* __restrict__ xts, int t, int h, int hx, int d, int c, int cp,
@@ -25,7 +26,7 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
   // row reads free of bank conflicts
   T* tile = reinterpret_cast<T*>(sm_f + ((c + 3) & ~3));
   T* tile2 = tile + 64 * d;                               // same, times row_scale
-  __shared__ float warp_tot[kPrepThreads / 32];
+  __shared__ float warp_tot[kGpThreads / 32];
   __shared__ float carry_s;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -39,14 +40,14 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
   // ---- the chunk's cumulative log gates: read if a pass before this one has made them, else a
   // block-wide inclusive scan of the log gates
   if (a_in != nullptr) {
-    for (int i = tid; i < c; i += kPrepThreads) sm_a[i] = a_in[(tok0 + i) * h + gh];
+    for (int i = tid; i < c; i += kGpThreads) sm_a[i] = a_in[(tok0 + i) * h + gh];
     __syncthreads();
   } else if (log_g != nullptr) {
     if (tid == 0) carry_s = 0.f;
     __syncthreads();
     // four consecutive gates per thread and round (their loads are independent), then one
     // block-wide scan of the per-thread totals: a 1024-token chunk is one round
-    for (int base = 0; base < c; base += 4 * kPrepThreads) {
+    for (int base = 0; base < c; base += 4 * kGpThreads) {
       const int i0 = base + 4 * tid;
       float p[4];
 #pragma unroll
@@ -68,17 +69,17 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
       for (int k = 0; k < 4; ++k)
         if (i0 + k < c) sm_a[i0 + k] = p[k] + pre;
       __syncthreads();
-      if (tid == kPrepThreads - 1) carry_s = p[3] + pre;
+      if (tid == kGpThreads - 1) carry_s = p[3] + pre;
       __syncthreads();
     }
   } else {
-    for (int i = tid; i < c; i += kPrepThreads) sm_a[i] = 0.f;
+    for (int i = tid; i < c; i += kGpThreads) sm_a[i] = 0.f;
     __syncthreads();
   }
   const float A = sm_a[c - 1];
   if (write_a && blockIdx.y == 0) {
     if (a_out != nullptr)
-      for (int i = tid; i < c; i += kPrepThreads) a_out[(tok0 + i) * h + gh] = sm_a[i];
+      for (int i = tid; i < c; i += kGpThreads) a_out[(tok0 + i) * h + gh] = sm_a[i];
     if (tid == 0 && A_out != nullptr) A_out[((size_t)batch * n + chunk) * h + gh] = A;
   }
   if (xt == nullptr) return;
@@ -92,14 +93,14 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
   const int tb_end = min(cp, (int)(blockIdx.y + 1) * tiles_per * 64);
   // The loads of tile k+1 are issued before tile k is transposed and written out, so a CTA always has
   // a tile's worth of reads in flight (64 tokens x d features: up to four 16-byte vectors per thread).
-  constexpr int kMaxVec = 4;
-  const int nvec = (64 * vec_per_row + kPrepThreads - 1) / kPrepThreads;  // <= kMaxVec for d <= 128
+  constexpr int kMaxVec = NV;  // 4 covers d <= 64, 8 covers d <= 128
+  const int nvec = (64 * vec_per_row + kGpThreads - 1) / kGpThreads;  // <= kMaxVec for d <= 128
   uint4 raw[kMaxVec];
   float fac[kMaxVec], rsc[kMaxVec];
   auto load_tile = [&](int tb) {
 #pragma unroll
     for (int q = 0; q < kMaxVec; ++q) {
-      const int idx = tid + q * kPrepThreads;
+      const int idx = tid + q * kGpThreads;
       raw[q] = make_uint4(0, 0, 0, 0);
       fac[q] = rsc[q] = 0.f;
       if (q < nvec && idx < 64 * vec_per_row) {
@@ -119,7 +120,7 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
     __syncthreads();
 #pragma unroll
     for (int q = 0; q < kMaxVec; ++q) {
-      const int idx = tid + q * kPrepThreads;
+      const int idx = tid + q * kGpThreads;
       if (q >= nvec || idx >= 64 * vec_per_row) continue;
       const int r = idx / vec_per_row, v = idx % vec_per_row;
       const float f = fac[q], rs = rsc[q];
@@ -153,7 +154,7 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
     if (tb + 64 < tb_end) load_tile(tb + 64);  // in flight while this tile is written out
     __syncthreads();
     // each thread writes 8 consecutive tokens of one feature row
-    for (int idx = tid; idx < d * 8; idx += kPrepThreads) {
+    for (int idx = tid; idx < d * 8; idx += kGpThreads) {
       const int row = idx >> 3, tv = idx & 7;
       const int chunk8 = ((tv ^ (row >> 3)) & 7) << 3;
       *reinterpret_cast<uint4*>(out_base + (size_t)row * cp + tb + tv * 8) =
@@ -330,10 +331,17 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
   const bool two_pass = write_a && xt != nullptr && log_g != nullptr && a_out != nullptr && !query_side && hx == h;
 #define PR_LAUNCH_PREP(TT, GRID, LG, AIN, XT, XTS, WRITE)                                                       \
   do {                                                                                                         \
-    PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    gate_prep_kernel<TT><<<GRID, kPrepThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,       \
-                                                         static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), t, \
-                                                         h, hx, d, c, cp, query_side, mult, WRITE);               \
+    if (d <= 64) {                                                                                             \
+      PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<TT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      gate_prep_kernel<TT, 4><<<GRID, kGpThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,   \
+                                                            static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), \
+                                                            t, h, hx, d, c, cp, query_side, mult, WRITE);         \
+    } else {                                                                                                   \
+      PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<TT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      gate_prep_kernel<TT, 8><<<GRID, kGpThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,   \
+                                                            static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), \
+                                                            t, h, hx, d, c, cp, query_side, mult, WRITE);         \
+    }                                                                                                          \
     PR_CUDA(cudaGetLastError());                                                                               \
   } while (0)
   if (dtype == PR_BF16) {
