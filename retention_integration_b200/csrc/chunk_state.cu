@@ -57,7 +57,11 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
                    const __grid_constant__ CUtensorMap tm_xs, const __grid_constant__ CUtensorMap tm_w) {
   using namespace cs;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t x_full[NS], x_empty[NS], w_full[NS], w_empty[NS], a_full[NG][NSA], a_empty[NG][NSA], acc_done;
+  // done[g][s]: the products of group g on stage s have completed.  ONE commit per stage and issuing thread
+  // serves both waiters - the expansion warps (their tensor-memory slot of two stages ago is free) and the TMA
+  // thread (the value tile of four stages ago is free): a commit costs the issuing thread ~150 clocks, a third
+  // of what the four products of a stage cost it.
+  __shared__ uint64_t x_full[NS], x_empty[NS], w_full[NS], w_empty[NS], a_full[NG][NSA], done[NG][NS], acc_done;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -87,13 +91,14 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
       mbar_init(&x_full[s], 1);
       mbar_init(&x_empty[s], 4 * NG);  // every expansion warp
       mbar_init(&w_full[s], 1);
-      mbar_init(&w_empty[s], gram_cta ? 1 : NG);  // one release per issuing thread
+      mbar_init(&w_empty[s], 1);  // Gram CTA only
     }
     for (int g = 0; g < NG; ++g)
       for (int s = 0; s < NSA; ++s) {
         mbar_init(&a_full[g][s], 4 * NG);  // every expansion warp fills its half of each tile's stage
-        mbar_init(&a_empty[g][s], 1);
       }
+    for (int g = 0; g < NG; ++g)
+      for (int s = 0; s < NS; ++s) mbar_init(&done[g][s], 1);
     mbar_init(&acc_done, gram_cta ? 1 : NG);
     fence_mbar_init();
   }
@@ -125,7 +130,8 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
         } else {
           mbar_expect_tx(&x_full[s], XT_BYTES);
           tma_load_2d(smX + s * XT_BYTES, &tm_xt, &x_full[s], kb * TOK, xrow);
-          if (!mbar_wait(&w_empty[s], ph ^ 1, &abort_flag)) break;
+          if (it >= NS && !(mbar_wait(&done[0][s], ph ^ 1, &abort_flag) && mbar_wait(&done[1][s], ph ^ 1, &abort_flag)))
+            break;
           mbar_expect_tx(&w_full[s], W_BYTES);
           tma_load_4d(smW + s * W_BYTES, &tm_w, &w_full[s], 0, xhead, chunk * p.c + kb * TOK, batch);
         }
@@ -166,8 +172,7 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
           for (int ks = 0; ks < TOK / 16; ++ks)
             umma_ts(tmem + COL_ACC + g * 64, tmem + COL_A + (g * NSA + sa) * 32 + ks * 8,
                     umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc, (it > 0 || ks > 0) ? 1u : 0u);
-          umma_commit(&a_empty[g][sa]);
-          umma_commit(&w_empty[s]);
+          umma_commit(&done[g][s]);
         }
       }
       if (ok) umma_commit(&acc_done);
@@ -214,9 +219,13 @@ chunk_state_kernel(const ChunkStateParams p, const __grid_constant__ CUtensorMap
           r1[4 * jj + 2] = Pack2<T>::mul(vc.z, vb.z);
           r1[4 * jj + 3] = Pack2<T>::mul(vc.w, vb.w);
         }
-        const int sa = it % NSA, pha = (it / NSA) & 1;
-        ok = mbar_wait(&a_empty[0][sa], pha ^ 1, &abort_flag) && mbar_wait(&a_empty[1][sa], pha ^ 1, &abort_flag);
-        if (!ok) break;
+        const int sa = it % NSA;
+        if (it >= NSA) {
+          // both tiles' products of stage it - NSA have read this tensor-memory slot
+          const int sp = (it - NSA) % NS, php = ((it - NSA) / NS) & 1;
+          ok = mbar_wait(&done[0][sp], php, &abort_flag) && mbar_wait(&done[1][sp], php, &abort_flag);
+          if (!ok) break;
+        }
         tc_fence_after();
         tmem_st16(tmem + lane_addr + COL_A + (0 * NSA + sa) * 32 + 16 * grp, r0);
         tmem_st16(tmem + lane_addr + COL_A + (1 * NSA + sa) * 32 + 16 * grp, r1);
