@@ -203,7 +203,7 @@ def run_reference(args, rank):
 
 
 # --------------------------------------------------------------------------- decode
-def decode_measure(dev, steps=512, with_extras=True):
+def decode_measure(dev, steps=512, with_extras=True, use_graph=True):
     """Inference workload: b=16, h=32, d=64 bf16 gated; a 2048-token prefill compressed into the
     state (switch_over 1024), then `steps` single-token steps whose cache grows from 1 to `steps`
     tokens (the reference's semantics: the caller's cache grows until the next switch-over).
@@ -229,19 +229,42 @@ def decode_measure(dev, steps=512, with_extras=True):
     lgc = F.logsigmoid(torch.randn(b, steps, h, generator=g)).to(dev)
 
     def decode_all():
+        y = None
         for i in range(steps):
-            prb.power_retention_inference(Qs[:, i:i + 1], Kc[:, :i + 1], Vc[:, :i + 1], lgc[:, :i + 1], state, sk,
-                                          switch_over_seq_len=1024)
+            y = prb.power_retention_inference(Qs[:, i:i + 1], Kc[:, :i + 1], Vc[:, :i + 1], lgc[:, :i + 1], state, sk,
+                                              switch_over_seq_len=1024)[0]
+        return y
 
-    decode_all()
-    torch.cuda.synchronize()
+    def timed_ms(fn, reps=1):
+        """Device time of `fn()`, replayed from a CUDA graph when `use_graph` (a serving loop replays its token
+        loop the same way: the Python launch code costs about as much as the 30 us kernel), else launched eagerly."""
+        y_ref = fn()
+        torch.cuda.synchronize()
+        graph = None
+        if use_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    y_g = fn()
+                graph.replay()
+                torch.cuda.synchronize()
+                if y_ref is not None and not torch.equal(y_g, y_ref):
+                    raise RuntimeError("graph replay and eager launches disagree")
+            except Exception:  # noqa: BLE001 - any refusal falls back to eager launches
+                graph = None
+                torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            graph.replay() if graph is not None else fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps, graph is not None
+
     ops.launch_log.reset(timing=False)
-    e0.record()
     decode_all()
-    e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
     launches = ops.launch_log.count
+    ms, replayed = timed_ms(decode_all)
     peaks = load_peaks()
     peak = peaks.get("hbm_gbs") or 6650.0
     state_bytes = state.numel() * 2 + sk.numel() * 4
@@ -254,6 +277,7 @@ def decode_measure(dev, steps=512, with_extras=True):
         "ms_per_step": ms / steps,
         "workload": f"power_retention_inference decode b16 h32 d64 bf16 gated, state [16,32,2080,64], cache 1..{steps}",
         "prefill_to_state_ms": prefill_ms, "gpu_launches": launches,
+        "launch": f"cuda graph replay of the {steps} captured steps" if replayed else "eager launches",
         "roofline": {"bound": "hbm", "kernel": "decode step (one kernel)", "achieved": step_gbs, "peak": peak,
                      "unit": "GB/s", "frac": step_gbs / peak,
                      "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
@@ -262,30 +286,25 @@ def decode_measure(dev, steps=512, with_extras=True):
     if with_extras:
         # the same step with an empty cache: the state read alone, launches queued back to back
         qd = Qs[:, :1].contiguous()
-        for _ in range(3):
-            prb.power_retention_inference(qd, None, None, None, state, sk)
-        torch.cuda.synchronize()
         n_state = 100
-        e0.record()
-        for _ in range(n_state):
-            prb.power_retention_inference(qd, None, None, None, state, sk)
-        e1.record()
-        torch.cuda.synchronize()
-        ms_state = e0.elapsed_time(e1) / n_state
+
+        def state_only():
+            y = None
+            for _ in range(n_state):
+                y = prb.power_retention_inference(qd, None, None, None, state, sk)[0]
+            return y
+
+        ms_state = timed_ms(state_only)[0] / n_state
         out["state_read"] = {"ms": ms_state, "achieved_gbs": state_bytes / (ms_state * 1e-3) / 1e9,
                              "frac": state_bytes / (ms_state * 1e-3) / 1e9 / peak}
         # pure-recurrent mode: the state is advanced and read once per token (read + write of the state)
         cache = RetentionCache(b, h, d, torch.bfloat16, dev, recurrent=True)
         cache.update_state(state.clone(), sk.clone())
-        for i in range(8):
-            cache.decode(Qs[:, i:i + 1], Kc[:, i:i + 1], Vc[:, i:i + 1], lgc[:, i:i + 1])
-        torch.cuda.synchronize()
-        e0.record()
-        for i in range(steps):
-            cache.decode(Qs[:, i:i + 1], Kc[:, i:i + 1], Vc[:, i:i + 1], lgc[:, i:i + 1])
-        e1.record()
-        torch.cuda.synchronize()
-        ms_rec = e0.elapsed_time(e1) / steps
+        def recurrent_all():
+            for i in range(steps):
+                cache.decode(Qs[:, i:i + 1], Kc[:, i:i + 1], Vc[:, i:i + 1], lgc[:, i:i + 1])
+
+        ms_rec = timed_ms(recurrent_all)[0] / steps
         out["recurrent"] = {"tokens_per_s": b / (ms_rec * 1e-3), "ms_per_step": ms_rec,
                             "achieved_gbs": 2 * state_bytes / (ms_rec * 1e-3) / 1e9,
                             "frac": 2 * state_bytes / (ms_rec * 1e-3) / 1e9 / peak}
@@ -399,7 +418,7 @@ def main():
 
     if args.workload == "decode":
         if rank == 0:
-            obj = decode_measure(dev, args.decode_steps)
+            obj = decode_measure(dev, args.decode_steps, use_graph=not args.no_graph)
             obj.update({"n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
                         "config": {"workload": obj["workload"]}})
             print(json.dumps(obj), flush=True)
@@ -552,7 +571,7 @@ def main():
         del Q, K, V, G, dO, graph
         torch.cuda.empty_cache()
         if world == 1:
-            extra["decode"] = decode_measure(dev, args.decode_steps)
+            extra["decode"] = decode_measure(dev, args.decode_steps, use_graph=not args.no_graph)
         else:
             extra["seq_parallel"] = seqpar_measure(dev, rank, world, args.seq_t)
 

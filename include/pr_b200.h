@@ -234,7 +234,10 @@ int pr_decode_state_strided(int dtype, int b, int h, int hq, int d, const void* 
  * normalised into O [b,1,hq,d].  K/V/log_g and state/sum_of_keys may each be absent.  part_y
  * [b,hq,pr_decode_nsplit(),d] and part_l [b,hq,pr_decode_nsplit()] are needed (and a second, tiny
  * kernel runs) only when b*h*ceil(hq/h/4) < 384, where each (batch, head) pair is split over several
- * CTAs; a_scratch is unused (kept for callers of the earlier three-kernel step) and may be NULL. */
+ * CTAs; a_scratch is unused (kept for callers of the earlier three-kernel step) and may be NULL.
+ * The state is streamed by TMA into shared memory and contracted with phi(q) by tcgen05.mma (it never
+ * passes through registers); state and sum_of_keys must be 16-byte aligned and dense.  The kernel's
+ * waits are bounded: pr_device_check() reports PR_ERR_TIMEOUT if one ran out. */
 int pr_decode_step(int dtype, int b, int tk, int h, int hq, int d, const void* Q, const void* K, const void* V,
                    const float* log_g, const void* state, const float* sum_of_keys, float scale, float* a_scratch,
                    float* part_y, float* part_l, void* O, int device, void* stream);

@@ -7,6 +7,10 @@
 //                     y = sum_D phi(q~)[D] S[D,:],  l = sum_D phi(q~)[D] s[D].
 //                     HBM bound: 128-bit loads, each 128-byte state row read by 8 threads,
 //                     D split over several CTAs; partial sums go to a small workspace.
+//   pr_decode_step  : the whole step in one kernel; the state is streamed by TMA and contracted on
+//                     the tensor cores (decode_tc_kernel below).  pr_decode_state / pr_decode_finish
+//                     are the same step in two CUDA-core kernels, kept for callers that want the
+//                     partial sums.
 //   pr_decode_finish: adds the attention over the tokens cached since the last
 //                     switch-over, sums the partials, normalises and writes the output.
 //   pr_state_merge  : prefill-to-state switch-over: new_state = state*exp(a_last) + S_chunk,
@@ -279,26 +283,65 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
   }
 }
 
-// The whole decode step for one (batch, kv head, group of up to RG query heads) in one CTA: the
-// state rows [d_begin, d_end) and the cached tokens [t_begin, t_end) of split `blockIdx.y` are
-// streamed once, both into the same per-lane accumulators (lane sub = tid & 7 owns eight output
-// features in both phases).  The gate sums the step needs are formed here from log_g itself:
-// the total a_last (the state's decay, folded into the query as exp(a_last / 2)) and, per cached
-// token j, the suffix sum of the gates after j, so no cumulative-gate scratch is written or read.
-// With one split the CTA normalises and writes the output itself; otherwise it writes partial
-// sums and decode_merge_kernel finishes.
+// The whole decode step for one (batch, kv head, group of up to RG query heads) in one CTA, with
+// the state read-out on the tensor cores.  Split `blockIdx.y` takes the 64-row state stages
+// [st_begin, st_begin + n_st) and the cached tokens [t_begin, t_end).  The gate sums the step needs
+// are formed here from log_g itself: the total a_last (the state's decay, folded into the query as
+// exp(a_last / 2)) and, per cached token j, the suffix sum of the gates after j, so no
+// cumulative-gate scratch is written or read.  With one split the CTA normalises and writes the
+// output itself; otherwise it writes partial sums and decode_merge_kernel finishes.
+//
+// y = phi(q~)^T S is a [1 x 2080] x [2080 x 64] product per query head.  On the CUDA cores it costs
+// some 80 issued instructions per 512 bytes of state, which left the step bound by instruction issue
+// and by the bytes a 64-register thread can keep in flight, not by HBM.  Here the state never
+// passes through registers: one thread streams it with TMA, 64 rows (8 KB) per stage and NSB stages
+// in flight per CTA, into 128-byte-swizzled shared memory, where it is the N-major B operand of
+// tcgen05.mma; the A operand is one 8-row swizzle atom per stage holding phi(q~) of the group's
+// query heads in rows 0..nr-1 and zeros below (the descriptor's 8-row-group stride is 0, so all
+// sixteen row groups of the M = 128 product read that one atom and accumulator lanes r, r + 8, ...
+// are copies); the fp32 accumulator lives in 64 columns of tensor memory.  The streaming starts
+// before the gate sums and the queries are ready, so that serial prologue is hidden.
+//
+// Roles: warps 0-4 compute the attention over the cached tokens on the CUDA cores, as before
+// (gate suffix sums in blocks of 4 * CT tokens, synchronised among themselves with a named barrier),
+// at the same time as warp 5 builds the A atoms and the normaliser phi(q~) . sum_of_keys, one
+// thread of warp 6 issues the products and one thread of warp 7 drives the TMA ring.  Every wait
+// is bounded; a wait that runs out sets the CTA's abort flag and the device status word.
+namespace dec {
+constexpr int CT = 160;                                    // threads of the cache-attention warps
+constexpr int NSB = 5;                                     // state stages in flight per CTA
+constexpr int ST_ROWS = 64;                                // state rows per stage
+constexpr int B_BYTES = ST_ROWS * HD * 2;                  // 8 KB
+constexpr int A_BYTES = 1024;                              // one swizzle atom: 8 rows x 64 K
+constexpr int N_STAGES = (DEX + ST_ROWS - 1) / ST_ROWS;    // 33, the last one half full
+constexpr int TC_TMEM_COLS = 64;
+constexpr int MAX_DEVICES = 64;                               // device ordinals the entry points accept
+constexpr int K_BYTES = ST_ROWS * 4;                       // the stage's slice of sum_of_keys
+constexpr size_t TC_SMEM = 1024 + (size_t)NSB * (B_BYTES + A_BYTES + K_BYTES);
+}  // namespace dec
+
+__device__ __forceinline__ void bar_sync_named(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 template <typename T, int RG>
 __global__ void __launch_bounds__(dec::THREADS, RG == 1 ? 4 : 2)
-decode_fused_kernel(const T* __restrict__ Q, long long q_bs, const T* __restrict__ K, const T* __restrict__ V,
-                    long long kv_bs, const float* __restrict__ log_g, long long g_bs, const T* __restrict__ state,
-                    const float* __restrict__ sok, float scale, int tk, int h, int hq, int nsplit,
-                    float* __restrict__ part_y, float* __restrict__ part_l, T* __restrict__ O) {
+decode_tc_kernel(const __grid_constant__ CUtensorMap tm_state, const T* __restrict__ Q, long long q_bs,
+                 const T* __restrict__ K, const T* __restrict__ V, long long kv_bs, const float* __restrict__ log_g,
+                 long long g_bs, int has_state, const float* __restrict__ sok, float scale, int tk, int h, int hq,
+                 int nsplit, float* __restrict__ part_y, float* __restrict__ part_l, T* __restrict__ O,
+                 int* __restrict__ status) {
   using namespace dec;
-  constexpr int BLK = 4 * THREADS;  // cached tokens per gate block
-  __shared__ float sq[RG][HD];      // gated, scaled, rounded queries (state phase)
+  constexpr int BLK = 4 * CT;  // cached tokens per gate block
+  constexpr int CW = CT / 32;  // cache-attention warps
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t b_full[NSB], a_full[NSB], done[NSB], acc_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ float sq[RG][HD];                 // gated, scaled, rounded queries (state phase)
   __shared__ __align__(16) float sqr[RG][HD];  // raw queries (attention phase)
-  __shared__ float red_y[THREADS / 32][RG][HD];
-  __shared__ float red_l[THREADS / 32][RG];
+  __shared__ float red_y[CW + 1][RG][HD];      // per cache warp, then the state's
+  __shared__ float red_l[CW + 1][RG];
   __shared__ float sfx[BLK];
   __shared__ float wsum[THREADS / 32][2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -309,6 +352,48 @@ decode_fused_kernel(const T* __restrict__ Q, long long q_bs, const T* __restrict
   const bool gated = (log_g != nullptr) && tk > 0;
   const int t_per = (tk + nsplit - 1) / nsplit;
   const int t_begin = min(tk, split * t_per), t_end = min(tk, t_begin + t_per);
+  const int st_per = (N_STAGES + nsplit - 1) / nsplit;
+  const int st_begin = min(N_STAGES, split * st_per);
+  const int n_st = has_state ? min(N_STAGES, st_begin + st_per) - st_begin : 0;
+
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smB = smem_raw + (sbase - smem_u32(smem_raw));  // NSB x B_BYTES
+  uint8_t* smA = smB + NSB * B_BYTES;                      // NSB x A_BYTES
+  uint8_t* smK = smA + NSB * A_BYTES;                      // NSB x K_BYTES
+  const float* kbase = sok + (size_t)bh * DEX;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < NSB; ++s) {
+      mbar_init(&b_full[s], 1);
+      mbar_init(&a_full[s], 1);
+      mbar_init(&done[s], 1);
+    }
+    mbar_init(&acc_done, 1);
+    fence_mbar_init();
+  }
+  // rows nr..7 of every A atom stay zero for the whole kernel
+  for (int i = tid; i < NSB * A_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(smA)[i] = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  if (warp == 0 && n_st > 0) {
+    tmem_alloc(&tmem_base_s, TC_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = n_st > 0 ? tmem_base_s : 0u;
+
+  // the first stages are requested before anything else is known
+  if (warp == 7 && lane == 0) {
+    for (int it = 0; it < min(n_st, NSB); ++it) {
+      const int D0 = (st_begin + it) * ST_ROWS;
+      const uint32_t kb = (uint32_t)min(ST_ROWS, DEX - D0) * 4u;
+      mbar_expect_tx(&b_full[it], B_BYTES + kb);
+      tma_load_3d(smB + it * B_BYTES, &tm_state, &b_full[it], 0, D0, bh);
+      bulk_load_1d(smK + it * K_BYTES, kbase + D0, kb, &b_full[it]);
+    }
+  }
 
   // ---- gate sums: the total, and the part after this split's last token
   float a_last = 0.f, tail = 0.f;
@@ -348,207 +433,254 @@ decode_fused_kernel(const T* __restrict__ Q, long long q_bs, const T* __restrict
   __syncthreads();
 
   const int sub = tid & 7;
-  float acc[RG][8];
-  float accl[RG];
+  if (warp < CW) {
+    // ------------------------------------------------ cached tokens, newest block first
+    float acc[RG][8];
+    float accl[RG];
 #pragma unroll
-  for (int r = 0; r < RG; ++r) {
-    accl[r] = 0.f;
+    for (int r = 0; r < RG; ++r) {
+      accl[r] = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[r][k] = 0.f;
-  }
-
-  // ---- state rows
-  if (state != nullptr) {
-    const int rows_per_split = (DEX + nsplit - 1) / nsplit;
-    const int d_begin = split * rows_per_split, d_end = min(DEX, d_begin + rows_per_split);
-    int D = d_begin + (tid >> 3);
-    int a = 0, b = 0;
-    if (D < DEX) exact_decode(D, &a, &b);
-    const T* sbase = state + (size_t)bh * DEX * HD;
-    const float* kbase = sok + (size_t)bh * DEX;
-    constexpr int UN = PR_DEC_UN;
-    for (; D < d_end; D += UN * ROWS_PER_ITER) {
-      uint4 v[UN];
-      float sk[UN];
-      int ra[UN], rb[UN];
+      for (int k = 0; k < 8; ++k) acc[r][k] = 0.f;
+    }
+    if (K != nullptr && t_end > t_begin) {
+      const float s2 = scale * scale;
+      const int slot = lane >> 3;
+      const T* kb = K + (size_t)batch * kv_bs + (size_t)head * HD + sub * 8;
+      const T* vb = V + (size_t)batch * kv_bs + (size_t)head * HD + sub * 8;
+      float q[RG][8];
 #pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        const int Du = D + u * ROWS_PER_ITER;
-        ra[u] = a;
-        rb[u] = b;
-        if (Du < d_end) {
-          v[u] = __ldg(reinterpret_cast<const uint4*>(sbase + (size_t)Du * HD + sub * 8));
-          sk[u] = __ldg(kbase + Du);
+      for (int r = 0; r < RG; ++r) {
+        const float4 q0 = *reinterpret_cast<const float4*>(&sqr[r][sub * 8]);
+        const float4 q1 = *reinterpret_cast<const float4*>(&sqr[r][sub * 8 + 4]);
+        q[r][0] = q0.x; q[r][1] = q0.y; q[r][2] = q0.z; q[r][3] = q0.w;
+        q[r][4] = q1.x; q[r][5] = q1.y; q[r][6] = q1.z; q[r][7] = q1.w;
+      }
+      for (int blk_end = t_end; blk_end > t_begin; blk_end -= BLK) {
+        const int blk_lo = max(t_begin, blk_end - BLK);
+        const int n_blk = blk_end - blk_lo;
+        if (gated) {
+          // sfx[i] = sum of the gates after token blk_lo + i (up to the newest token of the cache)
+          const float* gp = log_g + (size_t)batch * g_bs + head;
+          float g4[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = 4 * tid + k;
+            g4[k] = i < n_blk ? gp[(size_t)(blk_lo + i) * h] : 0.f;
+          }
+          const float mine = g4[0] + g4[1] + g4[2] + g4[3];
+          // inclusive reverse scan of the per-thread totals over the block
+          float inc = mine;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const float o = __shfl_down_sync(0xffffffffu, inc, off);
+            if (lane + off < 32) inc += o;
+          }
+          if (lane == 0) wsum[warp][0] = inc;
+          bar_sync_named(1, CT);
+          float after = tail;  // everything after this thread's four tokens
+#pragma unroll
+          for (int w = 0; w < CW; ++w) {
+            if (w > warp) after += wsum[w][0];
+          }
+          after += inc - mine;
+          float blk_total = 0.f;
+#pragma unroll
+          for (int w = 0; w < CW; ++w) blk_total += wsum[w][0];
+          sfx[4 * tid + 3] = after;
+          sfx[4 * tid + 2] = after + g4[3];
+          sfx[4 * tid + 1] = after + g4[3] + g4[2];
+          sfx[4 * tid + 0] = after + g4[3] + g4[2] + g4[1];
+          tail += blk_total;
+          bar_sync_named(1, CT);
         }
-        b += ROWS_PER_ITER;
-        while (b >= HD && a < HD) {
-          b = b - HD + a + 1;
-          ++a;
+        constexpr int UNT = 2;
+        // the trip count depends on the warp only: every lane takes part in the shuffles, lanes whose
+        // token lies outside the block contribute zero weight
+        for (int base = warp * 4; base < n_blk; base += CW * 4 * UNT) {
+          uint4 kv[UNT], vv[UNT];
+          float sf[UNT];
+#pragma unroll
+          for (int u = 0; u < UNT; ++u) {
+            const int i = base + slot + CW * 4 * u;
+            kv[u] = vv[u] = make_uint4(0, 0, 0, 0);
+            sf[u] = 0.f;
+            if (i < n_blk) {
+              const size_t j = (size_t)(blk_lo + i);
+              kv[u] = *reinterpret_cast<const uint4*>(kb + j * h * HD);
+              vv[u] = *reinterpret_cast<const uint4*>(vb + j * h * HD);
+              if (gated) sf[u] = sfx[i];
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < UNT; ++u) {
+            const int i = base + slot + CW * 4 * u;
+            const uint32_t kw[4] = {kv[u].x, kv[u].y, kv[u].z, kv[u].w};
+            const uint32_t vw[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+            float kf[8], vf[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 p2 = Pack2<T>::to_f32(kw[k]);
+              kf[2 * k] = p2.x;
+              kf[2 * k + 1] = p2.y;
+              const float2 v2 = Pack2<T>::to_f32(vw[k]);
+              vf[2 * k] = v2.x;
+              vf[2 * k + 1] = v2.y;
+            }
+            const float gf = (i < n_blk) ? (gated ? s2 * __expf(sf[u]) : s2) : 0.f;
+#pragma unroll
+            for (int r = 0; r < RG; ++r) {
+              float sdot = 0.f;
+#pragma unroll
+              for (int k = 0; k < 8; ++k) sdot = fmaf(kf[k], q[r][k], sdot);
+              sdot += __shfl_xor_sync(0xffffffffu, sdot, 1);
+              sdot += __shfl_xor_sync(0xffffffffu, sdot, 2);
+              sdot += __shfl_xor_sync(0xffffffffu, sdot, 4);
+              const float wgt = gf * sdot * sdot;
+              if (sub == 0) accl[r] += wgt;
+#pragma unroll
+              for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(wgt, vf[k], acc[r][k]);
+            }
+          }
+        }
+        if (gated) bar_sync_named(1, CT);  // sfx is rewritten by the next block
+      }
+    }
+    // the four tokens a warp covers per pass (lanes with equal sub)
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float t = acc[r][k];
+        t += __shfl_xor_sync(0xffffffffu, t, 8);
+        t += __shfl_xor_sync(0xffffffffu, t, 16);
+        acc[r][k] = t;
+      }
+      float t = accl[r];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+      accl[r] = t;
+    }
+    if (lane < 8) {
+#pragma unroll
+      for (int r = 0; r < RG; ++r)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) red_y[warp][r][lane * 8 + k] = acc[r][k];
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < RG; ++r) red_l[warp][r] = accl[r];
+    }
+    if (warp == CW - 1) {
+      // this warp owns tensor-memory lanes 0-31: fetch the state's share of the output
+      bool have = n_st > 0 && mbar_wait(&acc_done, 0, &abort_flag);
+      if (have) tc_fence_after();
+#pragma unroll
+      for (int j = 0; j < HD / 16; ++j) {
+        uint32_t v[16];
+        if (have) {
+          tmem_ld16(tmem + j * 16, v);
+          tmem_wait_ld();
+        }
+        if (lane < RG) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) red_y[CW][lane][j * 16 + k] = have ? __uint_as_float(v[k]) : 0.f;
         }
       }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------ A atoms and the normaliser
+    float l_acc[RG];
 #pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        if (D + u * ROWS_PER_ITER >= d_end) break;
-        float x[8];
-        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 p2 = Pack2<T>::to_f32(w[k]);
-          x[2 * k] = p2.x;
-          x[2 * k + 1] = p2.y;
+    for (int r = 0; r < RG; ++r) l_acc[r] = 0.f;
+    if (n_st > 0) {
+      int D = st_begin * ST_ROWS + 2 * lane;  // this lane's rows D and D + 1 of every stage
+      int a = 0, b = 0;
+      exact_decode(min(D, DEX - 1), &a, &b);
+      const uint32_t a_off = swz128(0, lane >> 2) + (lane & 3) * 4;
+      for (int it = 0; it < n_st; ++it) {
+        const int s = it % NSB;
+        if (it >= NSB && !mbar_wait(&done[s], ((it / NSB) - 1) & 1, &abort_flag)) break;
+        if (!mbar_wait(&b_full[s], (it / NSB) & 1, &abort_flag)) break;  // the stage's sum_of_keys slice
+        const bool in = D < DEX;  // D is even and so is DEX: D + 1 is inside whenever D is
+        int a1 = a, b1 = b + 1;
+        if (b1 >= HD) {
+          a1 = min(a + 1, HD - 1);
+          b1 = a1;
         }
+        float2 sk = make_float2(0.f, 0.f);
+        if (in) sk = *reinterpret_cast<const float2*>(smK + s * K_BYTES + 8 * lane);
 #pragma unroll
         for (int r = 0; r < RG; ++r) {
           if (r < nr) {
-            const float phi = float(T(sq[r][min(ra[u], HD - 1)] * sq[r][min(rb[u], HD - 1)]));
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(phi, x[k], acc[r][k]);
-            accl[r] = fmaf(phi, sk[u], accl[r]);
+            const uint32_t w = in ? Pack2<T>::from_f32(sq[r][a] * sq[r][b], sq[r][a1] * sq[r][b1]) : 0u;
+            // row r of the atom: swz128(r, c) = r * 128 + ((c ^ r) << 4) for r < 8
+            *reinterpret_cast<uint32_t*>(smA + s * A_BYTES + r * 128 + ((a_off ^ (r << 4)))) = w;
+            const float2 ph = Pack2<T>::to_f32(w);
+            l_acc[r] = fmaf(ph.x, sk.x, fmaf(ph.y, sk.y, l_acc[r]));
           }
         }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[s]);
+        D += ST_ROWS;
+        b += ST_ROWS;
+        while (b >= HD && a < HD - 1) {
+          b = b - HD + a + 1;
+          ++a;
+        }
+        b = min(b, HD - 1);
       }
     }
-    // the eight lanes of a row hold the same normaliser term: keep one copy
-#pragma unroll
-    for (int r = 0; r < RG; ++r) accl[r] = (sub == 0) ? accl[r] : 0.f;
-  }
-
-  // ---- cached tokens, in blocks of BLK from the newest to the oldest
-  if (K != nullptr && t_end > t_begin) {
-    const float s2 = scale * scale;
-    const int slot = lane >> 3;
-    const T* kb = K + (size_t)batch * kv_bs + (size_t)head * HD + sub * 8;
-    const T* vb = V + (size_t)batch * kv_bs + (size_t)head * HD + sub * 8;
-    float q[RG][8];
 #pragma unroll
     for (int r = 0; r < RG; ++r) {
-      const float4 q0 = *reinterpret_cast<const float4*>(&sqr[r][sub * 8]);
-      const float4 q1 = *reinterpret_cast<const float4*>(&sqr[r][sub * 8 + 4]);
-      q[r][0] = q0.x; q[r][1] = q0.y; q[r][2] = q0.z; q[r][3] = q0.w;
-      q[r][4] = q1.x; q[r][5] = q1.y; q[r][6] = q1.z; q[r][7] = q1.w;
+      float t = l_acc[r];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+      if (lane == 0) red_l[CW][r] = t;
     }
-    for (int blk_end = t_end; blk_end > t_begin; blk_end -= BLK) {
-      const int blk_lo = max(t_begin, blk_end - BLK);
-      const int n_blk = blk_end - blk_lo;
-      if (gated) {
-        // sfx[i] = sum of the gates after token blk_lo + i (up to the newest token of the cache)
-        const float* gp = log_g + (size_t)batch * g_bs + head;
-        float g4[4];
+  } else if (warp == 6) {
+    // ------------------------------------------------ MMA issuer
+    if (lane == 0 && n_st > 0) {
+      const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
+      bool ok = true;
+      for (int it = 0; it < n_st; ++it) {
+        const int s = it % NSB, ph = (it / NSB) & 1;
+        ok = mbar_wait(&b_full[s], ph, &abort_flag) && mbar_wait(&a_full[s], ph, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smA + s * A_BYTES), b_addr = smem_u32(smB + s * B_BYTES);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int i = 4 * tid + k;
-          g4[k] = i < n_blk ? gp[(size_t)(blk_lo + i) * h] : 0.f;
-        }
-        const float mine = g4[0] + g4[1] + g4[2] + g4[3];
-        // inclusive reverse scan of the per-thread totals over the block
-        float inc = mine;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-          const float o = __shfl_down_sync(0xffffffffu, inc, off);
-          if (lane + off < 32) inc += o;
-        }
-        if (lane == 0) wsum[warp][0] = inc;
-        __syncthreads();
-        float after = tail;  // everything after this thread's four tokens
-#pragma unroll
-        for (int w = 0; w < THREADS / 32; ++w) {
-          if (w > warp) after += wsum[w][0];
-        }
-        after += inc - mine;
-        float blk_total = 0.f;
-#pragma unroll
-        for (int w = 0; w < THREADS / 32; ++w) blk_total += wsum[w][0];
-        sfx[4 * tid + 3] = after;
-        sfx[4 * tid + 2] = after + g4[3];
-        sfx[4 * tid + 1] = after + g4[3] + g4[2];
-        sfx[4 * tid + 0] = after + g4[3] + g4[2] + g4[1];
-        tail += blk_total;
-        __syncthreads();
+        for (int ks = 0; ks < ST_ROWS / 16; ++ks)
+          umma_ss(tmem, umma_desc_sw128(a_addr + ks * 32, 16, 0), umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc,
+                  (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&done[s]);
       }
-      constexpr int UNT = 2;
-      // the trip count depends on the warp only: every lane takes part in the shuffles, lanes whose
-      // token lies outside the block contribute zero weight
-      for (int base = warp * 4; base < n_blk; base += (THREADS / 32) * 4 * UNT) {
-        uint4 kv[UNT], vv[UNT];
-        float sf[UNT];
-#pragma unroll
-        for (int u = 0; u < UNT; ++u) {
-          const int i = base + slot + (THREADS / 32) * 4 * u;
-          kv[u] = vv[u] = make_uint4(0, 0, 0, 0);
-          sf[u] = 0.f;
-          if (i < n_blk) {
-            const size_t j = (size_t)(blk_lo + i);
-            kv[u] = *reinterpret_cast<const uint4*>(kb + j * h * HD);
-            vv[u] = *reinterpret_cast<const uint4*>(vb + j * h * HD);
-            if (gated) sf[u] = sfx[i];
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < UNT; ++u) {
-          const int i = base + slot + (THREADS / 32) * 4 * u;
-          const uint32_t kw[4] = {kv[u].x, kv[u].y, kv[u].z, kv[u].w};
-          const uint32_t vw[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
-          float kf[8], vf[8];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float2 p2 = Pack2<T>::to_f32(kw[k]);
-            kf[2 * k] = p2.x;
-            kf[2 * k + 1] = p2.y;
-            const float2 v2 = Pack2<T>::to_f32(vw[k]);
-            vf[2 * k] = v2.x;
-            vf[2 * k + 1] = v2.y;
-          }
-          const float gf = (i < n_blk) ? (gated ? s2 * __expf(sf[u]) : s2) : 0.f;
-#pragma unroll
-          for (int r = 0; r < RG; ++r) {
-            float sdot = 0.f;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) sdot = fmaf(kf[k], q[r][k], sdot);
-            sdot += __shfl_xor_sync(0xffffffffu, sdot, 1);
-            sdot += __shfl_xor_sync(0xffffffffu, sdot, 2);
-            sdot += __shfl_xor_sync(0xffffffffu, sdot, 4);
-            const float wgt = gf * sdot * sdot;
-            if (sub == 0) accl[r] += wgt;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(wgt, vf[k], acc[r][k]);
-          }
-        }
+      if (ok) umma_commit(&acc_done);
+    }
+  } else {
+    // ------------------------------------------------ TMA producer, stages NSB and up
+    if (lane == 0) {
+      for (int it = NSB; it < n_st; ++it) {
+        const int s = it % NSB;
+        if (!mbar_wait(&done[s], ((it / NSB) - 1) & 1, &abort_flag)) break;
+        const int D0 = (st_begin + it) * ST_ROWS;
+        const uint32_t kb = (uint32_t)min(ST_ROWS, DEX - D0) * 4u;
+        mbar_expect_tx(&b_full[s], B_BYTES + kb);
+        tma_load_3d(smB + s * B_BYTES, &tm_state, &b_full[s], 0, D0, bh);
+        bulk_load_1d(smK + s * K_BYTES, kbase + D0, kb, &b_full[s]);
       }
-      if (gated) __syncthreads();  // sfx is rewritten by the next block
     }
   }
 
-  // ---- reduce: the four rows / tokens a warp covers per pass (lanes with equal sub), then the warps
-#pragma unroll
-  for (int r = 0; r < RG; ++r) {
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float t = acc[r][k];
-      t += __shfl_xor_sync(0xffffffffu, t, 8);
-      t += __shfl_xor_sync(0xffffffffu, t, 16);
-      acc[r][k] = t;
-    }
-    float t = accl[r];
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-    accl[r] = t;
-  }
-  if (lane < 8) {
-#pragma unroll
-    for (int r = 0; r < RG; ++r)
-#pragma unroll
-      for (int k = 0; k < 8; ++k) red_y[warp][r][lane * 8 + k] = acc[r][k];
-  }
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < RG; ++r) red_l[warp][r] = accl[r];
-  }
+  tc_fence_before();
   __syncthreads();
+  if (tid == 0 && abort_flag) *status = ST_TIMEOUT;
   for (int i = tid; i < nr * HD; i += THREADS) {
     const int r = i / HD, e = i % HD;
     float yt = 0.f, lt = 0.f;
 #pragma unroll
-    for (int w = 0; w < THREADS / 32; ++w) {
+    for (int w = 0; w <= CW; ++w) {
       yt += red_y[w][r][e];
       lt += red_l[w][r];
     }
@@ -560,6 +692,7 @@ decode_fused_kernel(const T* __restrict__ Q, long long q_bs, const T* __restrict
       if (e == 0) part_l[row * nsplit + split] = lt;
     }
   }
+  if (warp == 0 && n_st > 0) tmem_dealloc(tmem, TC_TMEM_COLS);
 }
 
 // Pure-recurrent decode step: the state is advanced by one token and read in the same pass,
@@ -1081,13 +1214,14 @@ extern "C" int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, i
   PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_REQUIRE(state != nullptr || has_cache, PR_ERR_BAD_ARG, "neither a state nor cached tokens");
   PR_REQUIRE(state == nullptr || sum_of_keys != nullptr, PR_ERR_BAD_ARG, "a state needs its sum_of_keys");
-  PR_REQUIRE(Q && O && aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(state), PR_ERR_BAD_ARG,
-             "null or misaligned pointer");
+  PR_REQUIRE(Q && O && aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(state) && aligned16(sum_of_keys),
+             PR_ERR_BAD_ARG, "null or misaligned pointer");
   PR_REQUIRE(q_bstride >= (long long)hq * d && (!has_cache || kv_bstride >= (long long)tk * h * d) &&
                  (!gated || g_bstride >= (long long)tk * h),
              PR_ERR_BAD_ARG, "a batch stride is smaller than one batch entry");
   PR_REQUIRE(q_bstride % 8 == 0 && (!has_cache || kv_bstride % 8 == 0), PR_ERR_BAD_ARG,
              "the batch strides of Q, K, V must be multiples of 8 elements");
+  PR_REQUIRE(device >= 0 && device < dec::MAX_DEVICES, PR_ERR_BAD_ARG, "device ordinal %d out of range", device);
   const int nsplit = decode_split(b, h, hq);
   PR_REQUIRE(nsplit == 1 || (part_y != nullptr && part_l != nullptr), PR_ERR_BAD_ARG,
              "this problem is split %d ways and needs the partial-sum workspace", nsplit);
@@ -1096,12 +1230,34 @@ extern "C" int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, i
   const int rg = ratio == 1 ? 1 : dec::RG_MAX;
   dim3 grid(b * h, nsplit, (ratio + rg - 1) / rg);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = nullptr;
+  int rc = status_word(device, &status, nullptr);
+  if (rc) return rc;
+  CUtensorMap tm_state;
+  {
+    // without a state the map is never used; it still has to be a valid one
+    const void* base = state ? state : Q;
+    uint64_t dims[3] = {(uint64_t)dec::HD, (uint64_t)(state ? dec::DEX : 1), (uint64_t)(state ? b * h : 1)};
+    uint64_t strides[3] = {0, (uint64_t)dec::HD * 2, (uint64_t)dec::DEX * dec::HD * 2};
+    uint32_t box[3] = {(uint32_t)dec::HD, (uint32_t)(state ? dec::ST_ROWS : 1), 1};
+    rc = make_tmap(&tm_state, base, 2, 3, dims, strides, box, true);
+    if (rc) return rc;
+  }
 #define PR_LAUNCH_FUSED(TT, RGV)                                                                                      \
-  decode_fused_kernel<TT, RGV><<<grid, dec::THREADS, 0, s>>>(                                                          \
-      static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(has_cache ? K : nullptr),                          \
-      static_cast<const TT*>(has_cache ? V : nullptr), kv_bstride, gated ? log_g : nullptr, g_bstride,                \
-      static_cast<const TT*>(state), sum_of_keys, scale, has_cache ? tk : 0, h, hq, nsplit, part_y, part_l,            \
-      static_cast<TT*>(O))
+  do {                                                                                                                \
+    static bool configured[dec::MAX_DEVICES] = {false}; /* per instantiation and device */                           \
+    if (!configured[device]) {                                                                                        \
+      PR_CUDA(cudaFuncSetAttribute(decode_tc_kernel<TT, RGV>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                   (int)dec::TC_SMEM));                                                               \
+      PR_CUDA(cudaFuncSetAttribute(decode_tc_kernel<TT, RGV>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));  \
+      configured[device] = true;                                                                                      \
+    }                                                                                                                 \
+    decode_tc_kernel<TT, RGV><<<grid, dec::THREADS, dec::TC_SMEM, s>>>(                                               \
+        tm_state, static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(has_cache ? K : nullptr),              \
+        static_cast<const TT*>(has_cache ? V : nullptr), kv_bstride, gated ? log_g : nullptr, g_bstride,              \
+        state != nullptr ? 1 : 0, sum_of_keys, scale, has_cache ? tk : 0, h, hq, nsplit, part_y, part_l,              \
+        static_cast<TT*>(O), status);                                                                                 \
+  } while (0)
   if (dtype == PR_BF16) {
     if (rg == 1) PR_LAUNCH_FUSED(__nv_bfloat16, 1); else PR_LAUNCH_FUSED(__nv_bfloat16, 4);
   } else {
