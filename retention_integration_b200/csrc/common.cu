@@ -42,6 +42,14 @@ int status_word(int device, int** dev_ptr, volatile int** host_ptr) {
   return PR_OK;
 }
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PR_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, const uint64_t* dims,
               const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
   std::call_once(g_encode_once, [] {

@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(dec::THREADS)
 decode_state_kernel(const T* __restrict__ Q, const T* __restrict__ state, const float* __restrict__ sok,
                     const float* __restrict__ a_last, long long a_batch_stride, long long q_bs, float scale, int h,
                     int hq, int nsplit, float* __restrict__ part_y, float* __restrict__ part_l) {
+  pdl_launch_dependents();
+  pdl_wait();
   using namespace dec;
   __shared__ float sq[RG][HD];
   __shared__ float red_y[THREADS / 32][RG][HD];
@@ -183,6 +185,8 @@ decode_finish_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* 
                      const float* __restrict__ a, long long q_bs, long long kv_bs, float scale, int tk, int h, int hq,
                      int nsplit, const float* __restrict__ part_y, const float* __restrict__ part_l,
                      T* __restrict__ O) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int HD = dec::HD;
   __shared__ float red[4][HD + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -345,6 +349,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_state, const T* __restri
   __shared__ float sfx[BLK];
   __shared__ float wsum[THREADS / 32][2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
   const int bh = blockIdx.x, split = blockIdx.y, grp = blockIdx.z;
   const int batch = bh / h, head = bh % h;
   const int ratio = hq / h;
@@ -383,6 +388,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_state, const T* __restri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = n_st > 0 ? tmem_base_s : 0u;
+  pdl_wait();  // everything above overlaps the tail of the kernel before this one
 
   // the first stages are requested before anything else is known
   if (warp == 7 && lane == 0) {
@@ -707,6 +713,8 @@ decode_recurrent_kernel(const T* __restrict__ Q, long long q_bs, const T* __rest
                         long long kv_bs, const float* __restrict__ log_g, long long g_bs, const T* state,
                         const float* sok, T* new_state, float* new_sok, float scale, int h, int hq, int nsplit,
                         float* __restrict__ part_y, float* __restrict__ part_l, T* __restrict__ O) {
+  pdl_launch_dependents();
+  pdl_wait();
   using namespace dec;
   __shared__ float sq[RG][HD];
   __shared__ float skv[2][HD];  // the token's key and value
@@ -854,6 +862,8 @@ decode_recurrent_kernel(const T* __restrict__ Q, long long q_bs, const T* __rest
 template <typename T>
 __global__ void __launch_bounds__(dec::HD)
 decode_merge_kernel(const float* __restrict__ part_y, const float* __restrict__ part_l, int nsplit, T* __restrict__ O) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const int e = threadIdx.x;
   float yt = 0.f, lt = 0.f;
@@ -869,6 +879,8 @@ decode_merge_kernel(const float* __restrict__ part_y, const float* __restrict__ 
 // (batch, head); tk is small (below the switch-over length), so one block-wide scan per 256 tokens.
 __global__ void __launch_bounds__(256)
 decode_gate_cumsum_kernel(const float* __restrict__ log_g, long long g_bs, float* __restrict__ a, int tk, int h) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float warp_tot[8];
   __shared__ float carry_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -901,6 +913,8 @@ __global__ void state_merge_kernel(const T* __restrict__ state, const float* __r
                                    const T* __restrict__ S, const float* __restrict__ gram,
                                    const float* __restrict__ a_last, T* __restrict__ new_state,
                                    float* __restrict__ new_sok, int bh_total) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int HD = dec::HD, DEX = dec::DEX, DR = ref_dim(HD);
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 elements
   const size_t total = (size_t)bh_total * DEX * 8;
@@ -949,6 +963,8 @@ template <typename T>
 __global__ void state_to_chunk_kernel(const T* __restrict__ state, const float* __restrict__ sok,
                                       T* __restrict__ out16, float* __restrict__ out32, float* __restrict__ gram,
                                       T* __restrict__ ghi, T* __restrict__ glo, int bh_total) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int HD = dec::HD, DEX = dec::DEX, DR = ref_dim(HD);
   const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 8 elements
   if (gid < (size_t)bh_total * HD * HD && (gram || ghi)) {
@@ -1057,9 +1073,9 @@ static int pr::launch_decode_state(int dtype, int b, int h, int hq, int d, const
   dim3 grid(b * h, nsplit, (ratio + rg - 1) / rg);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define PR_LAUNCH_DECODE(TT, RGV)                                                                              \
-  decode_state_kernel<TT, RGV><<<grid, dec::THREADS, 0, s>>>(static_cast<const TT*>(Q), static_cast<const TT*>(state), \
+  PR_CUDA(launch(decode_state_kernel<TT, RGV>, dim3(grid), dim3(dec::THREADS), 0, s, static_cast<const TT*>(Q), static_cast<const TT*>(state), \
                                                              sum_of_keys, a_last, a_batch_stride, q_bs, scale, h,    \
-                                                             hq, nsplit, part_y, part_l)
+                                                             hq, nsplit, part_y, part_l))
   if (dtype == PR_BF16) {
     if (rg == 1) PR_LAUNCH_DECODE(__nv_bfloat16, 1); else PR_LAUNCH_DECODE(__nv_bfloat16, 4);
   } else if (dtype == PR_FP16) {
@@ -1094,15 +1110,15 @@ static int pr::launch_decode_finish(int dtype, int b, int tk, int h, int hq, int
   const int nsplit = decode_split(b, h, hq);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
-    decode_finish_kernel<__nv_bfloat16><<<b * hq, 128, 0, s>>>(
+    PR_CUDA(launch(decode_finish_kernel<__nv_bfloat16>, dim3(b * hq), dim3(128), 0, s, 
         static_cast<const __nv_bfloat16*>(Q), static_cast<const __nv_bfloat16*>(K),
         static_cast<const __nv_bfloat16*>(V), a, q_bs, kv_bs, scale, tk, h, hq, nsplit, part_y, part_l,
-        static_cast<__nv_bfloat16*>(O));
+        static_cast<__nv_bfloat16*>(O)));
   else if (dtype == PR_FP16)
-    decode_finish_kernel<__half><<<b * hq, 128, 0, s>>>(static_cast<const __half*>(Q), static_cast<const __half*>(K),
+    PR_CUDA(launch(decode_finish_kernel<__half>, dim3(b * hq), dim3(128), 0, s, static_cast<const __half*>(Q), static_cast<const __half*>(K),
                                                         static_cast<const __half*>(V), a, q_bs, kv_bs, scale, tk, h, hq,
                                                         nsplit,
-                                                        part_y, part_l, static_cast<__half*>(O));
+                                                        part_y, part_l, static_cast<__half*>(O)));
   else
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_CUDA(cudaGetLastError());
@@ -1123,13 +1139,13 @@ extern "C" int pr_state_merge(int dtype, int b, int h, int d, const void* state,
   const unsigned grid = (unsigned)((threads + 255) / 256);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
-    state_merge_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+    PR_CUDA(launch(state_merge_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, 
         static_cast<const __nv_bfloat16*>(state), sum_of_keys, static_cast<const __nv_bfloat16*>(S), gram, a_last,
-        static_cast<__nv_bfloat16*>(new_state), new_sum_of_keys, b * h);
+        static_cast<__nv_bfloat16*>(new_state), new_sum_of_keys, b * h));
   else if (dtype == PR_FP16)
-    state_merge_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(state), sum_of_keys,
+    PR_CUDA(launch(state_merge_kernel<__half>, dim3(grid), dim3(256), 0, s, static_cast<const __half*>(state), sum_of_keys,
                                                     static_cast<const __half*>(S), gram, a_last,
-                                                    static_cast<__half*>(new_state), new_sum_of_keys, b * h);
+                                                    static_cast<__half*>(new_state), new_sum_of_keys, b * h));
   else
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_CUDA(cudaGetLastError());
@@ -1153,13 +1169,13 @@ extern "C" int pr_state_to_chunk_layout(int dtype, int b, int h, int d, const vo
   const unsigned grid = (unsigned)((threads + 255) / 256);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16)
-    state_to_chunk_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+    PR_CUDA(launch(state_to_chunk_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, 
         static_cast<const __nv_bfloat16*>(state), sum_of_keys, static_cast<__nv_bfloat16*>(out16), out32, gram,
-        static_cast<__nv_bfloat16*>(gram_hi), static_cast<__nv_bfloat16*>(gram_lo), b * h);
+        static_cast<__nv_bfloat16*>(gram_hi), static_cast<__nv_bfloat16*>(gram_lo), b * h));
   else if (dtype == PR_FP16)
-    state_to_chunk_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(state), sum_of_keys,
+    PR_CUDA(launch(state_to_chunk_kernel<__half>, dim3(grid), dim3(256), 0, s, static_cast<const __half*>(state), sum_of_keys,
                                                       static_cast<__half*>(out16), out32, gram,
-                                                      static_cast<__half*>(gram_hi), static_cast<__half*>(gram_lo), b * h);
+                                                      static_cast<__half*>(gram_hi), static_cast<__half*>(gram_lo), b * h));
   else
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_CUDA(cudaGetLastError());
@@ -1177,7 +1193,7 @@ extern "C" int pr_gate_cumsum(int b, int t, int h, const float* log_g, long long
              t, h);
   PR_REQUIRE(log_g && a_out, PR_ERR_BAD_ARG, "null pointer");
   PR_CUDA(cudaSetDevice(device));
-  decode_gate_cumsum_kernel<<<b * h, 256, 0, static_cast<cudaStream_t>(stream)>>>(log_g, g_bstride, a_out, t, h);
+  PR_CUDA(launch(decode_gate_cumsum_kernel, dim3(b * h), dim3(256), 0, static_cast<cudaStream_t>(stream), log_g, g_bstride, a_out, t, h));
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }
@@ -1252,11 +1268,11 @@ extern "C" int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, i
       PR_CUDA(cudaFuncSetAttribute(decode_tc_kernel<TT, RGV>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));  \
       configured[device] = true;                                                                                      \
     }                                                                                                                 \
-    decode_tc_kernel<TT, RGV><<<grid, dec::THREADS, dec::TC_SMEM, s>>>(                                               \
+    PR_CUDA(launch(decode_tc_kernel<TT, RGV>, dim3(grid), dim3(dec::THREADS), dec::TC_SMEM, s,                                                \
         tm_state, static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(has_cache ? K : nullptr),              \
         static_cast<const TT*>(has_cache ? V : nullptr), kv_bstride, gated ? log_g : nullptr, g_bstride,              \
         state != nullptr ? 1 : 0, sum_of_keys, scale, has_cache ? tk : 0, h, hq, nsplit, part_y, part_l,              \
-        static_cast<TT*>(O), status);                                                                                 \
+        static_cast<TT*>(O), status));                                                                                 \
   } while (0)
   if (dtype == PR_BF16) {
     if (rg == 1) PR_LAUNCH_FUSED(__nv_bfloat16, 1); else PR_LAUNCH_FUSED(__nv_bfloat16, 4);
@@ -1267,9 +1283,9 @@ extern "C" int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, i
   PR_CUDA(cudaGetLastError());
   if (nsplit > 1) {
     if (dtype == PR_BF16)
-      decode_merge_kernel<__nv_bfloat16><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__nv_bfloat16*>(O));
+      PR_CUDA(launch(decode_merge_kernel<__nv_bfloat16>, dim3(b * hq), dim3(dec::HD), 0, s, part_y, part_l, nsplit, static_cast<__nv_bfloat16*>(O)));
     else
-      decode_merge_kernel<__half><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__half*>(O));
+      PR_CUDA(launch(decode_merge_kernel<__half>, dim3(b * hq), dim3(dec::HD), 0, s, part_y, part_l, nsplit, static_cast<__half*>(O)));
     PR_CUDA(cudaGetLastError());
   }
   return PR_OK;
@@ -1304,10 +1320,10 @@ extern "C" int pr_decode_recurrent(int dtype, int b, int h, int hq, int d, const
   dim3 grid(b * h, nsplit, groups);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define PR_LAUNCH_REC(TT, RGV)                                                                                        \
-  decode_recurrent_kernel<TT, RGV><<<grid, dec::THREADS, 0, s>>>(                                                      \
+  PR_CUDA(launch(decode_recurrent_kernel<TT, RGV>, dim3(grid), dim3(dec::THREADS), 0, s,                                                       \
       static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(K), static_cast<const TT*>(V), kv_bstride, log_g,  \
       g_bstride, static_cast<const TT*>(state), sum_of_keys, static_cast<TT*>(new_state), new_sum_of_keys, scale, h,  \
-      hq, nsplit, part_y, part_l, static_cast<TT*>(O))
+      hq, nsplit, part_y, part_l, static_cast<TT*>(O)))
   if (dtype == PR_BF16) {
     if (rg == 1) PR_LAUNCH_REC(__nv_bfloat16, 1); else PR_LAUNCH_REC(__nv_bfloat16, 4);
   } else {
@@ -1317,9 +1333,9 @@ extern "C" int pr_decode_recurrent(int dtype, int b, int h, int hq, int d, const
   PR_CUDA(cudaGetLastError());
   if (nsplit > 1) {
     if (dtype == PR_BF16)
-      decode_merge_kernel<__nv_bfloat16><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__nv_bfloat16*>(O));
+      PR_CUDA(launch(decode_merge_kernel<__nv_bfloat16>, dim3(b * hq), dim3(dec::HD), 0, s, part_y, part_l, nsplit, static_cast<__nv_bfloat16*>(O)));
     else
-      decode_merge_kernel<__half><<<b * hq, dec::HD, 0, s>>>(part_y, part_l, nsplit, static_cast<__half*>(O));
+      PR_CUDA(launch(decode_merge_kernel<__half>, dim3(b * hq), dim3(dec::HD), 0, s, part_y, part_l, nsplit, static_cast<__half*>(O)));
     PR_CUDA(cudaGetLastError());
   }
   return PR_OK;

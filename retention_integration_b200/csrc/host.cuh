@@ -8,6 +8,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "../../include/pr_b200.h"
 
@@ -48,5 +49,26 @@ int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, cons
               const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// 0 when the environment variable PR_PDL=0 asks for plain stream order (read once).
+bool pdl_enabled();
+
+// Kernel launch with programmatic stream serialisation allowed (see pdl_wait() in sm100.cuh): the
+// kernel may start while its predecessor in the stream drains and blocks at its own
+// griddepcontrol.wait.  Stream capture records the edge as a programmatic dependency.
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace pr
