@@ -299,7 +299,9 @@ int pr_state_to_chunk_layout(int dtype, int b, int h, int d, const void* state, 
  * compression) and what deploy/models/powercoder/kvgs_dynamic_cache.py:131-172 would hold as a cache
  * of length one.  Batch entries of q / k, v / log_g are q_bstride / kv_bstride / g_bstride elements
  * apart.  new_state, new_sum_of_keys may alias the inputs when hq / h <= 4.  part_y / part_l as for
- * pr_decode_step (needed only for small b*h). */
+ * pr_decode_step (needed only for small b*h).  The state moves by TMA in both directions (16-byte aligned,
+ * dense); the output reads the stored state as the reference's query_state does and takes the new token
+ * exactly, y = e^g (phi(q) . S) + (phi(q) . phi_K(k)) v, not through the 16-bit rounding of the advanced state. */
 int pr_decode_recurrent(int dtype, int b, int h, int hq, int d, const void* Q, long long q_bstride, const void* K,
                         const void* V, long long kv_bstride, const float* log_g, long long g_bstride,
                         const void* state, const float* sum_of_keys, void* new_state, float* new_sum_of_keys,

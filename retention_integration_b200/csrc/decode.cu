@@ -701,162 +701,6 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_state, const T* __restri
   if (warp == 0 && n_st > 0) tmem_dealloc(tmem, TC_TMEM_COLS);
 }
 
-// Pure-recurrent decode step: the state is advanced by one token and read in the same pass,
-//     S' = e^g S + phi_K(k) v^T,   z' = e^g z + phi_K(k),   y = phi(s q)^T S' / phi(s q) . z'
-// which is the reference's inference step with switch_over_seq_len = 1 (one cached token, then
-// compression, retention/power_retention_maker.py:354-382) without the cache round trip.  Every
-// state row is read once and written once; rows are owned by threads exactly as in the read-only
-// step, so with one group of query heads per kv head the update may be done in place.
-template <typename T, int RG>
-__global__ void __launch_bounds__(dec::THREADS, RG == 1 ? 4 : 2)
-decode_recurrent_kernel(const T* __restrict__ Q, long long q_bs, const T* __restrict__ Kt, const T* __restrict__ Vt,
-                        long long kv_bs, const float* __restrict__ log_g, long long g_bs, const T* state,
-                        const float* sok, T* new_state, float* new_sok, float scale, int h, int hq, int nsplit,
-                        float* __restrict__ part_y, float* __restrict__ part_l, T* __restrict__ O) {
-  pdl_launch_dependents();
-  pdl_wait();
-  using namespace dec;
-  __shared__ float sq[RG][HD];
-  __shared__ float skv[2][HD];  // the token's key and value
-  __shared__ float red_y[THREADS / 32][RG][HD];
-  __shared__ float red_l[THREADS / 32][RG];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int bh = blockIdx.x, split = blockIdx.y, grp = blockIdx.z;
-  const int batch = bh / h, head = bh % h;
-  const int ratio = hq / h;
-  const int r0 = grp * RG, nr = min(RG, ratio - r0);
-  const bool writer = (grp == 0);  // one group of query heads writes the new state
-  const float decay = log_g ? __expf(log_g[(size_t)batch * g_bs + head]) : 1.f;
-  for (int i = tid; i < RG * HD; i += THREADS) {
-    const int r = i / HD, e = i % HD;
-    float q = 0.f;
-    if (r < nr) q = float(Q[(size_t)batch * q_bs + (size_t)(head * ratio + r0 + r) * HD + e]);
-    sq[r][e] = float(T(q * scale));
-  }
-  if (tid < 2 * HD) {
-    const T* src = (tid < HD ? Kt : Vt) + (size_t)batch * kv_bs + (size_t)head * HD + (tid & (HD - 1));
-    skv[tid / HD][tid & (HD - 1)] = float(*src);
-  }
-  __syncthreads();
-
-  const int rows_per_split = (DEX + nsplit - 1) / nsplit;
-  const int d_begin = split * rows_per_split, d_end = min(DEX, d_begin + rows_per_split);
-  const int sub = tid & 7;
-  int D = d_begin + (tid >> 3);
-  int a = 0, b = 0;
-  if (D < DEX) exact_decode(D, &a, &b);
-  float vt[8];
-#pragma unroll
-  for (int k = 0; k < 8; ++k) vt[k] = skv[1][sub * 8 + k];
-  float acc[RG][8];
-  float accl[RG];
-#pragma unroll
-  for (int r = 0; r < RG; ++r) {
-    accl[r] = 0.f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) acc[r][k] = 0.f;
-  }
-  const T* sbase = state + (size_t)bh * DEX * HD;
-  const float* kbase = sok + (size_t)bh * DEX;
-  T* obase = new_state + (size_t)bh * DEX * HD;
-  float* okbase = new_sok + (size_t)bh * DEX;
-  constexpr int UN = PR_DEC_UN;
-  for (; D < d_end; D += UN * ROWS_PER_ITER) {
-    uint4 v[UN];
-    float sk[UN];
-    int ra[UN], rb[UN];
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int Du = D + u * ROWS_PER_ITER;
-      ra[u] = a;
-      rb[u] = b;
-      if (Du < d_end) {
-        v[u] = *reinterpret_cast<const uint4*>(sbase + (size_t)Du * HD + sub * 8);
-        sk[u] = kbase[Du];
-      }
-      b += ROWS_PER_ITER;
-      while (b >= HD && a < HD) {
-        b = b - HD + a + 1;
-        ++a;
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < UN; ++u) {
-      const int Du = D + u * ROWS_PER_ITER;
-      if (Du >= d_end) break;
-      const int ia = min(ra[u], HD - 1), ib = min(rb[u], HD - 1);
-      // key-side expansion entry of the new token, rounded like the inputs, with the pair weight
-      const float phik = float(T(skv[0][ia] * skv[0][ib])) * (ia == ib ? 1.f : 2.f);
-      float x[8];
-      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-      uint32_t ow[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 p2 = Pack2<T>::to_f32(w[k]);
-        // the reference rounds state * decay to the state's dtype before adding the update (:374-382)
-        const float2 od = Pack2<T>::to_f32(Pack2<T>::from_f32(p2.x * decay, p2.y * decay));
-        x[2 * k] = fmaf(phik, vt[2 * k], od.x);
-        x[2 * k + 1] = fmaf(phik, vt[2 * k + 1], od.y);
-        ow[k] = Pack2<T>::from_f32(x[2 * k], x[2 * k + 1]);
-      }
-      const float skn = fmaf(sk[u], decay, phik);
-      if (writer) {
-        *reinterpret_cast<uint4*>(obase + (size_t)Du * HD + sub * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-        if (sub == 0) okbase[Du] = skn;
-      }
-#pragma unroll
-      for (int r = 0; r < RG; ++r) {
-        if (r < nr) {
-          const float phi = float(T(sq[r][ia] * sq[r][ib]));
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc[r][k] = fmaf(phi, x[k], acc[r][k]);
-          accl[r] = fmaf(phi, skn, accl[r]);
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int r = 0; r < RG; ++r) {
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float t = acc[r][k];
-      t += __shfl_xor_sync(0xffffffffu, t, 8);
-      t += __shfl_xor_sync(0xffffffffu, t, 16);
-      acc[r][k] = t;
-    }
-    float t = (sub == 0) ? accl[r] : 0.f;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-    accl[r] = t;
-  }
-  if (lane < 8) {
-#pragma unroll
-    for (int r = 0; r < RG; ++r)
-#pragma unroll
-      for (int k = 0; k < 8; ++k) red_y[warp][r][lane * 8 + k] = acc[r][k];
-  }
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < RG; ++r) red_l[warp][r] = accl[r];
-  }
-  __syncthreads();
-  for (int i = tid; i < nr * HD; i += THREADS) {
-    const int r = i / HD, e = i % HD;
-    float yt = 0.f, lt = 0.f;
-#pragma unroll
-    for (int w = 0; w < THREADS / 32; ++w) {
-      yt += red_y[w][r][e];
-      lt += red_l[w][r];
-    }
-    const size_t row = (size_t)batch * hq + head * ratio + r0 + r;
-    if (nsplit == 1) {
-      O[row * HD + e] = T(yt * safe_recip(lt));
-    } else {
-      part_y[(row * nsplit + split) * HD + e] = yt;
-      if (e == 0) part_l[row * nsplit + split] = lt;
-    }
-  }
-}
 
 // Sums the partial results of a split decode step, normalises and writes the output.
 template <typename T>
@@ -1291,7 +1135,306 @@ extern "C" int pr_decode_step_strided(int dtype, int b, int tk, int h, int hq, i
   return PR_OK;
 }
 
-// Pure-recurrent decode step (see decode_recurrent_kernel): q [b,1,hq,d], k, v [b,1,h,d] (batch
+namespace pr {
+// Pure-recurrent decode step: the state is advanced by one token and read in the same pass,
+//     S' = e^g S + phi_K(k) v^T,   z' = e^g z + phi_K(k),   y = phi(s q)^T S' / phi(s q) . z'
+// which is the reference's inference step with switch_over_seq_len = 1 (one cached token, then
+// compression, retention/power_retention_maker.py:354-382) without the cache round trip.  Every
+// state row is read once and written once.
+//
+// The state is streamed by TMA in both directions (same roles and rings as
+// decode_tc_kernel).  A 64-row stage lands in swizzled shared memory and the tensor core contracts it,
+// as stored, with phi(s q); once those products have completed, warps 0-3 advance the stage in place,
+//     S' = round(round(e^g S) + phi_K(k) v^T),
+// and one thread of warp 4 hands it to a TMA store into new_state.  The output is
+//     y = e^g (phi(s q)^T S) + (phi(s q) . phi_K(k)) v,
+// i.e. the stored state is read as the reference's query_state reads it and the new token enters
+// exactly, as it does through the reference's attention over the one cached token
+// (power_retention_maker.py:354-363) - not through the 16-bit rounding of the advanced state.
+// Warp 5 advances the stage's slice of sum_of_keys, writes it, and forms the normaliser, the token's
+// weight phi(s q) . phi_K(k) and the A atoms.  A ring slot is refilled once its store has read it.
+// In place (new_state == state) every stage is loaded before it is stored and no other CTA touches
+// it; with several groups of query heads per kv head only group 0 stores, and the buffers must differ.
+template <typename T, int RG>
+__global__ void __launch_bounds__(dec::THREADS, RG == 1 ? 4 : 2)
+decode_recurrent_tc_kernel(const __grid_constant__ CUtensorMap tm_state, const __grid_constant__ CUtensorMap tm_new,
+                           const T* __restrict__ Q, long long q_bs, const T* __restrict__ Kt,
+                           const T* __restrict__ Vt, long long kv_bs, const float* __restrict__ log_g, long long g_bs,
+                           const float* sok, float* new_sok, float scale, int h, int hq, int nsplit,
+                           float* __restrict__ part_y, float* __restrict__ part_l, T* __restrict__ O,
+                           int* __restrict__ status) {
+  using namespace dec;
+  constexpr int UW = 4;  // warps advancing the state
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t b_full[NSB], u_full[NSB], a_full[NSB], done[NSB], st_done[NSB], acc_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  __shared__ float sq[RG][HD];
+  __shared__ float skv[2][HD];  // the token's key and value
+  __shared__ float red_y[RG][HD];
+  __shared__ float red_l[RG], red_c[RG];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  const int bh = blockIdx.x, split = blockIdx.y, grp = blockIdx.z;
+  const int batch = bh / h, head = bh % h;
+  const int ratio = hq / h;
+  const int r0 = grp * RG, nr = min(RG, ratio - r0);
+  const bool writer = (grp == 0);  // one group of query heads writes the new state
+  const int st_per = (N_STAGES + nsplit - 1) / nsplit;
+  const int st_begin = min(N_STAGES, split * st_per);
+  const int n_st = min(N_STAGES, st_begin + st_per) - st_begin;
+
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smB = smem_raw + (sbase - smem_u32(smem_raw));  // NSB x B_BYTES
+  uint8_t* smA = smB + NSB * B_BYTES;                      // NSB x A_BYTES
+  uint8_t* smK = smA + NSB * A_BYTES;                      // NSB x K_BYTES
+  const float* kbase = sok + (size_t)bh * DEX;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < NSB; ++s) {
+      mbar_init(&b_full[s], 1);
+      mbar_init(&u_full[s], UW);
+      mbar_init(&a_full[s], 1);
+      mbar_init(&done[s], 1);
+      mbar_init(&st_done[s], 1);
+    }
+    mbar_init(&acc_done, 1);
+    fence_mbar_init();
+  }
+  for (int i = tid; i < NSB * A_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(smA)[i] = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  if (warp == 0 && n_st > 0) {
+    tmem_alloc(&tmem_base_s, TC_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = n_st > 0 ? tmem_base_s : 0u;
+  pdl_wait();  // everything above overlaps the tail of the kernel before this one
+
+  if (warp == 7 && lane == 0) {
+    for (int it = 0; it < min(n_st, NSB); ++it) {
+      const int D0 = (st_begin + it) * ST_ROWS;
+      const uint32_t kb = (uint32_t)min(ST_ROWS, DEX - D0) * 4u;
+      mbar_expect_tx(&b_full[it], B_BYTES + kb);
+      tma_load_3d(smB + it * B_BYTES, &tm_state, &b_full[it], 0, D0, bh);
+      bulk_load_1d(smK + it * K_BYTES, kbase + D0, kb, &b_full[it]);
+    }
+  }
+
+  const float decay = log_g ? __expf(log_g[(size_t)batch * g_bs + head]) : 1.f;
+  for (int i = tid; i < RG * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    float q = 0.f;
+    if (r < nr) q = float(Q[(size_t)batch * q_bs + (size_t)(head * ratio + r0 + r) * HD + e]);
+    sq[r][e] = float(T(q * scale));
+  }
+  if (tid < 2 * HD) {
+    const T* src = (tid < HD ? Kt : Vt) + (size_t)batch * kv_bs + (size_t)head * HD + (tid & (HD - 1));
+    skv[tid / HD][tid & (HD - 1)] = float(*src);
+  }
+  __syncthreads();
+
+  if (warp < UW) {
+    // ------------------------------------------------ the state, advanced in place in shared memory
+    const int sub = tid & 7, row16 = tid >> 3;  // this thread's 16-byte column group and row within a pass
+    float vt[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) vt[k] = skv[1][sub * 8 + k];
+    int D = st_begin * ST_ROWS + row16;
+    int a = 0, b = 0;
+    exact_decode(min(D, DEX - 1), &a, &b);
+    for (int it = 0; it < n_st; ++it) {
+      const int s = it % NSB;
+      if (!mbar_wait(&done[s], (it / NSB) & 1, &abort_flag)) break;  // the stage has been read as stored
+      uint8_t* tile = smB + s * B_BYTES;
+#pragma unroll
+      for (int ps = 0; ps < ST_ROWS / 16; ++ps) {
+        const int r = row16 + 16 * ps;
+        if (writer && D < DEX) {
+          uint4* cell = reinterpret_cast<uint4*>(tile + swz128(r, sub));
+          const uint4 v = *cell;
+          // key-side expansion entry of the new token, rounded like the inputs, with the pair weight
+          const float phik = float(T(skv[0][a] * skv[0][b])) * (a == b ? 1.f : 2.f);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          uint32_t ow[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 p2 = Pack2<T>::to_f32(w[k]);
+            // the reference rounds state * decay to the state's dtype before adding the update (:374-382)
+            const float2 od = Pack2<T>::to_f32(Pack2<T>::from_f32(p2.x * decay, p2.y * decay));
+            ow[k] = Pack2<T>::from_f32(fmaf(phik, vt[2 * k], od.x), fmaf(phik, vt[2 * k + 1], od.y));
+          }
+          *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+        D += 16;
+        b += 16;
+        while (b >= HD && a < HD - 1) {
+          b = b - HD + a + 1;
+          ++a;
+        }
+        b = min(b, HD - 1);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&u_full[s]);
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------ stores of the advanced stages, then the output
+    if (lane == 0 && n_st > 0) {
+      bool ok = true;
+      for (int it = 0; it < n_st; ++it) {
+        const int s = it % NSB;
+        ok = mbar_wait(&u_full[s], (it / NSB) & 1, &abort_flag);
+        if (!ok) break;
+        if (writer) {
+          tma_store_3d(&tm_new, smB + s * B_BYTES, 0, (st_begin + it) * ST_ROWS, bh);
+          bulk_commit_group();
+          bulk_wait_group_read<1>();  // the store before this one has read its stage
+        }
+        if (it > 0) mbar_arrive(&st_done[(it - 1) % NSB]);
+      }
+      bulk_wait_group_read<0>();
+      if (ok) mbar_arrive(&st_done[(n_st - 1) % NSB]);
+      bulk_wait_group<0>();  // the stores are performed before this CTA is done
+    }
+    __syncwarp();
+    // this warp owns tensor-memory lanes 0-31: fetch the output
+    const bool have = n_st > 0 && mbar_wait(&acc_done, 0, &abort_flag);
+    if (have) tc_fence_after();
+#pragma unroll
+    for (int j = 0; j < HD / 16; ++j) {
+      uint32_t v[16];
+      if (have) {
+        tmem_ld16(tmem + j * 16, v);
+        tmem_wait_ld();
+      }
+      if (lane < RG) {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) red_y[lane][j * 16 + k] = have ? __uint_as_float(v[k]) : 0.f;
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------ sum_of_keys, the normaliser and the A atoms
+    float l_acc[RG], c_acc[RG];
+#pragma unroll
+    for (int r = 0; r < RG; ++r) l_acc[r] = c_acc[r] = 0.f;
+    if (n_st > 0) {
+      int D = st_begin * ST_ROWS + 2 * lane;  // this lane's rows D and D + 1 of every stage
+      int a = 0, b = 0;
+      exact_decode(min(D, DEX - 1), &a, &b);
+      float* okbase = new_sok + (size_t)bh * DEX;
+      const uint32_t a_off = swz128(0, lane >> 2) + (lane & 3) * 4;
+      for (int it = 0; it < n_st; ++it) {
+        const int s = it % NSB;
+        if (it >= NSB && !mbar_wait(&done[s], ((it / NSB) - 1) & 1, &abort_flag)) break;
+        if (!mbar_wait(&b_full[s], (it / NSB) & 1, &abort_flag)) break;  // the stage's sum_of_keys slice
+        const bool in = D < DEX;  // D is even and so is DEX: D + 1 is inside whenever D is
+        int a1 = a, b1 = b + 1;
+        if (b1 >= HD) {
+          a1 = min(a + 1, HD - 1);
+          b1 = a1;
+        }
+        float2 sk = make_float2(0.f, 0.f), pk = make_float2(0.f, 0.f);
+        if (in) {
+          sk = *reinterpret_cast<const float2*>(smK + s * K_BYTES + 8 * lane);
+          pk.x = float(T(skv[0][a] * skv[0][b])) * (a == b ? 1.f : 2.f);
+          pk.y = float(T(skv[0][a1] * skv[0][b1])) * (a1 == b1 ? 1.f : 2.f);
+          sk.x = fmaf(sk.x, decay, pk.x);
+          sk.y = fmaf(sk.y, decay, pk.y);
+          if (writer) *reinterpret_cast<float2*>(okbase + D) = sk;
+        }
+#pragma unroll
+        for (int r = 0; r < RG; ++r) {
+          if (r < nr) {
+            const uint32_t w = in ? Pack2<T>::from_f32(sq[r][a] * sq[r][b], sq[r][a1] * sq[r][b1]) : 0u;
+            *reinterpret_cast<uint32_t*>(smA + s * A_BYTES + r * 128 + ((a_off ^ (r << 4)))) = w;
+            const float2 ph = Pack2<T>::to_f32(w);
+            l_acc[r] = fmaf(ph.x, sk.x, fmaf(ph.y, sk.y, l_acc[r]));
+            c_acc[r] = fmaf(ph.x, pk.x, fmaf(ph.y, pk.y, c_acc[r]));
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[s]);
+        D += ST_ROWS;
+        b += ST_ROWS;
+        while (b >= HD && a < HD - 1) {
+          b = b - HD + a + 1;
+          ++a;
+        }
+        b = min(b, HD - 1);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+      float t = l_acc[r], u = c_acc[r];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        t += __shfl_xor_sync(0xffffffffu, t, off);
+        u += __shfl_xor_sync(0xffffffffu, u, off);
+      }
+      if (lane == 0) {
+        red_l[r] = t;
+        red_c[r] = u;
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------ MMA issuer: products on the stages as stored
+    if (lane == 0 && n_st > 0) {
+      const uint32_t idesc = umma_idesc(128, HD, Pack2<T>::is_bf16, false, true);
+      bool ok = true;
+      for (int it = 0; it < n_st; ++it) {
+        const int s = it % NSB, ph = (it / NSB) & 1;
+        ok = mbar_wait(&b_full[s], ph, &abort_flag) && mbar_wait(&a_full[s], ph, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smA + s * A_BYTES), b_addr = smem_u32(smB + s * B_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < ST_ROWS / 16; ++ks)
+          umma_ss(tmem, umma_desc_sw128(a_addr + ks * 32, 16, 0), umma_desc_sw128(b_addr + ks * 2048, 8192, 1024), idesc,
+                  (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&done[s]);
+      }
+      if (ok) umma_commit(&acc_done);
+    }
+  } else {
+    // ------------------------------------------------ TMA loads, stages NSB and up
+    if (lane == 0) {
+      for (int it = NSB; it < n_st; ++it) {
+        const int s = it % NSB;
+        if (!mbar_wait(&st_done[s], ((it / NSB) - 1) & 1, &abort_flag)) break;  // stored, hence read and advanced
+        const int D0 = (st_begin + it) * ST_ROWS;
+        const uint32_t kb = (uint32_t)min(ST_ROWS, DEX - D0) * 4u;
+        mbar_expect_tx(&b_full[s], B_BYTES + kb);
+        tma_load_3d(smB + s * B_BYTES, &tm_state, &b_full[s], 0, D0, bh);
+        bulk_load_1d(smK + s * K_BYTES, kbase + D0, kb, &b_full[s]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && abort_flag) *status = ST_TIMEOUT;
+  for (int i = tid; i < nr * HD; i += THREADS) {
+    const int r = i / HD, e = i % HD;
+    const float yt = fmaf(decay, red_y[r][e], red_c[r] * skv[1][e]), lt = red_l[r];
+    const size_t row = (size_t)batch * hq + head * ratio + r0 + r;
+    if (nsplit == 1) {
+      O[row * HD + e] = T(yt * safe_recip(lt));
+    } else {
+      part_y[(row * nsplit + split) * HD + e] = yt;
+      if (e == 0) part_l[row * nsplit + split] = lt;
+    }
+  }
+  if (warp == 0 && n_st > 0) tmem_dealloc(tmem, TC_TMEM_COLS);
+}
+
+}  // namespace pr
+
+// Pure-recurrent decode step (see decode_recurrent_tc_kernel): q [b,1,hq,d], k, v [b,1,h,d] (batch
 // entries q_bstride / kv_bstride elements apart), log_g [b,1,h] (g_bstride floats apart) or NULL.
 // new_state / new_sum_of_keys may alias state / sum_of_keys when hq / h <= 4 (each state row is then
 // read and written by one thread only); with more query heads per kv head they must be other buffers.
@@ -1305,7 +1448,10 @@ extern "C" int pr_decode_recurrent(int dtype, int b, int h, int hq, int d, const
   PR_REQUIRE(b > 0 && h > 0 && hq > 0 && hq % h == 0, PR_ERR_BAD_ARG, "bad sizes b=%d h=%d hq=%d", b, h, hq);
   PR_REQUIRE(dtype == PR_BF16 || dtype == PR_FP16, PR_ERR_BAD_ARG, "dtype %d", dtype);
   PR_REQUIRE(Q && K && V && state && sum_of_keys && new_state && new_sum_of_keys && O, PR_ERR_BAD_ARG, "null pointer");
-  PR_REQUIRE(aligned16(Q) && aligned16(state) && aligned16(new_state), PR_ERR_BAD_ARG, "misaligned pointer");
+  PR_REQUIRE(aligned16(Q) && aligned16(state) && aligned16(new_state) && aligned16(sum_of_keys) &&
+                 aligned16(new_sum_of_keys),
+             PR_ERR_BAD_ARG, "misaligned pointer");
+  PR_REQUIRE(device >= 0 && device < dec::MAX_DEVICES, PR_ERR_BAD_ARG, "device ordinal %d out of range", device);
   PR_REQUIRE(q_bstride >= (long long)hq * d && kv_bstride >= (long long)h * d && (!log_g || g_bstride >= h),
              PR_ERR_BAD_ARG, "a batch stride is smaller than one batch entry");
   const int ratio = hq / h;
@@ -1319,11 +1465,32 @@ extern "C" int pr_decode_recurrent(int dtype, int b, int h, int hq, int d, const
   PR_CUDA(cudaSetDevice(device));
   dim3 grid(b * h, nsplit, groups);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = nullptr;
+  int rc = status_word(device, &status, nullptr);
+  if (rc) return rc;
+  CUtensorMap tm_state, tm_new;
+  {
+    uint64_t dims[3] = {(uint64_t)dec::HD, (uint64_t)dec::DEX, (uint64_t)b * h};
+    uint64_t strides[3] = {0, (uint64_t)dec::HD * 2, (uint64_t)dec::DEX * dec::HD * 2};
+    uint32_t box[3] = {(uint32_t)dec::HD, (uint32_t)dec::ST_ROWS, 1};
+    if ((rc = make_tmap(&tm_state, state, 2, 3, dims, strides, box, true))) return rc;
+    if ((rc = make_tmap(&tm_new, new_state, 2, 3, dims, strides, box, true))) return rc;
+  }
 #define PR_LAUNCH_REC(TT, RGV)                                                                                        \
-  PR_CUDA(launch(decode_recurrent_kernel<TT, RGV>, dim3(grid), dim3(dec::THREADS), 0, s,                                                       \
-      static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(K), static_cast<const TT*>(V), kv_bstride, log_g,  \
-      g_bstride, static_cast<const TT*>(state), sum_of_keys, static_cast<TT*>(new_state), new_sum_of_keys, scale, h,  \
-      hq, nsplit, part_y, part_l, static_cast<TT*>(O)))
+  do {                                                                                                                \
+    static bool configured[dec::MAX_DEVICES] = {false}; /* per instantiation and device */                           \
+    if (!configured[device]) {                                                                                        \
+      PR_CUDA(cudaFuncSetAttribute(decode_recurrent_tc_kernel<TT, RGV>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                   (int)dec::TC_SMEM));                                                               \
+      PR_CUDA(cudaFuncSetAttribute(decode_recurrent_tc_kernel<TT, RGV>,                                               \
+                                   cudaFuncAttributePreferredSharedMemoryCarveout, 100));                             \
+      configured[device] = true;                                                                                      \
+    }                                                                                                                 \
+    PR_CUDA(launch(decode_recurrent_tc_kernel<TT, RGV>, grid, dim3(dec::THREADS), dec::TC_SMEM, s, tm_state, tm_new,  \
+                   static_cast<const TT*>(Q), q_bstride, static_cast<const TT*>(K), static_cast<const TT*>(V),        \
+                   kv_bstride, log_g, g_bstride, sum_of_keys, new_sum_of_keys, scale, h, hq, nsplit, part_y, part_l,  \
+                   static_cast<TT*>(O), status));                                                                     \
+  } while (0)
   if (dtype == PR_BF16) {
     if (rg == 1) PR_LAUNCH_REC(__nv_bfloat16, 1); else PR_LAUNCH_REC(__nv_bfloat16, 4);
   } else {
