@@ -67,6 +67,7 @@ def make_inputs(b, t, h, d, device, seed0=0, heads=None):
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of each tensor-core kernel, from an ncu
 # capture of this benchmark at t = 65536 with two heads per launch (0.25 GB of operands per launch, twice the L2);
 # traffic grows in proportion to the heads processed.  None: not captured.
+NCU_DRAM_BYTES_DECODE_STATE = 147.0e6  # decode_tc_kernel, b16 h32: dram__bytes_read + write per launch
 NCU_DRAM_BYTES_T65536_H2 = {"pr_expand_grad": 86.2e6, "pr_chunk_dkv": 187.2e6, "pr_chunk_out": 105.4e6,
                             "pr_chunk_state": 55.8e6, "pr_chunk_dq": 110.1e6}
 
@@ -281,7 +282,10 @@ def decode_measure(dev, steps=512, with_extras=True, use_graph=True):
         "roofline": {"bound": "hbm", "kernel": "decode step (one kernel)", "achieved": step_gbs, "peak": peak,
                      "unit": "GB/s", "frac": step_gbs / peak,
                      "peak_source": "measured" if "hbm_gbs" in peaks else "fallback",
-                     "algorithmic_bytes_per_step": step_bytes, "state_bytes": state_bytes, "traffic": None},
+                     "algorithmic_bytes_per_step": step_bytes, "state_bytes": state_bytes,
+                     "traffic": NCU_DRAM_BYTES_DECODE_STATE + (step_bytes - state_bytes),
+                     "traffic_source": "ncu dram bytes read+write of one launch with 5-8 cached tokens (147 MB for "
+                                       "141 MB of state), plus the algorithmic bytes of the average step's cache"},
     }
     if with_extras:
         # the same step with an empty cache: the state read alone, launches queued back to back
