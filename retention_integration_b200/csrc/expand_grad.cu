@@ -11,11 +11,11 @@
 // Key side (gradient of the chunk state, retention/_update_state/reference.py:55-83):
 //   W = V, State = w (.) dS_m, Gs = dG_m + dG_m^T, g_i = 1, mult = 1, f_i = exp((A_m - a_i)/2).
 //
-// One CTA owns 256 tokens (two row tiles of 128) of one (batch, chunk, head), so that each
-// state tile fetched from L2 feeds two products.  The expansion gradient dphi is never
-// written to memory: tiles of 128 expanded rows are produced in tensor memory, one buffer
-// per row tile, and drained by the row tile's four warps while the tensor core fills the
-// other buffer.  Each thread owns one token row and keeps x~ and dx~ in registers; the
+// One CTA owns one row tile of 128 tokens of one (batch, chunk, head) and two CTAs share an SM
+// (Cfg<1>; Cfg<2> is the earlier shape, two row tiles in one CTA per SM, 7 % slower: measured
+// 0.302 vs 0.282 ms per launch at b1 t65536 h8).  The expansion gradient dphi is never written to
+// memory: tiles of 128 expanded rows are produced in tensor memory, two buffers per row tile, and
+// drained by the row tile's four warps while the tensor core fills the other buffer.  Each thread owns one token row and keeps x~ and dx~ in registers; the
 // triangle's (a, b) pattern is resolved at compile time, so the drain is two FMAs per entry.
 #include <type_traits>
 
@@ -29,12 +29,28 @@ namespace eg {
 constexpr int HD = 64;
 constexpr int D2 = ref_dim(HD);          // 2560 expanded rows (block layout, see layout.cuh)
 constexpr int NT = D2 / 128;             // 20 tiles of 128 rows = 8 first factors x 16
-constexpr int THREADS = 416;             // warps 0-3 / 4-7: one drain group per row tile, 8 TMA, 9-12 MMA (two per row tile)
 constexpr int TILE_BYTES = 128 * 128;
 constexpr int G_BYTES = 64 * 128;
-constexpr int NSS = 4;                   // state tiles in flight (TMA latency x L2 bandwidth needs ~100 KB per SM)
-constexpr uint32_t TMEM_COLS = 512;
-constexpr int ROWS = 256;                // token rows per CTA: two row tiles of 128
+// NRT row tiles of 128 tokens per CTA.  Warps: 4 NRT drain warps (one group of four per row tile), one
+// TMA warp, 2 NRT issuing warps (two threads per row tile).
+//   NRT = 2: one CTA per SM; each state tile fetched from L2 feeds two products.
+//   NRT = 1: two CTAs per SM, so that one CTA's prologue (operand loads, gating, Gram part) and epilogue
+//            (write-out) - a quarter of a CTA's life, all of it on the drain warps - run while the other
+//            CTA drains; the state tiles are fetched once per row tile, and the Gram operand borrows
+//            the last slot of the state ring until the Gram products have completed.
+template <int NRT>
+struct Cfg {
+  static constexpr int THREADS = 32 * (6 * NRT + 1);
+  static constexpr int ROWS = 128 * NRT;
+  static constexpr int NSS = NRT == 2 ? 4 : 2;  // state tiles in flight per CTA (64 KB per SM either way)
+  static constexpr bool G_IN_RING = NRT == 1;
+  static constexpr uint32_t TMEM_COLS = 256 * NRT;
+  static constexpr size_t SMEM =
+      1024 + (size_t)(2 * NRT + NSS) * TILE_BYTES + (G_IN_RING ? 0 : 2 * G_BYTES) + (size_t)NRT * 64 * 128 * 4;
+};
+#ifndef PR_EG_NRT
+#define PR_EG_NRT 1
+#endif
 // Tensor memory: two 128-column buffers per row tile, buffer b of row tile rt at (2 rt + b) * 128.
 // Before the first use of buffer 1 its columns hold the Gram part: the gated row as A operand
 // (32 columns at +0) and u = x~ Gs (64 columns at +64), read into the accumulators' initial value.
@@ -59,12 +75,15 @@ struct ExpandGradParams {
   int* status;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(eg::THREADS, 1)
+template <typename T, int NRT>
+__global__ void __launch_bounds__(eg::Cfg<NRT>::THREADS, NRT == 1 ? 2 : 1)
 expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_s,
                    const __grid_constant__ CUtensorMap tm_ghi, const __grid_constant__ CUtensorMap tm_glo) {
   using namespace eg;
+  constexpr int THREADS = Cfg<NRT>::THREADS, ROWS = Cfg<NRT>::ROWS, NSS = Cfg<NRT>::NSS;
+  constexpr uint32_t TMEM_COLS = Cfg<NRT>::TMEM_COLS;
+  constexpr int W_TMA = 4 * NRT;  // the TMA warp; issuing warps follow
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t w_full, g_full, xa_full[2], u_full[2], s_full[NSS], s_empty[NSS], d_full[2][2], d_empty[2][2];
   __shared__ uint32_t tmem_base_s;
@@ -94,11 +113,13 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
 
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (sbase - smem_u32(smem_raw));
-  uint8_t* smW = sm;                            // 2 x TILE_BYTES (one per row tile)
-  uint8_t* smX = smW + 2 * TILE_BYTES;          // 2 x TILE_BYTES
-  uint8_t* smS = smX + 2 * TILE_BYTES;          // NSS x TILE_BYTES (ring of state tiles)
-  uint8_t* smG = smS + NSS * TILE_BYTES;        // hi, lo
-  float* smR = reinterpret_cast<float*>(smG + 2 * G_BYTES);  // 2 x [64][128] fp32: dx~ terms indexed at run time
+  uint8_t* smW = sm;                            // NRT x TILE_BYTES (one per row tile)
+  uint8_t* smX = smW + NRT * TILE_BYTES;        // NRT x TILE_BYTES
+  uint8_t* smS = smX + NRT * TILE_BYTES;        // NSS x TILE_BYTES (ring of state tiles)
+  // Gram operand (hi, lo): its own 16 KB, or the ring's last slot until the Gram products are done
+  uint8_t* smG = Cfg<NRT>::G_IN_RING ? smS + (NSS - 1) * TILE_BYTES : smS + NSS * TILE_BYTES;
+  // NRT x [64][128] fp32: dx~ terms indexed at run time
+  float* smR = reinterpret_cast<float*>(smS + NSS * TILE_BYTES + (Cfg<NRT>::G_IN_RING ? 0 : 2 * G_BYTES));
 
   if (tid == 0) {
     abort_flag = 0;
@@ -114,7 +135,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
     }
     for (int s = 0; s < NSS; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 2);  // both issuing threads release a state tile
+      mbar_init(&s_empty[s], NRT);  // one issuing thread per row tile releases a state tile
     }
     fence_mbar_init();
   }
@@ -128,10 +149,10 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
   const uint32_t tmem = tmem_base_s;
   const int ch = (batch * p.n_chunks + chunk) * p.h + gh;
 
-  if (warp == 8) {
+  if (warp == W_TMA) {
     if (lane == 0) {
-      mbar_expect_tx(&w_full, 4 * TILE_BYTES);
-      for (int rt = 0; rt < 2; ++rt) {
+      mbar_expect_tx(&w_full, 2 * NRT * TILE_BYTES);
+      for (int rt = 0; rt < NRT; ++rt) {
         tma_load_4d(smW + rt * TILE_BYTES, &tm_w, &w_full, 0, head, chunk * p.c + row0 + rt * 128, batch);
         tma_load_4d(smX + rt * TILE_BYTES, &tm_x, &w_full, 0, head, chunk * p.c + row0 + rt * 128, batch);
       }
@@ -141,17 +162,19 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
       for (int nt = 0; nt < NT; ++nt) {
         const int s = nt % NSS, ph = (nt / NSS) & 1;
         if (!mbar_wait(&s_empty[s], ph ^ 1, &abort_flag)) break;
+        // the slot lent to the Gram operand is free once the Gram products have completed
+        if (Cfg<NRT>::G_IN_RING && nt == NSS - 1 && !mbar_wait(&u_full[0], 0, &abort_flag)) break;
         mbar_expect_tx(&s_full[s], TILE_BYTES);
         tma_load_2d(smS + s * TILE_BYTES, &tm_s, &s_full[s], 0, ch * D2 + nt * 128);
       }
     }
-  } else if (warp >= 9) {
+  } else if (warp > W_TMA) {
     // Two issuing threads per row tile, one per tensor-memory buffer (even / odd state tiles): a thread
     // needs ~108 clocks per tcgen05.mma it issues and more per commit, whatever the shape (measured), and
     // traced timelines showed one thread per row tile setting the kernel's pace at ~1300 clocks per tile
     // against ~900 for the drain.
     if (lane == 0) {
-      const int rt = (warp - 9) >> 1, par = (warp - 9) & 1;
+      const int rt = (warp - (W_TMA + 1)) >> 1, par = (warp - (W_TMA + 1)) & 1;
       bool ok = mbar_wait(&w_full, 0, &abort_flag);
       const uint32_t w_addr = smem_u32(smW) + rt * TILE_BYTES;
       const uint32_t idesc = umma_idesc(128, 128, Pack2<T>::is_bf16, false, false);
@@ -364,7 +387,7 @@ expand_grad_kernel(const ExpandGradParams p, const __grid_constant__ CUtensorMap
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && abort_flag) *p.status = ST_TIMEOUT;
-  if (warp == 0) tmem_dealloc(tmem, eg::TMEM_COLS);
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 }  // namespace pr
@@ -391,7 +414,8 @@ extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int
   p.hx = hx;
   p.n_chunks = n;
   p.c = c;
-  p.tiles_per_chunk = (c + ROWS - 1) / ROWS;
+  using C = Cfg<PR_EG_NRT>;
+  p.tiles_per_chunk = (c + C::ROWS - 1) / C::ROWS;
   p.chunk_lo = chunk_lo;
   p.chunk_hi = chunk_hi;
   p.query_side = query_side;
@@ -421,16 +445,21 @@ extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int
     if ((rc = make_tmap(&tm_ghi, g_hi, 2, 2, dg, st, box_g, true))) return rc;
     if ((rc = make_tmap(&tm_glo, g_lo, 2, 2, dg, st, box_g, true))) return rc;
   }
-  const size_t smem = 1024 + (4 + NSS) * TILE_BYTES + 2 * G_BYTES + 2 * 64 * 128 * 4;
+  const size_t smem = C::SMEM;
   dim3 grid(p.tiles_per_chunk * n, hx, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
-    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    expand_grad_kernel<__nv_bfloat16><<<grid, THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
+    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__nv_bfloat16, PR_EG_NRT>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__nv_bfloat16, PR_EG_NRT>,
+                                 cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    expand_grad_kernel<__nv_bfloat16, PR_EG_NRT><<<grid, C::THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
   } else {
-    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    expand_grad_kernel<__half><<<grid, THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
+    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__half, PR_EG_NRT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__half, PR_EG_NRT>,
+                                 cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    expand_grad_kernel<__half, PR_EG_NRT><<<grid, C::THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
   }
   PR_CUDA(cudaGetLastError());
   return PR_OK;
