@@ -281,7 +281,12 @@ int pr_retention_fwd(const pr_problem* problem, const void* Q, const void* K, co
                      float* final_state, float* final_gram, int device, void* stream);
 
 /* Backward.  dO [b,t,hq,d] -> dQ, dK, dV (shapes of Q, K, V) and dlog_G [b,t,h] fp32 (NULL when
- * ungated).  `saved` as the forward left it; had_carry = 1 when the forward was given carries. */
+ * ungated).  `saved` as the forward left it; had_carry = 1 when the forward was given carries.
+ * The query-side branch (expand_grad on the saved states, chunk_dq) runs on a second stream that
+ * the library owns (one per device, created at the first call - make that call outside any
+ * stream capture), forked from and joined back into `stream` with events, so everything is
+ * complete in `stream` order when the call's work is; PR_BWD_OVERLAP=0 in the environment keeps
+ * the whole pass on `stream`. */
 int pr_retention_bwd(const pr_problem* problem, const void* Q, const void* K, const void* V, const float* log_G,
                      const void* O, const void* dO, int had_carry, void* saved, void* scratch, void* dQ, void* dK,
                      void* dV, float* dlog_G, int device, void* stream);

@@ -8,6 +8,8 @@
 // Memory: the caller allocates everything.  `saved` is what the backward needs from the
 // forward (gate sums, row sums, scanned states and Gram matrices); `scratch` is dead when the
 // call returns its work to the stream and may be reused by the next call on the same stream.
+#include <mutex>
+
 #include "host.cuh"
 #include "layout.cuh"
 
@@ -89,6 +91,39 @@ Saved carve_saved(void* base, const Sizes& s) {
   v.zlo = c.take<void>(s.zh);
   v.zfull = c.take<float>(s.zfull);
   return v;
+}
+
+// The backward has two independent branches after dout_prep: the query side (expand_grad on the
+// saved states, then chunk_dq) needs nothing from the reverse scan, which heads the key side
+// (gate_prep, chunk_state, scan, expand_grad, chunk_dkv).  The query side is enqueued on a second
+// stream, forked from and joined back into the caller's stream with events, so that its CTAs fill
+// the partial last wave of each key-side launch (and vice versa).  One stream and event pair per
+// device, created on first use (outside any stream capture: a capture of the caller's stream
+// then records the fork and the join like any cross-stream dependency); `mu` is held while a
+// backward is being enqueued, so concurrent callers take turns at using the pair.
+struct SideStream {
+  std::mutex mu;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+constexpr int kMaxDevices = 64;
+SideStream g_side[kMaxDevices];
+
+bool overlap_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PR_BWD_OVERLAP");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// with s->mu held
+int side_stream_ready(SideStream* s) {
+  if (s->stream != nullptr) return PR_OK;
+  PR_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+  PR_CUDA(cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming));
+  PR_CUDA(cudaEventCreateWithFlags(&s->join, cudaEventDisableTiming));
+  return PR_OK;
 }
 
 }  // namespace
@@ -186,29 +221,53 @@ extern "C" int pr_retention_bwd(const pr_problem* prob, const void* Q, const voi
   const int group = p.hq / p.h;
   // dy = dO / l, dl = -<O, dO> / l
   if ((rc = pr_dout_prep(p.dtype, (long long)p.b * p.t * p.hq, p.d, O, dO, sv.l, dy, dl, device, stream))) return rc;
-  // gradient of the state read-out: dZ_m, dZg_m from the gated queries
-  if ((rc = pr_gate_prep(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, log_G, Q, gated ? sv.a : nullptr, nullptr, QT, dl,
-                         QTs, 1, p.scale, 0, device, stream)))  // the forward's cumulative gates are read, not rescanned
-    return rc;
-  if ((rc = pr_chunk_state(p.dtype, p.b, p.t, p.h, group, p.d, p.c, QT, QTs, dy, dZ, dZg, 0, device, stream))) return rc;
-  // reverse scans (in place: dZ becomes w (.) dS_m)
-  if ((rc = pr_state_scan_bwd(p.dtype, p.b, s.n, p.h, p.d, E, dZ, sv.Z, sv.A, nullptr, nullptr, partS, dZg, sv.zfull,
-                              ghi, glo, nullptr, nullptr, partG, device, stream)))
-    return rc;
-  // gradients through the expansions
-  if ((rc = pr_expand_grad(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, dy, Q, sv.Z, sv.zhi, sv.zlo, a, A, dl, 1, p.scale,
-                           2.f, had_carry ? 0 : 1, s.n - 1, dqs, gq, device, stream)))
-    return rc;
-  if ((rc = pr_expand_grad(p.dtype, p.b, p.t, p.h, p.h, p.d, p.c, V, K, dZ, ghi, glo, a, A, nullptr, 0, 1.f, 1.f, 0,
-                           s.n - 2, dks, wk, device, stream)))
-    return rc;
-  // attention backward merged with the state-path terms
-  if ((rc = pr_chunk_dq(p.dtype, p.b, p.t, p.hq, p.h, p.d, p.c, Q, dO, K, V, a, dl, sv.l, dqs, p.scale, 2, dQ, daq,
-                        device, stream)))
-    return rc;
-  if ((rc = pr_chunk_dkv(p.dtype, p.b, p.t, p.hq, p.h, p.d, p.c, Q, dO, K, V, dZ, a, A, dl, sv.l, dks, s.n - 2, p.scale,
-                         2, dK, dV, dak, device, stream)))
-    return rc;
+
+  // ---- query side, on the second stream when there is one: gradient through the read-out's expansion
+  // (saved states), then the attention backward merged with it
+  PR_REQUIRE(device >= 0 && device < kMaxDevices, PR_ERR_BAD_ARG, "device ordinal %d out of range", device);
+  SideStream* side = overlap_enabled() ? &g_side[device] : nullptr;
+  std::unique_lock<std::mutex> lock;
+  void* qstream = stream;
+  if (side != nullptr) {
+    lock = std::unique_lock<std::mutex>(side->mu);
+    PR_CUDA(cudaSetDevice(device));
+    if ((rc = side_stream_ready(side))) return rc;
+    PR_CUDA(cudaEventRecord(side->fork, static_cast<cudaStream_t>(stream)));
+    PR_CUDA(cudaStreamWaitEvent(side->stream, side->fork, 0));
+    qstream = side->stream;
+  }
+  rc = pr_expand_grad(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, dy, Q, sv.Z, sv.zhi, sv.zlo, a, A, dl, 1, p.scale, 2.f,
+                      had_carry ? 0 : 1, s.n - 1, dqs, gq, device, qstream);
+  if (!rc)
+    rc = pr_chunk_dq(p.dtype, p.b, p.t, p.hq, p.h, p.d, p.c, Q, dO, K, V, a, dl, sv.l, dqs, p.scale, 2, dQ, daq, device,
+                     qstream);
+  if (side != nullptr) {
+    // joined even after an error, so that a capture of the caller's stream is left in a closable state
+    cudaEventRecord(side->join, side->stream);
+  }
+
+  // ---- key side: gradient of the state read-out (dZ_m, dZg_m from the gated queries; the forward's
+  // cumulative gates are read, not rescanned), reverse scans (in place: dZ becomes w (.) dS_m), gradient
+  // through the chunk states' expansion, attention backward merged with it
+  if (!rc)
+    rc = pr_gate_prep(p.dtype, p.b, p.t, p.h, p.hq, p.d, p.c, log_G, Q, gated ? sv.a : nullptr, nullptr, QT, dl, QTs, 1,
+                      p.scale, 0, device, stream);
+  if (!rc) rc = pr_chunk_state(p.dtype, p.b, p.t, p.h, group, p.d, p.c, QT, QTs, dy, dZ, dZg, 0, device, stream);
+  if (!rc)
+    rc = pr_state_scan_bwd(p.dtype, p.b, s.n, p.h, p.d, E, dZ, sv.Z, sv.A, nullptr, nullptr, partS, dZg, sv.zfull, ghi,
+                           glo, nullptr, nullptr, partG, device, stream);
+  if (!rc)
+    rc = pr_expand_grad(p.dtype, p.b, p.t, p.h, p.h, p.d, p.c, V, K, dZ, ghi, glo, a, A, nullptr, 0, 1.f, 1.f, 0,
+                        s.n - 2, dks, wk, device, stream);
+  if (!rc)
+    rc = pr_chunk_dkv(p.dtype, p.b, p.t, p.hq, p.h, p.d, p.c, Q, dO, K, V, dZ, a, A, dl, sv.l, dks, s.n - 2, p.scale, 2,
+                      dK, dV, dak, device, stream);
+  if (side != nullptr) {
+    cudaError_t e = cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), side->join, 0);
+    if (!rc && e != cudaSuccess) rc = fail(PR_ERR_CUDA, "joining the second stream failed: %s", cudaGetErrorString(e));
+    lock.unlock();
+  }
+  if (rc) return rc;
   if (gated)
     return pr_gate_grad(p.b, p.t, p.h, p.hq, p.c, daq, gq, dak, wk, partS, s.blocksS, partG, s.blocksG, dlog_G, device,
                         stream);
