@@ -200,6 +200,38 @@ def test_native_sequencer_equals_python_sequencer(cuda_device, gated, r):
         assert torch.equal(a[key], b[key]), key
 
 
+def test_step_captured_in_a_cuda_graph_replays_bit_identically(cuda_device):
+    """A forward+backward captured from the caller's stream replays to the same bits as eager launches.  The
+    backward forks its query-side branch onto the library's second stream and joins it back with events; the
+    capture has to record that fork and join as dependencies of the one graph (a step left outside it, or
+    unjoined, would fail the capture or race with the replay)."""
+    import retention_integration_b200 as prb
+
+    Q, K, V, lg, dO = (x.to(cuda_device) for x in _case(1, 1024, 2, 2, 64, True, 1.0, seed=21))
+
+    def step():
+        q, k, v, g = (x.detach().clone().requires_grad_(True) for x in (Q, K, V, lg))
+        O = prb.power_retention(q, k, v, g, deg=2, chunk_size=256)
+        O.backward(dO)
+        return O, q.grad, k.grad, v.grad, g.grad
+
+    eager = [x.clone() for x in step()]  # also the library's first call: its second stream exists from here on
+    side = torch.cuda.Stream(cuda_device)
+    side.wait_stream(torch.cuda.current_stream(cuda_device))
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream(cuda_device).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = step()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    for got, want in zip(captured, eager):
+        assert torch.equal(got, want)
+
+
 def test_gqa_equals_repeated_heads(cuda_device):
     """GQA == MHA with the kv heads repeated (perf/tests/gqa_tests.py:44-66)."""
     Q, K, V, lg, dO = _case(1, 512, 2, 4, 64, True, 2.0, seed=8)
