@@ -540,7 +540,7 @@ def main():
     # exiting) shows as a region several times longer than the sum of its own kernels, which the breakdown
     # pass has just measured.  Such a region is timed once more and both figures are reported.
     retimed_from = None
-    ksum = torch.tensor([sum(v["ms_per_step"] for v in kernels.values())], device=dev, dtype=torch.float64)
+    ksum = torch.tensor([sum(tot for _, tot in kernels.values()) / breakdown_steps], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ksum, op=dist.ReduceOp.MAX)  # every rank takes the same decision
     kernel_sum_ms = float(ksum.item())
