@@ -114,7 +114,7 @@ def test_decode_reads_cache_slices_in_place(cuda_device, ratio):
         assert torch.isfinite(y_view).all()
 
 
-def _decode_vs_oracle(dev, b, h, r, tk, seed, check_rows):
+def _decode_vs_oracle(dev, b, h, r, tk, seed, check_rows, dtype=torch.bfloat16, gate_shift=0.0):
     """One decode step (tq = 1, state given) against oracle.power_retention_inference, compared on the
     (batch, kv head) pairs in `check_rows` (the oracle expands every query, so a few pairs keep it quick)."""
     import retention_integration_b200 as prb
@@ -123,13 +123,14 @@ def _decode_vs_oracle(dev, b, h, r, tk, seed, check_rows):
     g = torch.Generator().manual_seed(seed)
     d, D = 64, 2080
     hq = h * r
-    Q = torch.randn(b, 1, hq, d, generator=g).bfloat16()
+    Q = torch.randn(b, 1, hq, d, generator=g).to(dtype)
     state, sok = make_state(b, h, d, 24, g)
+    state = state.to(dtype)
     K = V = lg = None
     if tk > 0:
-        K = torch.randn(b, tk, h, d, generator=g).bfloat16()
-        V = torch.randn(b, tk, h, d, generator=g).bfloat16()
-        lg = F.logsigmoid(torch.randn(b, tk, h, generator=g))
+        K = torch.randn(b, tk, h, d, generator=g).to(dtype)
+        V = torch.randn(b, tk, h, d, generator=g).to(dtype)
+        lg = F.logsigmoid(torch.randn(b, tk, h, generator=g) + gate_shift)
     to = lambda x: None if x is None else x.to(dev)
     Y, s2, k2 = prb.power_retention_inference(to(Q), to(K), to(V), to(lg), to(state), to(sok),
                                               switch_over_seq_len=1024)
@@ -159,3 +160,13 @@ def test_decode_at_benchmark_shape_unsplit_state_read(cuda_device, tk):
 def test_decode_state_read_split_in_two_and_five(cuda_device, b, h, r, tk):
     """192-200 (batch, head) pairs: the expanded dimension is read in two halves; 6 pairs: in five parts."""
     _decode_vs_oracle(cuda_device, b, h, r, tk, seed=b * h + tk, check_rows=[(0, 0), (b - 1, h - 1), (b // 2, h // 2)])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,h,r,tk", [(16, 32, 1, 1500), (4, 8, 2, 700), (2, 2, 8, 1300)])
+def test_decode_long_cache_both_dtypes(cuda_device, dtype, b, h, r, tk):
+    """Caches longer than one gate block of the attention warps (640 tokens: the suffix sums carry over from block
+    to block), query-head groups of two and of eight (two CTAs per kv head), fp16 as well as bf16 states.  Slow
+    gates keep the oldest cached tokens' weights alive, so a lost carry would show."""
+    _decode_vs_oracle(cuda_device, b, h, r, tk, seed=3 * b + tk, check_rows=[(0, 0), (b - 1, h - 1)], dtype=dtype,
+                      gate_shift=5.0)
