@@ -2,7 +2,7 @@
 """Benchmark of the power-retention hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload train|decode|seqpar]
+                    [--workload train|decode|seqpar|caller]
 
 Workload `train` (default): forward + backward of one power-retention layer at
 b=1, t=65536, h=8, d=64, deg=2, bf16, chunk 1024, gated (synthetic N(0,1) inputs,
@@ -334,6 +334,57 @@ def decode_measure(dev, steps=512, with_extras=True, use_graph=True):
     return out
 
 
+# --------------------------------------------------------------------------- caller glue
+def caller_prep_measure(dev, t=65536, h=8, d=64):
+    """The fused split + gate + rotary + layout write between the projection and the operator
+    (retention_integration_b200/caller.py) at the benchmark's shape, forward and gradient, against the
+    same glue written as the reference's callers write it (torch elementwise ops, deploy/nanoGPT/model.py:66-84)
+    on the same GPU.  HBM bound: bytes = projection output read + Q, K, V, log_g written (and the reverse)."""
+    import retention_integration_b200 as prb
+    from retention_integration_b200 import ops
+
+    b, W = 1, 3 * h * d + h
+    gen = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(b, t, W, generator=gen, device=dev).bfloat16()
+    sin, cos = prb.rotary_tables(t, d, dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    Q, K, V, lg = ops.caller_prep_fwd(x, cos, sin, h, h, d, True, prb.caller.GATE_BIAS, False)
+    dlg = torch.randn_like(lg)
+    ms_f = timed(lambda: ops.caller_prep_fwd(x, cos, sin, h, h, d, True, prb.caller.GATE_BIAS, False))
+    ms_b = timed(lambda: ops.caller_prep_bwd(x, cos, sin, h, h, d, True, prb.caller.GATE_BIAS, False, Q, K, V, dlg))
+
+    def unfused():
+        q, k, v = x[..., : 3 * h * d].split([h * d, h * d, h * d], dim=2)
+        q, k, v = q.view(b, t, h, d), k.view(b, t, h, d), v.view(b, t, h, d)
+        g = F.logsigmoid(prb.caller.GATE_BIAS + x[..., 3 * h * d:].float()).contiguous()
+        s2, c2 = sin.repeat_interleave(2, dim=1)[None, :, None], cos.repeat_interleave(2, dim=1)[None, :, None]
+        rot = lambda z: torch.stack((-z[..., 1::2], z[..., ::2]), -1).reshape(z.shape)
+        q = ((q * c2) + (rot(q) * s2)).to(x.dtype)
+        k = ((k * c2) + (rot(k) * s2)).to(x.dtype)
+        return q.contiguous(), k.contiguous(), v.contiguous(), g
+
+    ms_u = timed(unfused, reps=5)
+    peak = load_peaks().get("hbm_gbs") or 6650.0
+    bytes_f = b * t * (W * 2 + 3 * h * d * 2 + h * 4)
+    bytes_b = b * t * (3 * h * d * 2 + h * 4 + h * 2 + W * 2)  # gradients in, the gate column re-read, dqkvg out
+    return {"workload": f"split + logsigmoid gate + rotary + layout write, b{b} t{t} h{h} d{d} bf16 gated",
+            "fwd_ms": ms_f, "fwd_gbs": bytes_f / (ms_f * 1e-3) / 1e9, "fwd_frac_of_hbm_peak": bytes_f / (ms_f * 1e-3) / 1e9 / peak,
+            "bwd_ms": ms_b, "bwd_gbs": bytes_b / (ms_b * 1e-3) / 1e9, "bwd_frac_of_hbm_peak": bytes_b / (ms_b * 1e-3) / 1e9 / peak,
+            "unfused_torch_fwd_ms": ms_u, "algorithmic_bytes_fwd": bytes_f}
+
+
 # --------------------------------------------------------------------------- sequence parallel
 def seqpar_measure(dev, rank, world, t_total, steps=3, warmup=1):
     """b=1, t=t_total, h=8, d=64 bf16, chunk 1024, slow-decay gates, the sequence split evenly over the ranks
@@ -395,7 +446,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the decode / seq_parallel objects and e2e")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of replaying a graph")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "seqpar"])
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "seqpar", "caller"])
     ap.add_argument("--decode-steps", type=int, default=512, help="single-token steps of the decode workload")
     ap.add_argument("--seq-t", type=int, default=1048576, help="total tokens of the sequence-parallel workload")
     args = ap.parse_args()
@@ -424,6 +475,16 @@ def main():
         if rank == 0:
             obj = decode_measure(dev, args.decode_steps, use_graph=not args.no_graph)
             obj.update({"n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                        "config": {"workload": obj["workload"]}})
+            print(json.dumps(obj), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "caller":
+        if rank == 0:
+            obj = caller_prep_measure(dev)
+            obj.update({"metric": "caller_prep_gbs", "value": obj["fwd_gbs"], "unit": "GB/s", "n_gpus": 1,
+                        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
                         "config": {"workload": obj["workload"]}})
             print(json.dumps(obj), flush=True)
         if world > 1:
@@ -589,6 +650,7 @@ def main():
         torch.cuda.empty_cache()
         if world == 1:
             extra["decode"] = decode_measure(dev, args.decode_steps, use_graph=not args.no_graph)
+            extra["caller_prep"] = caller_prep_measure(dev)
         else:
             extra["seq_parallel"] = seqpar_measure(dev, rank, world, args.seq_t)
 

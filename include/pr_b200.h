@@ -291,6 +291,25 @@ int pr_retention_bwd(const pr_problem* problem, const void* Q, const void* K, co
                      const void* O, const void* dO, int had_carry, void* saved, void* scratch, void* dQ, void* dK,
                      void* dV, float* dlog_G, int device, void* stream);
 
+/* Between the caller's projection GEMM and the operator (deploy/nanoGPT/model.py:66-84,
+ * deploy/models/powercoder/modeling_powercoder.py:152-159): one pass over the projection output
+ * qkvg [b,t,row_stride] 16-bit, a token's row holding hq*d query, h*d key, h*d value features and,
+ * when gated, h gate pre-activations.  Writes Q [b,t,hq,d], K, V [b,t,h,d] (rotary applied to Q
+ * and K) and log_g [b,t,h] = logsigmoid(gate_bias + gate) fp32 - the tensors pr_retention_fwd takes.
+ * cos_table / sin_table [t, d/2] fp32 (batch entries table_bstride floats apart, 0 = one table);
+ * half_split = 0: rotary pairs (2i, 2i+1) as deploy/nanoGPT/model.py:153-164, 1: pairs (i, i+d/2)
+ * as modeling_powercoder.py:43-74.  Products and sum are rounded separately in fp32, then once to
+ * 16 bits, which reproduces model.py:159-164 bit for bit.  Any d that is a multiple of 8 (16 when
+ * half_split).  pr_caller_prep_bwd is its gradient: dQ, dK, dV, dlog_g -> dqkvg (same shape as
+ * qkvg, which it reads for the gate's derivative; padding columns of a wider row are left as they are). */
+int pr_caller_prep_fwd(int dtype, int b, int t, int h, int hq, int d, const void* qkvg, long long row_stride,
+                       const float* cos_table, const float* sin_table, long long table_bstride, int half_split,
+                       int gated, float gate_bias, void* Q, void* K, void* V, float* log_g, int device, void* stream);
+int pr_caller_prep_bwd(int dtype, int b, int t, int h, int hq, int d, const void* qkvg, long long row_stride,
+                       const float* cos_table, const float* sin_table, long long table_bstride, int half_split,
+                       int gated, float gate_bias, const void* dQ, const void* dK, const void* dV, const float* dlog_g,
+                       void* dqkvg, int device, void* stream);
+
 /* A state in the exact layout (state [b,h,d(d+1)/2,d], sum_of_keys [b,h,d(d+1)/2]) converted to the
  * chunk-state layout of the training kernels: out16 [b,h,D2,d] 16-bit, out32 the same in fp32 (a carry_in
  * for pr_discumsum_fwd), gram [b,h,d,d] fp32 (carry_in for pr_gram_scan_fwd), gram_hi / gram_lo 16-bit

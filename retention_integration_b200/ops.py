@@ -499,3 +499,33 @@ def decode_recurrent(q, k, v, log_g, state, sum_of_keys, new_state, new_sum_of_k
           ptr(sum_of_keys), ptr(new_state), ptr(new_sum_of_keys), c_float(scale), ptr(part_y), ptr(part_l), ptr(O),
           c_int(_dev(q)), stream_ptr(q.device))
     return O
+
+
+def caller_prep_fwd(qkvg, cos, sin, h: int, hq: int, d: int, gated: bool, gate_bias: float, half_split: bool):
+    """qkvg [b,t,W] 16-bit (W a multiple of 8, W >= (hq+2h)d + h when gated); cos, sin [t,d/2] or [b,t,d/2] fp32
+    -> Q [b,t,hq,d], K, V [b,t,h,d], log_g [b,t,h] fp32 or None (pr_caller_prep_fwd)."""
+    b, t, W = qkvg.shape
+    dev = qkvg.device
+    Q = torch.empty(b, t, hq, d, device=dev, dtype=qkvg.dtype)
+    K = torch.empty(b, t, h, d, device=dev, dtype=qkvg.dtype)
+    V = torch.empty(b, t, h, d, device=dev, dtype=qkvg.dtype)
+    log_g = torch.empty(b, t, h, device=dev, dtype=torch.float32) if gated else None
+    bstride = 0 if cos.dim() == 2 else t * (d // 2)
+    _call("pr_caller_prep_fwd", c_int(dtype_code(qkvg.dtype)), c_int(b), c_int(t), c_int(h), c_int(hq), c_int(d),
+          ptr(qkvg), c_longlong(W), ptr(cos), ptr(sin), c_longlong(bstride), c_int(int(half_split)), c_int(int(gated)),
+          c_float(gate_bias), ptr(Q), ptr(K), ptr(V), ptr(log_g), c_int(_dev(qkvg)), stream_ptr(dev))
+    return Q, K, V, log_g
+
+
+def caller_prep_bwd(qkvg, cos, sin, h: int, hq: int, d: int, gated: bool, gate_bias: float, half_split: bool, dQ, dK,
+                    dV, dlog_g):
+    """Gradient of caller_prep_fwd with respect to qkvg (same shape; columns past the used ones are zero)."""
+    b, t, W = qkvg.shape
+    used = (hq + 2 * h) * d + (h if gated else 0)
+    out = torch.empty_like(qkvg) if W == used else torch.zeros_like(qkvg)
+    bstride = 0 if cos.dim() == 2 else t * (d // 2)
+    _call("pr_caller_prep_bwd", c_int(dtype_code(qkvg.dtype)), c_int(b), c_int(t), c_int(h), c_int(hq), c_int(d),
+          ptr(qkvg), c_longlong(W), ptr(cos), ptr(sin), c_longlong(bstride), c_int(int(half_split)), c_int(int(gated)),
+          c_float(gate_bias), ptr(dQ), ptr(dK), ptr(dV), ptr(dlog_g), ptr(out), c_int(_dev(qkvg)),
+          stream_ptr(qkvg.device))
+    return out

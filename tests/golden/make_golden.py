@@ -137,6 +137,39 @@ def inference_cases(ref):
              new_sum_of_keys=npy(nk) if switched else None, meta=np.array([b, tq, tk, h, r, d, int(with_state), sw]))
 
 
+def caller_case(root):
+    """The glue of deploy/nanoGPT/model.py:66-84 on a random projection output, with the reference's own
+    rotary helpers (the module is loaded with a stub for its `retention.triton` import)."""
+    import importlib.util
+
+    stub = types.ModuleType("retention.triton")
+    stub.power_retention = None
+    sys.modules["retention.triton"] = stub
+    spec = importlib.util.spec_from_file_location("ref_nanogpt_model", os.path.join(root, "deploy", "nanoGPT", "model.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    g = torch.Generator().manual_seed(21)
+    B, T, h, r, d = 2, 48, 2, 2, 64
+    hq = h * r
+    qkv_size = (hq + 2 * h) * d
+    qkvg = rb(torch.randn(B, T, qkv_size + h, generator=g)).to(torch.bfloat16).requires_grad_(True)
+    # model.py:68-84, line by line
+    qkv = qkvg[..., :qkv_size]
+    q, k, v = qkv.split([hq * d, h * d, h * d], dim=2)
+    q, k, v = q.view(B, T, hq, d), k.view(B, T, h, d), v.view(B, T, h, d)
+    log_g = torch.nn.functional.logsigmoid(6.906768 + qkvg[..., qkv_size:].to(dtype=torch.float32)).contiguous()
+    pos = torch.arange(T, dtype=torch.float32).unsqueeze(0).unsqueeze(2)
+    sincos = m.get_sinusoidal_embeddings(pos, d, "cpu")
+    q = m.apply_rotary_position_embeddings(q, sincos)
+    k = m.apply_rotary_position_embeddings(k, sincos)
+    dq, dk, dv = (rb(torch.randn(*x.shape, generator=g)).to(torch.bfloat16) for x in (q, k, v))
+    dlg = torch.randn(B, T, h, generator=g)
+    torch.autograd.backward([q, k, v, log_g], [dq, dk, dv, dlg])
+    save("caller_prep_nanogpt", qkvg__bf16=bits(qkvg), Q__bf16=bits(q), K__bf16=bits(k), V__bf16=bits(v), log_g=npy(log_g),
+         sin=npy(sincos[0][0, :, 0]), cos=npy(sincos[1][0, :, 0]), dQ__bf16=bits(dq), dK__bf16=bits(dk), dV__bf16=bits(dv),
+         dlog_g=npy(dlg), dqkvg=npy(qkvg.grad), meta=np.array([B, T, h, r, d]))
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference>")
@@ -151,6 +184,7 @@ def main():
     training_case(ref, "train_gated_bf16", 6, 1, 256, 2, 64, 1, torch.bfloat16, True, 64)
     op_cases(ref)
     inference_cases(ref)
+    caller_case(sys.argv[1])
 
 
 if __name__ == "__main__":
