@@ -32,15 +32,19 @@ constexpr int ROWS_PER_ITER = THREADS / 8;  // 32 state rows per iteration
 constexpr int RG_MAX = 4;                   // query heads handled per CTA (template: 1 or 4)
 }  // namespace dec
 
-// exact-layout row -> (a, b), a <= b
+// exact-layout row -> (a, b), a <= b.  Row a starts at off(a) = a d - a (a - 1) / 2; the closed form
+// a = floor(((2d + 1) - sqrt((2d + 1)^2 - 8 D)) / 2) is evaluated in fp32 and corrected by at most a
+// step either way (a walk over the rows from 0 costs up to d iterations per call, which made the
+// layout-converting kernels issue-bound).
 __device__ __forceinline__ void exact_decode(int D, int* a, int* b) {
-  int aa = 0, off = 0;
-  while (off + (dec::HD - aa) <= D) {
-    off += dec::HD - aa;
-    ++aa;
-  }
+  constexpr int d = dec::HD;
+  auto off = [](int r) { return r * d - r * (r - 1) / 2; };
+  int aa = (int)(((float)(2 * d + 1) - sqrtf((float)((2 * d + 1) * (2 * d + 1)) - 8.f * (float)D)) * 0.5f);
+  aa = max(0, min(aa, d - 1));
+  while (aa + 1 <= d - 1 && off(aa + 1) <= D) ++aa;
+  while (aa > 0 && off(aa) > D) --aa;
   *a = aa;
-  *b = aa + (D - off);
+  *b = aa + (D - off(aa));
 }
 
 template <typename T, int RG>
