@@ -24,6 +24,13 @@ constexpr int kScanThreads = 256;
 #define PR_SCAN_UNROLL 4
 #endif
 constexpr int kScanUnroll = PR_SCAN_UNROLL;
+
+// fewer CTAs than two per SM: the launch cannot fill the GPU with resident CTAs
+inline bool few_ctas(long long ctas, int device) {
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  return ctas < 2ll * sms;
+}
 #ifndef PR_SCAN_MINB
 #define PR_SCAN_MINB 3
 #endif
@@ -163,8 +170,8 @@ scan_gram_bwd_kernel(const float* __restrict__ dZg, const float* __restrict__ Zg
 }
 
 // X, Y: [b, n(_out), h, E]; A: [b, n, h]; carries: [b, h, E] fp32
-template <typename T>
-__global__ void __launch_bounds__(kScanThreads, PR_SCAN_MINB)
+template <typename T, int UN>
+__global__ void __launch_bounds__(kScanThreads, UN <= kScanUnroll ? PR_SCAN_MINB : 2)
 scan_fwd_kernel(const T* X, T* Y, const float* __restrict__ A,  // X and Y may be the same buffer: no __restrict__
                 const float* __restrict__ carry_in, float* __restrict__ carry_out, int n, int n_out, int h,
                 size_t E, int state_blocks, GramScanArgs gram) {
@@ -192,18 +199,18 @@ scan_fwd_kernel(const T* X, T* Y, const float* __restrict__ A,  // X and Y may b
   const T* xin = X + ((size_t)batch * n * h + head) * E + e0;
   T* yout = Y ? Y + ((size_t)batch * n_out * h + head) * E + e0 : nullptr;
   const float* Ap = A + (size_t)batch * n * h + head;
-  for (int m0 = 0; m0 < n; m0 += kScanUnroll) {
-    uint4 xv[kScanUnroll];
-    float g[kScanUnroll];
+  for (int m0 = 0; m0 < n; m0 += UN) {
+    uint4 xv[UN];
+    float g[UN];
 #pragma unroll
-    for (int u = 0; u < kScanUnroll; ++u) {
+    for (int u = 0; u < UN; ++u) {
       if (m0 + u < n) {
         xv[u] = *reinterpret_cast<const uint4*>(xin + (size_t)(m0 + u) * in_stride);
         g[u] = __expf(Ap[(size_t)(m0 + u) * h]);
       }
     }
 #pragma unroll
-    for (int u = 0; u < kScanUnroll; ++u) {
+    for (int u = 0; u < UN; ++u) {
       if (m0 + u < n) {
         if (yout) *reinterpret_cast<uint4*>(yout + (size_t)(m0 + u) * in_stride) = pack8<T>(run);
         float x[8];
@@ -224,8 +231,8 @@ scan_fwd_kernel(const T* X, T* Y, const float* __restrict__ A,  // X and Y may b
 // dY, dX: [b, n, h, E] (may alias); Y: [b, n, h, E] states entering each chunk;
 // dA_part: [b, h, 8 * gridDim.x, n] per-warp partial sums of exp(A[m]) * <Y[m], G[m+1]>.
 // row_weights: apply the key-side weight (1 or 2) of expanded row (e / row_len) to dX.
-template <typename T>
-__global__ void __launch_bounds__(kScanThreads, PR_SCAN_MINB)
+template <typename T, int UN>
+__global__ void __launch_bounds__(kScanThreads, UN <= kScanUnroll ? PR_SCAN_MINB : 2)
 scan_bwd_kernel(const T* dY, const T* __restrict__ Y, T* dX, const float* __restrict__ A,  // dY may alias dX
                 const float* __restrict__ carry_in, float* __restrict__ carry_out, float* __restrict__ dA_part, int n,
                 int h, size_t E, int row_len, int row_weights, int state_blocks, GramScanArgs gram) {
@@ -262,11 +269,11 @@ scan_bwd_kernel(const T* dY, const T* __restrict__ Y, T* dX, const float* __rest
   float* part = reduce_only ? nullptr
                             : dA_part + (((size_t)batch * h + head) * state_blocks * (kScanThreads / 32) +
                                          blockIdx.x * (kScanThreads / 32) + warp) * n;
-  for (int m0 = n - 1; m0 >= 0; m0 -= kScanUnroll) {
-    uint4 gv[kScanUnroll], yv[kScanUnroll];
-    float g[kScanUnroll];
+  for (int m0 = n - 1; m0 >= 0; m0 -= UN) {
+    uint4 gv[UN], yv[UN];
+    float g[UN];
 #pragma unroll
-    for (int u = 0; u < kScanUnroll; ++u) {
+    for (int u = 0; u < UN; ++u) {
       const int m = m0 - u;
       if (m >= 0 && active) {
         gv[u] = *reinterpret_cast<const uint4*>(dY + base + (size_t)m * stride);
@@ -275,7 +282,7 @@ scan_bwd_kernel(const T* dY, const T* __restrict__ Y, T* dX, const float* __rest
       if (m >= 0) g[u] = __expf(Ap[(size_t)m * h]);
     }
 #pragma unroll
-    for (int u = 0; u < kScanUnroll; ++u) {
+    for (int u = 0; u < UN; ++u) {
       const int m = m0 - u;
       if (m < 0) continue;
       if (reduce_only) {
@@ -334,16 +341,21 @@ static int launch_scan_fwd(int dtype, int b, int n, int n_out, int h, long long 
   const int gram_blocks = gram.in ? (gram.d * gram.d + kScanThreads - 1) / kScanThreads : 0;
   dim3 grid((unsigned)(state_blocks + gram_blocks), h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PR_BF16)
-    scan_fwd_kernel<__nv_bfloat16><<<grid, kScanThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(X),
-                                                                static_cast<__nv_bfloat16*>(Y), A, carry_in, carry_out,
-                                                                n, n_out, h, (size_t)E, state_blocks, gram);
-  else if (dtype == PR_FP16)
-    scan_fwd_kernel<__half><<<grid, kScanThreads, 0, s>>>(static_cast<const __half*>(X), static_cast<__half*>(Y), A,
-                                                         carry_in, carry_out, n, n_out, h, (size_t)E, state_blocks,
-                                                         gram);
-  else
+  // Few CTAs (one or two heads per GPU: 80-160 CTAs of serial 64-chunk chains) cannot hide the memory latency
+  // with four chunks of loads in flight per thread; they get eight (two CTAs per SM).
+  const bool deep = few_ctas((long long)state_blocks * h * b, device);
+#define PR_LAUNCH_SCAN_F(TT, UNV)                                                                              \
+  scan_fwd_kernel<TT, UNV><<<grid, kScanThreads, 0, s>>>(static_cast<const TT*>(X), static_cast<TT*>(Y), A,     \
+                                                         carry_in, carry_out, n, n_out, h, (size_t)E,          \
+                                                         state_blocks, gram)
+  if (dtype == PR_BF16) {
+    if (deep) PR_LAUNCH_SCAN_F(__nv_bfloat16, 8); else PR_LAUNCH_SCAN_F(__nv_bfloat16, kScanUnroll);
+  } else if (dtype == PR_FP16) {
+    if (deep) PR_LAUNCH_SCAN_F(__half, 8); else PR_LAUNCH_SCAN_F(__half, kScanUnroll);
+  } else {
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  }
+#undef PR_LAUNCH_SCAN_F
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }
@@ -393,17 +405,20 @@ static int launch_scan_bwd(int dtype, int b, int n, int h, long long E, const vo
   const int gram_blocks = gram.in ? (gram.d * gram.d + 255) / 256 : 0;
   dim3 grid((unsigned)(state_blocks + gram_blocks), h, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PR_BF16)
-    scan_bwd_kernel<__nv_bfloat16><<<grid, kScanThreads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(dY), static_cast<const __nv_bfloat16*>(Y), static_cast<__nv_bfloat16*>(dX),
-        A, carry_in, carry_out, dA_part, n, h, (size_t)E, row_len, row_weights, state_blocks, gram);
-  else if (dtype == PR_FP16)
-    scan_bwd_kernel<__half><<<grid, kScanThreads, 0, s>>>(static_cast<const __half*>(dY),
-                                                         static_cast<const __half*>(Y), static_cast<__half*>(dX), A,
-                                                         carry_in, carry_out, dA_part, n, h, (size_t)E, row_len,
-                                                         row_weights, state_blocks, gram);
-  else
+  const bool deep = few_ctas((long long)state_blocks * h * b, device);  // as in the forward scan
+#define PR_LAUNCH_SCAN_B(TT, UNV)                                                                              \
+  scan_bwd_kernel<TT, UNV><<<grid, kScanThreads, 0, s>>>(static_cast<const TT*>(dY), static_cast<const TT*>(Y), \
+                                                         static_cast<TT*>(dX), A, carry_in, carry_out, dA_part, \
+                                                         n, h, (size_t)E, row_len, row_weights, state_blocks,  \
+                                                         gram)
+  if (dtype == PR_BF16) {
+    if (deep) PR_LAUNCH_SCAN_B(__nv_bfloat16, 8); else PR_LAUNCH_SCAN_B(__nv_bfloat16, kScanUnroll);
+  } else if (dtype == PR_FP16) {
+    if (deep) PR_LAUNCH_SCAN_B(__half, 8); else PR_LAUNCH_SCAN_B(__half, kScanUnroll);
+  } else {
     return fail(PR_ERR_BAD_ARG, "dtype %d", dtype);
+  }
+#undef PR_LAUNCH_SCAN_B
   PR_CUDA(cudaGetLastError());
   return PR_OK;
 }
