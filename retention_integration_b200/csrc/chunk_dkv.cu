@@ -508,8 +508,7 @@ extern "C" int pr_chunk_dkv(int dtype, int b, int t, int hq, int h, int d, int c
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define PR_LAUNCH_DKV(TT, DG)                                                                                      \
   do {                                                                                                             \
-    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<TT, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    PR_CUDA(cudaFuncSetAttribute(chunk_dkv_kernel<TT, DG>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));    \
+    PR_SMEM_ATTR((chunk_dkv_kernel<TT, DG>), smem, device, true);                                                   \
     chunk_dkv_kernel<TT, DG><<<grid, THREADS, smem, s>>>(p, tm_k, tm_v, tm_q, tm_dy, tm_ds);                         \
   } while (0)
   if (dtype == PR_BF16) {

@@ -529,8 +529,7 @@ extern "C" int pr_chunk_out(int dtype, int b, int n_chunks, int cq, int ck, int 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define PR_LAUNCH_OUT(TT, DG)                                                                                      \
   do {                                                                                                             \
-    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<TT, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    PR_CUDA(cudaFuncSetAttribute(chunk_out_kernel<TT, DG>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));    \
+    PR_SMEM_ATTR((chunk_out_kernel<TT, DG>), smem, device, true);                                                   \
     chunk_out_kernel<TT, DG><<<grid, THREADS, smem, s>>>(p, tm_q, tm_k, tm_v, tm_z, tm_ghi, tm_glo);                 \
   } while (0)
   if (dtype == PR_BF16) {

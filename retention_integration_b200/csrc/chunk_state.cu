@@ -292,8 +292,9 @@ static int launch_chunk_state(const ChunkStateParams& p, int b, const CUtensorMa
   using namespace cs;
   const size_t smem = 1024 + NS * (XT_BYTES + W_BYTES);
   static_assert(2 * GA_BYTES <= NS * W_BYTES, "Gram stages must fit in the value ring");
-  PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+  int device = 0;
+  PR_CUDA(cudaGetDevice(&device));  // the entry point has made the caller's device current
+  PR_SMEM_ATTR(chunk_state_kernel<T>, smem, device, true);
   const long long ctas = (long long)((p.n_tiles + NG - 1) / NG + (p.gram ? 1 : 0)) * b * p.n_chunks * p.nh;
   PR_REQUIRE(ctas < (1ll << 31), PR_ERR_BAD_ARG, "%lld CTAs exceed the grid limit", ctas);
   dim3 grid((unsigned)ctas);

@@ -449,16 +449,10 @@ extern "C" int pr_expand_grad(int dtype, int b, int t, int h, int hx, int d, int
   dim3 grid(p.tiles_per_chunk * n, hx, b);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == PR_BF16) {
-    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__nv_bfloat16, PR_EG_NRT>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__nv_bfloat16, PR_EG_NRT>,
-                                 cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    PR_SMEM_ATTR((expand_grad_kernel<__nv_bfloat16, PR_EG_NRT>), smem, device, true);
     expand_grad_kernel<__nv_bfloat16, PR_EG_NRT><<<grid, C::THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
   } else {
-    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__half, PR_EG_NRT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    PR_CUDA(cudaFuncSetAttribute(expand_grad_kernel<__half, PR_EG_NRT>,
-                                 cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+    PR_SMEM_ATTR((expand_grad_kernel<__half, PR_EG_NRT>), smem, device, true);
     expand_grad_kernel<__half, PR_EG_NRT><<<grid, C::THREADS, smem, s>>>(p, tm_w, tm_x, tm_s, tm_ghi, tm_glo);
   }
   PR_CUDA(cudaGetLastError());

@@ -50,6 +50,20 @@ int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, cons
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Dynamic shared memory of a kernel: the attribute is raised once per kernel instantiation and device (and
+// again only if a later launch needs more), not on every launch.  `carveout`: also ask for the largest
+// shared-memory partition.
+#define PR_SMEM_ATTR(kernel, bytes, device, carveout)                                                         \
+  do {                                                                                                        \
+    static int set_bytes_[64] = {0};                                                                          \
+    const int dev_ = (device);                                                                                \
+    if (dev_ < 0 || dev_ >= 64 || set_bytes_[dev_] < (int)(bytes)) {                                          \
+      PR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)));       \
+      if (carveout) PR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100)); \
+      if (dev_ >= 0 && dev_ < 64) set_bytes_[dev_] = (int)(bytes);                                            \
+    }                                                                                                         \
+  } while (0)
+
 // 0 when the environment variable PR_PDL=0 asks for plain stream order (read once).
 bool pdl_enabled();
 

@@ -345,12 +345,12 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
 #define PR_LAUNCH_PREP(TT, GRID, LG, AIN, XT, XTS, WRITE)                                                       \
   do {                                                                                                         \
     if (d <= 64) {                                                                                             \
-      PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<TT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      PR_SMEM_ATTR((gate_prep_kernel<TT, 4>), smem, device, false);                                            \
       gate_prep_kernel<TT, 4><<<GRID, kGpThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,   \
                                                             static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), \
                                                             t, h, hx, d, c, cp, query_side, mult, WRITE);         \
     } else {                                                                                                   \
-      PR_CUDA(cudaFuncSetAttribute(gate_prep_kernel<TT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      PR_SMEM_ATTR((gate_prep_kernel<TT, 8>), smem, device, false);                                            \
       gate_prep_kernel<TT, 8><<<GRID, kGpThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,   \
                                                             static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), \
                                                             t, h, hx, d, c, cp, query_side, mult, WRITE);         \
