@@ -1,4 +1,4 @@
-// Device-side toolkit for sm_100a: mbarrier, TMA (non-multicast), TMEM and
+// Device-side toolkit for sm_100a: mbarrier, TMA (each CTA loads its own tiles), TMEM and
 // tcgen05 wrappers in inline PTX, plus the shared-memory swizzle used by the
 // 128-byte-swizzled UMMA operand layouts.
 //
