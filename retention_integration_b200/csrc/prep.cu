@@ -15,7 +15,7 @@ namespace pr {
 constexpr int kPrepThreads = 256;   // gate_grad
 constexpr int kGpThreads = 128;     // gate_prep: small CTAs, eight per SM, four 16-byte loads in flight per thread
 
-template <typename T, int NV>
+template <typename T, int NV, bool PAIRED>
 __global__ void __launch_bounds__(kGpThreads, NV == 4 ? 8 : 4)
 gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in, const T* __restrict__ x,
                  float* __restrict__ a_out, float* __restrict__ A_out, T* __restrict__ xt,
@@ -99,6 +99,20 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
   const int nvec = (64 * vec_per_row + kGpThreads - 1) / kGpThreads;  // <= kMaxVec for d <= 128
   uint4 raw[kMaxVec];
   float fac[kMaxVec], rsc[kMaxVec];
+  // d = 64: a thread's vectors 2p and 2p + 1 hold the same eight features of tokens r and r + 1, so the
+  // transposing stores below write two tokens of a feature as one 32-bit word (half as many stores; the
+  // kernel is bound by instruction issue, not by bandwidth)
+  constexpr bool paired = PAIRED;  // d = 64
+  auto where = [&](int q, int* r, int* v) {
+    if (paired) {
+      *r = 2 * (tid >> 3) + (q & 1) + 32 * (q >> 1);
+      *v = tid & 7;
+    } else {
+      const int idx = tid + q * kGpThreads;
+      *r = idx / vec_per_row;
+      *v = idx % vec_per_row;
+    }
+  };
   auto load_tile = [&](int tb) {
 #pragma unroll
     for (int q = 0; q < kMaxVec; ++q) {
@@ -106,7 +120,8 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
       raw[q] = make_uint4(0, 0, 0, 0);
       fac[q] = rsc[q] = 0.f;
       if (q < nvec && idx < 64 * vec_per_row) {
-        const int r = idx / vec_per_row, v = idx % vec_per_row;
+        int r, v;
+        where(q, &r, &v);
         const int i = tb + r;
         if (i < c) {
           raw[q] = *reinterpret_cast<const uint4*>(x + ((tok0 + i) * hx + head) * (size_t)d + v * 8);
@@ -120,11 +135,13 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
   if (tb_begin < tb_end) load_tile(tb_begin);
   for (int tb = tb_begin; tb < tb_end; tb += 64) {
     __syncthreads();
+    uint32_t wa[4] = {0, 0, 0, 0}, wa2[4] = {0, 0, 0, 0};  // the even token of a pair, kept for the odd one
 #pragma unroll
     for (int q = 0; q < kMaxVec; ++q) {
       const int idx = tid + q * kGpThreads;
       if (q >= nvec || idx >= 64 * vec_per_row) continue;
-      const int r = idx / vec_per_row, v = idx % vec_per_row;
+      int r, v;
+      where(q, &r, &v);
       const float f = fac[q], rs = rsc[q];
       uint32_t w[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
       uint32_t w2[4];
@@ -135,6 +152,33 @@ gate_prep_kernel(const float* __restrict__ log_g, const float* __restrict__ a_in
         // the scaled copy multiplies the ROUNDED gated value, so that both copies describe the same x~
         float2 pr_ = Pack2<T>::to_f32(w[k]);
         w2[k] = Pack2<T>::from_f32(pr_.x * rs, pr_.y * rs);
+      }
+      if (paired) {
+        if ((q & 1) == 0) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            wa[k] = w[k];
+            wa2[k] = w2[k];
+          }
+          continue;
+        }
+        // tokens r - 1 (wa) and r (w): features v*8 .. v*8+7, one 32-bit store per feature
+        const int pos = ((((r >> 3) ^ v) & 7) << 3) + ((r - 1) & 7);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(tile) + (v * 8) * 64 + pos);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          dst[(2 * k) * 32] = __byte_perm(wa[k], w[k], 0x5410);
+          dst[(2 * k + 1) * 32] = __byte_perm(wa[k], w[k], 0x7632);
+        }
+        if (xts != nullptr) {
+          uint32_t* dst2 = reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(tile2) + (v * 8) * 64 + pos);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            dst2[(2 * k) * 32] = __byte_perm(wa2[k], w2[k], 0x5410);
+            dst2[(2 * k + 1) * 32] = __byte_perm(wa2[k], w2[k], 0x7632);
+          }
+        }
+        continue;
       }
       // features v*8 .. v*8+7 of token r: one 16-bit store each, into the row of its feature
       const int pos = ((((r >> 3) ^ v) & 7) << 3) + (r & 7);
@@ -342,20 +386,22 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
   // first small launch makes them and the transposing launch reads them.
   const float* a_in = (write_a == 0 && a_out != nullptr && log_g != nullptr) ? a_out : nullptr;
   const bool two_pass = write_a && xt != nullptr && log_g != nullptr && a_out != nullptr && !query_side && hx == h;
+#define PR_LAUNCH_PREP_K(KERNEL, TT, GRID, LG, AIN, XT, XTS, WRITE)                                            \
+  do {                                                                                                         \
+    PR_SMEM_ATTR(KERNEL, smem, device, false);                                                                 \
+    KERNEL<<<GRID, kGpThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out, static_cast<TT*>(XT), \
+                                          row_scale, static_cast<TT*>(XTS), t, h, hx, d, c, cp, query_side, mult, \
+                                          WRITE);                                                              \
+    PR_CUDA(cudaGetLastError());                                                                               \
+  } while (0)
 #define PR_LAUNCH_PREP(TT, GRID, LG, AIN, XT, XTS, WRITE)                                                       \
   do {                                                                                                         \
-    if (d <= 64) {                                                                                             \
-      PR_SMEM_ATTR((gate_prep_kernel<TT, 4>), smem, device, false);                                            \
-      gate_prep_kernel<TT, 4><<<GRID, kGpThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,   \
-                                                            static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), \
-                                                            t, h, hx, d, c, cp, query_side, mult, WRITE);         \
-    } else {                                                                                                   \
-      PR_SMEM_ATTR((gate_prep_kernel<TT, 8>), smem, device, false);                                            \
-      gate_prep_kernel<TT, 8><<<GRID, kGpThreads, smem, s>>>(LG, AIN, static_cast<const TT*>(x), a_out, A_out,   \
-                                                            static_cast<TT*>(XT), row_scale, static_cast<TT*>(XTS), \
-                                                            t, h, hx, d, c, cp, query_side, mult, WRITE);         \
-    }                                                                                                          \
-    PR_CUDA(cudaGetLastError());                                                                               \
+    if (d == 64)                                                                                               \
+      PR_LAUNCH_PREP_K((gate_prep_kernel<TT, 4, true>), TT, GRID, LG, AIN, XT, XTS, WRITE);                    \
+    else if (d < 64)                                                                                           \
+      PR_LAUNCH_PREP_K((gate_prep_kernel<TT, 4, false>), TT, GRID, LG, AIN, XT, XTS, WRITE);                   \
+    else                                                                                                       \
+      PR_LAUNCH_PREP_K((gate_prep_kernel<TT, 8, false>), TT, GRID, LG, AIN, XT, XTS, WRITE);                   \
   } while (0)
   if (dtype == PR_BF16) {
     if (two_pass) {
@@ -373,6 +419,7 @@ extern "C" int pr_gate_prep(int dtype, int b, int t, int h, int hx, int d, int c
     }
   }
 #undef PR_LAUNCH_PREP
+#undef PR_LAUNCH_PREP_K
   return PR_OK;
 }
 
