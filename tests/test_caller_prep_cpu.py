@@ -31,3 +31,17 @@ def test_rotary_is_a_rotation_in_both_pairings():
         assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), rtol=1e-5)
         back = cpo.rotary(y, -sin, cos, half)  # rotating by the opposite angle undoes it
         assert torch.allclose(back, x, atol=1e-5)
+
+
+def test_product_path_refuses_host_tensors():
+    """No CPU fallback: the package's prepare_qkvg raises on anything but CUDA 16-bit tensors."""
+    import pytest
+
+    import retention_integration_b200 as prb
+
+    x = torch.randn(1, 8, 3 * 64 + 8).bfloat16()
+    sin, cos = cpo.sinusoidal_tables(8, 64)
+    with pytest.raises(prb.PRError):
+        prb.prepare_qkvg(x, sin, cos, 1, 1, 64)
+    s2, c2 = prb.rotary_tables(8, 64, "cpu")  # the table helper itself is plain torch
+    assert torch.allclose(s2, sin) and torch.allclose(c2, cos)
