@@ -137,6 +137,30 @@ def _pad_head_dim(x, d_to):
     return torch.nn.functional.pad(x, (0, d_to - x.shape[-1]))
 
 
+# `chunk_size` blocks the computation; the result does not depend on it (the reference pads, chunks and scans
+# to the same function for every chunk size, and so do the kernels here - tested).  Small chunks are slow on
+# this hardware for a reason the arithmetic does not care about: every chunk's state (2560 x 64 per head) is written,
+# scanned and read again, 1.3 GB per pass at chunk 128 against 0.17 GB at chunk 1024 for the benchmark's shape
+# (5.3 vs 2.6 ms per step).  With AUTO_CHUNK the Python API therefore runs a request for a chunk below 1024 with the
+# largest multiple of it that is at most 1024 and pads the sequence by at most 1/16 more than the request would
+# (padding tokens are zero keys and values behind gates of 1: they change neither the outputs of the real tokens nor
+# the state after the last one).  The C ABI (pr_retention_fwd) always takes the chunk it is given.
+AUTO_CHUNK = True
+_FAST_CHUNK = 1024
+
+
+def effective_chunk(t: int, chunk_size):
+    """The chunk size power_retention runs with for a sequence of t tokens and a requested chunk_size."""
+    if not AUTO_CHUNK or chunk_size is None or chunk_size >= _FAST_CHUNK:
+        return chunk_size
+    padded = -(-t // chunk_size) * chunk_size  # what the request itself pads to
+    for m in range(_FAST_CHUNK // chunk_size, 1, -1):
+        ce = m * chunk_size
+        if -(-t // ce) * ce <= padded + padded // 16:
+            return ce
+    return chunk_size
+
+
 def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=False, deg=2, scale=None,
                     chunk_size=None, switch_over_seq_len=None):
     """Symmetric power retention, training forward (differentiable).
@@ -166,6 +190,7 @@ def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=
         return out[..., :d_orig]
     b, t, hq, d = Q.shape
     h = K.shape[2]
+    chunk_size = effective_chunk(t, chunk_size)
     if chunk_size is not None and switch_over_seq_len is None:
         switch_over_seq_len = chunk_size
     t_padded = t if chunk_size is None else -(-t // chunk_size) * chunk_size

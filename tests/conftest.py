@@ -19,3 +19,15 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def requested_chunk_sizes():
+    """The tests ask for particular chunk geometries (chunks shorter than a tile, not a multiple of it, many short
+    chunks ...): the package runs them as asked.  tests/test_gpu_auto_chunk.py switches the automatic choice on."""
+    from retention_integration_b200 import retention
+
+    old = retention.AUTO_CHUNK
+    retention.AUTO_CHUNK = False
+    yield
+    retention.AUTO_CHUNK = old

@@ -1,0 +1,49 @@
+"""retention.AUTO_CHUNK: a request for a small chunk runs with a larger one; everything the caller sees - padding,
+outputs, gradients, the state after the last token - is that of the request."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from tests._golden import rel_l2
+
+
+def test_effective_chunk_table():
+    from retention_integration_b200 import retention
+
+    retention.AUTO_CHUNK = True
+    want = {(65536, 128): 1024, (2000, 128): 1024, (1152, 128): 384, (512, 128): 512, (31, 128): 128, (4096, 256): 1024,
+            (65536, 1024): 1024, (65536, 2048): 2048, (300, None): None, (768, 192): 768, (5000, 64): 1024}
+    for (t, c), ce in want.items():
+        assert retention.effective_chunk(t, c) == ce, (t, c)
+        if c is not None and c < 1024:
+            assert ce % c == 0 and -(-t // ce) * ce <= (-(-t // c) * c) * 17 // 16
+    retention.AUTO_CHUNK = False
+    assert retention.effective_chunk(65536, 128) == 128
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("t,c,r,states", [(2000, 128, 1, False), (1152, 128, 2, True), (4096, 256, 1, True)])
+def test_auto_chunk_gives_the_requested_chunks_results(cuda_device, t, c, r, states):
+    import retention_integration_b200 as prb
+    from retention_integration_b200 import retention
+
+    g = torch.Generator().manual_seed(t + c)
+    b, h, d = 2, 2, 64
+    Q = torch.randn(b, t, h * r, d, generator=g).bfloat16().to(cuda_device)
+    K, V = (torch.randn(b, t, h, d, generator=g).bfloat16().to(cuda_device) for _ in range(2))
+    lg = F.logsigmoid(torch.randn(b, t, h, generator=g) + 2.0).to(cuda_device)
+    dO = torch.randn(b, t, h * r, d, generator=g).bfloat16().to(cuda_device)
+
+    def run(auto):
+        retention.AUTO_CHUNK = auto
+        leaves = [x.clone().requires_grad_(True) for x in (Q, K, V, lg)]
+        out = prb.power_retention(*leaves, deg=2, chunk_size=c, return_final_state=states)
+        O, final = out if states else (out, None)
+        O.backward(dO)
+        return [O] + [x.grad for x in leaves] + (list(final) if states else [])
+
+    asked, auto = run(False), run(True)
+    assert retention.effective_chunk(t, c) > c
+    for a, bb in zip(asked, auto):
+        assert a.shape == bb.shape
+        assert rel_l2(bb.float(), a.float()) < 6e-3
