@@ -1,5 +1,7 @@
 // Host-side plumbing of the C ABI: version, error string, status word, tensor maps.
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "host.cuh"
 #include "sm100.cuh"
@@ -39,6 +41,20 @@ int status_word(int device, int** dev_ptr, volatile int** host_ptr) {
   }
   if (dev_ptr) *dev_ptr = s.dev;
   if (host_ptr) *host_ptr = s.host;
+  return PR_OK;
+}
+
+int smem_attr(const void* kernel, size_t bytes, int device, bool carveout) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, size_t> set_bytes;
+  // never below the 48 KB every kernel may use without the attribute
+  const size_t want = bytes < 49152 ? 49152 : bytes;
+  std::lock_guard<std::mutex> lock(mu);
+  size_t& have = set_bytes[{kernel, device}];
+  if (have >= want) return PR_OK;
+  PR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want));
+  if (carveout) PR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+  have = want;
   return PR_OK;
 }
 

@@ -50,18 +50,15 @@ int make_tmap(CUtensorMap* out, const void* base, int elem_bytes, int rank, cons
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Dynamic shared memory of a kernel: the attribute is raised once per kernel instantiation and device (and
-// again only if a later launch needs more), not on every launch.  `carveout`: also ask for the largest
-// shared-memory partition.
-#define PR_SMEM_ATTR(kernel, bytes, device, carveout)                                                         \
-  do {                                                                                                        \
-    static int set_bytes_[64] = {0};                                                                          \
-    const int dev_ = (device);                                                                                \
-    if (dev_ < 0 || dev_ >= 64 || set_bytes_[dev_] < (int)(bytes)) {                                          \
-      PR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes)));       \
-      if (carveout) PR_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100)); \
-      if (dev_ >= 0 && dev_ < 64) set_bytes_[dev_] = (int)(bytes);                                            \
-    }                                                                                                         \
+// Dynamic shared memory of a kernel: the attribute is raised once per kernel and device (and again only when a
+// later launch needs more), not on every launch.  The record is kept per kernel function, not per call site: a
+// second site that set a smaller size for the same kernel would lower the limit under the first one's launches.
+// `carveout`: also ask for the largest shared-memory partition.
+int smem_attr(const void* kernel, size_t bytes, int device, bool carveout);
+#define PR_SMEM_ATTR(kernel, bytes, device, carveout)                                                    \
+  do {                                                                                                   \
+    int rc_ = ::pr::smem_attr(reinterpret_cast<const void*>(kernel), (bytes), (device), (carveout));     \
+    if (rc_) return rc_;                                                                                 \
   } while (0)
 
 // 0 when the environment variable PR_PDL=0 asks for plain stream order (read once).

@@ -149,9 +149,28 @@ AUTO_CHUNK = True
 _FAST_CHUNK = 1024
 
 
-def effective_chunk(t: int, chunk_size):
-    """The chunk size power_retention runs with for a sequence of t tokens and a requested chunk_size."""
-    if not AUTO_CHUNK or chunk_size is None or chunk_size >= _FAST_CHUNK:
+def effective_chunk(t: int, chunk_size, deg: int = 2):
+    """The chunk size power_retention runs with for a sequence of t tokens and a requested chunk_size.
+
+    Below 1024: the largest multiple of the request up to 1024 that pads by at most 1/16 more.  Above 1024 (slower
+    again: the intra-chunk attention grows with the chunk): the largest divisor of the request in [256, 1024], which
+    leaves the padded length as it is.  None (no chunking) on a long sequence: 1024 or 512 if that pads by at most
+    1/16; the quadratic form otherwise.  deg 4 forms no states and is never chunked."""
+    if not AUTO_CHUNK or deg != 2:
+        return chunk_size
+    if chunk_size is None:
+        if t <= 2 * _FAST_CHUNK:
+            return None
+        for ce in (_FAST_CHUNK, _FAST_CHUNK // 2):
+            if -(-t // ce) * ce <= t + t // 16:
+                return ce
+        return None
+    if chunk_size > _FAST_CHUNK:
+        for ce in range(_FAST_CHUNK, 255, -1):
+            if chunk_size % ce == 0:
+                return ce
+        return chunk_size
+    if chunk_size == _FAST_CHUNK:
         return chunk_size
     padded = -(-t // chunk_size) * chunk_size  # what the request itself pads to
     for m in range(_FAST_CHUNK // chunk_size, 1, -1):
@@ -190,8 +209,12 @@ def power_retention(Q, K, V, log_G=None, initial_state=None, return_final_state=
         return out[..., :d_orig]
     b, t, hq, d = Q.shape
     h = K.shape[2]
-    chunk_size = effective_chunk(t, chunk_size)
-    if chunk_size is not None and switch_over_seq_len is None:
+    requested = chunk_size
+    chunk_size = effective_chunk(t, chunk_size, deg)
+    if chunk_size != requested:
+        # the blocking is this function's own choice: one chunk is the quadratic form, several the chunked one
+        switch_over_seq_len = chunk_size
+    elif chunk_size is not None and switch_over_seq_len is None:
         switch_over_seq_len = chunk_size
     t_padded = t if chunk_size is None else -(-t // chunk_size) * chunk_size
     state_free = (switch_over_seq_len is None or t_padded <= switch_over_seq_len or chunk_size is None) and \

@@ -12,22 +12,29 @@ def test_effective_chunk_table():
 
     retention.AUTO_CHUNK = True
     want = {(65536, 128): 1024, (2000, 128): 1024, (1152, 128): 384, (512, 128): 512, (31, 128): 128, (4096, 256): 1024,
-            (65536, 1024): 1024, (65536, 2048): 2048, (300, None): None, (768, 192): 768, (5000, 64): 1024}
+            (65536, 1024): 1024, (300, None): None, (768, 192): 768, (5000, 64): 1024,
+            # above the fast size: a divisor of the request; no chunking asked for: chunked when the sequence is long
+            (65536, 2048): 1024, (65536, 4096): 1024, (5000, 1536): 768, (1000, 3000): 1000, (4096, 1031): 1031,
+            (3000, None): 1024, (70000, None): 1024, (2100, None): None, (500, None): None}
     for (t, c), ce in want.items():
         assert retention.effective_chunk(t, c) == ce, (t, c)
         if c is not None and c < 1024:
             assert ce % c == 0 and -(-t // ce) * ce <= (-(-t // c) * c) * 17 // 16
+        if c is not None and c > 1024:
+            assert c % ce == 0
+    assert retention.effective_chunk(65536, None, deg=4) is None  # deg 4 forms no states
     retention.AUTO_CHUNK = False
-    assert retention.effective_chunk(65536, 128) == 128
+    assert retention.effective_chunk(65536, 128) == 128 and retention.effective_chunk(65536, None) is None
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("t,c,r,states", [(2000, 128, 1, False), (1152, 128, 2, True), (4096, 256, 1, True)])
+@pytest.mark.parametrize("t,c,r,states", [(2000, 128, 1, False), (1152, 128, 2, True), (4096, 256, 1, True),
+                                          (3000, None, 1, False), (4000, 2048, 1, True), (3000, 3000, 2, False)])
 def test_auto_chunk_gives_the_requested_chunks_results(cuda_device, t, c, r, states):
     import retention_integration_b200 as prb
     from retention_integration_b200 import retention
 
-    g = torch.Generator().manual_seed(t + c)
+    g = torch.Generator().manual_seed(t + (c or 0))
     b, h, d = 2, 2, 64
     Q = torch.randn(b, t, h * r, d, generator=g).bfloat16().to(cuda_device)
     K, V = (torch.randn(b, t, h, d, generator=g).bfloat16().to(cuda_device) for _ in range(2))
@@ -43,7 +50,7 @@ def test_auto_chunk_gives_the_requested_chunks_results(cuda_device, t, c, r, sta
         return [O] + [x.grad for x in leaves] + (list(final) if states else [])
 
     asked, auto = run(False), run(True)
-    assert retention.effective_chunk(t, c) > c
+    assert retention.effective_chunk(t, c) != c
     for a, bb in zip(asked, auto):
         assert a.shape == bb.shape
         assert rel_l2(bb.float(), a.float()) < 6e-3
