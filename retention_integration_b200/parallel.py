@@ -227,6 +227,14 @@ def power_retention_sequence_parallel(Q, K, V, log_G=None, deg=2, scale=None, ch
     t, d = Q.shape[1], Q.shape[3]
     if t % chunk_size:
         raise PRError(f"the local block ({t} tokens) must be a multiple of chunk_size={chunk_size}")
+    from . import retention
+
+    if retention.AUTO_CHUNK and deg == 2 and chunk_size < 1024:
+        # as in power_retention: a small chunk is run with a multiple of it (here one that needs no padding)
+        for m in range(1024 // chunk_size, 1, -1):
+            if t % (m * chunk_size) == 0:
+                chunk_size = m * chunk_size
+                break
     comm = comm if comm is not None else DistComm()
     if log_G is not None:
         log_G = log_G.to(torch.float32).contiguous()
