@@ -54,3 +54,31 @@ def test_auto_chunk_gives_the_requested_chunks_results(cuda_device, t, c, r, sta
     for a, bb in zip(asked, auto):
         assert a.shape == bb.shape
         assert rel_l2(bb.float(), a.float()) < 6e-3
+
+
+@pytest.mark.gpu
+def test_auto_chunk_with_a_carried_state(cuda_device):
+    """Two segments chained through initial_state / return_final_state, each run with its own automatic chunk
+    (1024 for the first, 640 for the second), against the same chain at the requested chunk of 128."""
+    import retention_integration_b200 as prb
+    from retention_integration_b200 import retention
+
+    g = torch.Generator().manual_seed(77)
+    b, h, d, t1, t2 = 1, 2, 64, 1024, 1280
+    Q = torch.randn(b, t1 + t2, h, d, generator=g).bfloat16().to(cuda_device)
+    K, V = (torch.randn(b, t1 + t2, h, d, generator=g).bfloat16().to(cuda_device) for _ in range(2))
+    lg = F.logsigmoid(torch.randn(b, t1 + t2, h, generator=g) + 3.0).to(cuda_device)
+
+    def chain(auto):
+        retention.AUTO_CHUNK = auto
+        with torch.no_grad():
+            o1, st = prb.power_retention(Q[:, :t1], K[:, :t1], V[:, :t1], lg[:, :t1], chunk_size=128,
+                                         return_final_state=True)
+            o2, st2 = prb.power_retention(Q[:, t1:], K[:, t1:], V[:, t1:], lg[:, t1:], chunk_size=128, initial_state=st,
+                                          return_final_state=True)
+        return torch.cat([o1, o2], 1), st2
+
+    (o_a, st_a), (o_b, st_b) = chain(False), chain(True)
+    assert retention.effective_chunk(t1, 128) == 1024 and retention.effective_chunk(t2, 128) == 640
+    assert rel_l2(o_b.float(), o_a.float()) < 6e-3
+    assert rel_l2(st_b[0].float(), st_a[0].float()) < 6e-3 and rel_l2(st_b[1], st_a[1]) < 1e-3
