@@ -147,10 +147,15 @@ def test_fp16_inputs(cuda_device):
         assert rel_l2(ours[key], gold[key]) < TOL, key
 
 
+@pytest.mark.parametrize("auto_chunk", [False, True])
 @pytest.mark.parametrize("name", ["train_gated_fp32", "train_slow_decay_fp32", "train_gated_bf16",
                                   "train_ungated_gqa_pad_fp32", "train_short_quadratic_fp32"])
-def test_against_reference_golden_outputs(cuda_device, name):
-    """Same seeded inputs as the reference run that produced the fixture (inputs are bf16-exact)."""
+def test_against_reference_golden_outputs(cuda_device, name, auto_chunk):
+    """Same seeded inputs as the reference run that produced the fixture (inputs are bf16-exact); with the chunk
+    size the reference ran with, and with the one the package would choose by itself."""
+    from retention_integration_b200 import retention
+
+    retention.AUTO_CHUNK = auto_chunk
     g = load(name)
     b, t, h, d, r, gated, chunk, stride = g["meta"]
     ours = _run_ours(cuda_device, g["Q"].bfloat16(), g["K"].bfloat16(), g["V"].bfloat16(),
@@ -160,7 +165,11 @@ def test_against_reference_golden_outputs(cuda_device, name):
         assert rel_l2(ours[key][:, ::stride], g[key]) < tol, key
 
 
-def test_cfg1_shape_against_reference_golden(cuda_device):
+@pytest.mark.parametrize("auto_chunk", [False, True])
+def test_cfg1_shape_against_reference_golden(cuda_device, auto_chunk):
+    from retention_integration_b200 import retention
+
+    retention.AUTO_CHUNK = auto_chunk
     g = load("train_cfg1_fp32")  # b1 t1024 h4 d64 c128 gated: the reference's CPU-runnable case
     ours = _run_ours(cuda_device, g["Q"].bfloat16(), g["K"].bfloat16(), g["V"].bfloat16(), g["log_G"],
                      g["dO"].bfloat16(), 128)
