@@ -280,6 +280,13 @@ int pr_retention_fwd(const pr_problem* problem, const void* Q, const void* K, co
                      const float* carry_state, const float* carry_gram, void* O, void* saved, void* scratch,
                      float* final_state, float* final_gram, int device, void* stream);
 
+/* The chunk size to run a request with (0 = no chunking asked for): same results, fewer and longer chunks.
+ * The chunk size blocks the computation of retention/power_retention_maker.py:143-193 without changing its
+ * result; on this hardware 1024 is fastest (5.3 ms per step at chunk 128 against 2.6 at 1024 for b1 t65536 h8).
+ * pr_retention_fwd / _bwd run whatever pr_problem.c says; a host that wants the fast blocking passes
+ * c = pr_fast_chunk(t, its_chunk) and pads t to a multiple of it with zero tokens behind gates of 1. */
+int pr_fast_chunk(long long t, int requested_chunk);
+
 /* Backward.  dO [b,t,hq,d] -> dQ, dK, dV (shapes of Q, K, V) and dlog_G [b,t,h] fp32 (NULL when
  * ungated).  `saved` as the forward left it; had_carry = 1 when the forward was given carries.
  * The query-side branch (expand_grad on the saved states, chunk_dq) runs on a second stream that

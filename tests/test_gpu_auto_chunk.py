@@ -82,3 +82,17 @@ def test_auto_chunk_with_a_carried_state(cuda_device):
     assert retention.effective_chunk(t1, 128) == 1024 and retention.effective_chunk(t2, 128) == 640
     assert rel_l2(o_b.float(), o_a.float()) < 6e-3
     assert rel_l2(st_b[0].float(), st_a[0].float()) < 6e-3 and rel_l2(st_b[1], st_a[1]) < 1e-3
+
+
+def test_c_abi_helper_agrees_with_the_python_choice():
+    """pr_fast_chunk is pure host arithmetic: callable without a GPU."""
+    import ctypes
+
+    from retention_integration_b200 import _lib, retention
+
+    retention.AUTO_CHUNK = True
+    fn = _lib.lib().pr_fast_chunk
+    fn.argtypes, fn.restype = [ctypes.c_longlong, ctypes.c_int], ctypes.c_int
+    for t in (17, 500, 1000, 1152, 2000, 2100, 3000, 4096, 5000, 65536, 70000):
+        for c in (None, 64, 96, 128, 192, 256, 320, 512, 1024, 1031, 1536, 2048, 3000, 4096):
+            assert fn(t, c or 0) == (retention.effective_chunk(t, c) or 0), (t, c)
