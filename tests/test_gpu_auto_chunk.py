@@ -96,3 +96,31 @@ def test_c_abi_helper_agrees_with_the_python_choice():
     for t in (17, 500, 1000, 1152, 2000, 2100, 3000, 4096, 5000, 65536, 70000):
         for c in (None, 64, 96, 128, 192, 256, 320, 512, 1024, 1031, 1536, 2048, 3000, 4096):
             assert fn(t, c or 0) == (retention.effective_chunk(t, c) or 0), (t, c)
+
+
+def test_effective_chunk_properties():
+    """Whatever is asked for: the chosen chunk is a multiple of a small request (a divisor of a large one), never
+    above 1024 unless the request itself has no divisor there, pads by at most 1/16 more, and the C helper agrees."""
+    import ctypes
+    import random
+
+    from retention_integration_b200 import _lib, retention
+
+    retention.AUTO_CHUNK = True
+    fn = _lib.lib().pr_fast_chunk
+    fn.argtypes, fn.restype = [ctypes.c_longlong, ctypes.c_int], ctypes.c_int
+    rng = random.Random(0)
+    for _ in range(3000):
+        t = rng.randint(1, 300000)
+        c = rng.choice([None, rng.randint(1, 1023), rng.randint(1025, 9000), 16 * rng.randint(1, 512)])
+        ce = retention.effective_chunk(t, c)
+        assert fn(t, c or 0) == (ce or 0)
+        pad = lambda x: -(-t // x) * x
+        if c is None:
+            assert ce in (None, 512, 1024) and (ce is None or (t > 2048 and pad(ce) <= t + t // 16))
+        elif c < 1024:
+            assert ce % c == 0 and c <= ce <= 1024 and pad(ce) <= pad(c) + pad(c) // 16
+        elif c > 1024:
+            assert c % ce == 0 and (256 <= ce <= 1024 or ce == c) and pad(ce) <= pad(c)
+        else:
+            assert ce == c
