@@ -10,10 +10,13 @@ log_G = logsigmoid(N(0,1))).  A step is one forward+backward pass.  With N > 1 G
 kv heads are split across ranks (no collective on the data path); the reported value is
 batch*tokens per second of the whole job, timed on the device, max over ranks.
 
-The default line also carries the other two parts of the metric: at N = 1 a `decode` object
-(b=16, h=32, d=64: 2048-token prefill into the state, then 512 single-token steps), at N > 1 a
-`seq_parallel` object (b=1, t=1048576, h=8 split by sequence over the ranks, boundary states
-exchanged over NCCL).  `--workload decode|seqpar` prints those as lines of their own.
+The default line also carries the other parts of the metric: at N = 1 a `decode` object
+(b=16, h=32, d=64: 2048-token prefill into the state, then 512 single-token steps replayed from a
+CUDA graph) and a `caller_prep` object (the callers' split + gate + rotary glue at the training
+shape), at N > 1 a `seq_parallel` object (b=1, t=1048576, h=8 split by sequence over the ranks,
+boundary states exchanged over NCCL).  `--workload decode|seqpar|caller` prints those as lines of
+their own.  A timed region that takes several times the sum of its own kernels (a stall from
+outside the job) is timed once more; the line then carries both figures under `retimed`.
 
 One JSON line is printed by rank 0.  `--impl reference` times the CPU restatement of the
 reference's algorithm (oracle/) on the host cores instead.
