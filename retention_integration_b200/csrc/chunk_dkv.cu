@@ -241,7 +241,8 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
           for (int ks = 0; ks < 8; ++ks)
             umma_ts(tmem + COL_DV, tmem + COL_A + s * 64 + ks * 8,
                     umma_desc_sw128(z_addr + (ks >> 2) * Z_BYTES + (ks & 3) * 2048, 8192, 1024), idesc_o, 1u);
-          umma_commit(&a_empty[s]);
+          // one commit per item: it frees the ring stage for the TMA thread and, two items on, the
+          // tensor-memory slot for the expansion warps
           umma_commit(&r_empty[rs]);
         }
       }
@@ -376,8 +377,12 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
           uint32_t r0[32], r1[32];
           expand_stage<T, Y>(smK, tid, a0, k2, r0);
           expand_stage<T, Y>(smK, tid, a0 + 4, k2, r1);
-          const int s = k % NS, ph = (k / NS) & 1;
-          if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+          const int s = k % NS;
+          if (ok && k >= NS) {
+            // the slot was last used by item k - NS, whose completion is reported on its ring stage's barrier
+            const int g2 = n_steps + k - NS;
+            ok = mbar_wait(&r_empty[g2 % NR], (g2 / NR) & 1, &abort_flag);
+          }
           if (ok) {
             tc_fence_after();
             tmem_st32(tmem + lane_addr + COL_A + s * 64, r0);

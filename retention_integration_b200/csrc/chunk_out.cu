@@ -261,7 +261,8 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
             umma_ts(tmem + COL_ACC, tmem + COL_A + s * 64 + ks * 8,
                     umma_desc_sw128(z_addr + (ks >> 2) * Z_BYTES + (ks & 3) * 2048, 8192, 1024), idesc_v,
                     (nJ > 0 || k > 1 || ks > 0) ? 1u : 0u);
-          umma_commit(&a_empty[s]);
+          // one commit per item: it frees the ring stage for the TMA thread and, two items on, the
+          // tensor-memory slot for the expansion warps (a commit costs this thread ~150 clocks, a sixth of an item)
           umma_commit(&r_empty[rs]);
         }
       }
@@ -392,8 +393,14 @@ chunk_out_kernel(const ChunkOutParams p, const __grid_constant__ CUtensorMap tm_
           uint32_t r0[32], r1[32];
           expand_stage<T, Y>(smQ, tid, a0, q2, r0);
           expand_stage<T, Y>(smQ, tid, a0 + 4, q2, r1);
-          const int s = k % NS, ph = (k / NS) & 1;
-          if (ok) ok = mbar_wait(&a_empty[s], ph ^ 1, &abort_flag);
+          const int s = k % NS;
+          // the slot was last used by item k - 2: the Gram item (its own barrier) or a ring item, whose
+          // completion the issuing thread reports on the ring stage's barrier
+          if (ok && k == 2) ok = mbar_wait(&a_empty[0], 0, &abort_flag);
+          if (ok && k >= 3) {
+            const int g2 = nJ + k - 3;
+            ok = mbar_wait(&r_empty[g2 % NR], (g2 / NR) & 1, &abort_flag);
+          }
           if (ok) {
             tc_fence_after();
             tmem_st32(tmem + lane_addr + COL_A + s * 64, r0);
