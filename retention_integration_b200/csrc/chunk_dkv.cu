@@ -110,7 +110,7 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
   using namespace dkv;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t kv_full, r_full[NR], r_empty[NR], sp_full, pd_full, attn_done, acc_done;
-  __shared__ uint64_t a_full[NS], a_empty[NS];
+  __shared__ uint64_t a_full[NS];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   __shared__ __align__(16) float sm_aq[2][TW], sm_dl[2][TW], sm_il[2][TW];
@@ -154,7 +154,6 @@ chunk_dkv_kernel(const ChunkDkvParams p, const __grid_constant__ CUtensorMap tm_
     mbar_init(&acc_done, 1);
     for (int s = 0; s < NS; ++s) {
       mbar_init(&a_full[s], 4);
-      mbar_init(&a_empty[s], 1);
     }
     fence_mbar_init();
   }
